@@ -1,0 +1,60 @@
+/* bonsai_b200_ext.h -- additive entry points of the sm_100a build.
+ *
+ * None of these exists in the reference library; they do not change the meaning of any
+ * symbol in bonsai_p40.h.  Same conventions: device pointers owned by the caller, work is
+ * enqueued on `stream`, 0 = success, 1 = rejected shape, otherwise a CUDA error code.
+ */
+#ifndef BONSAI_B200_EXT_H
+#define BONSAI_B200_EXT_H
+
+#include "bonsai_p40.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Rotation and quantiser in one launch: xq = Q8_1(FWHT1024(signs * x)).  x is left untouched;
+ * if x_rot is not NULL it receives the rotated fp32 vector.  No counterpart in the reference,
+ * which launches src/kernels/elementwise_p40.cu:75 and src/kernels/gemv_p40.cu:200 in turn;
+ * the bytes written equal those two calls. */
+int bonsai_b200_fwht_quant(const float *x, const float *signs, void *xq, float *x_rot, int64_t n,
+                           bonsai_stream stream);
+
+/* Token batch for the mat-mul: X is fp32 [n_tok][n_in] (token-major); Xq receives the
+ * chunk-major [n_in/32][n_tok] Q8_1 layout that bonsai_p40_gemm reads (the reference has no
+ * entry point that produces it; its test builds it by hand, tests/test_p40.cpp:438-447).
+ * With rotate != 0 every token is first rotated in blocks of 1024 (signs: NULL or n_in values
+ * shared by all tokens).  Returns 1 if n_in % 32 != 0, or rotate and n_in % 1024 != 0. */
+int bonsai_b200_quant_batch(const float *X, const float *signs, void *Xq, int64_t n_in, int64_t n_tok,
+                            int rotate, bonsai_stream stream);
+
+/* Parity probe: the int32 value (sum of code*activation) - (sum of activation) of every
+ * 32-weight chunk of rows [row0, row0 + n_rows), written to out[n_rows][n_in/32].  These are
+ * the integers the reference computes in src/pq2_0.h:149-169 before scaling. */
+int bonsai_b200_gemv_chunk_sums(const void *W, const void *xq, int32_t *out, int64_t row0, int64_t n_rows,
+                                int64_t n_in, bonsai_stream stream);
+
+/* Synthetic PQ2_0 weights written on the device: n_blocks blocks whose codes are drawn per
+ * element from {0,1,2} with p = {0.33,0.34,0.33} plus code 3 at p = 0.001, and whose fp16
+ * scale is |z| * 0.02 with z approximately standard normal.  Counter-based: block i of a
+ * call depends only on (seed, first_block + i). */
+int bonsai_b200_synth_pq2_0(void *W, int64_t first_block, int64_t n_blocks, uint64_t seed, bonsai_stream stream);
+
+/* Launch options.  key "pdl": 1 = launch the mat-vec with programmatic stream serialisation,
+ * so that its weight stream starts while the previous kernel of the stream drains (weights
+ * must not be written by that previous kernel); 0 = plain launches (default).
+ * key "gemv_variant": -1 = automatic, otherwise a tuning index used by the benchmark sweep.
+ * Returns 0, or 1 for an unknown key. */
+int bonsai_b200_set_option(const char *key, int64_t value);
+
+/* Sticky status word written by device-side bounded waits: 0 = no kernel of this library has
+ * given up on a wait on the current device.  Synchronises the device. */
+int bonsai_b200_device_status(void);
+
+/* Version of this build as major * 10000 + minor * 100 + patch. */
+int bonsai_b200_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BONSAI_B200_EXT_H */

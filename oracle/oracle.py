@@ -1,0 +1,180 @@
+"""ctypes access to the CPU checkers (TEST INFRASTRUCTURE).
+
+`Oracle("port")` loads this repository's C restatement (oracle/libbonsai_oracle.so);
+`Oracle("reference")` loads the reference's own headers compiled by oracle/build_oracle.py
+(oracle/_ref/libbonsai_ref.so).  Both expose the same numpy-level methods so a test can run
+one against the other.  Only tests, the smoke check and the benchmark's CPU-baseline leg may
+import this module; the CUDA library has no dependency on it.
+"""
+import ctypes as C
+import os
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+PORT_SO = os.path.join(HERE, "libbonsai_oracle.so")
+REF_SO = os.path.join(HERE, "_ref", "libbonsai_ref.so")
+
+W_BYTES = 34
+A_BYTES = 36
+
+
+def _p(a):
+    return a.ctypes.data_as(C.c_void_p)
+
+
+def reference_available():
+    return os.path.exists(REF_SO)
+
+
+class Oracle:
+    def __init__(self, kind="port"):
+        self.kind = kind
+        if kind == "port":
+            if not os.path.exists(PORT_SO):
+                from .build_oracle import build_oracle
+                build_oracle()
+            self.lib, self.pre = C.CDLL(PORT_SO), "bo_"
+        elif kind == "reference":
+            if not os.path.exists(REF_SO):
+                raise FileNotFoundError("oracle/_ref/libbonsai_ref.so is not built (run oracle/build_oracle.py)")
+            self.lib, self.pre = C.CDLL(REF_SO), "ref_"
+        else:
+            raise ValueError(kind)
+        f = self._fn
+        f("f16_to_f32", C.c_float, [C.c_uint16])
+        f("f32_to_f16", C.c_uint16, [C.c_float])
+        f("quantize_q8_1", None, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int])
+        f("quantize_pq2_0", None, [C.c_void_p, C.c_void_p, C.c_int64])
+        f("dequantize_pq2_0", None, [C.c_void_p, C.c_void_p, C.c_int64])
+        f("fwht_blocks", None, [C.c_void_p, C.c_void_p, C.c_int64])
+        f("chunk_dot", C.c_float, [C.c_void_p, C.c_void_p, C.c_int])
+        f("row_dot", C.c_float, [C.c_void_p, C.c_void_p, C.c_int64])
+        f("gemv", None, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64])
+        f("gemm", None, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64])
+        f("gemv_mt", C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int])
+        f("gemm_mt", C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int])
+        f("repack_row", None, [C.c_void_p, C.c_int, C.c_void_p])
+        f("unpack_row", None, [C.c_void_p, C.c_int, C.c_void_p])
+        f("repack_unit_sumi", C.c_int32, [C.c_void_p, C.c_void_p, C.c_int, C.c_int])
+        f("repack_row_dot", C.c_float, [C.c_void_p, C.c_void_p, C.c_int])
+        if kind == "port":
+            f("chunk_sumi", C.c_int32, [C.c_void_p, C.c_void_p, C.c_int])
+            f("row_chunk_sums", None, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p])
+
+    def _fn(self, name, res, args):
+        fn = getattr(self.lib, self.pre + name)
+        fn.restype, fn.argtypes = res, args
+        setattr(self, "_" + name, fn)
+
+    # ---- scalars -----------------------------------------------------------------------
+    def f16_to_f32(self, h):
+        return float(self._f16_to_f32(int(h)))
+
+    def f32_to_f16(self, f):
+        return int(self._f32_to_f16(float(np.float32(f))))
+
+    # ---- activation side -----------------------------------------------------------------
+    def quantize_q8_1(self, x, permute=True):
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        out = np.zeros(x.size // 32 * A_BYTES, dtype=np.uint8)
+        self._quantize_q8_1(_p(x), _p(out), x.size, int(permute))
+        return out
+
+    def fwht_blocks(self, x, signs=None):
+        y = np.array(x, dtype=np.float32, copy=True).reshape(-1)
+        s = None if signs is None else np.ascontiguousarray(signs, dtype=np.float32)
+        self._fwht_blocks(_p(y), None if s is None else _p(s), y.size)
+        return y
+
+    def quantize_batch_chunk_major(self, X):
+        """X: fp32 [n_tok][n_in] -> Q8_1 bytes laid out [n_in/32][n_tok][36], each token quantised
+        alone (the layout the mat-mul consumes)."""
+        X = np.ascontiguousarray(X, dtype=np.float32)
+        n_tok, n_in = X.shape
+        per_tok = np.stack([self.quantize_q8_1(X[t]).reshape(n_in // 32, A_BYTES) for t in range(n_tok)], axis=1)
+        return np.ascontiguousarray(per_tok).reshape(-1)
+
+    # ---- weight side -----------------------------------------------------------------------
+    def quantize_pq2_0(self, w):
+        w = np.ascontiguousarray(w, dtype=np.float32)
+        out = np.zeros(w.size // 128 * W_BYTES, dtype=np.uint8)
+        self._quantize_pq2_0(_p(w), _p(out), w.size)
+        return out
+
+    def dequantize_pq2_0(self, wq):
+        wq = np.ascontiguousarray(wq, dtype=np.uint8)
+        y = np.zeros(wq.size // W_BYTES * 128, dtype=np.float32)
+        self._dequantize_pq2_0(_p(wq), _p(y), y.size)
+        return y
+
+    # ---- dots ------------------------------------------------------------------------------
+    def chunk_dot(self, wblk, ablk, iqs):
+        wblk = np.ascontiguousarray(wblk, dtype=np.uint8)
+        ablk = np.ascontiguousarray(ablk, dtype=np.uint8)
+        return np.float32(self._chunk_dot(_p(wblk), _p(ablk), iqs))
+
+    def row_chunk_sums(self, wrow, xq, n_in):
+        """int32 per-chunk sums of one row.  The reference exposes them only through the repacked
+        layout, so the reference flavour repacks the row first."""
+        wrow = np.ascontiguousarray(wrow, dtype=np.uint8)
+        xq = np.ascontiguousarray(xq, dtype=np.uint8)
+        out = np.zeros(n_in // 32, dtype=np.int32)
+        if self.kind == "port":
+            self._row_chunk_sums(_p(wrow), _p(xq), n_in, _p(out))
+            return out
+        nb = n_in // 128
+        rp = self.repack_row(wrow, nb)
+        for u in range(4 * nb):
+            out[4 * (u % nb) + u // nb] = self._repack_unit_sumi(_p(rp), _p(xq), nb, u)
+        return out
+
+    def gemv(self, W, xq, n_out, n_in, threads=1):
+        W = np.ascontiguousarray(W, dtype=np.uint8)
+        xq = np.ascontiguousarray(xq, dtype=np.uint8)
+        y = np.zeros(n_out, dtype=np.float32)
+        if threads > 1:
+            self._gemv_mt(_p(W), _p(xq), _p(y), n_out, n_in, threads)
+        else:
+            self._gemv(_p(W), _p(xq), _p(y), n_out, n_in)
+        return y
+
+    def gemm(self, W, Xq, n_out, n_in, n_tok, threads=1):
+        W = np.ascontiguousarray(W, dtype=np.uint8)
+        Xq = np.ascontiguousarray(Xq, dtype=np.uint8)
+        Y = np.zeros((n_out, n_tok), dtype=np.float32)
+        if threads > 1:
+            self._gemm_mt(_p(W), _p(Xq), _p(Y), n_out, n_in, n_tok, threads)
+        else:
+            self._gemm(_p(W), _p(Xq), _p(Y), n_out, n_in, n_tok)
+        return Y
+
+    # ---- repacked layout ----------------------------------------------------------------------
+    def repack_row(self, wrow, nb):
+        wrow = np.ascontiguousarray(wrow, dtype=np.uint8)
+        out = np.zeros(W_BYTES * nb, dtype=np.uint8)
+        self._repack_row(_p(wrow), nb, _p(out))
+        return out
+
+    def unpack_row(self, row, nb):
+        row = np.ascontiguousarray(row, dtype=np.uint8)
+        out = np.zeros(W_BYTES * nb, dtype=np.uint8)
+        self._unpack_row(_p(row), nb, _p(out))
+        return out
+
+    def repack(self, W, n_out, n_in):
+        nb = n_in // 128
+        W = np.ascontiguousarray(W, dtype=np.uint8).reshape(n_out, W_BYTES * nb)
+        return np.concatenate([self.repack_row(W[r], nb) for r in range(n_out)])
+
+    def repack_row_dot(self, row, xq, nb):
+        row = np.ascontiguousarray(row, dtype=np.uint8)
+        xq = np.ascontiguousarray(xq, dtype=np.uint8)
+        return np.float32(self._repack_row_dot(_p(row), _p(xq), nb))
+
+    def gemv_repack(self, Wr, x, n_out, n_in):
+        """Fused entry semantics: quantise fp32 x (not rotated), then repacked row dots."""
+        nb = n_in // 128
+        xq = self.quantize_q8_1(x)
+        Wr = np.ascontiguousarray(Wr, dtype=np.uint8).reshape(n_out, W_BYTES * nb)
+        return np.array([self.repack_row_dot(Wr[r], xq, nb) for r in range(n_out)], dtype=np.float32)

@@ -1,0 +1,132 @@
+"""Python access to libbonsai_p40.so (the sm_100a build) through its C ABI.
+
+The functions mirror include/bonsai_p40.h and include/bonsai_b200_ext.h one to one: same names
+(minus the prefix), same argument order, same integer return codes.  Tensors are torch CUDA tensors
+used only as device memory; the stream passed to the library is torch's current stream, so
+torch.cuda.Event timing brackets the library's kernels.
+
+There is no CPU fallback: importing works without a GPU (the symbols are checked), every compute
+call requires CUDA tensors and raises otherwise.
+"""
+import ctypes as C
+import os
+
+_PKG_DIR = os.path.dirname(os.path.abspath(__file__))
+_ROOT = os.path.dirname(_PKG_DIR)
+LIB_PATH = os.path.join(_ROOT, "libbonsai_p40.so")
+
+W_BLOCK_BYTES = 34
+A_BLOCK_BYTES = 36
+ENOTIMPL = 38
+
+_lib = None
+
+_VP, _I64, _INT, _U64, _F = C.c_void_p, C.c_int64, C.c_int, C.c_uint64, C.c_float
+
+#: every exported symbol with its C signature (also what the symbol-presence test checks)
+SIGNATURES = {
+    "bonsai_p40_gemv": (_INT, [_VP, _VP, _VP, _I64, _I64, _VP]),
+    "bonsai_p40_quant_activations": (_INT, [_VP, _VP, _I64, _VP]),
+    "bonsai_p40_gemm": (_INT, [_VP, _VP, _VP, _I64, _I64, _I64, _VP]),
+    "bonsai_p40_repack": (_INT, [_VP, _VP, _I64, _I64, _VP]),
+    "bonsai_p40_gemv_repack": (_INT, [_VP, _VP, _VP, _I64, _I64, _VP]),
+    "bonsai_p40_fwht": (_INT, [_VP, _VP, _I64, _VP]),
+    "bonsai_p40_rmsnorm": (_INT, [_VP, _VP, _VP, _I64, _I64, _F, _VP]),
+    "bonsai_p40_gdn_step": (_INT, [_VP] * 7 + [_INT] * 4 + [_VP]),
+    "bonsai_p40_attn": (_INT, [_VP] * 4 + [_INT] * 4 + [_F, _VP]),
+    "bonsai_b200_fwht_quant": (_INT, [_VP, _VP, _VP, _VP, _I64, _VP]),
+    "bonsai_b200_quant_batch": (_INT, [_VP, _VP, _VP, _I64, _I64, _INT, _VP]),
+    "bonsai_b200_gemv_chunk_sums": (_INT, [_VP, _VP, _VP, _I64, _I64, _I64, _VP]),
+    "bonsai_b200_synth_pq2_0": (_INT, [_VP, _I64, _I64, _U64, _VP]),
+    "bonsai_b200_set_option": (_INT, [C.c_char_p, _I64]),
+    "bonsai_b200_device_status": (_INT, []),
+    "bonsai_b200_version": (_INT, []),
+}
+
+
+def lib():
+    """Loads the shared library once.  Fails loudly when it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python {os.path.join(_ROOT, 'build.py')}` "
+                "(there is no fallback path)")
+        handle = C.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = handle
+    return _lib
+
+
+def _stream():
+    import torch
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _dev(t, name):
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor: this library has no CPU path")
+    if not t.is_contiguous():
+        raise RuntimeError(f"{name} must be contiguous")
+    return C.c_void_p(t.data_ptr())
+
+
+def set_option(key, value):
+    return lib().bonsai_b200_set_option(key.encode(), int(value))
+
+
+def device_status():
+    return lib().bonsai_b200_device_status()
+
+
+def version():
+    return lib().bonsai_b200_version()
+
+
+# ---- include/bonsai_p40.h ------------------------------------------------------------------------
+def gemv(W, xq, y, n_out, n_in):
+    return lib().bonsai_p40_gemv(_dev(W, "W"), _dev(xq, "xq"), _dev(y, "y"), n_out, n_in, _stream())
+
+
+def quant_activations(x, out, n):
+    return lib().bonsai_p40_quant_activations(_dev(x, "x"), _dev(out, "out"), n, _stream())
+
+
+def gemm(W, Xq, Y, n_out, n_in, n_tok):
+    return lib().bonsai_p40_gemm(_dev(W, "W"), _dev(Xq, "Xq"), _dev(Y, "Y"), n_out, n_in, n_tok, _stream())
+
+
+def repack(src, dst, n_out, n_in):
+    return lib().bonsai_p40_repack(_dev(src, "src"), _dev(dst, "dst"), n_out, n_in, _stream())
+
+
+def gemv_repack(W, x, y, n_out, n_in):
+    return lib().bonsai_p40_gemv_repack(_dev(W, "W"), _dev(x, "x"), _dev(y, "y"), n_out, n_in, _stream())
+
+
+def fwht(x, signs, n):
+    return lib().bonsai_p40_fwht(_dev(x, "x"), _dev(signs, "signs"), n, _stream())
+
+
+# ---- include/bonsai_b200_ext.h ---------------------------------------------------------------------
+def fwht_quant(x, signs, xq, x_rot, n):
+    return lib().bonsai_b200_fwht_quant(_dev(x, "x"), _dev(signs, "signs"), _dev(xq, "xq"), _dev(x_rot, "x_rot"), n,
+                                        _stream())
+
+
+def quant_batch(X, signs, Xq, n_in, n_tok, rotate):
+    return lib().bonsai_b200_quant_batch(_dev(X, "X"), _dev(signs, "signs"), _dev(Xq, "Xq"), n_in, n_tok,
+                                         int(bool(rotate)), _stream())
+
+
+def gemv_chunk_sums(W, xq, out, row0, n_rows, n_in):
+    return lib().bonsai_b200_gemv_chunk_sums(_dev(W, "W"), _dev(xq, "xq"), _dev(out, "out"), row0, n_rows, n_in,
+                                             _stream())
+
+
+def synth_pq2_0(W, first_block, n_blocks, seed):
+    return lib().bonsai_b200_synth_pq2_0(_dev(W, "W"), first_block, n_blocks, seed, _stream())

@@ -1,0 +1,175 @@
+// activation.cuh -- FWHT-1024 rotation and the Q8_1 quantiser (activation side of the path).
+//
+// Replaces, for sm_100a: fwht_1024_p40_kernel (src/kernels/elementwise_p40.cu:17-41) and
+// quant_q8_1_pq2_kernel (src/kernels/gemv_p40.cu:168-196).  Output bytes follow the reference's
+// HOST functions: fwht_blocks (src/fwht.h:20-42) and quantize_row_q8_1(..., permute = true)
+// (src/pq2_0.h:99-126).
+//
+// Both kernels are a handful of warps of latency-bound work (<= 70 KB in, <= 20 KB out per
+// decode vector), so the design goal is one launch and no shared-memory round trips:
+//   * rotation: one warp per 1024-block, 32 values per lane in registers; the ten butterfly
+//     stages run in the host's order (h = 1, 2, ..., 512), each output produced by exactly one
+//     a + b or a - b with a the lower-index operand, so the fp32 bits equal the host's;
+//   * quantiser: eight lanes per 32-chunk, four values per lane (the same register layout the
+//     rotation leaves behind, which is what lets the two fuse without a shuffle stage between).
+#pragma once
+
+#include "common.cuh"
+
+namespace b200 {
+
+// ---- quantiser core: 8 consecutive lanes own one 32-chunk, lane g (0..7) holds x[4g..4g+3] ----
+// Returns through `word` the Q8_1 data word this lane stores (word index g of qs) and through
+// `header` the d|s word (valid on every lane of the group).
+__device__ __forceinline__ void quantise_chunk_8lanes(const float (&v)[4], int lane, uint32_t &word, uint32_t &header) {
+    float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+#pragma unroll
+    for (int o = 1; o < 8; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float d = __fdiv_rn(amax, 127.0f);
+    const float id = d > 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
+    int sum = 0;
+    uint32_t packed = 0;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        int q = round_ties_away(__fmul_rn(v[e], id));
+        q = max(-127, min(127, q));
+        sum += q;
+        packed |= ((uint32_t)q & 0xFFu) << (8 * e);
+    }
+#pragma unroll
+    for (int o = 1; o < 8; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    // 4x4 byte transpose among the four lanes of each half-group: element j = 4g + e lands at
+    // position 16*(j>>4) + 4*(j&3) + ((j>>2)&3) = byte (g&3) of word 4*(g>>2) + e, so this lane
+    // (word g) gathers byte (g&3) from the lanes of its half-group.
+    const int m = lane & 3;
+    const int base = lane & ~3;
+    word = 0;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const uint32_t other = __shfl_sync(0xffffffffu, packed, base + k);
+        word |= ((other >> (8 * m)) & 0xFFu) << (8 * k);
+    }
+    header = f32_to_f16_bits_ties_away(d) | (((uint32_t)sum & 0xFFFFu) << 16);
+}
+
+// One thread per four inputs.  X is [n_tok][n_in]; output block index = chunk * tok_stride + tok
+// (tok_stride = 1 with n_tok = 1 gives the plain vector layout).
+__global__ void __launch_bounds__(256) quant_q8_1_kernel(const float *__restrict__ X, uint32_t *__restrict__ out,
+                                                         int n_in, int n_tok) {
+    pdl_launch_dependents();
+    pdl_wait_prior_grid();
+    const int lane = threadIdx.x & 31;
+    const int per_tok = n_in >> 2;
+    const long long total = (long long)per_tok * n_tok;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    // whole warps iterate together: total is a multiple of 8 and a warp covers 32 threads
+    for (long long i0 = (long long)blockIdx.x * blockDim.x + (threadIdx.x & ~31); i0 < total; i0 += stride) {
+        const long long i = i0 + lane;
+        const bool live = i < total;
+        const long long ic = live ? i : total - 1;
+        const int tok = (int)(ic / per_tok);
+        const int g4 = (int)(ic - (long long)tok * per_tok);
+        const float4 f = *reinterpret_cast<const float4 *>(X + (size_t)tok * n_in + 4 * (size_t)g4);
+        const float v[4] = {f.x, f.y, f.z, f.w};
+        uint32_t word, header;
+        quantise_chunk_8lanes(v, lane, word, header);
+        if (live) {
+            const int chunk = g4 >> 3;
+            uint32_t *blk = out + 9 * ((size_t)chunk * n_tok + tok);
+            blk[1 + (lane & 7)] = word;
+            if ((lane & 7) == 0) blk[0] = header;
+        }
+    }
+}
+
+// ---- rotation: one warp per 1024-block ---------------------------------------------------------
+// Lane l holds v[r][e] = element r*128 + 4*l + e (r = 0..7, e = 0..3): index bits 0-1 are e,
+// bits 2-6 the lane, bits 7-9 r.
+__device__ __forceinline__ void fwht1024_warp(float (&v)[8][4], int lane) {
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {   // h = 1, 2: inside the lane
+        float a = v[r][0], b = v[r][1], c = v[r][2], d = v[r][3];
+        float s0 = __fadd_rn(a, b), s1 = __fsub_rn(a, b), s2 = __fadd_rn(c, d), s3 = __fsub_rn(c, d);
+        v[r][0] = __fadd_rn(s0, s2); v[r][2] = __fsub_rn(s0, s2);
+        v[r][1] = __fadd_rn(s1, s3); v[r][3] = __fsub_rn(s1, s3);
+    }
+#pragma unroll
+    for (int s = 0; s < 5; ++s) {   // h = 4 .. 64: across lanes
+        const bool upper = (lane >> s) & 1;
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float mine = v[r][e];
+                const float other = __shfl_xor_sync(0xffffffffu, mine, 1 << s);
+                v[r][e] = upper ? __fsub_rn(other, mine) : __fadd_rn(mine, other);
+            }
+    }
+#pragma unroll
+    for (int s = 0; s < 3; ++s) {   // h = 128, 256, 512: across r
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+            if (!((r >> s) & 1)) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float a = v[r][e], b = v[r | (1 << s)][e];
+                    v[r][e] = __fadd_rn(a, b);
+                    v[r | (1 << s)][e] = __fsub_rn(a, b);
+                }
+            }
+    }
+#pragma unroll
+    for (int r = 0; r < 8; ++r)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v[r][e] = __fmul_rn(v[r][e], 0.03125f);
+}
+
+// blocks = n_tok * (n_in / 1024) warps.  X [n_tok][n_in] read-only; x_rot (nullable, may alias X)
+// receives the rotated values; xq (nullable) the Q8_1 blocks at chunk * n_tok + tok.
+__global__ void __launch_bounds__(128) fwht_quant_kernel(const float *X, const float *__restrict__ signs, float *x_rot,
+                                                         uint32_t *__restrict__ xq, int n_in, int n_tok) {
+    pdl_launch_dependents();
+    pdl_wait_prior_grid();
+    const int lane = threadIdx.x & 31;
+    const int blocks_per_tok = n_in / FWHT_N;
+    const long long nwarps = (long long)blocks_per_tok * n_tok;
+    const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (w >= nwarps) return;
+    const int tok = (int)(w / blocks_per_tok);
+    const int blk = (int)(w - (long long)tok * blocks_per_tok);
+    const size_t base = (size_t)tok * n_in + (size_t)blk * FWHT_N;
+
+    float v[8][4];
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+        const float4 f = *reinterpret_cast<const float4 *>(X + base + r * 128 + 4 * lane);
+        v[r][0] = f.x; v[r][1] = f.y; v[r][2] = f.z; v[r][3] = f.w;
+    }
+    if (signs) {
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+            const float4 s = *reinterpret_cast<const float4 *>(signs + (size_t)blk * FWHT_N + r * 128 + 4 * lane);
+            v[r][0] = __fmul_rn(v[r][0], s.x); v[r][1] = __fmul_rn(v[r][1], s.y);
+            v[r][2] = __fmul_rn(v[r][2], s.z); v[r][3] = __fmul_rn(v[r][3], s.w);
+        }
+    }
+    fwht1024_warp(v, lane);
+    if (x_rot) {
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+            *reinterpret_cast<float4 *>(x_rot + base + r * 128 + 4 * lane) = make_float4(v[r][0], v[r][1], v[r][2], v[r][3]);
+    }
+    if (xq) {
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+            uint32_t word, header;
+            quantise_chunk_8lanes(v[r], lane, word, header);
+            const int chunk = blk * 32 + r * 4 + (lane >> 3);
+            uint32_t *dst = xq + 9 * ((size_t)chunk * n_tok + tok);
+            dst[1 + (lane & 7)] = word;
+            if ((lane & 7) == 0) dst[0] = header;
+        }
+    }
+}
+
+}  // namespace b200

@@ -1,0 +1,149 @@
+// common.cuh -- device helpers shared by every kernel of the sm_100a build.
+//
+// Arithmetic rules (they make the device output equal the reference's HOST code bit for bit):
+//   * every fp32 operation that the host performs is issued as one explicit IEEE operation
+//     (__fmul_rn / __fadd_rn / __fdiv_rn), so the compiler can neither fuse nor approximate it;
+//   * fp32 -> fp16 uses the host's ties-away rule, not the hardware ties-to-even conversion;
+//   * float -> int uses ties-away (lroundf semantics), not ties-to-even.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace b200 {
+
+constexpr int W_BLOCK_BYTES = 34;   // PQ2_0 block: fp16 scale + 32 code bytes (128 weights)
+constexpr int A_BLOCK_BYTES = 36;   // Q8_1 block: fp16 scale + int16 sum + 32 int8
+constexpr int FWHT_N = 1024;
+
+// Sticky status word: bounded waits write a non-zero code here instead of spinning forever.
+__device__ int g_device_status = 0;
+
+enum : int { STATUS_OK = 0, STATUS_MBARRIER_TIMEOUT = 1 };
+
+// ---- fp16 <-> fp32 -------------------------------------------------------------------------
+__device__ __forceinline__ float f16_bits_to_f32(uint32_t h) {
+    return __half2float(__ushort_as_half((unsigned short)h));   // exact widening
+}
+
+// Host rule of the reference (src/p40_common.h:91-112): the first dropped mantissa bit alone
+// decides the bump, i.e. nearest with ties away from zero; subnormals and overflow included.
+__device__ __forceinline__ uint32_t f32_to_f16_bits_ties_away(float f) {
+    const uint32_t x = __float_as_uint(f);
+    const uint32_t sign = (x >> 16) & 0x8000u;
+    const uint32_t e8 = (x >> 23) & 255u;
+    const uint32_t frac = x & 0x7FFFFFu;
+    if (e8 == 255u) return sign | 0x7C00u | (frac ? 0x200u : 0u);
+    int e = (int)e8 - 112;
+    if (e >= 31) return sign | 0x7C00u;
+    if (e <= 0) {
+        if (e < -10) return sign;
+        const uint32_t full = frac | 0x800000u;
+        const uint32_t sh = (uint32_t)(14 - e);
+        return sign | ((full >> sh) + ((full >> (sh - 1)) & 1u));
+    }
+    uint32_t q = (frac >> 13) + ((frac >> 12) & 1u);
+    if (q == 1024u) { q = 0; e += 1; if (e >= 31) return sign | 0x7C00u; }
+    return sign | ((uint32_t)e << 10) | q;
+}
+
+// lroundf semantics for |t| < 2^23 (a NaN gives 0, as the host's conversion does on x86-64).
+__device__ __forceinline__ int round_ties_away(float t) {
+    const float r = truncf(t);
+    const float frac = __fsub_rn(t, r);          // exact
+    int q = (t == t) ? (int)r : 0;
+    if (fabsf(frac) >= 0.5f) q += (t < 0.0f) ? -1 : 1;
+    return q;
+}
+
+// ---- integer dot ------------------------------------------------------------------------------
+// Four unsigned bytes of `w` times four signed bytes of `a`, plus c (reference: the host dp4a
+// emulation, src/p40_common.h:131-140, applied to codes 0..3 which are non-negative either way).
+__device__ __forceinline__ int dp4a_us(uint32_t w, int a, int c) {
+    int r;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(r) : "r"(w), "r"(a), "r"(c));
+    return r;
+}
+
+// Sum over one 32-weight chunk of code * activation, starting from `init`.  w0 / w1 are the two
+// 16-code words, a[0..7] the eight activation words of the permuted Q8_1 block: field k of word w
+// pairs with activation word 4w + k (src/pq2_0.h:155-166).  Fields are masked in place and the
+// factor 4^k is divided out between steps, which is exact because every partial sum is a multiple
+// of it; callers pass init = -64 * s so that the result is (sum code*a) - s.
+__device__ __forceinline__ int chunk_sumi_scaled(uint32_t w0, uint32_t w1, const int (&a)[8], int init64) {
+    int acc = init64;
+    acc = dp4a_us(w0 & 0xC0C0C0C0u, a[3], acc);
+    acc = dp4a_us(w1 & 0xC0C0C0C0u, a[7], acc);
+    acc >>= 2;
+    acc = dp4a_us(w0 & 0x30303030u, a[2], acc);
+    acc = dp4a_us(w1 & 0x30303030u, a[6], acc);
+    acc >>= 2;
+    acc = dp4a_us(w0 & 0x0C0C0C0Cu, a[1], acc);
+    acc = dp4a_us(w1 & 0x0C0C0C0Cu, a[5], acc);
+    acc >>= 2;
+    acc = dp4a_us(w0 & 0x03030303u, a[0], acc);
+    acc = dp4a_us(w1 & 0x03030303u, a[4], acc);
+    return acc;
+}
+
+// ---- shared-memory barriers and bulk copies (sm_90+ PTX, no cluster multicast anywhere) -------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_fence_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: returns false (and records the status word) instead of spinning forever.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity) {
+    for (uint32_t it = 0; it < (1u << 22); ++it)
+        if (mbar_try_wait(bar, parity)) return true;
+    atomicExch(&g_device_status, STATUS_MBARRIER_TIMEOUT);
+    return false;
+}
+// 1-D bulk copy global -> shared of `bytes` (multiple of 16, both addresses 16-byte aligned),
+// completion counted on `bar`.
+__device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t bytes, uint64_t *bar, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+        ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
+        : "memory");
+}
+__device__ __forceinline__ uint64_t policy_evict_first() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+// Programmatic dependent launch: both are no-ops unless the launch carries the attribute.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait_prior_grid() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+__device__ __forceinline__ uint32_t ldg_nc_u32(const void *p) {
+    uint32_t v;
+    asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(v) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint32_t ldg_nc_u16(const void *p) {
+    unsigned short v;
+    asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(v) : "l"(p));
+    return v;
+}
+
+}  // namespace b200
