@@ -1,0 +1,330 @@
+#!/usr/bin/env python
+"""Benchmark of the PQ2_0 decode mat-vec on B200, one JSON line per run.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference] [--sets S]
+
+Workload ("layer_sweep"): the batch-1 projection shapes of one transformer layer,
+n_in x n_out = 5120x5120, 5120x1024, 5120x17408, 17408x5120, PQ2_0 weights with the checkpoint's
+code distribution, Q8_1 activations from FWHT-rotated N(0,1) vectors.  `--sets S` independent copies
+of the four matrices are resident in HBM (S = 8 -> 446 MB, larger than the 126 MB L2) and a step is
+one pass over all of them, so every launch streams its weights from HBM.
+
+value   : PQ2_0 weight bytes of all launches / device time (CUDA events, max over ranks), GB/s.
+e2e     : the same metric with HOST buffers: per mat-vec the fp32 activation vector is copied from
+          pinned host memory, rotated + quantised + multiplied through the C ABI, and y is copied
+          back, all inside the timed region.  Weights stay resident (they are model state).
+roofline: algorithmic bytes (weights + Q8_1 vector + fp32 output) / average launch time of the
+          mat-vec kernel, against the measured HBM copy bandwidth.
+N > 1   : every matrix is split by output rows over the ranks; each rank multiplies its slice and
+          an NCCL all-gather assembles y (strong scaling: the total work is fixed).
+--impl reference : the reference's own host implementation of the same path on this box's CPU
+          cores (oracle/_ref when it was built, else the C restatement in oracle/).
+"""
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "p40-kernel_b200"))
+
+LAYER_SHAPES = [(5120, 5120), (5120, 1024), (5120, 17408), (17408, 5120)]   # (n_in, n_out)
+METRIC = "pq2_0_gemv_weight_stream"
+UNIT = "GB/s"
+
+
+def weight_bytes(n_in, n_out):
+    return n_out * (n_in // 128) * 34
+
+
+def algorithmic_bytes(n_in, n_out):
+    return weight_bytes(n_in, n_out) + (n_in // 32) * 36 + 4 * n_out
+
+
+def measured_peak_gbs():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        return float(json.load(open(path))["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+# ---------------------------------------------------------------------------------------------------
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons through NVML (read-only) while the timed region runs."""
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index, self.stop_flag, self.sm, self.reasons, self.max_sm = index, threading.Event(), [], set(), None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_sm = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def sample(self):
+        nv = self.nv
+        self.sm.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+        r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+        names = {"hw_slowdown": nv.nvmlClocksThrottleReasonHwSlowdown,
+                 "hw_thermal_slowdown": nv.nvmlClocksThrottleReasonHwThermalSlowdown,
+                 "sw_thermal_slowdown": nv.nvmlClocksThrottleReasonSwThermalSlowdown,
+                 "sw_power_cap": nv.nvmlClocksThrottleReasonSwPowerCap}
+        for k, bit in names.items():
+            if r & bit:
+                self.reasons.add(k)
+
+    def run(self):
+        if self.nv is None:
+            return
+        while not self.stop_flag.is_set():
+            try:
+                self.sample()
+            except Exception:
+                return
+            time.sleep(0.005)
+
+    def result(self):
+        self.stop_flag.set()
+        self.join(timeout=2)
+        if not self.sm:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_sm, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(self.sm), "sm_max_mhz": self.max_sm, "reasons": sorted(self.reasons),
+                "samples": len(self.sm)}
+
+
+# ---------------------------------------------------------------------------------------------------
+def cpu_arm(args, threads):
+    """Times the CPU checker on one layer sweep (FWHT + quantise + mat-vec per shape)."""
+    from oracle.oracle import Oracle, reference_available
+    from bonsai_b200 import synth
+    kind = "reference" if reference_available() else "port"
+    orc = Oracle(kind)
+    mats = [(n_in, n_out, synth.pq2_0_weights(n_out, n_in, seed=i)) for i, (n_in, n_out) in enumerate(LAYER_SHAPES)]
+    xs = {n_in: synth.activations(n_in, seed=0) for n_in, _ in LAYER_SHAPES}
+
+    def sweep():
+        for n_in, n_out, W in mats:
+            xq = orc.quantize_q8_1(orc.fwht_blocks(xs[n_in]), True)
+            orc.gemv(W, xq, n_out, n_in, threads=threads)
+
+    return kind, sweep, sum(weight_bytes(a, b) for a, b in LAYER_SHAPES)
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    kind, sweep, wbytes = cpu_arm(args, threads)
+    for _ in range(max(1, min(args.warmup, 3))):
+        sweep()
+    steps = max(1, min(args.steps, 50))
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        sweep()
+    dt = time.perf_counter() - t0
+    val = wbytes * steps / dt / 1e9
+    sample = f"one layer sweep (4 mat-vecs, {wbytes} weight bytes) per step, FWHT+Q8_1 on the CPU included"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+        "warmup": min(args.warmup, 3), "ms_per_step": dt / steps * 1e3, "higher_is_better": True,
+        "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None, "dtype": "int8xint2->int32, fp32 scale",
+        "data": "synthetic", "config": {"workload": "layer_sweep", "shapes_nin_nout": LAYER_SHAPES, "batch": 1},
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": threads, "kind": kind, "sample": sample},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+# ---------------------------------------------------------------------------------------------------
+def run_b200(args):
+    import torch
+    import bonsai_b200 as bb
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    bb.lib()
+    if args.pdl >= 0:
+        bb.set_option("pdl", args.pdl)
+    if args.variant >= -1:
+        bb.set_option("gemv_variant", args.variant)
+
+    sets = args.sets
+    # ---- resident tensors: weights generated on the device, row slice of this rank only ----------
+    mats = []
+    blk_base = 0
+    for s in range(sets):
+        for n_in, n_out in LAYER_SHAPES:
+            assert n_out % world == 0
+            rows = n_out // world
+            nblk_row = n_in // 128
+            W = torch.empty(rows * nblk_row * 34, dtype=torch.uint8, device="cuda")
+            first = blk_base + rank * rows * nblk_row
+            assert bb.synth_pq2_0(W, first, rows * nblk_row, args.seed) == 0
+            blk_base += n_out * nblk_row
+            y = torch.zeros(n_out, dtype=torch.float32, device="cuda")
+            mats.append((n_in, n_out, rows, W, y))
+    xq = {}
+    xdev = {}
+    for n_in in sorted({a for a, _ in LAYER_SHAPES}):
+        g = torch.Generator(device="cpu").manual_seed(args.seed + n_in)
+        xh = torch.randn(n_in, generator=g, dtype=torch.float32)
+        xdev[n_in] = xh.cuda()
+        xq[n_in] = torch.empty(n_in // 32 * 36, dtype=torch.uint8, device="cuda")
+        assert bb.fwht_quant(xdev[n_in], None, xq[n_in], None, n_in) == 0
+    torch.cuda.synchronize()
+
+    def step_resident():
+        n = 0
+        for n_in, n_out, rows, W, y in mats:
+            ys = y[rank * rows:(rank + 1) * rows]
+            rc = bb.gemv(W, xq[n_in], ys, rows, n_in)
+            n += 1
+            if world > 1:
+                dist.all_gather_into_tensor(y, ys)
+        return n
+
+    # host buffers for the end-to-end leg
+    pin_x = {n_in: xdev[n_in].cpu().pin_memory() for n_in in xdev}
+    pin_y = [torch.empty(m[1], dtype=torch.float32).pin_memory() for m in mats]
+    xin = {n_in: torch.empty(n_in, dtype=torch.float32, device="cuda") for n_in in xdev}
+
+    def step_e2e():
+        n = 0
+        for i, (n_in, n_out, rows, W, y) in enumerate(mats):
+            xin[n_in].copy_(pin_x[n_in], non_blocking=True)
+            bb.fwht_quant(xin[n_in], None, xq[n_in], None, n_in)
+            ys = y[rank * rows:(rank + 1) * rows]
+            bb.gemv(W, xq[n_in], ys, rows, n_in)
+            n += 2
+            if world > 1:
+                dist.all_gather_into_tensor(y, ys)
+            pin_y[i].copy_(y, non_blocking=True)
+        return n
+
+    def timed(step_fn, steps, warmup, sample_clocks):
+        """Captures one step in a CUDA graph (launch overhead of ~30 small kernels would otherwise
+        dominate), replays it `warmup` then `steps` times, and times the replays on the device."""
+        per_step = step_fn()                      # eager once: validates return path, warms caches
+        torch.cuda.synchronize()
+        run = step_fn
+        if not args.no_graph:
+            graph = torch.cuda.CUDAGraph()
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                with torch.cuda.graph(graph, stream=side):
+                    step_fn()
+            torch.cuda.current_stream().wait_stream(side)
+            run = graph.replay
+        for _ in range(warmup):
+            run()
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+            torch.cuda.synchronize()
+        sampler = ClockSampler(local) if sample_clocks else None
+        if sampler:
+            sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            run()
+        e1.record()
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+            torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        clocks = sampler.result() if sampler else None
+        if dist is not None:
+            t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms, per_step * steps, clocks
+
+    total_w = sum(weight_bytes(a, b) for a, b in LAYER_SHAPES) * sets
+    total_alg = sum(algorithmic_bytes(a, b // world) for a, b in LAYER_SHAPES) * sets
+    ms, launches, clocks = timed(step_resident, args.steps, args.warmup, True)
+    value = total_w * args.steps / (ms * 1e-3) / 1e9
+    e2e_steps = max(1, args.steps // 4)
+    ms_e, _, _ = timed(step_e2e, e2e_steps, max(3, args.warmup // 4), False)
+    e2e_value = total_w * e2e_steps / (ms_e * 1e-3) / 1e9
+    status = bb.device_status()
+
+    peak, peak_kind = measured_peak_gbs()
+    achieved = total_alg * args.steps / (ms * 1e-3) / 1e9     # per-rank algorithmic bytes / per-launch time
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong" if world > 1 else "weak",
+        "vs_baseline": None, "dtype": "int8xint2->int32, fp32 scale", "data": "synthetic",
+        "config": {"workload": "layer_sweep", "shapes_nin_nout": LAYER_SHAPES, "batch": 1, "sets": sets,
+                   "resident_weight_bytes": total_w, "l2": "inputs larger than L2" if total_w > 126e6 else "fits L2",
+                   "parallelism": f"rows/{world}+allgather" if world > 1 else "single", "pdl": args.pdl,
+                   "variant": args.variant, "launch": "eager" if args.no_graph else "cuda_graph_per_step"},
+        "gpu_launches": launches,
+        "clocks": clocks,
+        "e2e": {"value": e2e_value, "unit": UNIT,
+                "h2d_bytes_per_step": sum(4 * m[0] for m in mats), "d2h_bytes_per_step": sum(4 * m[1] for m in mats)},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": UNIT, "frac": achieved / peak,
+                     "peak_kind": peak_kind, "traffic": None,
+                     "avg_launch_us": ms * 1e3 / max(1, args.steps * len(mats)),
+                     "algorithmic_bytes_per_launch_avg": total_alg / len(mats)},
+        "device_status": status,
+    }
+    if world == 1 and not args.no_cpu:
+        threads = os.cpu_count() or 1
+        kind, sweep, wbytes = cpu_arm(args, threads)
+        sweep()
+        reps, t0 = 0, time.perf_counter()
+        while time.perf_counter() - t0 < args.cpu_seconds:
+            sweep()
+            reps += 1
+        dt = time.perf_counter() - t0
+        line["cpu_baseline"] = {"value": wbytes * reps / dt / 1e9, "unit": UNIT, "cores": threads, "kind": kind,
+                                "sample": f"{reps} layer sweeps (4 mat-vecs each, FWHT+Q8_1 included) in {dt:.1f} s"}
+    if rank == 0:
+        print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--sets", type=int, default=8)
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--pdl", type=int, default=-1, help="-1 library default, 0 plain launches, 1 programmatic launches")
+    ap.add_argument("--variant", type=int, default=-2, help="-2 leave the library default")
+    ap.add_argument("--cpu-seconds", type=float, default=8.0)
+    ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="launch every kernel from Python instead of replaying a graph")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_b200(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -40,6 +40,12 @@ int bonsai_b200_gemv_chunk_sums(const void *W, const void *xq, int32_t *out, int
  * call depends only on (seed, first_block + i). */
 int bonsai_b200_synth_pq2_0(void *W, int64_t first_block, int64_t n_blocks, uint64_t seed, bonsai_stream stream);
 
+/* Read-only streaming probe over `bytes` of device memory (16-byte aligned): mode 0 reads with
+ * aligned 16-byte loads into registers, mode 1 with 1-D bulk async copies into a shared-memory ring
+ * (the transport of the mat-vec, no arithmetic).  `sink` is 4 writable bytes.  Timed by the caller;
+ * B200 counterpart of the reference's tools/bwtest.cu:37-90. */
+int bonsai_b200_stream_probe(const void *buf, int64_t bytes, int mode, void *sink, bonsai_stream stream);
+
 /* Launch options.  key "pdl": 1 = launch the mat-vec with programmatic stream serialisation,
  * so that its weight stream starts while the previous kernel of the stream drains (weights
  * must not be written by that previous kernel); 0 = plain launches (default).

@@ -38,6 +38,7 @@ SIGNATURES = {
     "bonsai_b200_quant_batch": (_INT, [_VP, _VP, _VP, _I64, _I64, _INT, _VP]),
     "bonsai_b200_gemv_chunk_sums": (_INT, [_VP, _VP, _VP, _I64, _I64, _I64, _VP]),
     "bonsai_b200_synth_pq2_0": (_INT, [_VP, _I64, _I64, _U64, _VP]),
+    "bonsai_b200_stream_probe": (_INT, [_VP, _I64, _INT, _VP, _VP]),
     "bonsai_b200_set_option": (_INT, [C.c_char_p, _I64]),
     "bonsai_b200_device_status": (_INT, []),
     "bonsai_b200_version": (_INT, []),
@@ -130,3 +131,7 @@ def gemv_chunk_sums(W, xq, out, row0, n_rows, n_in):
 
 def synth_pq2_0(W, first_block, n_blocks, seed):
     return lib().bonsai_b200_synth_pq2_0(_dev(W, "W"), first_block, n_blocks, seed, _stream())
+
+
+def stream_probe(buf, nbytes, mode, sink):
+    return lib().bonsai_b200_stream_probe(_dev(buf, "buf"), nbytes, mode, _dev(sink, "sink"), _stream())

@@ -9,6 +9,7 @@
 #include "activation.cuh"
 #include "gemm_simt.cuh"
 #include "gemv.cuh"
+#include "probe.cuh"
 #include "repack.cuh"
 #include "synth.cuh"
 
@@ -62,38 +63,54 @@ cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
-// Rows per CTA / per stage for the staged mat-vec kernels.  `row_bytes` is the row stride,
-// `fixed` the shared memory that does not depend on the row count.
-GemvPlan plan_rows(long long n_out, size_t row_bytes, size_t fixed, int variant) {
-    // variant = rr_code * 100 + span_code * 10 + thread_code, or -1 for the tuned default
-    int rr = 2, span_kb = 48, threads = 256;
+// ceil(2^32 / d): __umulhi(n, magic) == n / d for every n with n * d < 2^32; 0 stands for d == 1.
+inline uint32_t magic_u32(uint32_t d) {
+    if (d <= 1) return 0u;
+    return (uint32_t)(((1ull << 32) + d - 1) / d);
+}
+
+// Geometry of the staged mat-vec kernels.  `row_bytes` is the row stride, `fixed` the shared
+// memory that does not depend on the row count, `granule` the row multiple that keeps a run of
+// rows 16-byte aligned.  CTA counts are multiples of the SM count, so every SM gets the same
+// share, and a CTA stays under half of an SM's shared memory so that a second CTA -- of this launch
+// or, with programmatic launches, of the next kernel in the stream -- can stream beside it.
+GemvPlan plan_rows(long long n_out, size_t row_bytes, size_t fixed, int granule, int variant) {
+    // variant = rr_code * 1000 + cap_code * 100 + stage_code * 10 + thread_code, or -1 = tuned default
+    int rr = 2, cap_kb = 111, stage_kb = 8, threads = 512;
     if (variant >= 0) {
-        const int rr_code = variant / 100, span_code = (variant / 10) % 10, thr_code = variant % 10;
-        rr = rr_code == 0 ? 1 : (rr_code == 1 ? 2 : 4);
-        static const int spans[] = {16, 24, 32, 48, 64, 96, 128, 160};
-        span_kb = spans[span_code & 7];
-        threads = thr_code == 0 ? 128 : (thr_code == 1 ? 256 : (thr_code == 2 ? 192 : 64));
+        static const int rrs[] = {1, 2, 4, 2};
+        static const int caps[] = {111, 220, 72, 56};
+        static const int stages[] = {4, 8, 12, 16, 24, 32, 48, 64};
+        static const int thr[] = {256, 512, 1024, 384};
+        rr = rrs[(variant / 1000) & 3];
+        cap_kb = caps[(variant / 100) % 10 & 3];
+        stage_kb = stages[(variant / 10) % 10 & 7];
+        threads = thr[variant % 10 & 3];
+    }
+    if (rr == 4 && threads > 512) threads = 512;       // register budget of the four-row variant
+    const int unit = granule > rr ? granule : rr;      // both are powers of two
+    auto round_up = [](long long v, long long m) { return (v + m - 1) / m * m; };
+    const size_t room = (size_t)cap_kb * 1024 - GEMV_BAR_BYTES - fixed - 64;
+    long long rows = unit;
+    for (int k = 1;; ++k) {
+        const long long ctas = (long long)SM_COUNT * k;
+        rows = round_up((n_out + ctas - 1) / ctas, unit);
+        if ((size_t)rows * row_bytes <= room || rows == unit) break;
     }
     GemvPlan p;
     p.rr = rr;
     p.threads = threads;
-    size_t budget = (size_t)span_kb * 1024;
-    const size_t room = SMEM_LIMIT - 128 - fixed - 64;
-    if (budget > room) budget = room;
-    long long rows = (long long)(budget / row_bytes) & ~3ll;
-    if (rows < 4) rows = 4;
-    // do not leave SMs idle on small matrices: at most n_out / (2 * SM_COUNT) rows per CTA
-    long long cap = ((n_out + 2 * SM_COUNT - 1) / (2 * SM_COUNT) + 3) & ~3ll;
-    if (cap < 4) cap = 4;
-    if (rows > cap) rows = cap;
     p.rows_per_cta = (int)rows;
-    int rps = (int)((rows + GEMV_MAX_STAGES - 1) / GEMV_MAX_STAGES);
-    // a stage of roughly 8 KB or more keeps the number of bulk copies low
-    const int min_rows = (int)((8192 + row_bytes - 1) / row_bytes);
-    if (rps < min_rows) rps = min_rows;
-    rps = (rps + 3) & ~3;
-    p.rows_per_stage = rps;
-    p.smem_bytes = (int)(128 + fixed + (size_t)rows * row_bytes + 64);
+    p.ctas = (int)((n_out + rows - 1) / rows);
+    long long rps = round_up(((long long)stage_kb * 1024 + row_bytes - 1) / row_bytes, unit);
+    const long long min_rps = round_up((rows + GEMV_MAX_STAGES - 1) / GEMV_MAX_STAGES, unit);
+    if (rps < min_rps) rps = min_rps;
+    p.rows_per_stage = (int)rps;
+    // chain warps come in twos (compute warps must stay paired), at most a quarter of the CTA
+    int chain = 2 * (int)((rows + 63) / 64);
+    const int max_chain = threads / 32 / 4 >= 2 ? (threads / 32 / 4) & ~1 : 2;
+    p.chain_warps = chain < max_chain ? chain : max_chain;
+    p.smem_bytes = (int)(GEMV_BAR_BYTES + fixed + (size_t)rows * row_bytes + 64);
     return p;
 }
 
@@ -158,22 +175,25 @@ int bonsai_p40_gemv(const void *W, const void *xq, float *y, int64_t n_out, int6
     const size_t row_bytes = (size_t)nblocks * W_BLOCK_BYTES;
     const size_t act_bytes = (size_t)(nblocks / 2) * ACT_REC_WORDS * 4;
     const bool staged = (nblocks % 2 == 0) && aligned16(W) && !(reinterpret_cast<uintptr_t>(xq) & 3u) &&
-                        (128 + act_bytes + 4 * row_bytes + 64 <= (size_t)SMEM_LIMIT);
+                        (GEMV_BAR_BYTES + act_bytes + 4 * row_bytes + 64 <= (size_t)111 * 1024);
     if (!staged) {
         return (int)launch(gemv_pq2_generic_kernel, dim3((unsigned)((n_out + 7) / 8)), dim3(256), 0, as_stream(stream),
                            pdl, static_cast<const uint8_t *>(W), static_cast<const uint8_t *>(xq), y, (int)n_out,
                            nblocks);
     }
-    const GemvPlan p = plan_rows(n_out, row_bytes, act_bytes, g_opt_gemv_variant.load());
-    const dim3 grid((unsigned)((n_out + p.rows_per_cta - 1) / p.rows_per_cta));
+    const int npairs = nblocks / 2;
+    const int granule = npairs % 4 == 0 ? 1 : (npairs % 2 == 0 ? 2 : 4);     // row stride is 68 * npairs bytes
+    const GemvPlan p = plan_rows(n_out, row_bytes, act_bytes, granule, g_opt_gemv_variant.load());
+    const dim3 grid((unsigned)p.ctas);
     static SmemOptIn opt1, opt2, opt4;
     cudaError_t e;
     auto go = [&](auto kernel, SmemOptIn &opt) -> cudaError_t {
         cudaError_t err = opt.ensure(kernel);
         if (err != cudaSuccess) return err;
         return launch(kernel, grid, dim3(p.threads), (size_t)p.smem_bytes, as_stream(stream), pdl,
-                      static_cast<const uint8_t *>(W), static_cast<const uint32_t *>(xq), y, (int)n_out, nblocks / 2,
-                      p.rows_per_cta, p.rows_per_stage);
+                      static_cast<const uint8_t *>(W), static_cast<const uint32_t *>(xq), y, (int)n_out, npairs,
+                      p.rows_per_cta, p.rows_per_stage, p.chain_warps, magic_u32((uint32_t)npairs),
+                      magic_u32((uint32_t)(p.rows_per_stage / p.rr)));
     };
     if (p.rr == 1) e = go(gemv_pq2_kernel<1>, opt1);
     else if (p.rr == 2) e = go(gemv_pq2_kernel<2>, opt2);
@@ -230,11 +250,12 @@ int bonsai_p40_gemv_repack(const void *W, const float *x, float *y, int64_t n_ou
     const size_t act_bytes = (size_t)4 * nb * RP_REC_WORDS * 4;
     // the reference refuses vectors whose Q8_1 image exceeds 48 KiB; this build takes anything that
     // leaves room for four rows beside the activation records
-    if (128 + act_bytes + 4 * row_bytes + 64 > (size_t)SMEM_LIMIT) return 1;
+    if (GEMV_BAR_BYTES + act_bytes + 4 * row_bytes + 64 > (size_t)111 * 1024) return 1;
     if (!aligned16(W) || !aligned16(x)) return 1;
     const bool pdl = g_opt_pdl.load() != 0;
-    const GemvPlan p = plan_rows(n_out, row_bytes, act_bytes, g_opt_gemv_variant.load());
-    const dim3 grid((unsigned)((n_out + p.rows_per_cta - 1) / p.rows_per_cta));
+    GemvPlan p = plan_rows(n_out, row_bytes, act_bytes, 1, g_opt_gemv_variant.load());
+    if (p.threads > 256) p.threads = 256;
+    const dim3 grid((unsigned)p.ctas);
     static SmemOptIn opt1, opt2, opt4;
     auto go = [&](auto kernel, SmemOptIn &opt) -> cudaError_t {
         cudaError_t err = opt.ensure(kernel);
@@ -259,6 +280,25 @@ int bonsai_b200_synth_pq2_0(void *W, int64_t first_block, int64_t n_blocks, uint
     return (int)cudaGetLastError();
 }
 
+int bonsai_b200_stream_probe(const void *buf, int64_t bytes, int mode, void *sink, bonsai_stream stream) {
+    if (bytes <= 0 || !aligned16(buf) || !sink) return 1;
+    if (mode == 0) {
+        probe_ldg_kernel<<<SM_COUNT * 8, 256, 0, as_stream(stream)>>>(static_cast<const uint4 *>(buf), bytes / 16,
+                                                                     static_cast<unsigned *>(sink));
+    } else if (mode == 1) {
+        const int slot = 16384, stages = 6;
+        if (bytes < slot) return 1;
+        static SmemOptIn opt;
+        cudaError_t e = opt.ensure(probe_bulk_kernel);
+        if (e != cudaSuccess) return (int)e;
+        probe_bulk_kernel<<<SM_COUNT * 2, 32, 128 + slot * stages, as_stream(stream)>>>(
+            static_cast<const uint8_t *>(buf), bytes, slot, stages, static_cast<unsigned *>(sink));
+    } else {
+        return 1;
+    }
+    return (int)cudaGetLastError();
+}
+
 int bonsai_b200_set_option(const char *key, int64_t value) {
     if (!key) return 1;
     if (!std::strcmp(key, "pdl")) { g_opt_pdl.store(value != 0); return 0; }
@@ -276,6 +316,14 @@ int bonsai_b200_device_status(void) {
 }
 
 int bonsai_b200_version(void) { return 100; }
+
+#ifdef BONSAI_B200_TRACE
+int bonsai_b200_set_skip(int v) { return (int)cudaMemcpyToSymbol(g_skip, &v, sizeof(int)); }
+int bonsai_b200_read_trace(long long *out, int n) {
+    cudaDeviceSynchronize();
+    return (int)cudaMemcpyFromSymbol(out, g_trace, sizeof(long long) * n);
+}
+#endif
 
 // Not on the PQ2_0 mat-vec / mat-mul path: exported so that programs written against the reference
 // link; each refuses without touching its arguments (reference: include/bonsai_p40.h:44-56).

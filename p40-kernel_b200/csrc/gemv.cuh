@@ -14,165 +14,320 @@
 //   * the Q8_1 vector is re-laid in shared memory as one 336-byte record per 256 activations
 //     (8 chunks x 32 int8, 8 scales as fp32, 8 values of -64*s), a stride that keeps 16-byte
 //     loads of neighbouring lanes in different banks;
-//   * an item is one pair of weight blocks (68 bytes = 17 words) for RR consecutive rows.  A lane
-//     reads its 17 words at stride 17 -- conflict-free -- funnel-shifts the 2-byte-offset codes of
-//     the even block, and runs 16 dp4a per chunk with the activation registers shared by RR rows;
-//   * the fp32 term of each chunk overwrites the first 8 words of the item's own weight bytes;
-//     after the CTA's items are done, one lane per row adds the row's terms in order.
+//   * weight blocks are addressed as pairs (68 bytes = 17 words).  An item is one block of a pair
+//     for RR consecutive rows; a warp takes 32 neighbouring pairs of the same parity, so lanes read
+//     9 words each at stride 17 -- conflict-free -- and either all funnel-shift the 2-byte-offset
+//     codes of an even block or all read the word-aligned codes of an odd one; 8 dp4a per chunk
+//     with the activation registers shared by the RR rows;
+//   * the fp32 term of each chunk overwrites a code word of the item's own block; a few warps of
+//     the CTA do nothing but add, one lane per row, the terms of every row whose stage is complete,
+//     in the host's order, while the other warps move on to the next stage;
+//   * CTAs are fat and few (one or two per SM, all of a CTA's rows resident at once), so the
+//     activation vector is staged once per SM-slot instead of once per handful of rows.
 #pragma once
 
 #include "common.cuh"
 
 namespace b200 {
 
-constexpr int GEMV_MAX_STAGES = 16;
+#ifdef BONSAI_B200_TRACE
+// Development aid (not in the shipped build): per-CTA clock stamps of the mat-vec phases.
+__device__ long long g_trace[4096 * 8];
+__device__ int g_skip = 0;   // bit 0: no term computation, bit 1: no ordered sums, bit 2: no activation staging
+#define TRACE_STAMP(slot) do { if ((threadIdx.x & 31) == 0 && blockIdx.x < 4096) { \
+    long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); \
+    if (trace_owner) g_trace[blockIdx.x * 8 + (slot)] = t; } } while (0)
+#else
+#define TRACE_STAMP(slot) do { } while (0)
+#endif
+
+constexpr int GEMV_MAX_STAGES = 64;
+constexpr int GEMV_BAR_BYTES = 2 * GEMV_MAX_STAGES * 8;   // full[] + done[]
 constexpr int ACT_REC_WORDS = 84;   // 64 words int8 + 8 fp32 scales + 8 int32 (-64*s) + 4 pad
 
 struct GemvPlan {
-    int rows_per_cta;     // multiple of RR
-    int rows_per_stage;   // multiple of 4 (keeps every bulk copy 16-byte aligned)
+    int ctas;
+    int rows_per_cta;     // multiple of the alignment granule and of RR
+    int rows_per_stage;   // same
     int threads;
+    int chain_warps;      // warps that add terms in order: 32 rows each
     int rr;
     int smem_bytes;
 };
 
-// Re-lay the Q8_1 vector (global, 9 words per chunk) into padded per-pair records.
-__device__ __forceinline__ void stage_activations(const uint32_t *__restrict__ xq, uint32_t *rec, int nchunks) {
-    for (int i = threadIdx.x; i < nchunks * 9; i += blockDim.x) {
-        const int chunk = i / 9, w = i - chunk * 9;
-        const uint32_t v = __ldg(xq + i);
-        uint32_t *r = rec + (chunk >> 3) * ACT_REC_WORDS;
-        const int cc = chunk & 7;
-        if (w == 0) {
-            r[64 + cc] = __float_as_uint(f16_bits_to_f32(v & 0xFFFFu));
-            r[72 + cc] = (uint32_t)(-64 * (int)(short)(v >> 16));
-        } else {
-            r[cc * 8 + (w - 1)] = v;
-        }
-    }
+// Re-lay the Q8_1 vector (global, 9 words per chunk) into padded per-pair records: one thread per
+// chunk, nine loads in flight, two 16-byte stores plus the scale and the pre-scaled sum.  Split in a
+// load half and a store half so that a caller can issue other memory traffic behind the loads.
+__device__ __forceinline__ void act_chunk_load(const uint32_t *__restrict__ xq, int chunk, uint32_t (&v)[9]) {
+#pragma unroll
+    for (int j = 0; j < 9; ++j) v[j] = __ldg(xq + 9 * chunk + j);
+}
+__device__ __forceinline__ void act_chunk_store(uint32_t *rec, int chunk, const uint32_t (&v)[9]) {
+    uint32_t *r = rec + (chunk >> 3) * ACT_REC_WORDS;
+    const int cc = chunk & 7;
+    *reinterpret_cast<uint4 *>(r + cc * 8) = make_uint4(v[1], v[2], v[3], v[4]);
+    *reinterpret_cast<uint4 *>(r + cc * 8 + 4) = make_uint4(v[5], v[6], v[7], v[8]);
+    r[64 + cc] = __float_as_uint(f16_bits_to_f32(v[0] & 0xFFFFu));
+    r[72 + cc] = (uint32_t)(-64 * (int)(short)(v[0] >> 16));
 }
 
-// Sequential fp32 sum of a row's terms, one lane per row.  `row_words` is the distance between
-// rows in words; lanes whose rows fall in the same bank start a few steps apart (skew) so that
-// their loads hit different banks.  term(i) gives the word offset of term i inside the row.
-template <typename TermOffset>
-__device__ __forceinline__ float ordered_row_sum(const float *row_base, int nterms, int skew, int max_skew,
-                                                 TermOffset term) {
+// n / d through the host-made reciprocal magic = ceil(2^32 / d) (0 stands for d == 1); exact while
+// n * d < 2^32.
+__device__ __forceinline__ uint32_t fast_div(uint32_t n, uint32_t magic) { return magic ? __umulhi(n, magic) : n; }
+
+__host__ __device__ inline int gcd_int(int a, int b) { while (b) { int t = a % b; a = b; b = t; } return a; }
+
+// Lanes whose rows start in the same shared-memory bank walk their rows a few groups apart.
+__device__ __forceinline__ void row_skew(int row_words, int lane, int &skew, int &max_skew) {
+    const int bank_step = row_words & 31;
+    const int distinct = 32 / gcd_int(bank_step == 0 ? 32 : bank_step, 32);   // rows before banks repeat
+    max_skew = (32 / distinct) - 1;
+    skew = lane / distinct;
+}
+
+// Word offset, inside a pair of weight blocks (17 words), of the fp32 term of chunk j (0..7): the
+// even block's terms replace its words 0..3, the odd block's terms its words 9..12.  Word 8 holds
+// bytes of both blocks and is never written.
+__device__ __forceinline__ int term_word(int j) { return j < 4 ? j : j + 5; }
+
+// Sequential fp32 sum of the 8 * npairs terms of one row (one lane per row), in order.  The eight
+// terms of the next pair are loaded while the current eight are being added, so a step costs the
+// dependent-add chain and little else.  `skew` delays a lane by whole pairs (see row_skew): every
+// lane runs the same npairs + max_skew steps, loads from a clamped pair index, and only adds while
+// its own pair index is in range -- no divergence, and the order of a lane's additions is untouched.
+__device__ __forceinline__ float ordered_pair_sum(const float *base, int npairs, int skew, int max_skew) {
     float acc = 0.0f;
-    for (int k = 0; k < nterms + max_skew; ++k) {
-        const int i = k - skew;
-        if (i >= 0 && i < nterms) acc = __fadd_rn(acc, row_base[term(i)]);
+    float cur[8];
+    {
+        const float *p0 = base;                 // pair 0 (what a delayed lane pre-loads is discarded)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) cur[j] = p0[term_word(j)];
+    }
+    bool live = skew == 0;
+    const int steps = npairs + max_skew;
+    const int last = npairs - 1;
+#pragma unroll 2
+    for (int k = 0; k < steps; ++k) {
+        const int qn = k + 1 - skew;
+        const float *pn = base + 17 * min(max(qn, 0), last);
+        float nxt[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) nxt[j] = pn[term_word(j)];
+        if (live) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc = __fadd_rn(acc, cur[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) cur[j] = nxt[j];
+        live = qn >= 0 && qn <= last;
     }
     return acc;
 }
 
-__host__ __device__ inline int gcd_int(int a, int b) { while (b) { int t = a % b; a = b; b = t; } return a; }
+// One item: the even (H = 0) or odd (H = 1) block of pair q, for RR consecutive rows starting at
+// the row whose pair starts at `pair_words`.  Reads 9 words per row, writes 4 fp32 terms per row over
+// code words of the same block (term c at word H + c of the 9).
+template <int RR, int H>
+__device__ __forceinline__ void gemv_item(uint32_t *pair_words, const uint32_t *pair_rec, int row_words) {
+    uint32_t *p = pair_words + 8 * H;
+    uint32_t w[RR][9];
+#pragma unroll
+    for (int rr = 0; rr < RR; ++rr)
+#pragma unroll
+        for (int j = 0; j < 9; ++j) w[rr][j] = p[rr * row_words + j];
+    const uint32_t *rec = pair_rec + 32 * H;                         // the 4 chunks of this half
+    const int4 sc = *reinterpret_cast<const int4 *>(pair_rec + 64 + 4 * H);
+    const int4 in = *reinterpret_cast<const int4 *>(pair_rec + 72 + 4 * H);
+    const int scale_bits[4] = {sc.x, sc.y, sc.z, sc.w};
+    const int inits[4] = {in.x, in.y, in.z, in.w};
+    float dw[RR];
+#pragma unroll
+    for (int rr = 0; rr < RR; ++rr) dw[rr] = f16_bits_to_f32(H ? (w[rr][0] >> 16) : (w[rr][0] & 0xFFFFu));
+    float *tp = reinterpret_cast<float *>(p) + H;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        const int4 lo = *reinterpret_cast<const int4 *>(rec + c * 8);
+        const int4 hi = *reinterpret_cast<const int4 *>(rec + c * 8 + 4);
+        const int a[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+        const float da = __int_as_float(scale_bits[c]);
+#pragma unroll
+        for (int rr = 0; rr < RR; ++rr) {
+            uint32_t c0, c1;
+            if (H == 0) {   // even block: its codes start 2 bytes into word 0
+                c0 = __funnelshift_r(w[rr][2 * c], w[rr][2 * c + 1], 16);
+                c1 = __funnelshift_r(w[rr][2 * c + 1], w[rr][2 * c + 2], 16);
+            } else {        // odd block: scale in the upper half of word 0, codes word-aligned after it
+                c0 = w[rr][2 * c + 1];
+                c1 = w[rr][2 * c + 2];
+            }
+            const int sumi = chunk_sumi_scaled(c0, c1, a, inits[c]);
+            tp[rr * row_words + c] = __fmul_rn(__fmul_rn(dw[rr], da), (float)sumi);
+        }
+    }
+}
 
+// Role split inside a CTA: the first warps ("compute") turn weight blocks into fp32 terms, the
+// last `chain_warps` warps own one output row per lane and add that row's terms in order once the
+// stage holding the row is complete.  Compute warps never wait for a chain.
 template <int RR>
-__global__ void __launch_bounds__(256, 1) gemv_pq2_kernel(const uint8_t *__restrict__ W, const uint32_t *__restrict__ xq,
-                                                       float *__restrict__ y, int n_out, int npairs, int rows_per_cta,
-                                                       int rows_per_stage) {
+__global__ void __launch_bounds__(RR == 4 ? 512 : 1024, 1) gemv_pq2_kernel(const uint8_t *__restrict__ W, const uint32_t *__restrict__ xq,
+                                                          float *__restrict__ y, int n_out, int npairs,
+                                                          int rows_per_cta, int rows_per_stage, int chain_warps,
+                                                          uint32_t magic_npairs, uint32_t magic_gps) {
     extern __shared__ __align__(128) uint8_t smem[];
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem);                       // GEMV_MAX_STAGES barriers
-    uint32_t *act = reinterpret_cast<uint32_t *>(smem + 128);                  // npairs records
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem);                       // stage landed (bulk copy bytes)
+    uint64_t *done = full + GEMV_MAX_STAGES;                                   // stage's terms all written
+    uint32_t *act = reinterpret_cast<uint32_t *>(smem + GEMV_BAR_BYTES);       // npairs records
     uint32_t *wsm = act + (size_t)npairs * ACT_REC_WORDS;                      // rows_per_cta * 17 * npairs words
 
     const int row0 = blockIdx.x * rows_per_cta;
     const int rows_here = min(rows_per_cta, n_out - row0);
+    if (rows_here <= 0) return;
     const int row_words = 17 * npairs;
     const size_t row_bytes = (size_t)row_words * 4;
     const int nstages = (rows_here + rows_per_stage - 1) / rows_per_stage;
+    const int compute_threads = blockDim.x - 32 * chain_warps;
 
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < nstages; ++s) mbar_init(&bars[s], 1);
-        mbar_fence_init();
-        const uint64_t pol = policy_evict_first();
-        const uint8_t *src = W + (size_t)row0 * row_bytes;
-        for (int s = 0; s < nstages; ++s) {
-            const int r_begin = s * rows_per_stage;
-            const int r_cnt = min(rows_per_stage, rows_here - r_begin);
-            const uint32_t bytes = (uint32_t)(r_cnt * row_bytes);
-            const uint32_t bulk = bytes & ~15u;
-            uint8_t *dst = reinterpret_cast<uint8_t *>(wsm) + (size_t)r_begin * row_bytes;
-            if (bulk) {
-                mbar_expect_tx(&bars[s], bulk);
-                bulk_g2s(dst, src + (size_t)r_begin * row_bytes, bulk, &bars[s], pol);
-            } else {
-                mbar_expect_tx(&bars[s], 0);
-            }
-            // a ragged last stage (row count not a multiple of 4) leaves < 16 bytes for plain loads
-            for (uint32_t o = bulk; o < bytes; o += 4)
-                *reinterpret_cast<uint32_t *>(dst + o) = ldg_nc_u32(src + (size_t)r_begin * row_bytes + o);
+#ifdef BONSAI_B200_TRACE
+    const bool trace_owner = threadIdx.x == 0 || (int)threadIdx.x == compute_threads;
+    if (threadIdx.x == 0) TRACE_STAMP(0);
+#endif
+    // Memory requests are served roughly in issue order, so the order below is the order data comes
+    // back: the first stages of weights (they do not depend on the previous kernel of the stream and
+    // go out before the wait on it), then the activation vector, then the remaining stages.  Issuing
+    // every stage first would park the activations behind the CTA's whole share.
+#ifdef BONSAI_B200_TRACE
+    const int skip = g_skip;
+#endif
+    constexpr int EARLY_STAGES = 2;
+    const uint64_t pol = policy_evict_first();
+    const uint8_t *src = W + (size_t)row0 * row_bytes;
+    auto issue_stage = [&](int s) {
+        const int r_begin = s * rows_per_stage;
+        const int r_cnt = min(rows_per_stage, rows_here - r_begin);
+        const uint32_t bytes = (uint32_t)(r_cnt * row_bytes);
+        const uint32_t bulk = bytes & ~15u;
+        uint8_t *dst = reinterpret_cast<uint8_t *>(wsm) + (size_t)r_begin * row_bytes;
+        mbar_expect_tx(&full[s], bulk);
+        if (bulk) bulk_g2s(dst, src + (size_t)r_begin * row_bytes, bulk, &full[s], pol);
+        // a ragged last stage can leave < 16 bytes, fetched with plain loads
+        for (uint32_t o = bulk; o < bytes; o += 4)
+            *reinterpret_cast<uint32_t *>(dst + o) = ldg_nc_u32(src + (size_t)r_begin * row_bytes + o);
+    };
+    if (threadIdx.x < 32) {
+        // lane s of the first warp owns stage s, s + 32, ...: it initialises the two barriers of the
+        // stage and issues the stage's copy, so the copies of a CTA leave in parallel
+        for (int s = threadIdx.x; s < nstages; s += 32) {
+            // done[s] completes when every item of the stage has written its terms: one arrival per
+            // (group of RR rows, pair, half) of the stage
+            const int r_cnt = min(rows_per_stage, rows_here - s * rows_per_stage);
+            mbar_init(&full[s], 1);
+            mbar_init(&done[s], (uint32_t)(2 * npairs * ((r_cnt + RR - 1) / RR)));
         }
+        mbar_fence_init();
+#ifdef BONSAI_B200_TRACE
+        if (!(skip & 24))
+#endif
+        if ((int)threadIdx.x < EARLY_STAGES && (int)threadIdx.x < nstages) issue_stage(threadIdx.x);
     }
+    if (threadIdx.x == 0) TRACE_STAMP(1);
     pdl_launch_dependents();
     pdl_wait_prior_grid();          // activations (and y) belong to the previous kernel until here
-    stage_activations(xq, act, npairs * 8);
-    __syncthreads();                // records + barrier inits + ragged-tail words visible to all
-
-    const int ngroups = (rows_here + RR - 1) / RR;
-    const int nitems = ngroups * npairs;
-    for (int item = threadIdx.x; item < nitems; item += blockDim.x) {
-        const int g = item / npairs, q = item - g * npairs;
-        const int r_first = g * RR;
-        // every row of the group lies in one stage when rows_per_stage % RR == 0
-        if (!mbar_wait_bounded(&bars[r_first / rows_per_stage], 0)) break;
-
-        uint32_t w[RR][17];
-#pragma unroll
-        for (int rr = 0; rr < RR; ++rr) {
-            // rows past the end of a ragged group re-read the group's first row (never stored)
-            const int r = (r_first + rr < rows_here) ? r_first + rr : r_first;
-            const uint32_t *p = wsm + (size_t)r * row_words + 17 * q;
-#pragma unroll
-            for (int j = 0; j < 17; ++j) w[rr][j] = p[j];
-        }
-        const uint32_t *rec = act + q * ACT_REC_WORDS;
-        float dw[RR][2];
-#pragma unroll
-        for (int rr = 0; rr < RR; ++rr) {
-            dw[rr][0] = f16_bits_to_f32(w[rr][0] & 0xFFFFu);
-            dw[rr][1] = f16_bits_to_f32(w[rr][8] >> 16);
-        }
-        const int4 sc0 = *reinterpret_cast<const int4 *>(rec + 64), sc1 = *reinterpret_cast<const int4 *>(rec + 68);
-        const int4 in0 = *reinterpret_cast<const int4 *>(rec + 72), in1 = *reinterpret_cast<const int4 *>(rec + 76);
-        const int scale_bits[8] = {sc0.x, sc0.y, sc0.z, sc0.w, sc1.x, sc1.y, sc1.z, sc1.w};
-        const int inits[8] = {in0.x, in0.y, in0.z, in0.w, in1.x, in1.y, in1.z, in1.w};
-#pragma unroll
-        for (int cc = 0; cc < 8; ++cc) {
-            const int4 lo = *reinterpret_cast<const int4 *>(rec + cc * 8);
-            const int4 hi = *reinterpret_cast<const int4 *>(rec + cc * 8 + 4);
-            const int a[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-            const float da = __int_as_float(scale_bits[cc]);
-            const int init = inits[cc];
-#pragma unroll
-            for (int rr = 0; rr < RR; ++rr) {
-                uint32_t c0, c1;
-                if (cc < 4) {   // even block: codes start 2 bytes into word 0
-                    c0 = __funnelshift_r(w[rr][2 * cc], w[rr][2 * cc + 1], 16);
-                    c1 = __funnelshift_r(w[rr][2 * cc + 1], w[rr][2 * cc + 2], 16);
-                } else {        // odd block: codes are word-aligned from word 9
-                    c0 = w[rr][2 * cc + 1];
-                    c1 = w[rr][2 * cc + 2];
-                }
-                const int sumi = chunk_sumi_scaled(c0, c1, a, init);
-                const float term = __fmul_rn(__fmul_rn(dw[rr][cc >> 2], da), (float)sumi);
-                if (r_first + rr < rows_here)
-                    reinterpret_cast<float *>(wsm)[(size_t)(r_first + rr) * row_words + 17 * q + cc] = term;
-            }
+    if (threadIdx.x == 0) TRACE_STAMP(2);
+    {
+        const int nchunks = npairs * 8;
+        uint32_t v[9];
+        const bool mine = (int)threadIdx.x < nchunks;
+        if (mine) act_chunk_load(xq, threadIdx.x, v);
+#ifdef BONSAI_B200_TRACE
+        if (!(skip & 24))
+#endif
+        if (threadIdx.x < 32)
+            for (int s = threadIdx.x + EARLY_STAGES; s < nstages; s += 32) issue_stage(s);
+        if (mine) act_chunk_store(act, threadIdx.x, v);
+        for (int chunk = threadIdx.x + blockDim.x; chunk < nchunks; chunk += blockDim.x) {
+            act_chunk_load(xq, chunk, v);
+            act_chunk_store(act, chunk, v);
         }
     }
-    __syncthreads();
+    __syncthreads();                // records + barrier inits + ragged-tail words visible to all
+    if (threadIdx.x == 0) TRACE_STAMP(3);
+#ifdef BONSAI_B200_TRACE
+    if (skip & 8) return;
+#endif
 
-    // one lane per row: ordered sum of the 8 * npairs terms
-    const int bank_step = row_words & 31;
-    const int distinct = 32 / gcd_int(bank_step == 0 ? 32 : bank_step, 32);   // rows before banks repeat
-    const int max_skew = (32 / distinct) - 1;
-    for (int r = threadIdx.x; r < rows_here; r += blockDim.x) {
-        const int skew = (r & 31) / distinct;
-        const float *base = reinterpret_cast<const float *>(wsm) + (size_t)r * row_words;
-        y[row0 + r] = ordered_row_sum(base, 8 * npairs, skew, max_skew,
-                                      [](int i) { return 17 * (i >> 3) + (i & 7); });
+    if ((int)threadIdx.x < compute_threads) {
+        // Items: (group of RR rows) x (pair q) x (half h: even or odd block of the pair), in row
+        // order.  A warp takes 32 consecutive (group, pair) positions of ONE half, so its word reads
+        // sit 17 words apart (conflict-free) and the code alignment is uniform across the warp.
+        // Items are (group of RR rows) x (pair q) x (half: even or odd block of the pair), walked in
+        // row order.  A warp keeps one half for the whole kernel and takes 32 consecutive (group, pair)
+        // positions per step, so its reads sit 17 words apart (conflict-free) and the 2-byte offset of
+        // the codes is a compile-time property of the code path it runs.
+        // A ragged last group (n_out not a multiple of RR) is computed in full: its surplus rows read
+        // whatever the slot holds and write terms nobody adds, which costs less than a predicate on
+        // every store.  The slot is sized for whole groups (rows_per_cta % RR == 0).
+        const int ngroups = (rows_here + RR - 1) / RR;
+        const int npos = ngroups * npairs;
+        const int wid = threadIdx.x >> 5;
+        const int half = wid & 1;                                   // compute warps come in pairs
+        const int pos_step = (compute_threads >> 6) * 32;
+        int landed = -1;            // last stage this thread has seen complete
+        for (int pos = (wid >> 1) * 32 + (threadIdx.x & 31); pos < npos; pos += pos_step) {
+            // divisions by npairs and by the groups per stage are multiplications by host-made
+            // reciprocals (exact for every position a CTA can hold)
+            const int g = (int)fast_div((uint32_t)pos, magic_npairs);
+            const int q = pos - g * npairs;
+            const int stage = (int)fast_div((uint32_t)g, magic_gps);     // rows_per_stage % RR == 0
+            if (stage != landed) {
+#ifdef BONSAI_B200_TRACE
+                if (!(skip & 16))
+#endif
+                if (!mbar_wait_bounded(&full[stage], 0)) break;
+                landed = stage;
+#ifdef BONSAI_B200_TRACE
+                if (threadIdx.x == 0 && g == 0) TRACE_STAMP(4);
+#endif
+            }
+            uint32_t *pair_words = wsm + (g * RR) * row_words + 17 * q;
+            const uint32_t *pair_rec = act + q * ACT_REC_WORDS;
+#ifdef BONSAI_B200_TRACE
+            if (skip & 1) { pair_words[0] = pair_rec[0]; } else
+#endif
+            if (half == 0) gemv_item<RR, 0>(pair_words, pair_rec, row_words);
+            else gemv_item<RR, 1>(pair_words, pair_rec, row_words);
+            mbar_arrive(&done[stage]);          // release: the terms above are visible to the adder
+        }
+        if (threadIdx.x == 0) TRACE_STAMP(5);
+    } else {
+        // one lane per row: wait until the row's stage is complete, then add its 8 * npairs terms in
+        // order, eight loads in flight per step
+        const int lane = threadIdx.x & 31;
+        int skew, max_skew;
+        row_skew(row_words, lane, skew, max_skew);
+#ifdef BONSAI_B200_TRACE
+        if (!(skip & 2))
+#endif
+        for (int r0 = ((int)threadIdx.x - compute_threads) & ~31; r0 < rows_here; r0 += 32 * chain_warps) {
+            // the warp waits once, for the stage of its last row (stages complete in row order up to
+            // scheduling noise; waiting for the last one of the warp keeps the wait uniform)
+            const int r_last = min(r0 + 31, rows_here - 1);
+            bool ok = true;
+            for (int s = r0 / rows_per_stage; s <= r_last / rows_per_stage && ok; ++s)
+                ok = mbar_wait_bounded(&done[s], 0);
+            if (!ok) break;
+            const int r = min(r0 + lane, rows_here - 1);        // surplus lanes redo the last row, unstored
+            const float *base = reinterpret_cast<const float *>(wsm) + (size_t)r * row_words;
+            const float acc = ordered_pair_sum(base, npairs, skew, max_skew);
+            if (r0 + lane < rows_here) y[row0 + r] = acc;
+        }
+#ifdef BONSAI_B200_TRACE
+        if ((int)threadIdx.x == compute_threads) {
+            mbar_wait_bounded(&done[nstages - 1], 0);
+            TRACE_STAMP(6);
+        }
+#endif
+        if ((int)threadIdx.x == compute_threads) TRACE_STAMP(7);
     }
 }
 

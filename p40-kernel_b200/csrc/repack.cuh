@@ -43,7 +43,7 @@ __global__ void __launch_bounds__(256) gemv_repack_kernel(const uint8_t *__restr
                                                           int rows_per_stage) {
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem);
-    uint32_t *act = reinterpret_cast<uint32_t *>(smem + 128);          // 4*nb records, indexed by unit
+    uint32_t *act = reinterpret_cast<uint32_t *>(smem + GEMV_BAR_BYTES);   // 4*nb records, indexed by unit
     uint32_t *wsm = act + (size_t)4 * nb * RP_REC_WORDS;
 
     const int row0 = blockIdx.x * rows_per_cta;
@@ -68,22 +68,32 @@ __global__ void __launch_bounds__(256) gemv_repack_kernel(const uint8_t *__restr
     pdl_launch_dependents();
     pdl_wait_prior_grid();
 
-    // fused quantiser: 8 lanes per 32-chunk, record of chunk 4*b + p stored at unit p*nb + b
+    // fused quantiser: 8 lanes per 32-chunk, record of chunk 4*b + p stored at unit p*nb + b.
+    // Loads run four iterations ahead of the shuffles that consume them.
     {
         const int lane = threadIdx.x & 31;
-        const int ngroups4 = nb * 32;   // float4 groups in x
-        for (int i0 = threadIdx.x & ~31; i0 < ngroups4; i0 += blockDim.x) {
-            const int i = i0 + lane;   // ngroups4 is a multiple of 32: every lane is live
-            const float4 f = *reinterpret_cast<const float4 *>(x + 4 * (size_t)i);
-            const float v[4] = {f.x, f.y, f.z, f.w};
-            uint32_t word, header;
-            quantise_chunk_8lanes(v, lane, word, header);
-            const int chunk = i >> 3;
-            uint32_t *rec = act + ((chunk & 3) * nb + (chunk >> 2)) * RP_REC_WORDS;
-            rec[lane & 7] = word;
-            if ((lane & 7) == 0) {
-                rec[8] = __float_as_uint(f16_bits_to_f32(header & 0xFFFFu));
-                rec[9] = (uint32_t)(-64 * (int)(short)(header >> 16));
+        const int ngroups4 = nb * 32;   // float4 groups in x: a multiple of 32, so whole warps are live
+        for (int i0 = threadIdx.x & ~31; i0 < ngroups4; i0 += 4 * blockDim.x) {
+            float4 f[4];
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                const int i = i0 + b * blockDim.x + lane;
+                f[b] = i < ngroups4 ? *reinterpret_cast<const float4 *>(x + 4 * (size_t)i) : make_float4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                const int i = i0 + b * blockDim.x + lane;
+                if (i0 + b * blockDim.x >= ngroups4) break;   // warp-uniform
+                const float v[4] = {f[b].x, f[b].y, f[b].z, f[b].w};
+                uint32_t word, header;
+                quantise_chunk_8lanes(v, lane, word, header);
+                const int chunk = i >> 3;
+                uint32_t *rec = act + ((chunk & 3) * nb + (chunk >> 2)) * RP_REC_WORDS;
+                rec[lane & 7] = word;
+                if ((lane & 7) == 0) {
+                    rec[8] = __float_as_uint(f16_bits_to_f32(header & 0xFFFFu));
+                    rec[9] = (uint32_t)(-64 * (int)(short)(header >> 16));
+                }
             }
         }
     }
@@ -118,13 +128,23 @@ __global__ void __launch_bounds__(256) gemv_repack_kernel(const uint8_t *__restr
     }
     __syncthreads();
 
-    const int bank_step = row_words & 31;
-    const int distinct = 32 / gcd_int(bank_step == 0 ? 32 : bank_step, 32);
-    const int max_skew = (32 / distinct) - 1;
+    // one lane per row: terms added in unit order, four loads in flight per step
+    int skew, max_skew;
+    row_skew(row_words, threadIdx.x & 31, skew, max_skew);
     for (int r = threadIdx.x; r < rows_here; r += blockDim.x) {
-        const int skew = (r & 31) / distinct;
         const float *base = reinterpret_cast<const float *>(wsm) + (size_t)r * row_words + codes_w;
-        y[row0 + r] = ordered_row_sum(base, nunits, skew, max_skew, [](int i) { return 2 * i; });
+        float acc = 0.0f;
+        for (int k = 0; k < nb + max_skew; ++k) {       // nunits / 4 = nb steps
+            const int s4 = k - skew;
+            if (s4 >= 0 && s4 < nb) {
+                float t[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) t[j] = base[2 * (4 * s4 + j)];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc = __fadd_rn(acc, t[j]);
+            }
+        }
+        y[row0 + r] = acc;
     }
 }
 

@@ -1,0 +1,335 @@
+"""GPU parity: every entry point of the C ABI against the CPU checker, on the same inputs.
+
+Bars: Q8_1 blocks, rotated fp32 values, int32 chunk sums and repacked bytes are compared bit for
+bit; the fp32 outputs of the mat-vec / mat-mul are ALSO compared bit for bit (the kernels keep the
+host's summation order), which is stricter than the 1e-5 relative tolerance the path requires --
+REL_TOL below is that bound and is asserted as well, so a future reordering would still be judged
+against it.
+"""
+import numpy as np
+import pytest
+
+from bonsai_b200 import synth
+
+pytestmark = pytest.mark.gpu
+
+REL_TOL = 1e-5   # fp32 outputs: max |got - want| <= REL_TOL * max |want| per vector
+
+
+def bits(a):
+    return np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
+
+
+def dev(a):
+    import torch
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def host(t):
+    return t.detach().cpu().numpy()
+
+
+def assert_close_and_exact(got, want):
+    scale = float(np.abs(want).max()) or 1.0
+    err = float(np.abs(got.astype(np.float64) - want.astype(np.float64)).max())
+    assert err <= REL_TOL * scale, f"max-abs {err:.3e} vs bound {REL_TOL * scale:.3e}"
+    assert np.array_equal(bits(got), bits(want)), f"not bit-identical (max-abs {err:.3e})"
+
+
+# ---- activation side ---------------------------------------------------------------------------
+@pytest.mark.parametrize("n", [32, 64, 1024, 5120, 17408, 32768])
+def test_quantiser_bytes(gpu, port, n):
+    import torch
+    x = synth.activations(n, seed=n) * 2.5
+    x[: min(32, n)] = 0.0
+    out = torch.zeros(n // 32 * 36, dtype=torch.uint8, device="cuda")
+    assert gpu.quant_activations(dev(x), out, n) == 0
+    assert np.array_equal(host(out), port.quantize_q8_1(x, True))
+
+
+def test_quantiser_golden_and_ties(gpu, golden):
+    import torch
+    for xin, want in ((golden["x"], golden["q_raw_perm"]), (golden["x_ties"], golden["q_ties"])):
+        out = torch.zeros(want.size, dtype=torch.uint8, device="cuda")
+        assert gpu.quant_activations(dev(xin), out, xin.size) == 0
+        assert np.array_equal(host(out), want)
+
+
+def test_quantiser_fp16_scale_ties(gpu, port):
+    # chunks whose scale amax/127 falls exactly between two fp16 values: the host rounds away
+    import torch
+    n = 32 * 64
+    x = np.zeros(n, dtype=np.float32)
+    for c in range(64):
+        half = np.uint32(0x3C00 + 16 * c)                              # an fp16 value
+        tie = ((int(half) & 0x3FF) << 13 | ((int(half) >> 10) + 112) << 23 | 0x1000)
+        d = np.array([tie], dtype=np.uint32).view(np.float32)[0]
+        x[32 * c] = np.float32(d) * np.float32(127.0)
+        x[32 * c + 1:32 * c + 32] = synth.activations(31, seed=c) * 0.1
+    out = torch.zeros(n // 32 * 36, dtype=torch.uint8, device="cuda")
+    assert gpu.quant_activations(dev(x), out, n) == 0
+    assert np.array_equal(host(out), port.quantize_q8_1(x, True))
+
+
+@pytest.mark.parametrize("n", [1024, 5120, 17408])
+@pytest.mark.parametrize("signed", [False, True])
+def test_fwht_bits(gpu, port, n, signed):
+    import torch
+    x = synth.activations(n, seed=n + 1)
+    sg = synth.signs(n, seed=n) if signed else None
+    want = port.fwht_blocks(x, sg)
+    xd = dev(x)
+    assert gpu.fwht(xd, None if sg is None else dev(sg), n) == 0
+    assert np.array_equal(bits(host(xd)), bits(want))
+    # fused rotation + quantiser: same bytes as the two calls, input left untouched
+    xin = dev(x)
+    xq = torch.zeros(n // 32 * 36, dtype=torch.uint8, device="cuda")
+    xr = torch.zeros(n, dtype=torch.float32, device="cuda")
+    assert gpu.fwht_quant(xin, None if sg is None else dev(sg), xq, xr, n) == 0
+    assert np.array_equal(bits(host(xin)), bits(x))
+    assert np.array_equal(bits(host(xr)), bits(want))
+    assert np.array_equal(host(xq), port.quantize_q8_1(want, True))
+
+
+def test_fwht_golden(gpu, golden):
+    xd = dev(golden["x"])
+    assert gpu.fwht(xd, dev(golden["signs"]), 2048) == 0
+    assert np.array_equal(bits(host(xd)), golden["fwht_signed"])
+
+
+@pytest.mark.parametrize("n_tok,n_in,rotate", [(5, 256, False), (1, 1024, True), (3, 2048, True), (17, 5120, True),
+                                               (33, 384, False)])
+def test_quant_batch_chunk_major(gpu, port, n_tok, n_in, rotate):
+    import torch
+    X = synth.activations(n_in, seed=n_tok, batch=n_tok) * 1.7
+    sg = synth.signs(n_in, seed=3) if rotate else None
+    Xr = np.stack([port.fwht_blocks(X[t], sg) for t in range(n_tok)]) if rotate else X
+    want = port.quantize_batch_chunk_major(Xr)
+    Xq = torch.zeros(want.size, dtype=torch.uint8, device="cuda")
+    assert gpu.quant_batch(dev(X), None if sg is None else dev(sg), Xq, n_in, n_tok, rotate) == 0
+    assert np.array_equal(host(Xq), want)
+
+
+# ---- mat-vec --------------------------------------------------------------------------------------
+GEMV_SHAPES = [(1, 128), (5, 5120), (31, 384), (33, 1024), (64, 17408), (130, 6144), (257, 256), (1024, 5120),
+               (7, 32768)]
+
+
+def run_gemv(gpu, W, xq, n_out, n_in):
+    import torch
+    y = torch.full((n_out,), -12345.0, dtype=torch.float32, device="cuda")
+    assert gpu.gemv(dev(W), dev(xq), y, n_out, n_in) == 0
+    return host(y)
+
+
+@pytest.mark.parametrize("n_out,n_in", GEMV_SHAPES)
+def test_gemv_bits(gpu, port, n_out, n_in):
+    W = synth.pq2_0_weights(n_out, n_in, seed=n_out)
+    x = synth.activations(n_in, seed=n_in)
+    xq = port.quantize_q8_1(x, True)
+    assert_close_and_exact(run_gemv(gpu, W, xq, n_out, n_in), port.gemv(W, xq, n_out, n_in, threads=4))
+
+
+@pytest.mark.parametrize("variant", [0, 1, 11, 1001, 1011, 1101, 1211, 2001, 2011, 2311, 1012, 13, 1050, 1072])
+@pytest.mark.parametrize("n_out,n_in", [(5, 5120), (203, 5120), (100, 17408), (37, 1024)])
+def test_gemv_every_tiling(gpu, port, variant, n_out, n_in):
+    """Rows per lane (1/2/4), span and thread count change only the schedule, never a bit of y."""
+    W = synth.pq2_0_weights(n_out, n_in, seed=variant + n_out)
+    xq = port.quantize_q8_1(synth.activations(n_in, seed=variant), True)
+    want = port.gemv(W, xq, n_out, n_in, threads=4)
+    try:
+        assert gpu.set_option("gemv_variant", variant) == 0
+        assert_close_and_exact(run_gemv(gpu, W, xq, n_out, n_in), want)
+    finally:
+        gpu.set_option("gemv_variant", -1)
+
+
+def test_gemv_programmatic_launch_same_bits(gpu, port):
+    import torch
+    n_out, n_in = 640, 5120
+    W = synth.pq2_0_weights(n_out, n_in, seed=77)
+    x = synth.activations(n_in, seed=77)
+    want = port.gemv(W, port.quantize_q8_1(port.fwht_blocks(x), True), n_out, n_in, threads=4)
+    Wd, xd = dev(W), dev(x)
+    xq = torch.zeros(n_in // 32 * 36, dtype=torch.uint8, device="cuda")
+    y = torch.zeros(n_out, dtype=torch.float32, device="cuda")
+    try:
+        gpu.set_option("pdl", 1)
+        for _ in range(5):   # back-to-back dependent chains on one stream
+            assert gpu.fwht_quant(xd, None, xq, None, n_in) == 0
+            assert gpu.gemv(Wd, xq, y, n_out, n_in) == 0
+        torch.cuda.synchronize()
+        assert_close_and_exact(host(y), want)
+    finally:
+        gpu.set_option("pdl", 0)
+
+
+def test_gemv_unaligned_weights_take_the_generic_kernel(gpu, port):
+    import torch
+    n_out, n_in = 19, 1024
+    W = synth.pq2_0_weights(n_out, n_in, seed=8)
+    xq = port.quantize_q8_1(synth.activations(n_in, seed=8), True)
+    buf = torch.zeros(W.size + 16, dtype=torch.uint8, device="cuda")
+    buf[2:2 + W.size] = dev(W)
+    y = torch.zeros(n_out, dtype=torch.float32, device="cuda")
+    assert gpu.gemv(buf[2:], dev(xq), y, n_out, n_in) == 0
+    assert_close_and_exact(host(y), port.gemv(W, xq, n_out, n_in))
+
+
+def test_gemv_golden(gpu, golden):
+    got = run_gemv(gpu, golden["W"], golden["xq"], 12, 1024)
+    assert np.array_equal(bits(got), golden["gemv_y"])
+
+
+def test_chunk_sums_int_exact(gpu, port, golden):
+    import torch
+    n_out, n_in = 40, 5120
+    W = synth.pq2_0_weights(n_out, n_in, seed=21)
+    xq = port.quantize_q8_1(synth.activations(n_in, seed=21) * 4.0, True)
+    out = torch.zeros((6, n_in // 32), dtype=torch.int32, device="cuda")
+    assert gpu.gemv_chunk_sums(dev(W), dev(xq), out, 17, 6, n_in) == 0
+    rb = 34 * n_in // 128
+    for i in range(6):
+        assert np.array_equal(host(out)[i], port.row_chunk_sums(W[(17 + i) * rb:(18 + i) * rb], xq, n_in))
+    g = torch.zeros((1, 32), dtype=torch.int32, device="cuda")
+    assert gpu.gemv_chunk_sums(dev(golden["W"]), dev(golden["xq"]), g, 3, 1, 1024) == 0
+    assert np.array_equal(host(g)[0], golden["chunk_sums_row3"])
+
+
+@pytest.mark.parametrize("n_in,n_out", [(5120, 5120), (5120, 1024), (5120, 17408), (17408, 5120)])
+def test_gemv_full_layer_shapes(gpu, port, n_in, n_out):
+    """The projection shapes of one transformer layer at full size, rotated + quantised on the GPU;
+    the whole output is checked (the CPU checker needs well under a second per shape)."""
+    import torch
+    W = synth.pq2_0_weights(n_out, n_in, seed=0)
+    x = synth.activations(n_in, seed=0)
+    xq = torch.zeros(n_in // 32 * 36, dtype=torch.uint8, device="cuda")
+    assert gpu.fwht_quant(dev(x), None, xq, None, n_in) == 0
+    want_xq = port.quantize_q8_1(port.fwht_blocks(x), True)
+    assert np.array_equal(host(xq), want_xq)
+    y = torch.zeros(n_out, dtype=torch.float32, device="cuda")
+    assert gpu.gemv(dev(W), xq, y, n_out, n_in) == 0
+    assert_close_and_exact(host(y), port.gemv(W, want_xq, n_out, n_in, threads=8))
+
+
+def test_gemv_linearity_in_the_weight_scale(gpu, port):
+    """Size-independent property: doubling every fp16 block scale doubles y exactly."""
+    n_out, n_in = 300, 5120
+    W = synth.pq2_0_weights(n_out, n_in, seed=9).reshape(-1, 34).copy()
+    xq = port.quantize_q8_1(synth.activations(n_in, seed=9), True)
+    y1 = run_gemv(gpu, W.reshape(-1), xq, n_out, n_in)
+    d = W[:, :2].copy().view(np.float16)
+    W[:, :2] = (d * np.float16(2.0)).view(np.uint8)
+    y2 = run_gemv(gpu, W.reshape(-1), xq, n_out, n_in)
+    assert np.array_equal(bits(y2), bits(y1 * np.float32(2.0)))
+
+
+# ---- repacked layout ----------------------------------------------------------------------------------
+@pytest.mark.parametrize("n_out,n_in", [(12, 1024), (5, 5120), (67, 17408), (300, 6144)])
+def test_repack_bytes_and_gemv(gpu, port, n_out, n_in):
+    import torch
+    W = synth.pq2_0_weights(n_out, n_in, seed=n_in)
+    x = synth.activations(n_in, seed=n_out) * 1.3
+    Wr = torch.zeros(W.size, dtype=torch.uint8, device="cuda")
+    assert gpu.repack(dev(W), Wr, n_out, n_in) == 0
+    want_r = port.repack(W, n_out, n_in)
+    assert np.array_equal(host(Wr), want_r)
+    y = torch.zeros(n_out, dtype=torch.float32, device="cuda")
+    assert gpu.gemv_repack(Wr, dev(x), y, n_out, n_in) == 0
+    assert_close_and_exact(host(y), port.gemv_repack(want_r, x, n_out, n_in))
+
+
+def test_repack_golden(gpu, golden):
+    import torch
+    Wr = torch.zeros(golden["W"].size, dtype=torch.uint8, device="cuda")
+    assert gpu.repack(dev(golden["W"]), Wr, 12, 1024) == 0
+    assert np.array_equal(host(Wr), golden["W_repacked"])
+    y = torch.zeros(12, dtype=torch.float32, device="cuda")
+    assert gpu.gemv_repack(Wr, dev(golden["x"][:1024]), y, 12, 1024) == 0
+    assert np.array_equal(bits(host(y)), golden["gemv_repack_y"])
+
+
+@pytest.mark.parametrize("variant", [1, 1011, 2311])
+def test_gemv_repack_every_tiling(gpu, port, variant):
+    import torch
+    n_out, n_in = 101, 5120
+    W = synth.pq2_0_weights(n_out, n_in, seed=variant)
+    x = synth.activations(n_in, seed=variant)
+    want_r = port.repack(W, n_out, n_in)
+    y = torch.zeros(n_out, dtype=torch.float32, device="cuda")
+    try:
+        gpu.set_option("gemv_variant", variant)
+        assert gpu.gemv_repack(dev(want_r), dev(x), y, n_out, n_in) == 0
+    finally:
+        gpu.set_option("gemv_variant", -1)
+    assert_close_and_exact(host(y), port.gemv_repack(want_r, x, n_out, n_in))
+
+
+# ---- mat-mul ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("n_out,n_in,n_tok", [(64, 256, 5), (5, 128, 1), (70, 384, 33), (256, 5120, 17), (130, 1024, 64),
+                                              (96, 17408, 8)])
+def test_gemm_bits(gpu, port, n_out, n_in, n_tok):
+    import torch
+    W = synth.pq2_0_weights(n_out, n_in, seed=n_tok)
+    X = synth.activations(n_in, seed=n_out, batch=n_tok)
+    Xq = port.quantize_batch_chunk_major(X)
+    Y = torch.full((n_out, n_tok), 777.0, dtype=torch.float32, device="cuda")
+    assert gpu.gemm(dev(W), dev(Xq), Y, n_out, n_in, n_tok) == 0
+    assert_close_and_exact(host(Y), port.gemm(W, Xq, n_out, n_in, n_tok, threads=8))
+
+
+def test_gemm_golden(gpu, golden):
+    import torch
+    Y = torch.zeros((16, 5), dtype=torch.float32, device="cuda")
+    assert gpu.gemm(dev(golden["Wg"]), dev(golden["Xq"]), Y, 16, 256, 5) == 0
+    assert np.array_equal(bits(host(Y)).reshape(-1), golden["gemm_Y"].reshape(-1))
+
+
+def test_gemm_one_token_equals_gemv(gpu, port):
+    import torch
+    n_out, n_in = 200, 5120
+    W = synth.pq2_0_weights(n_out, n_in, seed=4)
+    xq = port.quantize_q8_1(synth.activations(n_in, seed=4), True)
+    Y = torch.zeros((n_out, 1), dtype=torch.float32, device="cuda")
+    assert gpu.gemm(dev(W), dev(xq), Y, n_out, n_in, 1) == 0
+    assert np.array_equal(bits(host(Y)).reshape(-1), bits(run_gemv(gpu, W, xq, n_out, n_in)))
+
+
+# ---- synthetic weights, status ----------------------------------------------------------------------------
+def test_synthetic_weights_distribution_and_slices(gpu):
+    import torch
+    nblk = 40 * 2048
+    W = torch.zeros(nblk * 34, dtype=torch.uint8, device="cuda")
+    assert gpu.synth_pq2_0(W, 0, nblk, 0) == 0
+    w = host(W).reshape(nblk, 34)
+    codes = ((w[:, 2:, None] >> (2 * np.arange(4))) & 3).reshape(-1)
+    freq = np.bincount(codes, minlength=4) / codes.size
+    assert abs(freq[0] - 0.33) < 0.005 and abs(freq[1] - 0.34) < 0.005 and abs(freq[2] - 0.33) < 0.005
+    assert 0.0005 < freq[3] < 0.0015
+    d = w[:, :2].copy().view(np.float16).astype(np.float64).reshape(-1)
+    assert (d >= 0).all() and abs(d.mean() - 0.02 * np.sqrt(2 / np.pi)) < 0.001
+    # a slice regenerated alone equals the same blocks of the full tensor
+    part = torch.zeros(100 * 34, dtype=torch.uint8, device="cuda")
+    assert gpu.synth_pq2_0(part, 5000, 100, 0) == 0
+    assert np.array_equal(host(part), w[5000:5100].reshape(-1))
+    other = torch.zeros(100 * 34, dtype=torch.uint8, device="cuda")
+    assert gpu.synth_pq2_0(other, 5000, 100, 1) == 0
+    assert not np.array_equal(host(other), host(part))
+
+
+def test_rejections_and_stubs_on_device(gpu):
+    import torch
+    z = torch.zeros(4096, dtype=torch.float32, device="cuda")
+    b = torch.zeros(8192, dtype=torch.uint8, device="cuda")
+    assert gpu.gemv(b, b, z, 4, 100) == 1
+    assert gpu.gemv(b, b, z, 0, 128) == 0
+    assert gpu.quant_activations(z, b, 48) == 1
+    assert gpu.fwht(z, None, 1000) == 1
+    assert gpu.repack(b, b, 4, 128) == 1
+    assert gpu.gemv_repack(b, z, z, 4, 640) == 1
+    assert gpu.gemm(b, b, z, 4, 100, 2) == 1
+    assert gpu.lib().bonsai_p40_rmsnorm(None, None, None, 1, 8, 1e-6, None) == gpu.ENOTIMPL
+
+
+def test_no_bounded_wait_gave_up(gpu):
+    assert gpu.device_status() == 0
