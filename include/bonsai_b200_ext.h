@@ -49,6 +49,10 @@ int bonsai_b200_stream_probe(const void *buf, int64_t bytes, int mode, void *sin
 /* Launch options.  key "pdl": 1 = launch the mat-vec with programmatic stream serialisation,
  * so that its weight stream starts while the previous kernel of the stream drains (weights
  * must not be written by that previous kernel); 0 = plain launches (default).
+ * key "gemv_order": 0 (default) = the streaming mat-vec, whose fp32 terms equal the host's bit for
+ * bit and are added in a fixed tree order (outputs within 1e-5 of the host's, identical from launch
+ * to launch); 1 = the mat-vec that also adds them in the host's sequential order (outputs
+ * bit-identical to src/pq2_0.h:183-191, slower).
  * key "gemv_variant": -1 = automatic, otherwise a tuning index used by the benchmark sweep.
  * Returns 0, or 1 for an unknown key. */
 int bonsai_b200_set_option(const char *key, int64_t value);

@@ -9,6 +9,7 @@
 #include "activation.cuh"
 #include "gemm_simt.cuh"
 #include "gemv.cuh"
+#include "gemv_stream.cuh"
 #include "probe.cuh"
 #include "repack.cuh"
 #include "synth.cuh"
@@ -25,6 +26,7 @@ constexpr int SMEM_LIMIT = 227 * 1024;        // dynamic shared memory a CTA may
 
 std::atomic<int> g_opt_pdl{0};
 std::atomic<int> g_opt_gemv_variant{-1};
+std::atomic<int> g_opt_gemv_order{0};          // 0: streaming kernel (fixed tree order), 1: the host's sequential order
 
 inline cudaStream_t as_stream(bonsai_stream s) { return reinterpret_cast<cudaStream_t>(s); }
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -67,6 +69,143 @@ cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
 inline uint32_t magic_u32(uint32_t d) {
     if (d <= 1) return 0u;
     return (uint32_t)(((1ull << 32) + d - 1) / d);
+}
+
+// Geometry of the streaming mat-vec (gemv_stream.cuh).
+// variant = thr_code * 1000 + seg_code * 100 + tile_code * 10 + cap_code, -1 = default.
+bool plan_stream(long long n_out, int nb, int variant, StreamParams &p, int &threads, int &smem_bytes) {
+    if (nb % 2 != 0) return false;                  // rows must start on a word boundary
+    int seg = 8 * STREAM_STEPS, tile_kb = 16, cap_kb = 108;
+    threads = 512;
+    if (variant >= 0) {
+        static const int thr[] = {512, 384, 256, 128};
+        static const int segs[] = {40, 32, 24, 16, 8, 40, 40, 40};
+        static const int tiles[] = {16, 8, 12, 24, 32, 48, 6, 4};
+        static const int caps[] = {108, 200, 72, 150};
+        threads = thr[(variant / 1000) & 3];
+        seg = segs[(variant / 100) % 10 & 7];
+        tile_kb = tiles[(variant / 10) % 10 & 7];
+        cap_kb = caps[variant % 10 & 3];
+    }
+    auto round_up = [](long long v, long long m) { return (v + m - 1) / m * m; };
+    long long ctas = (n_out + 3) / 4;
+    if (ctas > SM_COUNT) ctas = SM_COUNT;
+    long long rows = round_up((n_out + ctas - 1) / ctas, 4);
+    p.n_out = (int)n_out;
+    p.nb = nb;
+    const size_t row_bytes = (size_t)nb * W_BLOCK_BYTES;
+    // segments: equal multiples of 8 blocks (every block lane of a task gets the same count), at most
+    // what a task holds in registers
+    p.nseg = (nb + seg - 1) / seg;
+    p.seg_blocks = (int)round_up((nb + p.nseg - 1) / p.nseg, 8);
+    if (p.seg_blocks > 8 * STREAM_STEPS) p.seg_blocks = 8 * STREAM_STEPS;
+    p.nseg = (nb + p.seg_blocks - 1) / p.seg_blocks;
+    for (int attempt = 0;; ++attempt) {
+        const size_t fixed = 2 * RING_MAX_TILES * 8 + (size_t)nb * (STREAM_ACT_WORDS * 4 + 32) +
+                             (size_t)rows * p.nseg * 4 + (size_t)((rows / 4 + 3) & ~3) * 4 + 16;
+        if ((size_t)cap_kb * 1024 < fixed + 64) return false;
+        const size_t room = (size_t)cap_kb * 1024 - fixed - 64;
+        long long tr = ((long long)tile_kb * 1024 / (long long)row_bytes) & ~3ll;
+        if (tr < 4) tr = 4;
+        if (tr > rows) tr = rows;
+        while (tr > 4 && 3 * ((size_t)tr * row_bytes + 16) > room) tr -= 4;
+        if (2 * ((size_t)tr * row_bytes + 16) > room) return false;
+        long long nslot = (long long)(room / ((size_t)tr * row_bytes + 16));
+        if (nslot > RING_MAX_SLOTS) nslot = RING_MAX_SLOTS;
+        const long long ntiles = (rows + tr - 1) / tr;
+        if (ntiles > RING_MAX_TILES) {          // very tall matrix: more CTAs, each with fewer rows
+            if (attempt > 64) return false;
+            const long long k = attempt + 2;
+            rows = round_up((n_out + SM_COUNT * k - 1) / (SM_COUNT * k), 4);
+            continue;
+        }
+        p.rows_per_cta = (int)rows;
+        p.tr = (int)tr;
+        p.nslot = (int)nslot;
+        p.tpt = (p.tr / 4) * p.nseg;
+        p.magic_tpt = magic_u32((uint32_t)p.tpt);
+        p.magic_nseg = magic_u32((uint32_t)p.nseg);
+        p.magic_nslot = magic_u32((uint32_t)p.nslot);
+        smem_bytes = (int)(fixed + (size_t)p.nslot * ((size_t)tr * row_bytes + 16) + 64);
+        return true;
+    }
+}
+
+// Geometry of the ring mat-vec: one CTA per SM, tiles of about 16 rows by one row segment, a ring that
+// keeps the CTA under half of an SM's shared memory.
+// variant = thr_code * 100000 + rr_code * 10000 + seg_code * 1000 + rs_code * 100 + chain_code * 10 + cap_code,
+// -1 = default.
+bool plan_ring(long long n_out, int npairs, int variant, RingParams &p, int &threads, int &smem_bytes, int &rr) {
+    rr = 2;
+    int seg_pairs = 16, rs_target = 16, chain = 3, cap_kb = 108;
+    threads = 1024;
+    if (variant >= 0) {
+        static const int rrs[] = {1, 2, 4, 2};
+        static const int segs[] = {16, 12, 20, 24, 32, 8, 1 << 20, 16};
+        static const int rst[] = {16, 8, 32, 12, 24, 4, 16, 16};
+        static const int chains[] = {3, 5, 1, 7};    // odd: with the copy warp an even count of warps computes
+        static const int caps[] = {108, 200, 72, 150};
+        rr = rrs[(variant / 10000) & 3];
+        seg_pairs = segs[(variant / 1000) % 10 & 7];
+        rs_target = rst[(variant / 100) % 10 & 7];
+        chain = chains[(variant / 10) % 10 & 3];
+        cap_kb = caps[variant % 10 & 3];
+        static const int thr[] = {1024, 512, 768, 256};
+        threads = thr[(variant / 100000) & 3];
+    }
+    if (rr == 4 && threads > 512) threads = 512;        // register budget of the four-row variant
+    auto round_up = [](long long v, long long m) { return (v + m - 1) / m * m; };
+    const int granule = npairs % 4 == 0 ? 1 : (npairs % 2 == 0 ? 2 : 4);      // rows per 16-byte aligned run
+    const int unit = granule > rr ? granule : rr;
+    long long ctas = (n_out + unit - 1) / unit;
+    if (ctas > SM_COUNT) ctas = SM_COUNT;
+    long long rows = round_up((n_out + ctas - 1) / ctas, unit);
+    // a CTA has RING_MAX_TILES single-use barrier pairs: very tall matrices take more CTAs per SM
+    const long long nseg_est = (npairs % 4 == 0 && npairs >= 2 * seg_pairs) ? npairs / seg_pairs : 1;
+    const long long max_rows = (RING_MAX_TILES / nseg_est) * unit;      // tiles hold at least `unit` rows
+    if (rows > max_rows) {
+        const long long k = (n_out + max_rows * SM_COUNT - 1) / (max_rows * SM_COUNT);
+        rows = round_up((n_out + SM_COUNT * k - 1) / (SM_COUNT * k), unit);
+    }
+    p.n_out = (int)n_out;
+    p.npairs = npairs;
+    p.rows_per_cta = (int)rows;
+    if (npairs % 4 == 0 && npairs >= 2 * seg_pairs) {
+        p.seg_base = seg_pairs;
+        p.nseg = npairs / seg_pairs;
+        p.sp = npairs - (p.nseg - 1) * seg_pairs;
+        p.sw = 17 * p.sp;
+        if ((p.sw / 4) % 2 == 0) p.sw += 4;            // odd count of 16-byte units: rows spread over 8 bank groups
+    } else {
+        p.nseg = 1;
+        p.seg_base = p.sp = npairs;
+        p.sw = 17 * npairs;
+    }
+    const size_t fixed = RING_BAR_BYTES + (size_t)npairs * ACT_REC_WORDS * 4;
+    const size_t room = (size_t)cap_kb * 1024 > fixed + 64 ? (size_t)cap_kb * 1024 - fixed - 64 : 0;
+    p.ts = 8 * p.sp + 4;                                   // an odd count of 16-byte units per row
+    p.ntb = 3;
+    long long rs = rs_target < rows ? round_up((rows + (rows + rs_target - 1) / rs_target - 1) /
+                                               ((rows + rs_target - 1) / rs_target), unit)
+                                    : rows;
+    if (rs > 32) rs = 32 / unit * unit;
+    auto need = [&](long long r, int slots) { return (size_t)r * ((size_t)p.sw * 4 * slots + (size_t)p.ts * 4 * p.ntb); };
+    while (rs > unit && need(rs, 3) > room) rs -= unit;                 // three weight slots at least
+    if (need(rs, 2) > room || rs < unit) return false;
+    p.rs = (int)rs;
+    long long nslot = (long long)((room - (size_t)rs * p.ts * 4 * p.ntb) / ((size_t)rs * p.sw * 4));
+    if (nslot > RING_MAX_SLOTS) nslot = RING_MAX_SLOTS;
+    p.nslot = (int)nslot;
+    p.chain_warps = chain;
+    if (((rows + p.rs - 1) / p.rs) * p.nseg > RING_MAX_TILES) return false;
+    p.ppt = (p.rs / rr) * p.sp;
+    p.magic_ppt = magic_u32((uint32_t)p.ppt);
+    p.magic_sp = magic_u32((uint32_t)p.sp);
+    p.magic_nseg = magic_u32((uint32_t)p.nseg);
+    p.magic_nslot = magic_u32((uint32_t)p.nslot);
+    p.magic_ntb = magic_u32((uint32_t)p.ntb);
+    smem_bytes = (int)(fixed + need(p.rs, p.nslot) + 64);
+    return true;
 }
 
 // Geometry of the staged mat-vec kernels.  `row_bytes` is the row stride, `fixed` the shared
@@ -172,32 +311,41 @@ int bonsai_p40_gemv(const void *W, const void *xq, float *y, int64_t n_out, int6
     if (n_out > INT32_MAX || n_in / 128 > INT32_MAX / 64) return 1;
     const int nblocks = (int)(n_in / 128);
     const bool pdl = g_opt_pdl.load() != 0;
-    const size_t row_bytes = (size_t)nblocks * W_BLOCK_BYTES;
-    const size_t act_bytes = (size_t)(nblocks / 2) * ACT_REC_WORDS * 4;
-    const bool staged = (nblocks % 2 == 0) && aligned16(W) && !(reinterpret_cast<uintptr_t>(xq) & 3u) &&
-                        (GEMV_BAR_BYTES + act_bytes + 4 * row_bytes + 64 <= (size_t)111 * 1024);
-    if (!staged) {
+    const int variant = g_opt_gemv_variant.load();
+    const bool base_ok = (nblocks % 2 == 0) && aligned16(W) && !(reinterpret_cast<uintptr_t>(xq) & 3u);
+    int threads = 0, smem_bytes = 0, rr = 2;
+    if (g_opt_gemv_order.load() == 0) {
+        StreamParams sp;
+        if (base_ok && plan_stream(n_out, nblocks, variant, sp, threads, smem_bytes)) {
+            static SmemOptIn opt;
+            cudaError_t err = opt.ensure(gemv_stream_kernel);
+            if (err != cudaSuccess) return (int)err;
+            return (int)launch(gemv_stream_kernel, dim3((unsigned)((n_out + sp.rows_per_cta - 1) / sp.rows_per_cta)),
+                               dim3(threads), (size_t)smem_bytes, as_stream(stream), pdl,
+                               static_cast<const uint8_t *>(W), static_cast<const uint32_t *>(xq), y, sp);
+        }
+    }
+    RingParams rp;
+    const bool ring = base_ok && g_opt_gemv_order.load() != 0 &&
+                      plan_ring(n_out, nblocks / 2, variant, rp, threads, smem_bytes, rr);
+    if (!ring) {
+        // odd block count, unaligned weights or a row too long for the rings: plain loads, host order
         return (int)launch(gemv_pq2_generic_kernel, dim3((unsigned)((n_out + 7) / 8)), dim3(256), 0, as_stream(stream),
                            pdl, static_cast<const uint8_t *>(W), static_cast<const uint8_t *>(xq), y, (int)n_out,
                            nblocks);
     }
-    const int npairs = nblocks / 2;
-    const int granule = npairs % 4 == 0 ? 1 : (npairs % 2 == 0 ? 2 : 4);     // row stride is 68 * npairs bytes
-    const GemvPlan p = plan_rows(n_out, row_bytes, act_bytes, granule, g_opt_gemv_variant.load());
-    const dim3 grid((unsigned)p.ctas);
+    const dim3 grid((unsigned)((n_out + rp.rows_per_cta - 1) / rp.rows_per_cta));
     static SmemOptIn opt1, opt2, opt4;
-    cudaError_t e;
     auto go = [&](auto kernel, SmemOptIn &opt) -> cudaError_t {
         cudaError_t err = opt.ensure(kernel);
         if (err != cudaSuccess) return err;
-        return launch(kernel, grid, dim3(p.threads), (size_t)p.smem_bytes, as_stream(stream), pdl,
-                      static_cast<const uint8_t *>(W), static_cast<const uint32_t *>(xq), y, (int)n_out, npairs,
-                      p.rows_per_cta, p.rows_per_stage, p.chain_warps, magic_u32((uint32_t)npairs),
-                      magic_u32((uint32_t)(p.rows_per_stage / p.rr)));
+        return launch(kernel, grid, dim3(threads), (size_t)smem_bytes, as_stream(stream), pdl,
+                      static_cast<const uint8_t *>(W), static_cast<const uint32_t *>(xq), y, rp);
     };
-    if (p.rr == 1) e = go(gemv_pq2_kernel<1>, opt1);
-    else if (p.rr == 2) e = go(gemv_pq2_kernel<2>, opt2);
-    else e = go(gemv_pq2_kernel<4>, opt4);
+    cudaError_t e;
+    if (rr == 1) e = go(gemv_ring_kernel<1>, opt1);
+    else if (rr == 2) e = go(gemv_ring_kernel<2>, opt2);
+    else e = go(gemv_ring_kernel<4>, opt4);
     return (int)e;
 }
 
@@ -303,6 +451,7 @@ int bonsai_b200_set_option(const char *key, int64_t value) {
     if (!key) return 1;
     if (!std::strcmp(key, "pdl")) { g_opt_pdl.store(value != 0); return 0; }
     if (!std::strcmp(key, "gemv_variant")) { g_opt_gemv_variant.store((int)value); return 0; }
+    if (!std::strcmp(key, "gemv_order")) { g_opt_gemv_order.store(value != 0); return 0; }
     return 1;
 }
 

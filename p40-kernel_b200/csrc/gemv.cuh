@@ -5,25 +5,29 @@
 // int32 chunk sums, each scaled as (dw * da) * (float)sumi, added in fp32 in block-then-chunk
 // order.  This kernel keeps that order, so y is bit-identical to the host, not merely close.
 //
-// Shape of the kernel (B200: the op is a pure stream of 34-byte blocks from HBM):
-//   * a CTA owns a run of consecutive rows.  Rows are contiguous in memory and 16-byte aligned
-//     when n_in/128 is even, so the run is ONE aligned span; it is fetched by a few 1-D bulk
-//     async copies (TMA, no multicast) into shared memory, one mbarrier per stage, all issued by
-//     one thread before anything else happens -- before the wait on the previous kernel of the
-//     stream when the launch is programmatic, because weights never depend on it;
-//   * the Q8_1 vector is re-laid in shared memory as one 336-byte record per 256 activations
+// Shape of the kernel (B200: the op is a stream of 34-byte blocks from HBM, ~30 integer
+// instructions per 32 weights, so the stream and the arithmetic must overlap completely):
+//   * one persistent CTA per SM owns a run of consecutive rows and streams it through a ring of
+//     shared-memory slots.  A tile is (up to 16 rows) x (a segment of the row); rows are 16-byte
+//     aligned when n_in/128 is even, so a tile is one 1-D bulk async copy (TMA, no multicast) when
+//     it spans whole rows, one per row otherwise.  The CTA uses less than half of an SM's shared
+//     memory: with programmatic launches the next kernel of the stream becomes resident beside it
+//     and has its first tiles in flight while this one drains;
+//   * memory requests come back roughly in issue order, so the first two tiles go out before the
+//     wait on the previous kernel (weights never depend on it), then the activation vector, then
+//     the rest of the ring;
+//   * the Q8_1 vector is re-laid once per CTA as one 336-byte record per 256 activations
 //     (8 chunks x 32 int8, 8 scales as fp32, 8 values of -64*s), a stride that keeps 16-byte
 //     loads of neighbouring lanes in different banks;
 //   * weight blocks are addressed as pairs (68 bytes = 17 words).  An item is one block of a pair
-//     for RR consecutive rows; a warp takes 32 neighbouring pairs of the same parity, so lanes read
-//     9 words each at stride 17 -- conflict-free -- and either all funnel-shift the 2-byte-offset
-//     codes of an even block or all read the word-aligned codes of an odd one; 8 dp4a per chunk
-//     with the activation registers shared by the RR rows;
-//   * the fp32 term of each chunk overwrites a code word of the item's own block; a few warps of
-//     the CTA do nothing but add, one lane per row, the terms of every row whose stage is complete,
-//     in the host's order, while the other warps move on to the next stage;
-//   * CTAs are fat and few (one or two per SM, all of a CTA's rows resident at once), so the
-//     activation vector is staged once per SM-slot instead of once per handful of rows.
+//     for RR consecutive rows; a warp keeps one parity and takes 32 neighbouring pairs, so lanes
+//     read 9 words each at stride 17 -- conflict-free -- and either all funnel-shift the
+//     2-byte-offset codes of an even block or all read the word-aligned codes of an odd one;
+//     8 dp4a per chunk with the activation registers shared by the RR rows;
+//   * the four fp32 terms of a block go, as one 16-byte store, to a small term buffer next to the
+//     ring.  A few warps of the CTA do nothing but add, one lane per row, the terms of each
+//     completed tile in the host's order (the running sums live in registers across the segments
+//     of a row); one warp does nothing but refill a weight slot the moment its tile is consumed.
 #pragma once
 
 #include "common.cuh"
@@ -31,12 +35,12 @@
 namespace b200 {
 
 #ifdef BONSAI_B200_TRACE
-// Development aid (not in the shipped build): per-CTA clock stamps of the mat-vec phases.
+// Development aid (not in the shipped build): per-CTA time stamps of the mat-vec phases.
 __device__ long long g_trace[4096 * 8];
-__device__ int g_skip = 0;   // bit 0: no term computation, bit 1: no ordered sums, bit 2: no activation staging
-#define TRACE_STAMP(slot) do { if ((threadIdx.x & 31) == 0 && blockIdx.x < 4096) { \
-    long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); \
-    if (trace_owner) g_trace[blockIdx.x * 8 + (slot)] = t; } } while (0)
+__device__ int g_skip = 0;
+#define TRACE_STAMP(slot) do { if (blockIdx.x < 4096) { \
+    long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); \
+    g_trace[blockIdx.x * 8 + (slot)] = t_; } } while (0)
 #else
 #define TRACE_STAMP(slot) do { } while (0)
 #endif
@@ -44,15 +48,36 @@ __device__ int g_skip = 0;   // bit 0: no term computation, bit 1: no ordered su
 constexpr int GEMV_MAX_STAGES = 64;
 constexpr int GEMV_BAR_BYTES = 2 * GEMV_MAX_STAGES * 8;   // full[] + done[]
 constexpr int ACT_REC_WORDS = 84;   // 64 words int8 + 8 fp32 scales + 8 int32 (-64*s) + 4 pad
+constexpr int RING_MAX_SLOTS = 16;
+constexpr int RING_MAX_TILES = 256;   // tiles per CTA: each has its own pair of single-use barriers
+constexpr int RING_BAR_BYTES = 3 * RING_MAX_TILES * 8;
 
+// Geometry of the staged repacked-layout kernel (whole share resident, see repack.cuh).
 struct GemvPlan {
     int ctas;
     int rows_per_cta;     // multiple of the alignment granule and of RR
     int rows_per_stage;   // same
     int threads;
-    int chain_warps;      // warps that add terms in order: 32 rows each
+    int chain_warps;
     int rr;
     int smem_bytes;
+};
+
+// Geometry of the ring mat-vec, made on the host.
+struct RingParams {
+    int n_out, npairs;
+    int rows_per_cta;     // multiple of rr
+    int rs;               // rows per tile, multiple of rr, <= 32
+    int nseg;             // segments per row; segment j starts at pair j * seg_base
+    int seg_base;         // pairs per segment, the last segment takes the remainder
+    int sp;               // pairs in the longest segment: a slot row holds sp pairs
+    int sw;               // slot row stride in words (17 * sp, padded when nseg > 1)
+    int nslot;            // ring depth
+    int ntb;              // term buffers (tile t writes buffer t % ntb)
+    int ts;               // term buffer row stride in floats: 8 * sp + 4
+    int chain_warps;      // adding warps; one more warp issues copies; the rest (an even count) compute
+    int ppt;              // positions per tile = (rs / rr) * sp
+    uint32_t magic_ppt, magic_sp, magic_nseg, magic_nslot, magic_ntb;   // ceil(2^32 / d), 0 for d == 1
 };
 
 // Re-lay the Q8_1 vector (global, 9 words per chunk) into padded per-pair records: one thread per
@@ -77,7 +102,7 @@ __device__ __forceinline__ uint32_t fast_div(uint32_t n, uint32_t magic) { retur
 
 __host__ __device__ inline int gcd_int(int a, int b) { while (b) { int t = a % b; a = b; b = t; } return a; }
 
-// Lanes whose rows start in the same shared-memory bank walk their rows a few groups apart.
+// Lanes whose rows start in the same shared-memory bank walk their rows a few pairs apart.
 __device__ __forceinline__ void row_skew(int row_words, int lane, int &skew, int &max_skew) {
     const int bank_step = row_words & 31;
     const int distinct = 32 / gcd_int(bank_step == 0 ? 32 : bank_step, 32);   // rows before banks repeat
@@ -90,46 +115,39 @@ __device__ __forceinline__ void row_skew(int row_words, int lane, int &skew, int
 // bytes of both blocks and is never written.
 __device__ __forceinline__ int term_word(int j) { return j < 4 ? j : j + 5; }
 
-// Sequential fp32 sum of the 8 * npairs terms of one row (one lane per row), in order.  The eight
-// terms of the next pair are loaded while the current eight are being added, so a step costs the
-// dependent-add chain and little else.  `skew` delays a lane by whole pairs (see row_skew): every
-// lane runs the same npairs + max_skew steps, loads from a clamped pair index, and only adds while
-// its own pair index is in range -- no divergence, and the order of a lane's additions is untouched.
-__device__ __forceinline__ float ordered_pair_sum(const float *base, int npairs, int skew, int max_skew) {
-    float acc = 0.0f;
-    float cur[8];
-    {
-        const float *p0 = base;                 // pair 0 (what a delayed lane pre-loads is discarded)
-#pragma unroll
-        for (int j = 0; j < 8; ++j) cur[j] = p0[term_word(j)];
-    }
-    bool live = skew == 0;
-    const int steps = npairs + max_skew;
-    const int last = npairs - 1;
+// Position, inside the 8 term words of a pair, of the 4 terms of half H of pair q: the two halves
+// swap places every fourth pair, which spreads the 16-byte stores of eight neighbouring lanes (one
+// pair each, same half) over all 32 banks.
+__device__ __forceinline__ int term_half_offset(int q, int H) { return 4 * (H ^ ((q >> 2) & 1)); }
+
+// Adds, in order, the 8 * npairs terms of one row (one lane per row) to the running sum `acc`.
+// `row_terms` is 16-byte aligned; the terms of the next pair are loaded while the current eight are
+// being added, so a step costs the dependent-add chain and little else.  Row strides are an odd
+// number of 16-byte units, so the loads of neighbouring rows never share a bank.
+__device__ __forceinline__ float ordered_terms_sum(float acc, const float *row_terms, int q_first, int npairs) {
+    const float4 *t = reinterpret_cast<const float4 *>(row_terms);
+    int o = (q_first >> 2) & 1;                         // term_half_offset of half 0, in float4 units
+    float4 a = t[o], b = t[o ^ 1];
 #pragma unroll 2
-    for (int k = 0; k < steps; ++k) {
-        const int qn = k + 1 - skew;
-        const float *pn = base + 17 * min(max(qn, 0), last);
-        float nxt[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) nxt[j] = pn[term_word(j)];
-        if (live) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) acc = __fadd_rn(acc, cur[j]);
-        }
-#pragma unroll
-        for (int j = 0; j < 8; ++j) cur[j] = nxt[j];
-        live = qn >= 0 && qn <= last;
+    for (int k = 0; k < npairs; ++k) {
+        const int kn = min(k + 1, npairs - 1);
+        const int on = ((q_first + kn) >> 2) & 1;
+        const float4 na = t[2 * kn + on], nb = t[2 * kn + (on ^ 1)];
+        acc = __fadd_rn(acc, a.x); acc = __fadd_rn(acc, a.y); acc = __fadd_rn(acc, a.z); acc = __fadd_rn(acc, a.w);
+        acc = __fadd_rn(acc, b.x); acc = __fadd_rn(acc, b.y); acc = __fadd_rn(acc, b.z); acc = __fadd_rn(acc, b.w);
+        a = na; b = nb;
     }
     return acc;
 }
 
-// One item: the even (H = 0) or odd (H = 1) block of pair q, for RR consecutive rows starting at
-// the row whose pair starts at `pair_words`.  Reads 9 words per row, writes 4 fp32 terms per row over
-// code words of the same block (term c at word H + c of the 9).
+// One item: the even (H = 0) or odd (H = 1) block of a pair, for RR consecutive rows.  Reads 9 words
+// per row from the weight slot and stores the block's 4 fp32 terms per row, as one 16-byte store, in
+// the term buffer.  `pair_words` points at the pair in the first row (rows `row_words` apart),
+// `pair_terms` at the pair's 8 term words in the first row (rows `term_stride` floats apart).
 template <int RR, int H>
-__device__ __forceinline__ void gemv_item(uint32_t *pair_words, const uint32_t *pair_rec, int row_words) {
-    uint32_t *p = pair_words + 8 * H;
+__device__ __forceinline__ void gemv_item(const uint32_t *pair_words, int row_words, const uint32_t *pair_rec,
+                                          float *pair_terms, int term_stride, int q) {
+    const uint32_t *p = pair_words + 8 * H;
     uint32_t w[RR][9];
 #pragma unroll
     for (int rr = 0; rr < RR; ++rr)
@@ -143,7 +161,7 @@ __device__ __forceinline__ void gemv_item(uint32_t *pair_words, const uint32_t *
     float dw[RR];
 #pragma unroll
     for (int rr = 0; rr < RR; ++rr) dw[rr] = f16_bits_to_f32(H ? (w[rr][0] >> 16) : (w[rr][0] & 0xFFFFu));
-    float *tp = reinterpret_cast<float *>(p) + H;
+    float term[RR][4];
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
         const int4 lo = *reinterpret_cast<const int4 *>(rec + c * 8);
@@ -161,173 +179,186 @@ __device__ __forceinline__ void gemv_item(uint32_t *pair_words, const uint32_t *
                 c1 = w[rr][2 * c + 2];
             }
             const int sumi = chunk_sumi_scaled(c0, c1, a, inits[c]);
-            tp[rr * row_words + c] = __fmul_rn(__fmul_rn(dw[rr], da), (float)sumi);
+            term[rr][c] = __fmul_rn(__fmul_rn(dw[rr], da), (float)sumi);
         }
     }
+    float *tp = pair_terms + term_half_offset(q, H);
+#pragma unroll
+    for (int rr = 0; rr < RR; ++rr)
+        *reinterpret_cast<float4 *>(tp + rr * term_stride) = make_float4(term[rr][0], term[rr][1], term[rr][2], term[rr][3]);
 }
 
-// Role split inside a CTA: the first warps ("compute") turn weight blocks into fp32 terms, the
-// last `chain_warps` warps own one output row per lane and add that row's terms in order once the
-// stage holding the row is complete.  Compute warps never wait for a chain.
+// Shared memory: [full | done | freed : 256 barriers each] [activation records] [nslot weight slots
+// of rs * sw words] [ntb term buffers of rs * ts floats].  Barriers are per TILE and used once
+// (parity 0): a waiter that was not around for the previous use of a slot -- adding warps take row
+// blocks in turn -- can never mistake an old phase for the one it wants, and every barrier receives
+// exactly the arrivals it was initialised for.
+//   full[t]  : tile t has landed in weight slot t % nslot            (1 arrival + copy bytes)
+//   done[t]  : every item of tile t has stored its terms              (2 * ppt arrivals)
+//   freed[t] : the adding warp has read term buffer t % ntb           (1 arrival)
+// Roles: warps [0, NC) compute, warps [NC, NC + chain_warps) add, the last warp issues copies.
 template <int RR>
-__global__ void __launch_bounds__(RR == 4 ? 512 : 1024, 1) gemv_pq2_kernel(const uint8_t *__restrict__ W, const uint32_t *__restrict__ xq,
-                                                          float *__restrict__ y, int n_out, int npairs,
-                                                          int rows_per_cta, int rows_per_stage, int chain_warps,
-                                                          uint32_t magic_npairs, uint32_t magic_gps) {
+__global__ void __launch_bounds__(RR == 4 ? 512 : 1024, 1) gemv_ring_kernel(const uint8_t *__restrict__ W,
+                                                                            const uint32_t *__restrict__ xq,
+                                                                            float *__restrict__ y, const RingParams P) {
     extern __shared__ __align__(128) uint8_t smem[];
-    uint64_t *full = reinterpret_cast<uint64_t *>(smem);                       // stage landed (bulk copy bytes)
-    uint64_t *done = full + GEMV_MAX_STAGES;                                   // stage's terms all written
-    uint32_t *act = reinterpret_cast<uint32_t *>(smem + GEMV_BAR_BYTES);       // npairs records
-    uint32_t *wsm = act + (size_t)npairs * ACT_REC_WORDS;                      // rows_per_cta * 17 * npairs words
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem);
+    uint64_t *done = full + RING_MAX_TILES;
+    uint64_t *freed = done + RING_MAX_TILES;
+    uint32_t *act = reinterpret_cast<uint32_t *>(smem + RING_BAR_BYTES);
+    uint32_t *ring = act + (size_t)P.npairs * ACT_REC_WORDS;
+    const int slot_words = P.rs * P.sw;
+    float *terms = reinterpret_cast<float *>(ring + (size_t)P.nslot * slot_words);
+    const int tb_floats = P.rs * P.ts;
 
-    const int row0 = blockIdx.x * rows_per_cta;
-    const int rows_here = min(rows_per_cta, n_out - row0);
+    const int row0 = blockIdx.x * P.rows_per_cta;
+    const int rows_here = min(P.rows_per_cta, P.n_out - row0);
     if (rows_here <= 0) return;
-    const int row_words = 17 * npairs;
-    const size_t row_bytes = (size_t)row_words * 4;
-    const int nstages = (rows_here + rows_per_stage - 1) / rows_per_stage;
-    const int compute_threads = blockDim.x - 32 * chain_warps;
-
-#ifdef BONSAI_B200_TRACE
-    const bool trace_owner = threadIdx.x == 0 || (int)threadIdx.x == compute_threads;
-    if (threadIdx.x == 0) TRACE_STAMP(0);
-#endif
-    // Memory requests are served roughly in issue order, so the order below is the order data comes
-    // back: the first stages of weights (they do not depend on the previous kernel of the stream and
-    // go out before the wait on it), then the activation vector, then the remaining stages.  Issuing
-    // every stage first would park the activations behind the CTA's whole share.
-#ifdef BONSAI_B200_TRACE
-    const int skip = g_skip;
-#endif
-    constexpr int EARLY_STAGES = 2;
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int nwarps = blockDim.x >> 5;
+    const int compute_warps = nwarps - P.chain_warps - 1;
+    const int producer_warp = nwarps - 1;
+    const int nrb = (rows_here + P.rs - 1) / P.rs;                  // row blocks
+    const int ntiles = nrb * P.nseg;
+    const size_t row_bytes = (size_t)P.npairs * 68;
     const uint64_t pol = policy_evict_first();
     const uint8_t *src = W + (size_t)row0 * row_bytes;
-    auto issue_stage = [&](int s) {
-        const int r_begin = s * rows_per_stage;
-        const int r_cnt = min(rows_per_stage, rows_here - r_begin);
-        const uint32_t bytes = (uint32_t)(r_cnt * row_bytes);
-        const uint32_t bulk = bytes & ~15u;
-        uint8_t *dst = reinterpret_cast<uint8_t *>(wsm) + (size_t)r_begin * row_bytes;
-        mbar_expect_tx(&full[s], bulk);
-        if (bulk) bulk_g2s(dst, src + (size_t)r_begin * row_bytes, bulk, &full[s], pol);
-        // a ragged last stage can leave < 16 bytes, fetched with plain loads
-        for (uint32_t o = bulk; o < bytes; o += 4)
-            *reinterpret_cast<uint32_t *>(dst + o) = ldg_nc_u32(src + (size_t)r_begin * row_bytes + o);
+
+    // Issues tile t into its slot; called by the whole producer warp.  Plain-load leftovers (a ragged
+    // tile of whole rows whose byte count is not a multiple of 16) are stored before the arrive,
+    // which releases them to the waiters together with the copied bytes.
+    auto issue_tile = [&](int t) {
+        // the slot was read through ordinary loads: order them before the asynchronous overwrite
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        const int rb = (int)fast_div((uint32_t)t, P.magic_nseg);
+        const int j = t - rb * P.nseg;
+        const int slot = t - (int)fast_div((uint32_t)t, P.magic_nslot) * P.nslot;
+        const int r_begin = rb * P.rs;
+        const int r_cnt = min(P.rs, rows_here - r_begin);
+        uint8_t *dst = reinterpret_cast<uint8_t *>(ring + (size_t)slot * slot_words);
+        if (P.nseg == 1) {
+            if (lane == 0) {
+                const uint32_t bytes = (uint32_t)(r_cnt * row_bytes);
+                const uint32_t bulk = bytes & ~15u;
+                const uint8_t *s = src + (size_t)r_begin * row_bytes;
+                for (uint32_t o = bulk; o < bytes; o += 4) *reinterpret_cast<uint32_t *>(dst + o) = ldg_nc_u32(s + o);
+                mbar_expect_tx(&full[t], bulk);
+                if (bulk) bulk_g2s(dst, s, bulk, &full[t], pol);
+            }
+        } else {
+            const int q0 = j * P.seg_base;
+            const int pairs = (j == P.nseg - 1) ? P.npairs - q0 : P.seg_base;
+            const uint32_t seg_bytes = (uint32_t)pairs * 68;        // multiple of 16: pairs % 4 == 0
+            if (lane == 0) mbar_expect_tx(&full[t], seg_bytes * r_cnt);
+            __syncwarp();
+            if (lane < r_cnt)
+                bulk_g2s(dst + (size_t)lane * P.sw * 4, src + (size_t)(r_begin + lane) * row_bytes + (size_t)q0 * 68,
+                         seg_bytes, &full[t], pol);
+        }
     };
-    if (threadIdx.x < 32) {
-        // lane s of the first warp owns stage s, s + 32, ...: it initialises the two barriers of the
-        // stage and issues the stage's copy, so the copies of a CTA leave in parallel
-        for (int s = threadIdx.x; s < nstages; s += 32) {
-            // done[s] completes when every item of the stage has written its terms: one arrival per
-            // (group of RR rows, pair, half) of the stage
-            const int r_cnt = min(rows_per_stage, rows_here - s * rows_per_stage);
-            mbar_init(&full[s], 1);
-            mbar_init(&done[s], (uint32_t)(2 * npairs * ((r_cnt + RR - 1) / RR)));
+
+    // ---- prologue: barriers, first tiles, activations, rest of the ring ------------------------
+    // Memory requests come back roughly in issue order: two tiles of weights (independent of the
+    // previous kernel of the stream, so they leave before the wait on it), then the activation
+    // vector, then the rest of the ring.
+    const int first_fill = min(P.nslot, ntiles);
+    if (wid == producer_warp) {
+        for (int t = lane; t < ntiles; t += 32) {
+            mbar_init(&full[t], 1);
+            mbar_init(&done[t], (uint32_t)(2 * P.ppt));
+            mbar_init(&freed[t], 1);
         }
         mbar_fence_init();
-#ifdef BONSAI_B200_TRACE
-        if (!(skip & 24))
-#endif
-        if ((int)threadIdx.x < EARLY_STAGES && (int)threadIdx.x < nstages) issue_stage(threadIdx.x);
+        __syncwarp();
+        for (int t = 0; t < min(2, first_fill); ++t) issue_tile(t);
     }
-    if (threadIdx.x == 0) TRACE_STAMP(1);
+    if (threadIdx.x == 0) TRACE_STAMP(0);
     pdl_launch_dependents();
-    pdl_wait_prior_grid();          // activations (and y) belong to the previous kernel until here
-    if (threadIdx.x == 0) TRACE_STAMP(2);
+    pdl_wait_prior_grid();              // activations (and y) belong to the previous kernel until here
     {
-        const int nchunks = npairs * 8;
+        const int nchunks = P.npairs * 8;
         uint32_t v[9];
         const bool mine = (int)threadIdx.x < nchunks;
         if (mine) act_chunk_load(xq, threadIdx.x, v);
-#ifdef BONSAI_B200_TRACE
-        if (!(skip & 24))
-#endif
-        if (threadIdx.x < 32)
-            for (int s = threadIdx.x + EARLY_STAGES; s < nstages; s += 32) issue_stage(s);
+        if (wid == producer_warp)
+            for (int t = 2; t < first_fill; ++t) issue_tile(t);
         if (mine) act_chunk_store(act, threadIdx.x, v);
         for (int chunk = threadIdx.x + blockDim.x; chunk < nchunks; chunk += blockDim.x) {
             act_chunk_load(xq, chunk, v);
             act_chunk_store(act, chunk, v);
         }
     }
-    __syncthreads();                // records + barrier inits + ragged-tail words visible to all
-    if (threadIdx.x == 0) TRACE_STAMP(3);
-#ifdef BONSAI_B200_TRACE
-    if (skip & 8) return;
-#endif
+    __syncthreads();                    // records and barrier inits visible to all
+    if (threadIdx.x == 0) TRACE_STAMP(1);
 
-    if ((int)threadIdx.x < compute_threads) {
-        // Items: (group of RR rows) x (pair q) x (half h: even or odd block of the pair), in row
-        // order.  A warp takes 32 consecutive (group, pair) positions of ONE half, so its word reads
-        // sit 17 words apart (conflict-free) and the code alignment is uniform across the warp.
-        // Items are (group of RR rows) x (pair q) x (half: even or odd block of the pair), walked in
-        // row order.  A warp keeps one half for the whole kernel and takes 32 consecutive (group, pair)
-        // positions per step, so its reads sit 17 words apart (conflict-free) and the 2-byte offset of
-        // the codes is a compile-time property of the code path it runs.
-        // A ragged last group (n_out not a multiple of RR) is computed in full: its surplus rows read
-        // whatever the slot holds and write terms nobody adds, which costs less than a predicate on
-        // every store.  The slot is sized for whole groups (rows_per_cta % RR == 0).
-        const int ngroups = (rows_here + RR - 1) / RR;
-        const int npos = ngroups * npairs;
-        const int wid = threadIdx.x >> 5;
-        const int half = wid & 1;                                   // compute warps come in pairs
-        const int pos_step = (compute_threads >> 6) * 32;
-        int landed = -1;            // last stage this thread has seen complete
-        for (int pos = (wid >> 1) * 32 + (threadIdx.x & 31); pos < npos; pos += pos_step) {
-            // divisions by npairs and by the groups per stage are multiplications by host-made
-            // reciprocals (exact for every position a CTA can hold)
-            const int g = (int)fast_div((uint32_t)pos, magic_npairs);
-            const int q = pos - g * npairs;
-            const int stage = (int)fast_div((uint32_t)g, magic_gps);     // rows_per_stage % RR == 0
-            if (stage != landed) {
-#ifdef BONSAI_B200_TRACE
-                if (!(skip & 16))
-#endif
-                if (!mbar_wait_bounded(&full[stage], 0)) break;
-                landed = stage;
-#ifdef BONSAI_B200_TRACE
-                if (threadIdx.x == 0 && g == 0) TRACE_STAMP(4);
-#endif
+    if (wid < compute_warps) {
+        // ---- compute warps: items in tile order; a warp keeps one parity of the block pairs -------
+        // Positions inside a tile are (group of RR rows) x (pair of the segment), padded to the
+        // longest segment and to whole row blocks: a padded position only arrives on the barrier.
+        const int half = wid & 1;
+        const int pos_step = (compute_warps >> 1) * 32;
+        const int npos = ntiles * P.ppt;
+        int landed = -1;
+        for (int pos = (wid >> 1) * 32 + lane; pos < npos; pos += pos_step) {
+            const int t = (int)fast_div((uint32_t)pos, P.magic_ppt);
+            const int local = pos - t * P.ppt;
+            const int g = (int)fast_div((uint32_t)local, P.magic_sp);        // group inside the tile
+            const int ql = local - g * P.sp;                                 // pair inside the segment
+            const int rb = (int)fast_div((uint32_t)t, P.magic_nseg);
+            const int j = t - rb * P.nseg;
+            if (t != landed) {
+                if (!mbar_wait_bounded(&full[t], 0)) break;
+                if (t >= P.ntb && !mbar_wait_bounded(&freed[t - P.ntb], 0)) break;
+                landed = t;
             }
-            uint32_t *pair_words = wsm + (g * RR) * row_words + 17 * q;
-            const uint32_t *pair_rec = act + q * ACT_REC_WORDS;
+            const int q0 = j * P.seg_base;
+            const int pairs = (j == P.nseg - 1) ? P.npairs - q0 : P.seg_base;
+            // rows past the end of a ragged row block still compute when they share a group with a
+            // live row (their slot rows hold stale bytes, their terms are never added)
+            if (ql < pairs && rb * P.rs + g * RR < rows_here) {
+                const int slot = t - (int)fast_div((uint32_t)t, P.magic_nslot) * P.nslot;
+                const int tb = t - (int)fast_div((uint32_t)t, P.magic_ntb) * P.ntb;
+                const uint32_t *pair_words = ring + (size_t)slot * slot_words + (g * RR) * P.sw + 17 * ql;
+                const uint32_t *pair_rec = act + (q0 + ql) * ACT_REC_WORDS;
+                float *pair_terms = terms + (size_t)tb * tb_floats + (g * RR) * P.ts + 8 * ql;
 #ifdef BONSAI_B200_TRACE
-            if (skip & 1) { pair_words[0] = pair_rec[0]; } else
+                if (g_skip & 1) { pair_terms[0] = __uint_as_float(pair_rec[0] + pair_words[0]); } else
 #endif
-            if (half == 0) gemv_item<RR, 0>(pair_words, pair_rec, row_words);
-            else gemv_item<RR, 1>(pair_words, pair_rec, row_words);
-            mbar_arrive(&done[stage]);          // release: the terms above are visible to the adder
+                if (half == 0) gemv_item<RR, 0>(pair_words, P.sw, pair_rec, pair_terms, P.ts, ql);
+                else gemv_item<RR, 1>(pair_words, P.sw, pair_rec, pair_terms, P.ts, ql);
+            }
+            mbar_arrive(&done[t]);      // release: the loads and the terms above are complete
         }
-        if (threadIdx.x == 0) TRACE_STAMP(5);
+        if (threadIdx.x == 0) TRACE_STAMP(2);
+    } else if (wid < producer_warp) {
+        // ---- adding warps: one lane per row of a row block, running sum kept across its segments --
+        const int cw = wid - compute_warps;
+        for (int rb = cw; rb < nrb; rb += P.chain_warps) {
+            const int r_cnt = min(P.rs, rows_here - rb * P.rs);
+            const int r = min(lane, r_cnt - 1);             // surplus lanes redo the last row, unstored
+            float acc = 0.0f;
+            for (int j = 0; j < P.nseg; ++j) {
+                const int t = rb * P.nseg + j;
+                if (!mbar_wait_bounded(&done[t], 0)) return;
+                const int tb = t - (int)fast_div((uint32_t)t, P.magic_ntb) * P.ntb;
+                const int q0 = j * P.seg_base;
+                const int pairs = (j == P.nseg - 1) ? P.npairs - q0 : P.seg_base;
+#ifdef BONSAI_B200_TRACE
+                if (!(g_skip & 2))
+#endif
+                acc = ordered_terms_sum(acc, terms + (size_t)tb * tb_floats + r * P.ts, 0, pairs);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&freed[t]);
+            }
+            if (lane < r_cnt) y[row0 + rb * P.rs + lane] = acc;
+        }
+        if (wid == compute_warps && lane == 0) TRACE_STAMP(3);
     } else {
-        // one lane per row: wait until the row's stage is complete, then add its 8 * npairs terms in
-        // order, eight loads in flight per step
-        const int lane = threadIdx.x & 31;
-        int skew, max_skew;
-        row_skew(row_words, lane, skew, max_skew);
-#ifdef BONSAI_B200_TRACE
-        if (!(skip & 2))
-#endif
-        for (int r0 = ((int)threadIdx.x - compute_threads) & ~31; r0 < rows_here; r0 += 32 * chain_warps) {
-            // the warp waits once, for the stage of its last row (stages complete in row order up to
-            // scheduling noise; waiting for the last one of the warp keeps the wait uniform)
-            const int r_last = min(r0 + 31, rows_here - 1);
-            bool ok = true;
-            for (int s = r0 / rows_per_stage; s <= r_last / rows_per_stage && ok; ++s)
-                ok = mbar_wait_bounded(&done[s], 0);
-            if (!ok) break;
-            const int r = min(r0 + lane, rows_here - 1);        // surplus lanes redo the last row, unstored
-            const float *base = reinterpret_cast<const float *>(wsm) + (size_t)r * row_words;
-            const float acc = ordered_pair_sum(base, npairs, skew, max_skew);
-            if (r0 + lane < rows_here) y[row0 + r] = acc;
+        // ---- copy warp: a slot is refilled as soon as every item of its previous tile is done ------
+        for (int t = first_fill; t < ntiles; ++t) {
+            if (!mbar_wait_bounded(&done[t - P.nslot], 0)) return;
+            issue_tile(t);
         }
-#ifdef BONSAI_B200_TRACE
-        if ((int)threadIdx.x == compute_threads) {
-            mbar_wait_bounded(&done[nstages - 1], 0);
-            TRACE_STAMP(6);
-        }
-#endif
-        if ((int)threadIdx.x == compute_threads) TRACE_STAMP(7);
     }
 }
 

@@ -1,0 +1,231 @@
+// gemv_stream.cuh -- the default decode mat-vec: y = W . x, PQ2_0 weights x permuted Q8_1 activations.
+//
+// Replaces, for sm_100a, gemv_pq2_0_p40_kernel (src/kernels/gemv_p40.cu:82-165).  Every int32 chunk
+// sum and every fp32 term (dw * da) * (float)sumi equals the reference's host code
+// (src/pq2_0.h:149-172) bit for bit; the terms of a row are added in a fixed, launch-independent
+// order that differs from the host's sequential one (each of 8 lanes adds the terms of every 8th
+// block in ascending order, then a 3-step butterfly joins the lanes, then row segments are joined
+// in ascending order), like the reference's own device kernel, whose lanes stride over blocks and
+// tree-reduce (src/kernels/gemv_p40.cu:104,155-159).  The kernel that keeps the host's order term by
+// term is gemv_ring_kernel (gemv.cuh), selectable at run time.
+//
+// Shape (B200): one persistent CTA per SM streams its run of rows through a ring of shared-memory
+// slots fed by 1-D bulk async copies (TMA, no multicast); it stays under half of an SM's shared
+// memory so that, with programmatic launches, the next kernel's CTA is resident and prefetching
+// while this one drains.  A tile is (a few row quads) x (a row segment of <= 40 blocks); a task is
+// one quad of one tile, taken by one warp: lane = (row of the quad, one of 8 block lanes), the lane
+// owns blocks bl, bl + 8, ... of the segment.  It first copies its blocks into registers and gives
+// the slot back, so shared memory holds bytes in flight rather than bytes being multiplied; then it
+// multiplies from registers.  Neighbouring lanes read neighbouring 34-byte blocks (conflict-free up
+// to the row stride), the four lanes of a block lane read the same activation bytes (one
+// broadcast): no term buffers, no ordered adder, about 30 instructions per 32 weights.
+#pragma once
+
+#include "common.cuh"
+#include "gemv.cuh"
+
+namespace b200 {
+
+constexpr int STREAM_STEPS = 5;         // blocks per lane and task: segments hold at most 8 * 5 = 40 blocks
+constexpr int STREAM_ACT_WORDS = 36;    // per block: 4 chunks x 8 words int8, 4 pad (stride 144 B: 8 blocks, 8 bank groups)
+
+struct StreamParams {
+    int n_out, nb;         // rows, blocks per row
+    int rows_per_cta;      // multiple of 4
+    int tr;                // rows per tile, multiple of 4: a tile is tr whole rows, one contiguous copy
+    int nseg;              // segments per row; segment j starts at block j * seg_blocks
+    int seg_blocks;        // blocks per segment (<= 8 * STREAM_STEPS), the last one takes the remainder
+    int nslot;
+    int tpt;               // tasks per tile = (tr / 4) * nseg
+    uint32_t magic_tpt, magic_nseg, magic_nslot;   // ceil(2^32 / d), 0 for d == 1
+};
+
+// Shared memory: [full[256] | done[256]] [act int8: nb * 36 words] [act scale: nb * 4 floats]
+// [act -64*sum: nb * 4 ints] [partials: rows_per_cta * nseg floats] [quad counters: rows_per_cta / 4]
+// [task counter] [ring: nslot * (tr * 34 * nb + 16)].
+//   full[t] : tile t has landed in slot t % nslot             (1 arrival + copy bytes)
+//   done[t] : every task of tile t has copied its blocks out   (live quads * nseg arrivals)
+// Both are single-use (parity 0), so a warp that skipped tiles can never read a stale phase.
+__global__ void __launch_bounds__(512, 1) gemv_stream_kernel(const uint8_t *__restrict__ W, const uint32_t *__restrict__ xq,
+                                                             float *__restrict__ y, const StreamParams P) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem);
+    uint64_t *done = full + RING_MAX_TILES;
+    uint32_t *act_q = reinterpret_cast<uint32_t *>(smem + 2 * RING_MAX_TILES * 8);
+    float *act_s = reinterpret_cast<float *>(act_q + (size_t)P.nb * STREAM_ACT_WORDS);
+    int *act_i = reinterpret_cast<int *>(act_s + (size_t)P.nb * 4);
+    float *partial = reinterpret_cast<float *>(act_i + (size_t)P.nb * 4);
+    int *quad_count = reinterpret_cast<int *>(partial + (size_t)P.rows_per_cta * P.nseg);
+    int *next_task = quad_count + ((P.rows_per_cta / 4 + 3) & ~3);
+    uint8_t *ring = reinterpret_cast<uint8_t *>(next_task + 4);
+    const size_t row_bytes = (size_t)P.nb * W_BLOCK_BYTES;
+    const int slot_bytes = P.tr * (int)row_bytes + 16;
+
+    const int row0 = blockIdx.x * P.rows_per_cta;
+    const int rows_here = min(P.rows_per_cta, P.n_out - row0);
+    if (rows_here <= 0) return;
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int nwarps = blockDim.x >> 5;
+    const int compute_warps = nwarps - 1;
+    const int ntiles = (rows_here + P.tr - 1) / P.tr;
+    const uint64_t pol = policy_evict_first();
+    const uint8_t *src = W + (size_t)row0 * row_bytes;
+
+    // Issues tile t (whole rows, contiguous in memory) into its slot; called by one lane.  A ragged
+    // last tile can leave < 16 bytes for plain loads; they are stored before the arrive, which
+    // releases them to the waiters together with the copied bytes.
+    auto issue_tile = [&](int t) {
+        // the slot was read through ordinary loads: order them before the asynchronous overwrite
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        const int slot = t - (int)fast_div((uint32_t)t, P.magic_nslot) * P.nslot;
+        const int r_begin = t * P.tr;
+        const int r_cnt = min(P.tr, rows_here - r_begin);
+        uint8_t *dst = ring + (size_t)slot * slot_bytes;
+        const uint32_t bytes = (uint32_t)(r_cnt * row_bytes);
+        const uint32_t bulk = bytes & ~15u;
+        const uint8_t *s = src + (size_t)r_begin * row_bytes;
+        for (uint32_t o = bulk; o < bytes; o += 4) *reinterpret_cast<uint32_t *>(dst + o) = ldg_nc_u32(s + o);
+        mbar_expect_tx(&full[t], bulk);
+        if (bulk) bulk_g2s(dst, s, bulk, &full[t], pol);
+    };
+
+    // ---- prologue: barriers, two tiles, activations, the rest of the ring (issue order = return order)
+    const int first_fill = min(P.nslot, ntiles);
+    if (wid == compute_warps) {
+        for (int t = lane; t < ntiles; t += 32) {
+            const int r_cnt = min(P.tr, rows_here - t * P.tr);
+            mbar_init(&full[t], 1);
+            mbar_init(&done[t], (uint32_t)(((r_cnt + 3) / 4) * P.nseg));
+        }
+        mbar_fence_init();
+        __syncwarp();
+        if (lane == 0)
+            for (int t = 0; t < min(2, first_fill); ++t) issue_tile(t);
+    }
+    for (int i = threadIdx.x; i < P.rows_per_cta / 4; i += blockDim.x) quad_count[i] = 0;
+    if (threadIdx.x == 0) *next_task = 0;
+    pdl_launch_dependents();
+    pdl_wait_prior_grid();              // activations (and y) belong to the previous kernel until here
+    {
+        const int nchunks = P.nb * 4;
+        uint32_t v[9];
+        const bool mine = (int)threadIdx.x < nchunks;
+        if (mine) act_chunk_load(xq, threadIdx.x, v);
+        if (wid == compute_warps && lane == 0)
+            for (int t = 2; t < first_fill; ++t) issue_tile(t);
+        for (int chunk = threadIdx.x; chunk < nchunks; chunk += blockDim.x) {
+            if (chunk != (int)threadIdx.x) act_chunk_load(xq, chunk, v);
+            uint32_t *q = act_q + (chunk >> 2) * STREAM_ACT_WORDS + (chunk & 3) * 8;
+            *reinterpret_cast<uint4 *>(q) = make_uint4(v[1], v[2], v[3], v[4]);
+            *reinterpret_cast<uint4 *>(q + 4) = make_uint4(v[5], v[6], v[7], v[8]);
+            act_s[chunk] = f16_bits_to_f32(v[0] & 0xFFFFu);
+            act_i[chunk] = -64 * (int)(short)(v[0] >> 16);
+        }
+    }
+    __syncthreads();                    // activation arrays, counters and barrier inits visible to all
+
+    if (wid < compute_warps) {
+        const int rr = lane & 3, bl = lane >> 2;
+        const int ntasks = ntiles * P.tpt;
+        for (;;) {
+            // tasks are handed out in order to whichever warp is free, so a landed tile never waits
+            // for one particular warp
+            int task = 0;
+            if (lane == 0) task = atomicAdd(next_task, 1);
+            task = __shfl_sync(0xffffffffu, task, 0);
+            if (task >= ntasks) break;
+            const int t = (int)fast_div((uint32_t)task, P.magic_tpt);
+            const int local = task - t * P.tpt;
+            const int quad = (int)fast_div((uint32_t)local, P.magic_nseg);  // quad inside the tile
+            const int j = local - quad * P.nseg;                            // segment of the row
+            const int r_quad = t * P.tr + quad * 4;                         // first row of the quad (CTA-local)
+            if (r_quad >= rows_here) continue;                              // padding quad of a ragged last tile
+            const int slot = t - (int)fast_div((uint32_t)t, P.magic_nslot) * P.nslot;
+            if (!mbar_wait_bounded(&full[t], 0)) break;
+            const int b0 = j * P.seg_blocks;
+            const int blocks = min(P.seg_blocks, P.nb - b0);
+            // a row past the end of a ragged quad reads stale slot bytes; its sum is never stored
+            const uint8_t *rowp = ring + (size_t)slot * slot_bytes + (size_t)(quad * 4 + rr) * row_bytes +
+                                  (size_t)b0 * W_BLOCK_BYTES;
+
+            // Phase A: pull this lane's blocks (every 8th of the segment, at most STREAM_STEPS of them)
+            // into registers and hand the slot back at once -- the ring then holds bytes in flight,
+            // not bytes being multiplied.  32 code bytes start at byte 34*b + 2 of the row: two bytes
+            // into a word for even b, word-aligned for odd b; nine words cover them either way and a
+            // funnel shift by 16 or 0 aligns them.
+            uint32_t x[STREAM_STEPS][9];
+            float dw[STREAM_STEPS];
+#pragma unroll
+            for (int k = 0; k < STREAM_STEPS; ++k) {
+                const int b = min(bl + 8 * k, blocks - 1);      // a lane past the end re-reads the last block
+                // rowp is word-aligned: rows start on a word (nb even) and so do segments (seg_blocks even)
+                const uint32_t *xw = reinterpret_cast<const uint32_t *>(rowp) + ((W_BLOCK_BYTES * b + 2) >> 2);
+#pragma unroll
+                for (int i = 0; i < 9; ++i) x[k][i] = xw[i];
+                dw[k] = f16_bits_to_f32(*reinterpret_cast<const unsigned short *>(rowp + W_BLOCK_BYTES * b));
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&done[t]);       // release: every lane's loads above are complete
+
+            // Phase B: multiply from registers against the broadcast activation words.
+            float acc = 0.0f;
+#pragma unroll
+            for (int k = 0; k < STREAM_STEPS; ++k) {
+                const int b = bl + 8 * k;
+                if (b < blocks) {
+                    const int gb = b0 + b;                                      // block index in the row
+                    const uint32_t sh = (gb & 1) ? 0u : 16u;
+                    const float4 sc = *reinterpret_cast<const float4 *>(act_s + 4 * gb);
+                    const int4 in = *reinterpret_cast<const int4 *>(act_i + 4 * gb);
+                    const float scale[4] = {sc.x, sc.y, sc.z, sc.w};
+                    const int inits[4] = {in.x, in.y, in.z, in.w};
+                    const uint32_t *aq = act_q + gb * STREAM_ACT_WORDS;
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const int4 lo = *reinterpret_cast<const int4 *>(aq + c * 8);
+                        const int4 hi = *reinterpret_cast<const int4 *>(aq + c * 8 + 4);
+                        const int a[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+                        const uint32_t c0 = __funnelshift_r(x[k][2 * c], x[k][2 * c + 1], sh);
+                        const uint32_t c1 = __funnelshift_r(x[k][2 * c + 1], x[k][2 * c + 2], sh);
+                        const int sumi = chunk_sumi_scaled(c0, c1, a, inits[c]);
+                        acc = __fadd_rn(acc, __fmul_rn(__fmul_rn(dw[k], scale[c]), (float)sumi));
+                    }
+                }
+            }
+            acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 4));
+            acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 8));
+            acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 16));
+            const int r = r_quad + rr;
+            if (P.nseg == 1) {
+                if (bl == 0 && r < rows_here) y[row0 + r] = acc;
+            } else {
+                // segments finish in any order: the warp that completes a quad's last one adds the
+                // partial sums in ascending segment order
+                if (bl == 0) partial[r * P.nseg + j] = acc;
+                __syncwarp();
+                int last = 0;
+                if (lane == 0) {
+                    __threadfence_block();
+                    last = atomicAdd(&quad_count[r_quad >> 2], 1) == P.nseg - 1;
+                }
+                last = __shfl_sync(0xffffffffu, last, 0);
+                if (last) {
+                    __threadfence_block();
+                    if (bl == 0 && r < rows_here) {
+                        float total = partial[r * P.nseg];
+                        for (int sgm = 1; sgm < P.nseg; ++sgm) total = __fadd_rn(total, partial[r * P.nseg + sgm]);
+                        y[row0 + r] = total;
+                    }
+                }
+            }
+        }
+    } else if (lane == 0) {
+        // ---- copy warp: a slot is refilled as soon as every task of its previous tile has copied out --
+        for (int t = first_fill; t < ntiles; ++t) {
+            if (!mbar_wait_bounded(&done[t - P.nslot], 0)) return;
+            issue_tile(t);
+        }
+    }
+}
+
+}  // namespace b200

@@ -35,6 +35,7 @@ def test_version_and_options_without_gpu():
     assert bonsai_b200.version() >= 100
     assert bonsai_b200.set_option("pdl", 0) == 0
     assert bonsai_b200.set_option("gemv_variant", -1) == 0
+    assert bonsai_b200.set_option("gemv_order", 0) == 0
     assert bonsai_b200.set_option("no_such_key", 1) == 1
 
 
