@@ -149,6 +149,7 @@ def run_reference(args):
 def run_b200(args):
     import torch
     import bonsai_b200 as bb
+    from bonsai_b200 import partition
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -165,6 +166,8 @@ def run_b200(args):
         bb.set_option("pdl", args.pdl)
     if args.variant >= -1:
         bb.set_option("gemv_variant", args.variant)
+    if args.order >= 0:
+        bb.set_option("gemv_order", args.order)
 
     sets = args.sets
     # ---- resident tensors: weights generated on the device, row slice of this rank only ----------
@@ -172,8 +175,8 @@ def run_b200(args):
     blk_base = 0
     for s in range(sets):
         for n_in, n_out in LAYER_SHAPES:
-            assert n_out % world == 0
-            rows = n_out // world
+            r_lo, r_hi = partition.row_slice(n_out, rank, world)
+            rows = r_hi - r_lo
             nblk_row = n_in // 128
             W = torch.empty(rows * nblk_row * 34, dtype=torch.uint8, device="cuda")
             first = blk_base + rank * rows * nblk_row
@@ -201,22 +204,37 @@ def run_b200(args):
                 dist.all_gather_into_tensor(y, ys)
         return n
 
-    # host buffers for the end-to-end leg
-    pin_x = {n_in: xdev[n_in].cpu().pin_memory() for n_in in xdev}
-    pin_y = [torch.empty(m[1], dtype=torch.float32).pin_memory() for m in mats]
-    xin = {n_in: torch.empty(n_in, dtype=torch.float32, device="cuda") for n_in in xdev}
+    # host buffers for the end-to-end leg: one pinned block with every activation vector of a step,
+    # one pinned block for every output of a step (one copy each way per step)
+    x_off, off = [], 0
+    for n_in, n_out, rows, W, y in mats:
+        x_off.append(off)
+        off += n_in
+    pin_x = torch.empty(off, dtype=torch.float32).pin_memory()
+    for (n_in, *_), o in zip(mats, x_off):
+        pin_x[o:o + n_in] = xdev[n_in].cpu()
+    dev_x = torch.empty(off, dtype=torch.float32, device="cuda")
+    y_all = torch.zeros(sum(m[1] for m in mats), dtype=torch.float32, device="cuda")
+    pin_y = torch.empty(y_all.numel(), dtype=torch.float32).pin_memory()
+    y_off, off = [], 0
+    for m in mats:
+        y_off.append(off)
+        off += m[1]
+    xq_e2e = [torch.empty(m[0] // 32 * 36, dtype=torch.uint8, device="cuda") for m in mats]
 
     def step_e2e():
         n = 0
+        dev_x.copy_(pin_x, non_blocking=True)
         for i, (n_in, n_out, rows, W, y) in enumerate(mats):
-            xin[n_in].copy_(pin_x[n_in], non_blocking=True)
-            bb.fwht_quant(xin[n_in], None, xq[n_in], None, n_in)
-            ys = y[rank * rows:(rank + 1) * rows]
-            bb.gemv(W, xq[n_in], ys, rows, n_in)
+            xi = dev_x[x_off[i]:x_off[i] + n_in]
+            bb.fwht_quant(xi, None, xq_e2e[i], None, n_in)
+            yo = y_all[y_off[i]:y_off[i] + n_out]
+            ys = yo[rank * rows:(rank + 1) * rows]
+            bb.gemv(W, xq_e2e[i], ys, rows, n_in)
             n += 2
             if world > 1:
-                dist.all_gather_into_tensor(y, ys)
-            pin_y[i].copy_(y, non_blocking=True)
+                dist.all_gather_into_tensor(yo, ys)
+        pin_y.copy_(y_all, non_blocking=True)
         return n
 
     def timed(step_fn, steps, warmup, sample_clocks):
@@ -270,6 +288,12 @@ def run_b200(args):
     status = bb.device_status()
 
     peak, peak_kind = measured_peak_gbs()
+    traffic = None
+    try:        # DRAM bytes per launch from the committed ncu capture, scaled by the bytes a launch streams
+        t = json.load(open(os.path.join(ROOT, "profiles", "gemv_stream_traffic.json")))
+        traffic = t["dram_bytes_per_launch"] / t["algorithmic_bytes_per_launch"] * (total_alg / len(mats))
+    except Exception:
+        pass
     achieved = total_alg * args.steps / (ms * 1e-3) / 1e9     # per-rank algorithmic bytes / per-launch time
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -278,13 +302,13 @@ def run_b200(args):
         "config": {"workload": "layer_sweep", "shapes_nin_nout": LAYER_SHAPES, "batch": 1, "sets": sets,
                    "resident_weight_bytes": total_w, "l2": "inputs larger than L2" if total_w > 126e6 else "fits L2",
                    "parallelism": f"rows/{world}+allgather" if world > 1 else "single", "pdl": args.pdl,
-                   "variant": args.variant, "launch": "eager" if args.no_graph else "cuda_graph_per_step"},
+                   "fp32_order": "host-sequential" if args.order == 1 else "fixed-tree", "variant": args.variant, "launch": "eager" if args.no_graph else "cuda_graph_per_step"},
         "gpu_launches": launches,
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": UNIT,
-                "h2d_bytes_per_step": sum(4 * m[0] for m in mats), "d2h_bytes_per_step": sum(4 * m[1] for m in mats)},
+                "h2d_bytes_per_step": int(pin_x.numel() * 4), "d2h_bytes_per_step": int(pin_y.numel() * 4)},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": UNIT, "frac": achieved / peak,
-                     "peak_kind": peak_kind, "traffic": None,
+                     "peak_kind": peak_kind, "traffic": traffic,
                      "avg_launch_us": ms * 1e3 / max(1, args.steps * len(mats)),
                      "algorithmic_bytes_per_launch_avg": total_alg / len(mats)},
         "device_status": status,
@@ -306,6 +330,36 @@ def run_b200(args):
         dist.destroy_process_group()
 
 
+def run_single(args):
+    """One shape, `--copies` distinct weight tensors, one plain launch per copy: the command the ncu
+    captures under profiles/ are taken with (nothing is timed here)."""
+    import torch
+    import bonsai_b200 as bb
+    n_in, n_out = args.single
+    torch.cuda.set_device(0)
+    bb.lib()
+    bb.set_option("pdl", max(args.pdl, 0))
+    if args.variant >= -1:
+        bb.set_option("gemv_variant", args.variant)
+    if args.order >= 0:
+        bb.set_option("gemv_order", args.order)
+    nblk = n_out * (n_in // 128)
+    Ws = []
+    for c in range(args.copies):
+        W = torch.empty(nblk * 34, dtype=torch.uint8, device="cuda")
+        assert bb.synth_pq2_0(W, c * nblk, nblk, args.seed) == 0
+        Ws.append(W)
+    x = torch.randn(n_in, device="cuda")
+    xq = torch.empty(n_in // 32 * 36, dtype=torch.uint8, device="cuda")
+    y = torch.empty(n_out, device="cuda")
+    assert bb.fwht_quant(x, None, xq, None, n_in) == 0
+    torch.cuda.synchronize()
+    for W in Ws:
+        assert bb.gemv(W, xq, y, n_out, n_in) == 0
+    torch.cuda.synchronize()
+    print(json.dumps({"single": [n_in, n_out], "copies": args.copies, "device_status": bb.device_status()}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -314,12 +368,18 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--sets", type=int, default=8)
     ap.add_argument("--seed", type=int, default=0)
-    ap.add_argument("--pdl", type=int, default=-1, help="-1 library default, 0 plain launches, 1 programmatic launches")
+    ap.add_argument("--pdl", type=int, default=1, help="0 plain launches, 1 programmatic launches (weights of the next "
+                    "mat-vec stream while the previous kernel drains)")
     ap.add_argument("--variant", type=int, default=-2, help="-2 leave the library default")
     ap.add_argument("--cpu-seconds", type=float, default=8.0)
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from Python instead of replaying a graph")
+    ap.add_argument("--single", type=int, nargs=2, metavar=("N_IN", "N_OUT"), help="profiling aid: launch one shape only")
+    ap.add_argument("--copies", type=int, default=8)
+    ap.add_argument("--order", type=int, default=-1, help="1: the mat-vec that keeps the host's summation order")
     args = ap.parse_args()
+    if args.single:
+        return run_single(args)
     if args.impl == "reference":
         run_reference(args)
     else:
