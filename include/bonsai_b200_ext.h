@@ -20,6 +20,14 @@ extern "C" {
 int bonsai_b200_fwht_quant(const float *x, const float *signs, void *xq, float *x_rot, int64_t n,
                            bonsai_stream stream);
 
+/* One decode projection in one call: xq_scratch = Q8_1(FWHT1024(signs * x)), then y = W . xq_scratch.
+ * xq_scratch is caller-provided device memory of n_in / 32 * 36 bytes (4-byte aligned) that the call
+ * overwrites; x is left untouched.  Two launches on `stream`; the result equals bonsai_b200_fwht_quant
+ * followed by bonsai_p40_gemv.  No counterpart in the reference, whose callers issue the steps themselves
+ * (docs/INTEGRATION.md:260-263).  Returns 1 if n_in % 1024 != 0 or n_out <= 0. */
+int bonsai_b200_linear(const void *W, const float *x, const float *signs, float *y, void *xq_scratch,
+                       int64_t n_out, int64_t n_in, bonsai_stream stream);
+
 /* Token batch for the mat-mul: X is fp32 [n_tok][n_in] (token-major); Xq receives the
  * chunk-major [n_in/32][n_tok] Q8_1 layout that bonsai_p40_gemm reads (the reference has no
  * entry point that produces it; its test builds it by hand, tests/test_p40.cpp:438-447).

@@ -35,6 +35,7 @@ SIGNATURES = {
     "bonsai_p40_gdn_step": (_INT, [_VP] * 7 + [_INT] * 4 + [_VP]),
     "bonsai_p40_attn": (_INT, [_VP] * 4 + [_INT] * 4 + [_F, _VP]),
     "bonsai_b200_fwht_quant": (_INT, [_VP, _VP, _VP, _VP, _I64, _VP]),
+    "bonsai_b200_linear": (_INT, [_VP, _VP, _VP, _VP, _VP, _I64, _I64, _VP]),
     "bonsai_b200_quant_batch": (_INT, [_VP, _VP, _VP, _I64, _I64, _INT, _VP]),
     "bonsai_b200_gemv_chunk_sums": (_INT, [_VP, _VP, _VP, _I64, _I64, _I64, _VP]),
     "bonsai_b200_synth_pq2_0": (_INT, [_VP, _I64, _I64, _U64, _VP]),
@@ -135,3 +136,8 @@ def synth_pq2_0(W, first_block, n_blocks, seed):
 
 def stream_probe(buf, nbytes, mode, sink):
     return lib().bonsai_b200_stream_probe(_dev(buf, "buf"), nbytes, mode, _dev(sink, "sink"), _stream())
+
+
+def linear(W, x, signs, y, xq_scratch, n_out, n_in):
+    return lib().bonsai_b200_linear(_dev(W, "W"), _dev(x, "x"), _dev(signs, "signs"), _dev(y, "y"),
+                                    _dev(xq_scratch, "xq_scratch"), n_out, n_in, _stream())

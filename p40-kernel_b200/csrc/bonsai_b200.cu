@@ -349,6 +349,14 @@ int bonsai_p40_gemv(const void *W, const void *xq, float *y, int64_t n_out, int6
     return (int)e;
 }
 
+int bonsai_b200_linear(const void *W, const float *x, const float *signs, float *y, void *xq_scratch, int64_t n_out,
+                       int64_t n_in, bonsai_stream stream) {
+    if (n_out <= 0 || n_in <= 0 || n_in % FWHT_N != 0 || !xq_scratch) return 1;
+    const int rc = bonsai_b200_fwht_quant(x, signs, xq_scratch, nullptr, n_in, stream);
+    if (rc != 0) return rc;
+    return bonsai_p40_gemv(W, xq_scratch, y, n_out, n_in, stream);
+}
+
 int bonsai_b200_gemv_chunk_sums(const void *W, const void *xq, int32_t *out, int64_t row0, int64_t n_rows,
                                 int64_t n_in, bonsai_stream stream) {
     if (n_in <= 0 || n_in % 128 != 0 || row0 < 0) return 1;

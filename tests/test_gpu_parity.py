@@ -282,6 +282,24 @@ def test_gemv_linearity_in_the_weight_scale(gpu, port):
     assert np.array_equal(bits(y2), bits(y1 * np.float32(2.0)))
 
 
+@pytest.mark.parametrize("n_out,n_in,signed", [(640, 5120, False), (300, 17408, True), (9, 1024, True)])
+def test_linear_one_call(gpu, port, n_out, n_in, signed):
+    """Rotation + quantiser + mat-vec through the single entry point with a caller-provided scratch."""
+    import torch
+    W = synth.pq2_0_weights(n_out, n_in, seed=n_out)
+    x = synth.activations(n_in, seed=n_out)
+    sg = synth.signs(n_in, seed=1) if signed else None
+    scratch = torch.zeros(n_in // 32 * 36, dtype=torch.uint8, device="cuda")
+    y = torch.zeros(n_out, dtype=torch.float32, device="cuda")
+    xd = dev(x)
+    assert gpu.linear(dev(W), xd, None if sg is None else dev(sg), y, scratch, n_out, n_in) == 0
+    want_xq = port.quantize_q8_1(port.fwht_blocks(x, sg), True)
+    assert np.array_equal(host(scratch), want_xq)
+    assert np.array_equal(bits(host(xd)), bits(x))
+    assert_close(host(y), port.gemv(W, want_xq, n_out, n_in, threads=4))
+    assert gpu.linear(dev(W), xd, None, y, scratch, n_out, 1000) == 1
+
+
 # ---- repacked layout ----------------------------------------------------------------------------------
 @pytest.mark.parametrize("n_out,n_in", [(12, 1024), (5, 5120), (67, 17408), (300, 6144)])
 def test_repack_bytes_and_gemv(gpu, port, n_out, n_in):
