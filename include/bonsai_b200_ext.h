@@ -28,6 +28,28 @@ int bonsai_b200_fwht_quant(const float *x, const float *signs, void *xq, float *
 int bonsai_b200_linear(const void *W, const float *x, const float *signs, float *y, void *xq_scratch,
                        int64_t n_out, int64_t n_in, bonsai_stream stream);
 
+/* The same projection for callers that must not allocate device memory and have no spare buffer to
+ * lend: the quantised activation vector lives in an array compiled into the library instead of in
+ * caller memory.  Typical callers: a plugin inside a host runtime that reserved the whole device for
+ * its own pool up front and hands out no sub-allocations to plugins (the reference's fork hook
+ * allocates its scratch lazily with cudaMalloc, integrations/prismml/bonsai-p40.diff:275-281, which
+ * such a host forbids), and latency-critical loops where a cudaMalloc would synchronise the device.
+ * This entry point has no counterpart in the reference.
+ *   - limit: n_in <= BONSAI_B200_LINEAR_STATIC_MAX_N_IN (the array is 36 864 bytes per GPU that loads
+ *     the library, held until the process exits); larger n_in returns BONSAI_B200_ETOOLARGE and
+ *     launches nothing.  Other shape errors return 1 as in bonsai_b200_linear.
+ *   - it calls no cudaMalloc / cudaFree nor any allocating library routine, on any call.
+ *   - the first call on each device looks up the array's device address (cudaGetSymbolAddress) and
+ *     remembers it; make that first call outside of any stream capture.
+ *   - every call on a device uses the same array and leaves its Q8_1 bytes there.  Nothing has to be
+ *     cleared between calls (each call overwrites the n_in / 32 blocks it then reads), but two calls
+ *     whose kernels overlap on the GPU -- different streams, or concurrent host threads -- race on it:
+ *     serialise them on one stream. */
+#define BONSAI_B200_LINEAR_STATIC_MAX_N_IN 32768
+#define BONSAI_B200_ETOOLARGE 2
+int bonsai_b200_linear_static(const void *W, const float *x, const float *signs, float *y, int64_t n_out,
+                              int64_t n_in, bonsai_stream stream);
+
 /* Token batch for the mat-mul: X is fp32 [n_tok][n_in] (token-major); Xq receives the
  * chunk-major [n_in/32][n_tok] Q8_1 layout that bonsai_p40_gemm reads (the reference has no
  * entry point that produces it; its test builds it by hand, tests/test_p40.cpp:438-447).

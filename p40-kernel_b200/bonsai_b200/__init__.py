@@ -36,6 +36,7 @@ SIGNATURES = {
     "bonsai_p40_attn": (_INT, [_VP] * 4 + [_INT] * 4 + [_F, _VP]),
     "bonsai_b200_fwht_quant": (_INT, [_VP, _VP, _VP, _VP, _I64, _VP]),
     "bonsai_b200_linear": (_INT, [_VP, _VP, _VP, _VP, _VP, _I64, _I64, _VP]),
+    "bonsai_b200_linear_static": (_INT, [_VP, _VP, _VP, _VP, _I64, _I64, _VP]),
     "bonsai_b200_quant_batch": (_INT, [_VP, _VP, _VP, _I64, _I64, _INT, _VP]),
     "bonsai_b200_gemv_chunk_sums": (_INT, [_VP, _VP, _VP, _I64, _I64, _I64, _VP]),
     "bonsai_b200_synth_pq2_0": (_INT, [_VP, _I64, _I64, _U64, _VP]),
@@ -141,3 +142,9 @@ def stream_probe(buf, nbytes, mode, sink):
 def linear(W, x, signs, y, xq_scratch, n_out, n_in):
     return lib().bonsai_b200_linear(_dev(W, "W"), _dev(x, "x"), _dev(signs, "signs"), _dev(y, "y"),
                                     _dev(xq_scratch, "xq_scratch"), n_out, n_in, _stream())
+
+
+def linear_static(W, x, signs, y, n_out, n_in):
+    """The projection whose scratch lives inside the library (no allocation, n_in <= 32768)."""
+    return lib().bonsai_b200_linear_static(_dev(W, "W"), _dev(x, "x"), _dev(signs, "signs"), _dev(y, "y"), n_out,
+                                           n_in, _stream())

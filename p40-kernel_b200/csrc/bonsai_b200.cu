@@ -357,6 +357,33 @@ int bonsai_b200_linear(const void *W, const float *x, const float *signs, float 
     return bonsai_p40_gemv(W, xq_scratch, y, n_out, n_in, stream);
 }
 
+// ---- projection without any allocation: the Q8_1 scratch is part of the library image -----------
+// In host code the array's name is only a handle: the device address comes from
+// cudaGetSymbolAddress, once per device, with that device current.
+static __device__ __align__(256) unsigned char g_linear_static_xq[BONSAI_B200_LINEAR_STATIC_MAX_N_IN / 32 * A_BLOCK_BYTES];
+
+int bonsai_b200_linear_static(const void *W, const float *x, const float *signs, float *y, int64_t n_out, int64_t n_in,
+                              bonsai_stream stream) {
+    if (n_in > BONSAI_B200_LINEAR_STATIC_MAX_N_IN) return BONSAI_B200_ETOOLARGE;
+    if (n_out <= 0 || n_in <= 0 || n_in % FWHT_N != 0) return 1;
+    constexpr int MAX_DEVICES = 64;
+    static std::atomic<void *> scratch_of_device[MAX_DEVICES];
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= MAX_DEVICES) return 1;
+    void *scratch = scratch_of_device[dev].load(std::memory_order_acquire);
+    if (!scratch) {     // first call on this device: resolve the device address of the array
+        e = cudaGetSymbolAddress(&scratch, g_linear_static_xq);
+        if (e != cudaSuccess) return (int)e;
+        if (!scratch) return (int)cudaErrorInvalidSymbol;
+        scratch_of_device[dev].store(scratch, std::memory_order_release);
+    }
+    const int rc = bonsai_b200_fwht_quant(x, signs, scratch, nullptr, n_in, stream);
+    if (rc != 0) return rc;
+    return bonsai_p40_gemv(W, scratch, y, n_out, n_in, stream);
+}
+
 int bonsai_b200_gemv_chunk_sums(const void *W, const void *xq, int32_t *out, int64_t row0, int64_t n_rows,
                                 int64_t n_in, bonsai_stream stream) {
     if (n_in <= 0 || n_in % 128 != 0 || row0 < 0) return 1;
