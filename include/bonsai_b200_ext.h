@@ -83,6 +83,8 @@ int bonsai_b200_stream_probe(const void *buf, int64_t bytes, int mode, void *sin
  * bit and are added in a fixed tree order (outputs within 1e-5 of the host's, identical from launch
  * to launch); 1 = the mat-vec that also adds them in the host's sequential order (outputs
  * bit-identical to src/pq2_0.h:183-191, slower).
+ * key "gemm_path": -1 (default) = the mat-mul picks its kernel by token count (tensor cores from 16
+ * tokens up), 0 = integer SIMT kernel, 1 = tcgen05 tensor-core kernel.  Both give the same bits.
  * key "gemv_variant": -1 = automatic, otherwise a tuning index used by the benchmark sweep.
  * Returns 0, or 1 for an unknown key. */
 int bonsai_b200_set_option(const char *key, int64_t value);

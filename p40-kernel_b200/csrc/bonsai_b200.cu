@@ -8,6 +8,7 @@
 
 #include "activation.cuh"
 #include "gemm_simt.cuh"
+#include "gemm_tc.cuh"
 #include "gemv.cuh"
 #include "gemv_stream.cuh"
 #include "probe.cuh"
@@ -26,7 +27,8 @@ constexpr int SMEM_LIMIT = 227 * 1024;        // dynamic shared memory a CTA may
 
 std::atomic<int> g_opt_pdl{0};
 std::atomic<int> g_opt_gemv_variant{-1};
-std::atomic<int> g_opt_gemv_order{0};          // 0: streaming kernel (fixed tree order), 1: the host's sequential order
+std::atomic<int> g_opt_gemv_order{0};
+std::atomic<int> g_opt_gemm_path{-1};          // -1: by token count, 0: integer SIMT kernel, 1: tensor-core kernel          // 0: streaming kernel (fixed tree order), 1: the host's sequential order
 
 inline cudaStream_t as_stream(bonsai_stream s) { return reinterpret_cast<cudaStream_t>(s); }
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -402,6 +404,19 @@ int bonsai_p40_gemm(const void *W, const void *Xq, float *Y, int64_t n_out, int6
     if (n_in <= 0 || n_in % 128 != 0) return 1;
     if (n_out <= 0 || n_tok <= 0) return 0;
     if (n_out > INT32_MAX || n_tok > INT32_MAX || (reinterpret_cast<uintptr_t>(Xq) & 3u)) return 1;
+    const int path = g_opt_gemm_path.load();
+    const bool tensor = path == 1 || (path < 0 && n_tok >= 16);       // a 64-token tile needs tokens to fill it
+    if (tensor) {
+        const dim3 grid((unsigned)((n_out + TC_M - 1) / TC_M), (unsigned)((n_tok + TC_N - 1) / TC_N));
+        if (grid.y > 65535) return 1;
+        static SmemOptIn opt;
+        cudaError_t err = opt.ensure(gemm_tc_kernel);
+        if (err != cudaSuccess) return (int)err;
+        gemm_tc_kernel<<<grid, TC_THREADS, TC_SMEM_BYTES, as_stream(stream)>>>(
+            static_cast<const uint8_t *>(W), static_cast<const uint32_t *>(Xq), Y, (int)n_out, (int)(n_in / 128),
+            (int)n_tok);
+        return (int)cudaGetLastError();
+    }
     const dim3 grid((unsigned)((n_out + GS_ROWS - 1) / GS_ROWS), (unsigned)((n_tok + GS_TOKS - 1) / GS_TOKS));
     if (grid.y > 65535) return 1;
     gemm_simt_kernel<<<grid, 256, 0, as_stream(stream)>>>(static_cast<const uint8_t *>(W),
@@ -487,6 +502,7 @@ int bonsai_b200_set_option(const char *key, int64_t value) {
     if (!std::strcmp(key, "pdl")) { g_opt_pdl.store(value != 0); return 0; }
     if (!std::strcmp(key, "gemv_variant")) { g_opt_gemv_variant.store((int)value); return 0; }
     if (!std::strcmp(key, "gemv_order")) { g_opt_gemv_order.store(value != 0); return 0; }
+    if (!std::strcmp(key, "gemm_path")) { g_opt_gemm_path.store((int)value); return 0; }
     return 1;
 }
 

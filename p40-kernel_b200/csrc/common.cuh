@@ -87,7 +87,7 @@ __device__ __forceinline__ int chunk_sumi_scaled(uint32_t w0, uint32_t w1, const
     return acc;
 }
 
-// ---- shared-memory barriers and bulk copies (sm_90+ PTX, no cluster multicast anywhere) -------
+// ---- shared-memory barriers and bulk copies (sm_90+ PTX, every copy is local to its CTA) -------
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 __device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {

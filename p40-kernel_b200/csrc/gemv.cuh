@@ -9,7 +9,7 @@
 // instructions per 32 weights, so the stream and the arithmetic must overlap completely):
 //   * one persistent CTA per SM owns a run of consecutive rows and streams it through a ring of
 //     shared-memory slots.  A tile is (up to 16 rows) x (a segment of the row); rows are 16-byte
-//     aligned when n_in/128 is even, so a tile is one 1-D bulk async copy (TMA, no multicast) when
+//     aligned when n_in/128 is even, so a tile is one 1-D bulk async copy (TMA, CTA-local) when
 //     it spans whole rows, one per row otherwise.  The CTA uses less than half of an SM's shared
 //     memory: with programmatic launches the next kernel of the stream becomes resident beside it
 //     and has its first tiles in flight while this one drains;

@@ -10,7 +10,7 @@
 // term is gemv_ring_kernel (gemv.cuh), selectable at run time.
 //
 // Shape (B200): one persistent CTA per SM streams its run of rows through a ring of shared-memory
-// slots fed by 1-D bulk async copies (TMA, no multicast); it stays under half of an SM's shared
+// slots fed by 1-D bulk async copies (TMA, CTA-local); it stays under half of an SM's shared
 // memory so that, with programmatic launches, the next kernel's CTA is resident and prefetching
 // while this one drains.  A tile is (a few row quads) x (a row segment of <= 40 blocks); a task is
 // one quad of one tile, taken by one warp: lane = (row of the quad, one of 8 block lanes), the lane

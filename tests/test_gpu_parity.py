@@ -354,6 +354,27 @@ def test_gemm_bits(gpu, port, n_out, n_in, n_tok):
     assert_close_and_exact(host(Y), port.gemm(W, Xq, n_out, n_in, n_tok, threads=8))
 
 
+@pytest.mark.parametrize("path", [0, 1])
+@pytest.mark.parametrize("n_out,n_in,n_tok", [(128, 128, 64), (64, 256, 5), (300, 5120, 100), (1024, 5120, 512), (200, 17408, 130),
+                                              (129, 384, 65)])
+def test_gemm_both_kernels_same_bits(gpu, port, path, n_out, n_in, n_tok):
+    """Integer SIMT kernel (path 0) and tcgen05 tensor-core kernel (path 1): both bit-identical to the host
+    loop, on full tiles, ragged rows, ragged tokens and odd block counts."""
+    import torch
+    W = synth.pq2_0_weights(n_out, n_in, seed=n_tok + path)
+    X = synth.activations(n_in, seed=n_out, batch=n_tok)
+    Xq = port.quantize_batch_chunk_major(X)
+    Y = torch.full((n_out, n_tok), 777.0, dtype=torch.float32, device="cuda")
+    try:
+        assert gpu.set_option("gemm_path", path) == 0
+        assert gpu.gemm(dev(W), dev(Xq), Y, n_out, n_in, n_tok) == 0
+        torch.cuda.synchronize()
+    finally:
+        gpu.set_option("gemm_path", -1)
+    assert_close_and_exact(host(Y), port.gemm(W, Xq, n_out, n_in, n_tok, threads=8))
+    assert gpu.device_status() == 0
+
+
 def test_gemm_golden(gpu, golden):
     import torch
     Y = torch.zeros((16, 5), dtype=torch.float32, device="cuda")
