@@ -227,11 +227,10 @@ def run_b200(args):
         dev_x.copy_(pin_x, non_blocking=True)
         for i, (n_in, n_out, rows, W, y) in enumerate(mats):
             xi = dev_x[x_off[i]:x_off[i] + n_in]
-            bb.fwht_quant(xi, None, xq_e2e[i], None, n_in)
             yo = y_all[y_off[i]:y_off[i] + n_out]
             ys = yo[rank * rows:(rank + 1) * rows]
-            bb.gemv(W, xq_e2e[i], ys, rows, n_in)
-            n += 2
+            bb.linear(W, xi, None, ys, xq_e2e[i], rows, n_in)       # rotation + quantiser + mat-vec, one kernel
+            n += 1
             if world > 1:
                 dist.all_gather_into_tensor(yo, ys)
         pin_y.copy_(y_all, non_blocking=True)
@@ -330,6 +329,135 @@ def run_b200(args):
         dist.destroy_process_group()
 
 
+def model_gemvs():
+    """(n_in, n_out) of every PQ2_0 mat-vec of one decoded token, in layer order: 64 layers (48 linear-
+    attention, every 4th full attention) plus the output head -- 401 mat-vecs, 6.8 GB of weights
+    (reference: include/bonsai_model.h:29-59, tools/check_gguf.py:45-62)."""
+    out = []
+    for layer in range(64):
+        if (layer + 1) % 4 == 0:
+            out += [(5120, 12288), (5120, 1024), (5120, 1024), (6144, 5120)]
+        else:
+            out += [(5120, 10240), (5120, 6144), (6144, 5120)]
+        out += [(5120, 17408), (5120, 17408), (17408, 5120)]
+    out.append((5120, 248320))
+    return out
+
+
+def _graph_time(torch, fn, steps, warmup):
+    fn()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            fn()
+    torch.cuda.current_stream().wait_stream(side)
+    for _ in range(warmup):
+        graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def run_decode_step(args):
+    """BASELINE config 2: the chain of 401 projections of one decoded token, each the rotation +
+    Q8_1 quantiser of a resident fp32 vector of its input width followed by the mat-vec (one fused kernel) (the values do not flow from one mat-vec to
+    the next; stream order does), replayed as one CUDA graph.  Reports tokens/s and weight GB/s."""
+    import torch
+    import bonsai_b200 as bb
+    torch.cuda.set_device(0)
+    bb.lib()
+    bb.set_option("pdl", max(args.pdl, 0))
+    shapes = model_gemvs()
+    ws, first = [], 0
+    for n_in, n_out in shapes:
+        nblk = n_out * (n_in // 128)
+        W = torch.empty(nblk * 34, dtype=torch.uint8, device="cuda")
+        assert bb.synth_pq2_0(W, first, nblk, args.seed) == 0
+        first += nblk
+        ws.append(W)
+    xs = {k: torch.randn(k, device="cuda") for k in {a for a, _ in shapes}}
+    xq = {k: torch.empty(k // 32 * 36, dtype=torch.uint8, device="cuda") for k in xs}
+    ys = {n: torch.empty(n, device="cuda") for n in {b for _, b in shapes}}
+
+    def token():
+        for (n_in, n_out), W in zip(shapes, ws):
+            bb.linear(W, xs[n_in], None, ys[n_out], xq[n_in], n_out, n_in)   # rotation + quantiser + mat-vec
+
+    steps = max(3, min(args.steps, 50))
+    sampler = ClockSampler(0)
+    sampler.start()
+    ms = _graph_time(torch, token, steps, max(3, min(args.warmup, 5)))
+    clocks = sampler.result()
+    wbytes = sum(weight_bytes(a, b) for a, b in shapes)
+    peak, peak_kind = measured_peak_gbs()
+    gbs = wbytes / (ms * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": "decode_tokens_per_s", "value": 1e3 / ms, "unit": "tokens/s", "n_gpus": 1, "steps": steps,
+        "warmup": max(3, min(args.warmup, 5)), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "int8xint2->int32, fp32 scale", "data": "synthetic",
+        "config": {"workload": "decode_step", "matvecs": len(shapes), "weight_bytes": wbytes, "batch": 1, "pdl": args.pdl,
+                   "l2": "inputs larger than L2", "launch": "cuda_graph_per_step"},
+        "gpu_launches": len(shapes) * steps, "clocks": clocks,
+        "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak,
+                     "peak_kind": peak_kind, "traffic": None},
+        "device_status": bb.device_status()}))
+
+
+def run_prefill(args):
+    """BASELINE config 3: M = 512 tokens through the two large projections; a step = token-batch rotation +
+    quantiser into the chunk-major layout, then the tensor-core mat-mul, for both matrices."""
+    import torch
+    import bonsai_b200 as bb
+    torch.cuda.set_device(0)
+    bb.lib()
+    n_tok = 512
+    mats = []
+    for n_in, n_out in [(5120, 17408), (17408, 5120)]:
+        nblk = n_out * (n_in // 128)
+        W = torch.empty(nblk * 34, dtype=torch.uint8, device="cuda")
+        assert bb.synth_pq2_0(W, 0, nblk, args.seed) == 0
+        X = torch.randn(n_tok, n_in, device="cuda")
+        Xq = torch.empty(n_in // 32 * n_tok * 36, dtype=torch.uint8, device="cuda")
+        Y = torch.empty(n_out, n_tok, device="cuda")
+        mats.append((n_in, n_out, W, X, Xq, Y))
+
+    def step():
+        for n_in, n_out, W, X, Xq, Y in mats:
+            assert bb.quant_batch(X, None, Xq, n_in, n_tok, True) == 0
+            assert bb.gemm(W, Xq, Y, n_out, n_in, n_tok) == 0
+
+    steps = max(3, min(args.steps, 30))
+    sampler = ClockSampler(0)
+    sampler.start()
+    ms = _graph_time(torch, step, steps, max(3, min(args.warmup, 5)))
+    clocks = sampler.result()
+    ops = sum(2.0 * n_tok * a * b for a, b, *_ in mats)
+    tops = ops / (ms * 1e-3) / 1e12
+    try:
+        bf16 = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"])
+        peak, kind = 2.0 * bf16, "2 x measured dense bf16 (no int8 figure is measured on this pool)"
+    except Exception:
+        peak, kind = 2.0 * 1590.0, "2 x fallback dense bf16"
+    print(json.dumps({
+        "metric": "pq2_0_prefill_gemm", "value": tops, "unit": "TOPS", "n_gpus": 1, "steps": steps,
+        "warmup": max(3, min(args.warmup, 5)), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "int8 x int8 -> int32 (tcgen05), fp32 scale", "data": "synthetic",
+        "config": {"workload": "prefill", "n_tok": n_tok, "shapes_nin_nout": [[5120, 17408], [17408, 5120]],
+                   "launch": "cuda_graph_per_step"},
+        "gpu_launches": 4 * steps, "clocks": clocks,
+        "roofline": {"bound": "tensor", "achieved": tops, "peak": peak, "unit": "TOPS", "frac": tops / peak,
+                     "peak_kind": kind, "traffic": None},
+        "device_status": bb.device_status()}))
+
+
 def run_single(args):
     """One shape, `--copies` distinct weight tensors, one plain launch per copy: the command the ncu
     captures under profiles/ are taken with (nothing is timed here)."""
@@ -367,6 +495,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--sets", type=int, default=8)
+    ap.add_argument("--workload", default="layer_sweep", choices=["layer_sweep", "decode_step", "prefill"],
+                    help="layer_sweep (default, the headline metric), decode_step (401 mat-vecs of one token), "
+                         "prefill (512-token mat-mul)")
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--pdl", type=int, default=1, help="0 plain launches, 1 programmatic launches (weights of the next "
                     "mat-vec stream while the previous kernel drains)")
@@ -380,6 +511,10 @@ def main():
     args = ap.parse_args()
     if args.single:
         return run_single(args)
+    if args.workload == "decode_step" and args.impl == "b200":
+        return run_decode_step(args)
+    if args.workload == "prefill" and args.impl == "b200":
+        return run_prefill(args)
     if args.impl == "reference":
         run_reference(args)
     else:

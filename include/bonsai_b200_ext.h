@@ -22,8 +22,9 @@ int bonsai_b200_fwht_quant(const float *x, const float *signs, void *xq, float *
 
 /* One decode projection in one call: xq_scratch = Q8_1(FWHT1024(signs * x)), then y = W . xq_scratch.
  * xq_scratch is caller-provided device memory of n_in / 32 * 36 bytes (4-byte aligned) that the call
- * overwrites; x is left untouched.  Two launches on `stream`; the result equals bonsai_b200_fwht_quant
- * followed by bonsai_p40_gemv.  No counterpart in the reference, whose callers issue the steps themselves
+ * overwrites; x is left untouched.  Two launches by default; with the option "fuse_linear" = 1 and a shape
+ * the streaming mat-vec takes, ONE launch (rotation and quantiser run in the mat-vec's prologue, once per
+ * CTA).  Either way y and the scratch equal bonsai_b200_fwht_quant followed by bonsai_p40_gemv.  No counterpart in the reference, whose callers issue the steps themselves
  * (docs/INTEGRATION.md:260-263).  Returns 1 if n_in % 1024 != 0 or n_out <= 0. */
 int bonsai_b200_linear(const void *W, const float *x, const float *signs, float *y, void *xq_scratch,
                        int64_t n_out, int64_t n_in, bonsai_stream stream);
@@ -85,6 +86,9 @@ int bonsai_b200_stream_probe(const void *buf, int64_t bytes, int mode, void *sin
  * bit-identical to src/pq2_0.h:183-191, slower).
  * key "gemm_path": -1 (default) = the mat-mul picks its kernel by token count (tensor cores from 16
  * tokens up), 0 = integer SIMT kernel, 1 = tcgen05 tensor-core kernel.  Both give the same bits.
+ * key "fuse_linear": 0 (default) = bonsai_b200_linear is two launches, 1 = one kernel when it can (saves a
+ * launch, but every CTA then waits for its own rotation before its first multiply: measured ~6 % slower
+ * on the 401-projection decode chain).
  * key "gemv_variant": -1 = automatic, otherwise a tuning index used by the benchmark sweep.
  * Returns 0, or 1 for an unknown key. */
 int bonsai_b200_set_option(const char *key, int64_t value);

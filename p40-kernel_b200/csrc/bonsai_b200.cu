@@ -28,6 +28,7 @@ constexpr int SMEM_LIMIT = 227 * 1024;        // dynamic shared memory a CTA may
 std::atomic<int> g_opt_pdl{0};
 std::atomic<int> g_opt_gemv_variant{-1};
 std::atomic<int> g_opt_gemv_order{0};
+std::atomic<int> g_opt_fuse_linear{0};         // 1: bonsai_b200_linear runs as one kernel when it can (measured slower)
 std::atomic<int> g_opt_gemm_path{-1};          // -1: by token count, 0: integer SIMT kernel, 1: tensor-core kernel          // 0: streaming kernel (fixed tree order), 1: the host's sequential order
 
 inline cudaStream_t as_stream(bonsai_stream s) { return reinterpret_cast<cudaStream_t>(s); }
@@ -320,11 +321,13 @@ int bonsai_p40_gemv(const void *W, const void *xq, float *y, int64_t n_out, int6
         StreamParams sp;
         if (base_ok && plan_stream(n_out, nblocks, variant, sp, threads, smem_bytes)) {
             static SmemOptIn opt;
-            cudaError_t err = opt.ensure(gemv_stream_kernel);
+            cudaError_t err = opt.ensure(gemv_stream_kernel<false>);
             if (err != cudaSuccess) return (int)err;
-            return (int)launch(gemv_stream_kernel, dim3((unsigned)((n_out + sp.rows_per_cta - 1) / sp.rows_per_cta)),
+            return (int)launch(gemv_stream_kernel<false>, dim3((unsigned)((n_out + sp.rows_per_cta - 1) / sp.rows_per_cta)),
                                dim3(threads), (size_t)smem_bytes, as_stream(stream), pdl,
-                               static_cast<const uint8_t *>(W), static_cast<const uint32_t *>(xq), y, sp);
+                               static_cast<const uint8_t *>(W), static_cast<const uint32_t *>(xq), y, sp,
+                               static_cast<const float *>(nullptr), static_cast<const float *>(nullptr),
+                               static_cast<uint32_t *>(nullptr));
         }
     }
     RingParams rp;
@@ -354,6 +357,21 @@ int bonsai_p40_gemv(const void *W, const void *xq, float *y, int64_t n_out, int6
 int bonsai_b200_linear(const void *W, const float *x, const float *signs, float *y, void *xq_scratch, int64_t n_out,
                        int64_t n_in, bonsai_stream stream) {
     if (n_out <= 0 || n_in <= 0 || n_in % FWHT_N != 0 || !xq_scratch) return 1;
+    if (n_out > INT32_MAX || !aligned16(x) || (signs && !aligned16(signs)) || (reinterpret_cast<uintptr_t>(xq_scratch) & 3u))
+        return 1;
+    // one launch when the streaming mat-vec takes the shape: rotation and quantiser run in its prologue
+    StreamParams sp;
+    int threads = 0, smem_bytes = 0;
+    if (g_opt_gemv_order.load() == 0 && g_opt_fuse_linear.load() != 0 && aligned16(W) &&
+        plan_stream(n_out, (int)(n_in / 128), g_opt_gemv_variant.load(), sp, threads, smem_bytes)) {
+        static SmemOptIn opt;
+        cudaError_t err = opt.ensure(gemv_stream_kernel<true>);
+        if (err != cudaSuccess) return (int)err;
+        return (int)launch(gemv_stream_kernel<true>, dim3((unsigned)((n_out + sp.rows_per_cta - 1) / sp.rows_per_cta)),
+                           dim3(threads), (size_t)smem_bytes, as_stream(stream), g_opt_pdl.load() != 0,
+                           static_cast<const uint8_t *>(W), static_cast<const uint32_t *>(nullptr), y, sp, x, signs,
+                           static_cast<uint32_t *>(xq_scratch));
+    }
     const int rc = bonsai_b200_fwht_quant(x, signs, xq_scratch, nullptr, n_in, stream);
     if (rc != 0) return rc;
     return bonsai_p40_gemv(W, xq_scratch, y, n_out, n_in, stream);
@@ -503,6 +521,7 @@ int bonsai_b200_set_option(const char *key, int64_t value) {
     if (!std::strcmp(key, "gemv_variant")) { g_opt_gemv_variant.store((int)value); return 0; }
     if (!std::strcmp(key, "gemv_order")) { g_opt_gemv_order.store(value != 0); return 0; }
     if (!std::strcmp(key, "gemm_path")) { g_opt_gemm_path.store((int)value); return 0; }
+    if (!std::strcmp(key, "fuse_linear")) { g_opt_fuse_linear.store(value != 0); return 0; }
     return 1;
 }
 

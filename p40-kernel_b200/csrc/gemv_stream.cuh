@@ -21,6 +21,7 @@
 // broadcast): no term buffers, no ordered adder, about 30 instructions per 32 weights.
 #pragma once
 
+#include "activation.cuh"
 #include "common.cuh"
 #include "gemv.cuh"
 
@@ -46,8 +47,16 @@ struct StreamParams {
 //   full[t] : tile t has landed in slot t % nslot             (1 arrival + copy bytes)
 //   done[t] : every task of tile t has copied its blocks out   (live quads * nseg arrivals)
 // Both are single-use (parity 0), so a warp that skipped tiles can never read a stale phase.
+//
+// FUSED = true is the one-launch projection: the CTA takes the fp32 activation vector instead of Q8_1
+// blocks, rotates it (FWHT-1024, one warp per 1024-block) and quantises it straight into its own
+// shared-memory tables while its first weight tiles are in flight; CTA 0 also writes the Q8_1 blocks
+// to `xq_out` so that the caller's scratch holds what the two-launch form would have left there.
+template <bool FUSED>
 __global__ void __launch_bounds__(512, 1) gemv_stream_kernel(const uint8_t *__restrict__ W, const uint32_t *__restrict__ xq,
-                                                             float *__restrict__ y, const StreamParams P) {
+                                                             float *__restrict__ y, const StreamParams P,
+                                                             const float *__restrict__ x, const float *__restrict__ signs,
+                                                             uint32_t *__restrict__ xq_out) {
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t *full = reinterpret_cast<uint64_t *>(smem);
     uint64_t *done = full + RING_MAX_TILES;
@@ -106,7 +115,56 @@ __global__ void __launch_bounds__(512, 1) gemv_stream_kernel(const uint8_t *__re
     if (threadIdx.x == 0) *next_task = 0;
     pdl_launch_dependents();
     pdl_wait_prior_grid();              // activations (and y) belong to the previous kernel until here
-    {
+    if (FUSED) {
+        // rotation + quantiser in the prologue: nb / 8 blocks of 1024 activations over the compute warps
+        const int nfb = P.nb >> 3;
+        bool first = true;
+        for (int fb0 = 0; fb0 < nfb || first; fb0 += compute_warps) {
+            const int fb = fb0 + wid;
+            const bool live = wid < compute_warps && fb < nfb;
+            float v[8][4];
+            if (live) {
+#pragma unroll
+                for (int r = 0; r < 8; ++r) {
+                    const float4 f = *reinterpret_cast<const float4 *>(x + (size_t)fb * FWHT_N + r * 128 + 4 * lane);
+                    v[r][0] = f.x; v[r][1] = f.y; v[r][2] = f.z; v[r][3] = f.w;
+                }
+            }
+            if (first) {
+                // every warp has issued its first loads: the rest of the ring may queue behind them
+                __syncthreads();
+                if (wid == compute_warps && lane == 0)
+                    for (int t = 2; t < first_fill; ++t) issue_tile(t);
+                first = false;
+            }
+            if (live) {
+                if (signs) {
+#pragma unroll
+                    for (int r = 0; r < 8; ++r) {
+                        const float4 sg = *reinterpret_cast<const float4 *>(signs + (size_t)fb * FWHT_N + r * 128 + 4 * lane);
+                        v[r][0] = __fmul_rn(v[r][0], sg.x); v[r][1] = __fmul_rn(v[r][1], sg.y);
+                        v[r][2] = __fmul_rn(v[r][2], sg.z); v[r][3] = __fmul_rn(v[r][3], sg.w);
+                    }
+                }
+                fwht1024_warp(v, lane);
+#pragma unroll
+                for (int r = 0; r < 8; ++r) {
+                    uint32_t word, header;
+                    quantise_chunk_8lanes(v[r], lane, word, header);
+                    const int chunk = fb * 32 + r * 4 + (lane >> 3);
+                    act_q[(chunk >> 2) * STREAM_ACT_WORDS + (chunk & 3) * 8 + (lane & 7)] = word;
+                    if ((lane & 7) == 0) {
+                        act_s[chunk] = f16_bits_to_f32(header & 0xFFFFu);
+                        act_i[chunk] = -64 * (int)(short)(header >> 16);
+                    }
+                    if (blockIdx.x == 0 && xq_out) {
+                        xq_out[9 * chunk + 1 + (lane & 7)] = word;
+                        if ((lane & 7) == 0) xq_out[9 * chunk] = header;
+                    }
+                }
+            }
+        }
+    } else {
         const int nchunks = P.nb * 4;
         uint32_t v[9];
         const bool mine = (int)threadIdx.x < nchunks;

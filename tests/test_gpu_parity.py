@@ -292,12 +292,23 @@ def test_linear_one_call(gpu, port, n_out, n_in, signed):
     scratch = torch.zeros(n_in // 32 * 36, dtype=torch.uint8, device="cuda")
     y = torch.zeros(n_out, dtype=torch.float32, device="cuda")
     xd = dev(x)
-    assert gpu.linear(dev(W), xd, None if sg is None else dev(sg), y, scratch, n_out, n_in) == 0
+    Wd, sd = dev(W), None if sg is None else dev(sg)
+    assert gpu.linear(Wd, xd, sd, y, scratch, n_out, n_in) == 0          # default: two launches
     want_xq = port.quantize_q8_1(port.fwht_blocks(x, sg), True)
     assert np.array_equal(host(scratch), want_xq)
     assert np.array_equal(bits(host(xd)), bits(x))
     assert_close(host(y), port.gemv(W, want_xq, n_out, n_in, threads=4))
-    assert gpu.linear(dev(W), xd, None, y, scratch, n_out, 1000) == 1
+    fused = host(y).copy()
+    try:
+        gpu.set_option("fuse_linear", 1)                                  # one kernel, rotation in its prologue: same bits
+        y.zero_()
+        scratch.zero_()
+        assert gpu.linear(Wd, xd, sd, y, scratch, n_out, n_in) == 0
+    finally:
+        gpu.set_option("fuse_linear", 0)
+    assert np.array_equal(host(scratch), want_xq)
+    assert np.array_equal(bits(host(y)), bits(fused))
+    assert gpu.linear(Wd, xd, None, y, scratch, n_out, 1000) == 1
 
 
 # ---- repacked layout ----------------------------------------------------------------------------------
