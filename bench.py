@@ -10,13 +10,18 @@ of the four matrices are resident in HBM (S = 8 -> 446 MB, larger than the 126 M
 one pass over all of them, so every launch streams its weights from HBM.
 
 value   : PQ2_0 weight bytes of all launches / device time (CUDA events, max over ranks), GB/s.
-e2e     : the same metric with HOST buffers: per mat-vec the fp32 activation vector is copied from
-          pinned host memory, rotated + quantised + multiplied through the C ABI, and y is copied
-          back, all inside the timed region.  Weights stay resident (they are model state).
-roofline: algorithmic bytes (weights + Q8_1 vector + fp32 output) / average launch time of the
-          mat-vec kernel, against the measured HBM copy bandwidth.
-N > 1   : every matrix is split by output rows over the ranks; each rank multiplies its slice and
-          an NCCL all-gather assembles y (strong scaling: the total work is fixed).
+--call  : "list" (default) hands the step's mat-vecs to bonsai_b200_chain_run, ONE persistent launch that
+          streams the matrices back to back; "matrix" calls bonsai_p40_gemv once per matrix (the
+          reference's ABI unchanged).  In list mode the per-matrix figure is measured too and
+          reported under "per_matrix_abi".
+e2e     : the same metric with HOST buffers: the step's fp32 activation vectors are copied from
+          pinned host memory (one block), rotated + quantised (one call) + multiplied through the C
+          ABI, and the outputs are copied back, all inside the timed region.  Weights stay resident
+          (they are model state).
+roofline: algorithmic bytes (weights + Q8_1 vectors + fp32 outputs) of a launch / its duration,
+          against the measured HBM copy bandwidth.
+N > 1   : every matrix is split by output rows over the ranks; each rank multiplies its slices and
+          an NCCL all-gather assembles the outputs (strong scaling: the total work is fixed).
 --impl reference : the reference's own host implementation of the same path on this box's CPU
           cores (oracle/_ref when it was built, else the C restatement in oracle/).
 """
@@ -194,7 +199,9 @@ def run_b200(args):
         assert bb.fwht_quant(xdev[n_in], None, xq[n_in], None, n_in) == 0
     torch.cuda.synchronize()
 
-    def step_resident():
+    use_list = args.call == "list"
+
+    def step_matrix():
         n = 0
         for n_in, n_out, rows, W, y in mats:
             ys = y[rank * rows:(rank + 1) * rows]
@@ -221,6 +228,43 @@ def run_b200(args):
         y_off.append(off)
         off += m[1]
     xq_e2e = [torch.empty(m[0] // 32 * 36, dtype=torch.uint8, device="cuda") for m in mats]
+
+    # list mode: the whole step is ONE launch of the persistent kernel (bonsai_b200_chain_run); with
+    # several ranks every rank multiplies its row slices and one all-gather moves all of them
+    # (rank-major: gathered[r] holds rank r's slice of every matrix, in matrix order)
+    slice_off, off = [], 0
+    for m in mats:
+        slice_off.append(off)
+        off += m[2]
+    y_local = torch.zeros(off, dtype=torch.float32, device="cuda")
+    y_gathered = torch.zeros(world * off, dtype=torch.float32, device="cuda") if world > 1 else None
+    chain = chain_e2e = None
+    if use_list:
+        chain = bb.Chain([(W, xq[n_in], None, y_local[o:o + rows], rows, n_in, 0)
+                          for (n_in, n_out, rows, W, y), o in zip(mats, slice_off)])
+        # end to end: the step's activation vectors arrive as one host block; FWHT-1024 and the quantiser
+        # work on 1024- and 32-element blocks, so ONE bonsai_b200_fwht_quant call over the concatenation
+        # rotates and quantises every vector (vector i's Q8_1 blocks start at byte x_off[i] / 32 * 36)
+        xq_all = torch.empty(dev_x.numel() // 32 * 36, dtype=torch.uint8, device="cuda")
+        chain_e2e = bb.Chain([(W, xq_all[xo // 32 * 36:(xo + n_in) // 32 * 36], None, y_local[o:o + rows], rows, n_in, 0)
+                              for (n_in, n_out, rows, W, y), o, xo in zip(mats, slice_off, x_off)])
+
+    def step_list():
+        assert chain.run() == 0
+        if world > 1:
+            dist.all_gather_into_tensor(y_gathered, y_local)
+        return 1
+
+    def step_list_e2e():
+        dev_x.copy_(pin_x, non_blocking=True)
+        assert bb.fwht_quant(dev_x, None, xq_all, None, dev_x.numel()) == 0
+        assert chain_e2e.run() == 0
+        if world > 1:
+            dist.all_gather_into_tensor(y_gathered, y_local)
+            pin_y.copy_(y_gathered, non_blocking=True)
+        else:
+            pin_y.copy_(y_local, non_blocking=True)
+        return 1
 
     def step_e2e():
         n = 0
@@ -279,18 +323,24 @@ def run_b200(args):
 
     total_w = sum(weight_bytes(a, b) for a, b in LAYER_SHAPES) * sets
     total_alg = sum(algorithmic_bytes(a, b // world) for a, b in LAYER_SHAPES) * sets
-    ms, launches, clocks = timed(step_resident, args.steps, args.warmup, True)
+    ms, launches, clocks = timed(step_list if use_list else step_matrix, args.steps, args.warmup, True)
     value = total_w * args.steps / (ms * 1e-3) / 1e9
     e2e_steps = max(1, args.steps // 4)
-    ms_e, _, _ = timed(step_e2e, e2e_steps, max(3, args.warmup // 4), False)
+    ms_e, _, _ = timed(step_list_e2e if use_list else step_e2e, e2e_steps, max(3, args.warmup // 4), False)
     e2e_value = total_w * e2e_steps / (ms_e * 1e-3) / 1e9
+    per_matrix = None
+    if use_list:        # the unchanged per-matrix ABI on the same tensors, for comparison
+        ms_m, launches_m, _ = timed(step_matrix, e2e_steps, max(3, args.warmup // 4), False)
+        per_matrix = {"call": "bonsai_p40_gemv per matrix", "value": total_w * e2e_steps / (ms_m * 1e-3) / 1e9,
+                      "unit": UNIT, "ms_per_step": ms_m / e2e_steps, "gpu_launches_per_step": launches_m // e2e_steps}
     status = bb.device_status()
+    launches_per_step = launches // args.steps
 
     peak, peak_kind = measured_peak_gbs()
     traffic = None
     try:        # DRAM bytes per launch from the committed ncu capture, scaled by the bytes a launch streams
-        t = json.load(open(os.path.join(ROOT, "profiles", "gemv_stream_traffic.json")))
-        traffic = t["dram_bytes_per_launch"] / t["algorithmic_bytes_per_launch"] * (total_alg / len(mats))
+        t = json.load(open(os.path.join(ROOT, "profiles", "gemv_chain_traffic.json" if use_list else "gemv_stream_traffic.json")))
+        traffic = t["dram_bytes_per_launch"] / t["algorithmic_bytes_per_launch"] * (total_alg / launches_per_step)
     except Exception:
         pass
     achieved = total_alg * args.steps / (ms * 1e-3) / 1e9     # per-rank algorithmic bytes / per-launch time
@@ -301,17 +351,22 @@ def run_b200(args):
         "config": {"workload": "layer_sweep", "shapes_nin_nout": LAYER_SHAPES, "batch": 1, "sets": sets,
                    "resident_weight_bytes": total_w, "l2": "inputs larger than L2" if total_w > 126e6 else "fits L2",
                    "parallelism": f"rows/{world}+allgather" if world > 1 else "single", "pdl": args.pdl,
-                   "fp32_order": "host-sequential" if args.order == 1 else "fixed-tree", "variant": args.variant, "launch": "eager" if args.no_graph else "cuda_graph_per_step"},
+                   "fp32_order": "host-sequential" if args.order == 1 else "fixed-tree", "variant": args.variant,
+                   "launch": "eager" if args.no_graph else "cuda_graph_per_step",
+                   "call": "bonsai_b200_chain_run: the step's mat-vecs as one persistent launch" if use_list
+                           else "bonsai_p40_gemv per matrix"},
         "gpu_launches": launches,
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": UNIT,
                 "h2d_bytes_per_step": int(pin_x.numel() * 4), "d2h_bytes_per_step": int(pin_y.numel() * 4)},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": UNIT, "frac": achieved / peak,
                      "peak_kind": peak_kind, "traffic": traffic,
-                     "avg_launch_us": ms * 1e3 / max(1, args.steps * len(mats)),
-                     "algorithmic_bytes_per_launch_avg": total_alg / len(mats)},
+                     "avg_launch_us": ms * 1e3 / max(1, launches),
+                     "algorithmic_bytes_per_launch_avg": total_alg / launches_per_step},
         "device_status": status,
     }
+    if per_matrix is not None:
+        line["per_matrix_abi"] = per_matrix
     if world == 1 and not args.no_cpu:
         threads = os.cpu_count() or 1
         kind, sweep, wbytes = cpu_arm(args, threads)
@@ -387,9 +442,25 @@ def run_decode_step(args):
     xq = {k: torch.empty(k // 32 * 36, dtype=torch.uint8, device="cuda") for k in xs}
     ys = {n: torch.empty(n, device="cuda") for n in {b for _, b in shapes}}
 
-    def token():
-        for (n_in, n_out), W in zip(shapes, ws):
-            bb.linear(W, xs[n_in], None, ys[n_out], xq[n_in], n_out, n_in)   # rotation + quantiser + mat-vec
+    launches_per_token = len(shapes)
+    if args.call == "list":
+        # one launch per token: projections that read the same vector share its quantised form, every
+        # other projection waits for all rows of the projections before it (its input is an output
+        # of the step in the real model; here the values do not flow, the waits do)
+        ops, prev = [], None
+        for i, ((n_in, n_out), W) in enumerate(zip(shapes, ws)):
+            fl = bb.OP_ROTATE | (bb.OP_SAME_INPUT if prev == n_in and i else (bb.OP_DEPENDS if i else 0))
+            ops.append((W, xs[n_in], None, ys[n_out], n_out, n_in, fl))
+            prev = n_in
+        chain = bb.Chain(ops)
+        launches_per_token = 1
+
+        def token():
+            assert chain.run() == 0
+    else:
+        def token():
+            for (n_in, n_out), W in zip(shapes, ws):
+                bb.linear(W, xs[n_in], None, ys[n_out], xq[n_in], n_out, n_in)   # rotation + quantiser + mat-vec
 
     steps = max(3, min(args.steps, 50))
     sampler = ClockSampler(0)
@@ -404,8 +475,9 @@ def run_decode_step(args):
         "warmup": max(3, min(args.warmup, 5)), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "int8xint2->int32, fp32 scale", "data": "synthetic",
         "config": {"workload": "decode_step", "matvecs": len(shapes), "weight_bytes": wbytes, "batch": 1, "pdl": args.pdl,
-                   "l2": "inputs larger than L2", "launch": "cuda_graph_per_step"},
-        "gpu_launches": len(shapes) * steps, "clocks": clocks,
+                   "l2": "inputs larger than L2", "launch": "cuda_graph_per_step",
+                   "call": "bonsai_b200_chain_run, one launch per token" if args.call == "list" else "bonsai_b200_linear per matrix"},
+        "gpu_launches": launches_per_token * steps, "clocks": clocks,
         "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak,
                      "peak_kind": peak_kind, "traffic": None},
         "device_status": bb.device_status()}))
@@ -498,6 +570,9 @@ def main():
     ap.add_argument("--workload", default="layer_sweep", choices=["layer_sweep", "decode_step", "prefill"],
                     help="layer_sweep (default, the headline metric), decode_step (401 mat-vecs of one token), "
                          "prefill (512-token mat-mul)")
+    ap.add_argument("--call", default="list", choices=["list", "matrix"],
+                    help="list (default): the step's mat-vecs as one persistent launch (bonsai_b200_chain_run); "
+                         "matrix: one bonsai_p40_gemv launch per matrix")
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--pdl", type=int, default=1, help="0 plain launches, 1 programmatic launches (weights of the next "
                     "mat-vec stream while the previous kernel drains)")

@@ -98,6 +98,47 @@ int bonsai_b200_set_option(const char *key, int64_t value);
 int bonsai_b200_device_status(void);
 
 /* Version of this build as major * 10000 + minor * 100 + patch. */
+/* ---- a list of projections in one persistent launch (no counterpart in the reference) ---------
+ * The reference launches one kernel per matrix (bonsai_p40_gemv, include/bonsai_p40.h:26-28).  On a
+ * B200 a decode projection streams for 0.2 - 4 us, about as long as a kernel takes to start and drain,
+ * so this entry point takes the whole list: weights of the next projection stream while the previous
+ * one is multiplied, and only a projection that reads an earlier projection's output waits.
+ *
+ * Each op computes y = W . q(x): W as for bonsai_p40_gemv; x is either the permuted Q8_1 blocks of
+ * the activation vector (as bonsai_p40_quantize_q8_1 / bonsai_b200_fwht_quant write them), or, with
+ * BONSAI_B200_OP_ROTATE, the fp32 vector itself, which the kernel rotates (FWHT-1024, optional signs)
+ * and quantises exactly as bonsai_b200_fwht_quant does.  y is bit-identical to bonsai_p40_gemv with
+ * the default kernel.
+ *   BONSAI_B200_OP_DEPENDS     x is written (as some y) by an earlier op of this list: the op starts
+ *                              only when every row of every earlier op is in memory.  Needs OP_ROTATE
+ *                              (ops write fp32).  Without this flag an op may start at any time, so x
+ *                              must not be an output of the list.
+ *   BONSAI_B200_OP_SAME_INPUT  same x (and kind) as the previous op: its quantised vector is reused.
+ * Shapes: n_in a multiple of 256 (of 1024 with OP_ROTATE), W and x 16-byte aligned.
+ * create() allocates a small device table (cudaMalloc) and copies the list; run() allocates nothing,
+ * launches one cooperative kernel of one CTA per SM on `stream` (plus a 4-byte memset) and can be
+ * captured in a CUDA graph; a chain object must not run on two streams at once.  Errors: 1 for a bad
+ * argument, otherwise the CUDA error code. */
+#define BONSAI_B200_OP_ROTATE 1u
+#define BONSAI_B200_OP_DEPENDS 2u
+#define BONSAI_B200_OP_SAME_INPUT 4u
+typedef struct bonsai_b200_op {
+    const void *W;
+    const void *x;
+    const float *signs;     /* OP_ROTATE only, may be NULL */
+    float *y;
+    int64_t n_out, n_in;
+    uint32_t flags;
+    uint32_t reserved;      /* 0 */
+} bonsai_b200_op;
+typedef struct bonsai_b200_chain bonsai_b200_chain;
+int bonsai_b200_chain_create(const bonsai_b200_op *ops, int64_t n_ops, bonsai_b200_chain **out);
+int bonsai_b200_chain_run(bonsai_b200_chain *chain, bonsai_stream stream);
+int bonsai_b200_chain_destroy(bonsai_b200_chain *chain);
+/* kernels launched so far by run() on this chain's behalf, and its geometry (threads per CTA, ring
+ * slots, bytes per slot, CTAs): for benchmarks and tests. */
+int bonsai_b200_chain_info(const bonsai_b200_chain *chain, int64_t out[4]);
+
 int bonsai_b200_version(void);
 
 #ifdef __cplusplus

@@ -41,6 +41,10 @@ SIGNATURES = {
     "bonsai_b200_gemv_chunk_sums": (_INT, [_VP, _VP, _VP, _I64, _I64, _I64, _VP]),
     "bonsai_b200_synth_pq2_0": (_INT, [_VP, _I64, _I64, _U64, _VP]),
     "bonsai_b200_stream_probe": (_INT, [_VP, _I64, _INT, _VP, _VP]),
+    "bonsai_b200_chain_create": (_INT, [_VP, _I64, _VP]),
+    "bonsai_b200_chain_run": (_INT, [_VP, _VP]),
+    "bonsai_b200_chain_destroy": (_INT, [_VP]),
+    "bonsai_b200_chain_info": (_INT, [_VP, _VP]),
     "bonsai_b200_set_option": (_INT, [C.c_char_p, _I64]),
     "bonsai_b200_device_status": (_INT, []),
     "bonsai_b200_version": (_INT, []),
@@ -148,3 +152,53 @@ def linear_static(W, x, signs, y, n_out, n_in):
     """The projection whose scratch lives inside the library (no allocation, n_in <= 32768)."""
     return lib().bonsai_b200_linear_static(_dev(W, "W"), _dev(x, "x"), _dev(signs, "signs"), _dev(y, "y"), n_out,
                                            n_in, _stream())
+
+
+# ---- a list of projections in one launch -------------------------------------------------------------
+OP_ROTATE, OP_DEPENDS, OP_SAME_INPUT = 1, 2, 4
+
+
+class Op(C.Structure):
+    """struct bonsai_b200_op"""
+    _fields_ = [("W", C.c_void_p), ("x", C.c_void_p), ("signs", C.c_void_p), ("y", C.c_void_p),
+                ("n_out", C.c_int64), ("n_in", C.c_int64), ("flags", C.c_uint32), ("reserved", C.c_uint32)]
+
+
+class Chain:
+    """bonsai_b200_chain_create / _run / _destroy.  `ops` is a list of (W, x, signs, y, n_out, n_in, flags)
+    with CUDA tensors; the tensors are kept alive by the object."""
+
+    def __init__(self, ops):
+        self._keep = [t for op in ops for t in op[:4] if t is not None]
+        arr = (Op * len(ops))()
+        for o, (W, x, signs, y, n_out, n_in, flags) in zip(arr, ops):
+            o.W, o.x, o.y = _dev(W, "W").value, _dev(x, "x").value, _dev(y, "y").value
+            o.signs = _dev(signs, "signs").value if signs is not None else None
+            o.n_out, o.n_in, o.flags, o.reserved = n_out, n_in, flags, 0
+        self._h = C.c_void_p()
+        rc = lib().bonsai_b200_chain_create(C.cast(arr, C.c_void_p), len(ops), C.byref(self._h))
+        if rc != 0:
+            self._h = C.c_void_p()
+            raise RuntimeError(f"bonsai_b200_chain_create returned {rc}")
+        self.n_ops = len(ops)
+
+    def run(self):
+        return lib().bonsai_b200_chain_run(self._h, _stream())
+
+    def info(self):
+        out = (C.c_int64 * 4)()
+        rc = lib().bonsai_b200_chain_info(self._h, C.cast(out, C.c_void_p))
+        if rc != 0:
+            raise RuntimeError(f"bonsai_b200_chain_info returned {rc}")
+        return {"threads": out[0], "nslot": out[1], "slot_bytes": out[2], "ctas": out[3]}
+
+    def close(self):
+        if self._h:
+            lib().bonsai_b200_chain_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

@@ -124,6 +124,56 @@ __device__ __forceinline__ void fwht1024_warp(float (&v)[8][4], int lane) {
         for (int e = 0; e < 4; ++e) v[r][e] = __fmul_rn(v[r][e], 0.03125f);
 }
 
+// ---- rotation split over warps: one warp per 128-element slice ----------------------------------
+// A 1024-block is eight slices r = 0..7 of 128 consecutive elements; lane l of the slice's warp holds
+// elements 4l .. 4l+3.  The butterflies with h = 1 .. 64 stay inside a slice (front); those with
+// h = 128, 256, 512 combine the eight slices element by element (back), through shared memory.  Every
+// output is still produced by the same a + b / a - b as in fwht1024_warp, stage by stage, so the bits
+// are the same: a - b is computed as (-b) + a ... with IEEE addition that is the same rounding.
+__device__ __forceinline__ void fwht_slice_front(float (&v)[4], int lane) {
+    {
+        const float a = v[0], b = v[1], c = v[2], d = v[3];
+        const float s0 = __fadd_rn(a, b), s1 = __fsub_rn(a, b), s2 = __fadd_rn(c, d), s3 = __fsub_rn(c, d);
+        v[0] = __fadd_rn(s0, s2); v[2] = __fsub_rn(s0, s2);
+        v[1] = __fadd_rn(s1, s3); v[3] = __fsub_rn(s1, s3);
+    }
+#pragma unroll
+    for (int s = 0; s < 5; ++s) {
+        const bool upper = (lane >> s) & 1;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float mine = v[e];
+            const float other = __shfl_xor_sync(0xffffffffu, mine, 1 << s);
+            v[e] = upper ? __fsub_rn(other, mine) : __fadd_rn(mine, other);
+        }
+    }
+}
+// `block` points at the eight front-transformed slices of one 1024-block ([8][32] float4); returns
+// slice r of the finished rotation (scaled by 1/32) for this lane.
+__device__ __forceinline__ void fwht_slice_back(const float4 *block, int r, int lane, float (&out)[4]) {
+    float a[8][4];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const float4 f = block[(r ^ j) * 32 + lane];
+        a[j][0] = f.x; a[j][1] = f.y; a[j][2] = f.z; a[j][3] = f.w;
+    }
+    // the element at index q of a pair (q, q | h) becomes a_lower + a_upper, the upper one a_lower - a_upper;
+    // with m = sign mask when this slice is the upper one:  new(q) = partner + (own ^ m)
+    const uint32_t m0 = (r & 1) ? 0x80000000u : 0u, m1 = (r & 2) ? 0x80000000u : 0u, m2 = (r & 4) ? 0x80000000u : 0u;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        float u[4];      // h = 128 at slices r, r^2, r^4, r^6
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+            u[k] = __fadd_rn(a[2 * k + 1][e], __uint_as_float(__float_as_uint(a[2 * k][e]) ^ m0));
+        // h = 256 at slices r (u[0] with u[1]) and r^4 (u[2] with u[3])
+        const float w0 = __fadd_rn(u[1], __uint_as_float(__float_as_uint(u[0]) ^ m1));
+        const float w1 = __fadd_rn(u[3], __uint_as_float(__float_as_uint(u[2]) ^ m1));
+        // h = 512 at slice r
+        out[e] = __fmul_rn(__fadd_rn(w1, __uint_as_float(__float_as_uint(w0) ^ m2)), 0.03125f);
+    }
+}
+
 // blocks = n_tok * (n_in / 1024) warps.  X [n_tok][n_in] read-only; x_rot (nullable, may alias X)
 // receives the rotated values; xq (nullable) the Q8_1 blocks at chunk * n_tok + tok.
 __global__ void __launch_bounds__(128) fwht_quant_kernel(const float *X, const float *__restrict__ signs, float *x_rot,

@@ -11,12 +11,15 @@
 #include "gemm_tc.cuh"
 #include "gemv.cuh"
 #include "gemv_stream.cuh"
+#include "gemv_chain.cuh"
 #include "probe.cuh"
 #include "repack.cuh"
 #include "synth.cuh"
 
 #include <atomic>
 #include <cstring>
+#include <new>
+#include <vector>
 
 using namespace b200;
 
@@ -29,6 +32,9 @@ std::atomic<int> g_opt_pdl{0};
 std::atomic<int> g_opt_gemv_variant{-1};
 std::atomic<int> g_opt_gemv_order{0};
 std::atomic<int> g_opt_fuse_linear{0};         // 1: bonsai_b200_linear runs as one kernel when it can (measured slower)
+std::atomic<int> g_opt_chain_threads{512};       // threads per CTA of the chain kernel: 512 or 768
+std::atomic<int> g_opt_chain_tile_kb{16};
+std::atomic<int> g_opt_chain_seg{40};            // longest row segment of one task, in blocks: 8, 16, 24, 32 or 40        // target bytes of one ring slot
 std::atomic<int> g_opt_gemm_path{-1};          // -1: by token count, 0: integer SIMT kernel, 1: tensor-core kernel          // 0: streaming kernel (fixed tree order), 1: the host's sequential order
 
 inline cudaStream_t as_stream(bonsai_stream s) { return reinterpret_cast<cudaStream_t>(s); }
@@ -404,6 +410,179 @@ int bonsai_b200_linear_static(const void *W, const float *x, const float *signs,
     return bonsai_p40_gemv(W, scratch, y, n_out, n_in, stream);
 }
 
+
+// ---- a list of projections in one persistent launch ------------------------------------------------
+struct bonsai_b200_chain {
+    ChainOp *d_ops = nullptr;
+    unsigned int *d_counter = nullptr;
+    int n_ops = 0, threads = 0, grid = 0, device = 0;
+    size_t smem = 0;
+    ChainGeom G{};
+};
+
+int bonsai_b200_chain_create(const bonsai_b200_op *ops, int64_t n_ops, bonsai_b200_chain **out) {
+    if (!ops || !out || n_ops <= 0 || n_ops > (1 << 20)) return 1;
+    *out = nullptr;
+    int dev = 0, sms = 0, smem_limit = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return (int)e;
+    if ((e = cudaDeviceGetAttribute(&smem_limit, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev)) != cudaSuccess) return (int)e;
+    if (sms <= 0) return 1;
+    auto round_up = [](long long v, long long m) { return (v + m - 1) / m * m; };
+    const long long tile_target = (long long)g_opt_chain_tile_kb.load() * 1024;
+    const int seg_max = g_opt_chain_seg.load();
+
+    std::vector<ChainOp> rec((size_t)n_ops);
+    ChainGeom G{};
+    long long slot_payload = 0;
+    int shift = 0, buf = 1, last_user[2] = {-1, -1}, ready_uses[2] = {0, 0};
+    bool any_rotate = false, any_q8 = false;
+    unsigned int signals = 0;
+    for (int64_t i = 0; i < n_ops; ++i) {
+        const bonsai_b200_op &o = ops[i];
+        ChainOp &r = rec[(size_t)i];
+        std::memset(&r, 0, sizeof(r));
+        const bool rotate = o.flags & BONSAI_B200_OP_ROTATE, depends = o.flags & BONSAI_B200_OP_DEPENDS;
+        const bool same = o.flags & BONSAI_B200_OP_SAME_INPUT;
+        if ((o.flags & ~7u) || o.reserved) return 1;
+        if (!o.W || !o.x || !o.y || o.n_out <= 0 || o.n_out > INT32_MAX || o.n_in <= 0) return 1;
+        if (o.n_in % 256 != 0 || (rotate && o.n_in % FWHT_N != 0) || o.n_in / 128 > 1024) return 1;
+        if (!aligned16(o.W) || !aligned16(o.x) || (o.signs && !aligned16(o.signs)) || (reinterpret_cast<uintptr_t>(o.y) & 3u))
+            return 1;
+        if (depends && !rotate) return 1;               // outputs are fp32: a dependent op must quantise
+        if (o.signs && !rotate) return 1;
+        if (same) {
+            if (i == 0 || depends) return 1;
+            const bonsai_b200_op &q = ops[i - 1];
+            if (q.x != o.x || q.n_in != o.n_in || q.signs != o.signs ||
+                ((q.flags ^ o.flags) & BONSAI_B200_OP_ROTATE))
+                return 1;
+        }
+        r.W = static_cast<const uint8_t *>(o.W);
+        r.x = o.x;
+        r.signs = o.signs;
+        r.y = o.y;
+        r.nb = (int)(o.n_in / 128);
+        r.n_out = (int)o.n_out;
+        long long ctas = (o.n_out + 3) / 4;
+        if (ctas > sms) ctas = sms;
+        r.rows_per_cta = (int)round_up((o.n_out + ctas - 1) / ctas, 4);
+        const long long used = (o.n_out + r.rows_per_cta - 1) / r.rows_per_cta;
+        r.nseg = (r.nb + seg_max - 1) / seg_max;
+        r.seg_blocks = (int)round_up((r.nb + r.nseg - 1) / r.nseg, 8);
+        if (r.seg_blocks > seg_max) r.seg_blocks = seg_max;
+        r.nseg = (r.nb + r.seg_blocks - 1) / r.seg_blocks;
+        const long long row_bytes = (long long)r.nb * W_BLOCK_BYTES;
+        long long tr = (tile_target / row_bytes) & ~3ll;
+        if (tr < 4) tr = 4;
+        if (tr > r.rows_per_cta) tr = r.rows_per_cta;
+        r.tr = (int)tr;
+        r.tpt = (r.tr / 4) * r.nseg;
+        r.magic_tpt = magic_u32((uint32_t)r.tpt);
+        r.magic_nseg = magic_u32((uint32_t)r.nseg);
+        r.cta_shift = shift;
+        shift = (int)((shift + used) % sms);            // the next op starts on the CTA after this one's last
+        r.flags = (rotate ? CHAIN_ROTATE : 0) | (depends ? CHAIN_DEPENDS : 0) | (same ? CHAIN_SAME_INPUT : 0);
+        if (depends) rec[(size_t)i - 1].flags |= CHAIN_SIGNAL;     // i > 0: op 0 may not depend
+        if (depends && i == 0) return 1;
+        if (!same) buf ^= 1;
+        r.buf = buf;
+        r.prev_user = same ? -1 : last_user[buf];
+        last_user[buf] = (int)i;
+        if (!same && !rotate) r.ready_parity = ready_uses[buf]++ & 1;
+        if (rotate) any_rotate = true; else any_q8 = true;
+        if (r.nb > G.nb_max) G.nb_max = r.nb;
+        if (r.nseg > 1) {        // only rows in several segments are joined through shared memory
+            if (r.rows_per_cta * r.nseg > G.partial_floats) G.partial_floats = r.rows_per_cta * r.nseg;
+            if (r.rows_per_cta / 4 > G.quad_ints) G.quad_ints = r.rows_per_cta / 4;
+        }
+        if (tr * row_bytes > slot_payload) slot_payload = tr * row_bytes;
+    }
+    // arrivals a dependent op must see: one per CTA for every signalling op before it
+    for (int64_t i = 0; i < n_ops; ++i) {
+        rec[(size_t)i].arrivals_needed = signals;
+        if (rec[(size_t)i].flags & CHAIN_SIGNAL) ++signals;
+    }
+    G.stage_blocks = any_q8 ? G.nb_max : 0;
+    G.rot_blocks = any_rotate ? (G.nb_max / 8 < 7 ? G.nb_max / 8 : 7) : 0;
+    G.partial_floats = (int)round_up(G.partial_floats, 4);
+    G.quad_ints = (int)round_up(G.quad_ints, 4);
+    G.slot_bytes = (int)round_up(slot_payload + 16, 128);
+    const size_t fixed = chain_fixed_bytes(G);
+    if (fixed + 3 * (size_t)G.slot_bytes > (size_t)smem_limit) return 1;
+    long long nslot = ((long long)smem_limit - (long long)fixed) / G.slot_bytes;
+    if (nslot > CHAIN_MAX_SLOTS) nslot = CHAIN_MAX_SLOTS;
+    G.nslot = (int)nslot;
+    G.magic_nslot = magic_u32((uint32_t)G.nslot);
+
+    bonsai_b200_chain *c = new (std::nothrow) bonsai_b200_chain;
+    if (!c) return (int)cudaErrorMemoryAllocation;
+    c->n_ops = (int)n_ops;
+    c->threads = g_opt_chain_threads.load();
+    c->grid = sms;
+    c->device = dev;
+    c->G = G;
+    c->smem = fixed + (size_t)G.nslot * G.slot_bytes;
+    // the launch is cooperative: every CTA must be resident at once
+    int per_sm = 0;
+    if (c->threads == 768) {
+        e = cudaFuncSetAttribute(gemv_chain_kernel<768>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_limit);
+        if (e == cudaSuccess) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gemv_chain_kernel<768>, 768, c->smem);
+    } else {
+        e = cudaFuncSetAttribute(gemv_chain_kernel<512>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_limit);
+        if (e == cudaSuccess) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gemv_chain_kernel<512>, 512, c->smem);
+    }
+    if (e == cudaSuccess && per_sm < 1) e = cudaErrorLaunchOutOfResources;
+    if (e == cudaSuccess) e = cudaMalloc(&c->d_ops, sizeof(ChainOp) * (size_t)n_ops);
+    if (e == cudaSuccess) e = cudaMalloc(&c->d_counter, 256);
+    if (e == cudaSuccess) e = cudaMemcpy(c->d_ops, rec.data(), sizeof(ChainOp) * (size_t)n_ops, cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) {
+        bonsai_b200_chain_destroy(c);
+        return (int)e;
+    }
+    *out = c;
+    return 0;
+}
+
+int bonsai_b200_chain_run(bonsai_b200_chain *c, bonsai_stream stream) {
+    if (!c || !c->d_ops) return 1;
+    cudaStream_t st = as_stream(stream);
+    cudaError_t e = cudaMemsetAsync(c->d_counter, 0, sizeof(unsigned int), st);
+    if (e != cudaSuccess) return (int)e;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)c->grid);
+    cfg.blockDim = dim3((unsigned)c->threads);
+    cfg.dynamicSmemBytes = c->smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeCooperative;
+    attr[0].val.cooperative = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const ChainOp *ops = c->d_ops;
+    if (c->threads == 768) e = cudaLaunchKernelEx(&cfg, gemv_chain_kernel<768>, ops, c->n_ops, c->G, c->d_counter);
+    else e = cudaLaunchKernelEx(&cfg, gemv_chain_kernel<512>, ops, c->n_ops, c->G, c->d_counter);
+    return (int)e;
+}
+
+int bonsai_b200_chain_destroy(bonsai_b200_chain *c) {
+    if (!c) return 0;
+    cudaError_t e1 = c->d_ops ? cudaFree(c->d_ops) : cudaSuccess;
+    cudaError_t e2 = c->d_counter ? cudaFree(c->d_counter) : cudaSuccess;
+    delete c;
+    return (int)(e1 != cudaSuccess ? e1 : e2);
+}
+
+int bonsai_b200_chain_info(const bonsai_b200_chain *c, int64_t out[4]) {
+    if (!c || !out) return 1;
+    out[0] = c->threads;
+    out[1] = c->G.nslot;
+    out[2] = c->G.slot_bytes;
+    out[3] = c->grid;
+    return 0;
+}
+
 int bonsai_b200_gemv_chunk_sums(const void *W, const void *xq, int32_t *out, int64_t row0, int64_t n_rows,
                                 int64_t n_in, bonsai_stream stream) {
     if (n_in <= 0 || n_in % 128 != 0 || row0 < 0) return 1;
@@ -522,6 +701,21 @@ int bonsai_b200_set_option(const char *key, int64_t value) {
     if (!std::strcmp(key, "gemv_order")) { g_opt_gemv_order.store(value != 0); return 0; }
     if (!std::strcmp(key, "gemm_path")) { g_opt_gemm_path.store((int)value); return 0; }
     if (!std::strcmp(key, "fuse_linear")) { g_opt_fuse_linear.store(value != 0); return 0; }
+    if (!std::strcmp(key, "chain_threads")) {
+        if (value != 512 && value != 768) return 1;
+        g_opt_chain_threads.store((int)value);
+        return 0;
+    }
+    if (!std::strcmp(key, "chain_seg")) {
+        if (value < 8 || value > 8 * STREAM_STEPS || value % 8 != 0) return 1;
+        g_opt_chain_seg.store((int)value);
+        return 0;
+    }
+    if (!std::strcmp(key, "chain_tile_kb")) {
+        if (value < 4 || value > 48) return 1;
+        g_opt_chain_tile_kb.store((int)value);
+        return 0;
+    }
     return 1;
 }
 
@@ -538,6 +732,14 @@ int bonsai_b200_version(void) { return 100; }
 
 #ifdef BONSAI_B200_TRACE
 int bonsai_b200_set_skip(int v) { return (int)cudaMemcpyToSymbol(g_skip, &v, sizeof(int)); }
+int bonsai_b200_read_tile_trace(long long *out, int n) {
+    cudaDeviceSynchronize();
+    return (int)cudaMemcpyFromSymbol(out, g_tile_trace, sizeof(long long) * n);
+}
+int bonsai_b200_read_chain_trace(long long *out, int n) {
+    cudaDeviceSynchronize();
+    return (int)cudaMemcpyFromSymbol(out, g_chain_trace, sizeof(long long) * n);
+}
 int bonsai_b200_read_trace(long long *out, int n) {
     cudaDeviceSynchronize();
     return (int)cudaMemcpyFromSymbol(out, g_trace, sizeof(long long) * n);

@@ -20,7 +20,7 @@ constexpr int FWHT_N = 1024;
 // Sticky status word: bounded waits write a non-zero code here instead of spinning forever.
 __device__ int g_device_status = 0;
 
-enum : int { STATUS_OK = 0, STATUS_MBARRIER_TIMEOUT = 1 };
+enum : int { STATUS_OK = 0, STATUS_MBARRIER_TIMEOUT = 1, STATUS_GRID_TIMEOUT = 2 };
 
 // ---- fp16 <-> fp32 -------------------------------------------------------------------------
 __device__ __forceinline__ float f16_bits_to_f32(uint32_t h) {
@@ -66,25 +66,22 @@ __device__ __forceinline__ int dp4a_us(uint32_t w, int a, int c) {
     return r;
 }
 
-// Sum over one 32-weight chunk of code * activation, starting from `init`.  w0 / w1 are the two
-// 16-code words, a[0..7] the eight activation words of the permuted Q8_1 block: field k of word w
-// pairs with activation word 4w + k (src/pq2_0.h:155-166).  Fields are masked in place and the
-// factor 4^k is divided out between steps, which is exact because every partial sum is a multiple
-// of it; callers pass init = -64 * s so that the result is (sum code*a) - s.
+// Sum over one 32-weight chunk of code * activation.  w0 / w1 are the two 16-code words, a[0..7] the
+// eight activation words of the permuted Q8_1 block: field k of word w pairs with activation word
+// 4w + k (src/pq2_0.h:155-166).  Fields are masked in place, so the four field sums come out scaled
+// by 64, 16, 4 and 1; they are four independent dp4a chains (the scheduler can overlap them), joined
+// as (s3 + 4 s2 + 16 s1 + 64 s0) >> 6, which is exact because the sum is a multiple of 64.  Callers
+// pass init64 = -64 * s so that the result is (sum code*a) - s.
 __device__ __forceinline__ int chunk_sumi_scaled(uint32_t w0, uint32_t w1, const int (&a)[8], int init64) {
-    int acc = init64;
-    acc = dp4a_us(w0 & 0xC0C0C0C0u, a[3], acc);
-    acc = dp4a_us(w1 & 0xC0C0C0C0u, a[7], acc);
-    acc >>= 2;
-    acc = dp4a_us(w0 & 0x30303030u, a[2], acc);
-    acc = dp4a_us(w1 & 0x30303030u, a[6], acc);
-    acc >>= 2;
-    acc = dp4a_us(w0 & 0x0C0C0C0Cu, a[1], acc);
-    acc = dp4a_us(w1 & 0x0C0C0C0Cu, a[5], acc);
-    acc >>= 2;
-    acc = dp4a_us(w0 & 0x03030303u, a[0], acc);
-    acc = dp4a_us(w1 & 0x03030303u, a[4], acc);
-    return acc;
+    int s3 = dp4a_us(w0 & 0xC0C0C0C0u, a[3], init64);
+    int s2 = dp4a_us(w0 & 0x30303030u, a[2], 0);
+    int s1 = dp4a_us(w0 & 0x0C0C0C0Cu, a[1], 0);
+    int s0 = dp4a_us(w0 & 0x03030303u, a[0], 0);
+    s3 = dp4a_us(w1 & 0xC0C0C0C0u, a[7], s3);
+    s2 = dp4a_us(w1 & 0x30303030u, a[6], s2);
+    s1 = dp4a_us(w1 & 0x0C0C0C0Cu, a[5], s1);
+    s0 = dp4a_us(w1 & 0x03030303u, a[4], s0);
+    return (s3 + (s2 << 2) + (s1 << 4) + (s0 << 6)) >> 6;
 }
 
 // ---- shared-memory barriers and bulk copies (sm_90+ PTX, every copy is local to its CTA) -------
@@ -132,6 +129,20 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity
         : "r"(smem_u32(bar)), "r"(parity), "r"(1u << 22)
         : "memory");
     if (!ok) atomicExch(&g_device_status, STATUS_MBARRIER_TIMEOUT);
+    return ok != 0;
+}
+// One non-blocking poll: has the phase with this parity completed?
+__device__ __forceinline__ bool mbar_test(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
     return ok != 0;
 }
 // 1-D bulk copy global -> shared of `bytes` (multiple of 16, both addresses 16-byte aligned),

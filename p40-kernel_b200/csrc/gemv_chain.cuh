@@ -1,0 +1,479 @@
+// gemv_chain.cuh -- a list of decode projections in ONE persistent launch.
+//
+// The per-matrix entry point (bonsai_p40_gemv, src/kernels/gemv_p40.cu:210-219 in the reference) pays,
+// for every matrix, a kernel start (barriers, activation vector, first-tile latency) and a tail (the
+// last tiles are multiplied after the last byte has landed); at batch 1 a projection streams for
+// 0.2 - 4 us, so start and tail cost as much as the stream.  Weights never depend on the previous
+// projection, only activations do.  Here one CTA per SM walks the whole list: a copy warp streams
+// the CTA's rows of op after op into one ring of shared-memory slots without ever stopping at an op
+// boundary, compute warps take (row quad x row segment) tasks exactly as gemv_stream_kernel does --
+// same lanes, same terms, same summation tree, so y is bit-identical to the per-matrix kernel -- and
+// a projection that reads an earlier projection's output waits on a grid-wide arrival counter
+// (bounded) while the ring keeps filling behind it.
+//
+// Warp roles (THREADS / 32 - 2 compute warps, 1 copy warp, 1 sequencer warp):
+//   sequencer : copies op records into a shared ring of 8, and for ops whose activations arrive as
+//               Q8_1 blocks stages them (one bulk copy) and re-lays them into one of two table
+//               buffers while the compute warps are still on the previous op;
+//   copy      : tile g of the CTA (whole rows of one op, <= slot bytes, one contiguous bulk copy)
+//               goes to slot g % nslot once every task of tile g - nslot has copied its blocks out;
+//   compute   : tasks are handed out in order across ops; entering an op a warp waits for its
+//               tables (Q8_1 ops), or -- ops that rotate and quantise an fp32 vector -- all compute
+//               warps meet, wait for the producers of that vector, and rotate it together.
+//
+// Barrier discipline.  Shared-memory barriers are reused, so a waiter identifies a phase by parity;
+// that is only sound when no waiter can fall two phases behind.  Every reused barrier here is waited
+// on by every one of its waiters in every phase, in order (gate, ready, xs, dep), or is guarded by a
+// monotonic counter (full[slot]: a task first sees `issued > g`, which the copy lane publishes after
+// arming the barrier for tile g, and the slot cannot be re-armed before that task has copied out).
+// Slot release is a plain counter because the number of tasks per tile changes from op to op.
+// Every wait is bounded; a time-out sets the status word and the warp leaves.
+#pragma once
+
+#include "activation.cuh"
+#include "common.cuh"
+#include "gemv.cuh"
+#include "gemv_stream.cuh"
+
+namespace b200 {
+
+#ifdef BONSAI_B200_TRACE
+// Development aid (not in the shipped build): time stamps of warp 0 at the op boundaries of the first 64 ops.
+__device__ long long g_chain_trace[64 * 160 * 4];
+#define CHAIN_STAMP(op_, k_) do { if (wid == 0 && lane == 0 && (op_) < 64 && blockIdx.x < 160) { \
+    long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); \
+    g_chain_trace[((op_) * 160 + blockIdx.x) * 4 + (k_)] = t_; } } while (0)
+__device__ long long g_tile_trace[2 * 512 * 4];
+#define TILE_STAMP(g_, k_) do { if ((blockIdx.x == 0 || blockIdx.x == 70) && (g_) < 512) { \
+    long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); \
+    g_tile_trace[((blockIdx.x ? 1 : 0) * 512 + (g_)) * 4 + (k_)] = t_; } } while (0)
+#else
+#define CHAIN_STAMP(op_, k_) do { } while (0)
+#define TILE_STAMP(g_, k_) do { } while (0)
+#endif
+
+enum : int { CHAIN_ROTATE = 1, CHAIN_DEPENDS = 2, CHAIN_SAME_INPUT = 4, CHAIN_SIGNAL = 8 };
+
+constexpr int CHAIN_MAX_SLOTS = 16;
+constexpr int CHAIN_OP_RING = 8;
+
+struct __align__(16) ChainOp {                 // 128 bytes, one per projection, device table
+    const uint8_t *W;
+    const void *x;                             // fp32 vector (CHAIN_ROTATE) or permuted Q8_1 blocks
+    const float *signs;
+    float *y;
+    int nb, n_out, rows_per_cta, tr;
+    int nseg, seg_blocks, tpt, flags;
+    uint32_t magic_tpt, magic_nseg;
+    int cta_shift;                             // CTA c takes the rows of CTA (c + shift) % grid
+    uint32_t arrivals_needed;                  // CHAIN_DEPENDS: signalling ops before this one
+    int buf;                                   // table buffer (0 / 1) this op reads
+    int ready_parity;                          // phase parity of ready[buf] (Q8_1 ops that fill a buffer)
+    int prev_user;                             // last op that read the previous contents of buf, or -1
+    int pad[9];
+};
+static_assert(sizeof(ChainOp) == 128, "op records are copied as 32 words");
+
+struct ChainGeom {
+    int nslot, slot_bytes;
+    uint32_t magic_nslot;
+    int nb_max;               // longest row, in blocks: sizes the tables
+    int stage_blocks;         // nb_max if any op takes Q8_1 blocks (staging area of the sequencer), else 0
+    int rot_blocks;           // 1024-blocks of rotation scratch (0 if no op rotates)
+    int partial_floats;       // per buffer: max rows_per_cta * nseg, multiple of 4
+    int quad_ints;            // per buffer: max rows_per_cta / 4, multiple of 4
+};
+
+// Shared-memory bytes before the ring (the host uses the same function).
+__host__ __device__ inline size_t chain_fixed_bytes(const ChainGeom &G) {
+    const size_t b = 384 + CHAIN_OP_RING * sizeof(ChainOp) + 2 * (size_t)G.nb_max * 176 + (size_t)G.stage_blocks * 144 +
+                     (size_t)G.rot_blocks * 4096 +
+                     2 * (size_t)G.partial_floats * 4 + 2 * (size_t)G.quad_ints * 4;
+    return (b + 127) & ~(size_t)127;
+}
+
+__device__ __forceinline__ bool spin_until_gt(volatile int *p, int v) {
+    uint32_t ns = 32;
+    for (uint32_t n = 0; n < (1u << 22); ++n) {
+        if (*p > v) return true;
+        __nanosleep(ns);
+        ns = min(ns * 2, 256u);
+    }
+    atomicExch(&g_device_status, STATUS_MBARRIER_TIMEOUT);
+    return false;
+}
+__device__ __forceinline__ bool spin_until_eq(volatile int *p, int v) {
+    uint32_t ns = 32;
+    for (uint32_t n = 0; n < (1u << 22); ++n) {
+        if (*p == v) return true;
+        __nanosleep(ns);
+        ns = min(ns * 2, 256u);
+    }
+    atomicExch(&g_device_status, STATUS_MBARRIER_TIMEOUT);
+    return false;
+}
+// Grid-wide arrival counter, polled by one lane: acquire at device scope, bounded.
+__device__ __forceinline__ bool grid_counter_wait(const unsigned int *counter, unsigned int target) {
+    uint32_t ns = 32;
+    for (uint32_t n = 0; n < (1u << 22); ++n) {
+        unsigned int v;
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
+        if (v >= target) return true;
+        __nanosleep(ns);
+        ns = min(ns * 2, 256u);
+    }
+    atomicExch(&g_device_status, STATUS_GRID_TIMEOUT);
+    return false;
+}
+
+template <int THREADS>
+__global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *__restrict__ ops, const int n_ops,
+                                                                const ChainGeom G, unsigned int *grid_counter) {
+    constexpr int C = THREADS / 32 - 2;         // compute warps
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem);      // [16] tile landed in slot
+    uint64_t *ready = full + CHAIN_MAX_SLOTS;                 // [2]  tables of a Q8_1 op are filled
+    uint64_t *gate = ready + 2;                               // [2]  every compute warp has finished op (index & 1)
+    uint64_t *xs = gate + 2;                                  // [1]  rotate: every warp has written its blocks
+    uint64_t *dep = xs + 1;                                   // [1]  rotate: the producers of x have arrived
+    uint64_t *stage_full = dep + 1;                           // [1]  Q8_1 staging copy landed
+    int *done_cnt = reinterpret_cast<int *>(smem + 192);      // [16] tasks of the slot's tile that have copied out
+    int *expect_cnt = done_cnt + CHAIN_MAX_SLOTS;             // [16] ... of how many
+    volatile int *ctrl = expect_cnt + CHAIN_MAX_SLOTS;        // [16] 0 issued, 1 ops_loaded, 2 next_task, 3 copy_op, 4-7 op_done
+    ChainOp *opring = reinterpret_cast<ChainOp *>(smem + 384);
+    uint8_t *p = smem + 384 + CHAIN_OP_RING * sizeof(ChainOp);
+    const size_t table_bytes = (size_t)G.nb_max * 176;
+    uint8_t *tables = p;
+    p += 2 * table_bytes;
+    uint32_t *stage = reinterpret_cast<uint32_t *>(p);
+    p += (size_t)G.stage_blocks * 144;
+    float4 *scratch = reinterpret_cast<float4 *>(p);
+    p += (size_t)G.rot_blocks * FWHT_N * 4;
+    float *partial_base = reinterpret_cast<float *>(p);
+    p += 2 * (size_t)G.partial_floats * 4;
+    int *quad_base = reinterpret_cast<int *>(p);
+    uint8_t *ring = smem + chain_fixed_bytes(G);
+
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int ncta = (int)gridDim.x;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < CHAIN_MAX_SLOTS; ++s) mbar_init(&full[s], 1);
+        mbar_init(&ready[0], 1);
+        mbar_init(&ready[1], 1);
+        mbar_init(&gate[0], C);
+        mbar_init(&gate[1], C);
+        mbar_init(xs, C);
+        mbar_init(dep, 1);
+        mbar_init(stage_full, 1);
+        mbar_fence_init();
+    }
+    for (int i = threadIdx.x; i < 3 * CHAIN_MAX_SLOTS; i += THREADS) done_cnt[i] = 0;     // done, expect, ctrl
+    for (int i = threadIdx.x; i < 2 * G.quad_ints; i += THREADS) quad_base[i] = 0;
+    __syncthreads();
+
+    // rows of op R that this CTA owns
+    auto cta_rows = [&](const ChainOp &R, int &row0, int &rows_here) {
+        int c = (int)blockIdx.x + R.cta_shift;
+        if (c >= ncta) c -= ncta;
+        row0 = c * R.rows_per_cta;
+        rows_here = max(0, min(R.rows_per_cta, R.n_out - row0));
+    };
+
+    if (wid < C) {
+        // ================================ compute warps ================================
+        const int rr = lane & 3, bl = lane >> 2;
+        int op = -1, flags = 0;
+        int issued_seen = 0;
+        uint32_t xs_phase = 0, dep_phase = 0;     // every compute warp takes part in every meeting, so it counts them itself
+        int task_base = 0, ntasks = 0, g_base = 0, ntiles = 0, row0 = 0, rows_here = 0;
+        for (;;) {
+            int task = 0;
+            if (lane == 0) task = atomicAdd(const_cast<int *>(&ctrl[2]), 1);
+            task = __shfl_sync(0xffffffffu, task, 0);
+            bool alive = true;
+            while (task >= task_base + ntasks) {
+                // ---- leave op `op`
+                if (op >= 0) {
+                    if (flags & CHAIN_SIGNAL) __threadfence();          // this warp's y rows, before its arrival below
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (flags & CHAIN_SIGNAL) {
+                            const int old = atomicAdd(const_cast<int *>(&ctrl[4 + (op & 3)]), 1);
+                            if (old == C - 1) {                         // the CTA's rows of every op so far are written
+                                ctrl[4 + (op & 3)] = 0;
+                                __threadfence();
+                                atomicAdd(grid_counter, 1u);
+                            }
+                        }
+                        mbar_arrive(&gate[op & 1]);
+                    }
+                }
+                task_base += ntasks;
+                g_base += ntiles;
+                ++op;
+                if (op >= n_ops) { alive = false; break; }
+                // ---- enter op `op`
+                CHAIN_STAMP(op, 0);
+                if (!spin_until_gt(&ctrl[1], op)) { alive = false; break; }
+                if (op >= 2 && !mbar_wait_bounded(&gate[op & 1], ((op - 2) >> 1) & 1)) { alive = false; break; }
+                const ChainOp &R = opring[op & (CHAIN_OP_RING - 1)];
+                flags = R.flags;
+                cta_rows(R, row0, rows_here);
+                ntiles = (rows_here + R.tr - 1) / R.tr;
+                ntasks = ntiles * R.tpt;
+                if (!(flags & CHAIN_SAME_INPUT)) {
+                    if (flags & CHAIN_ROTATE) {
+                        // every compute warp has left op - 1: both table buffers' readers are gone
+                        if (op >= 1 && !mbar_wait_bounded(&gate[(op - 1) & 1], ((op - 1) >> 1) & 1)) { alive = false; break; }
+                        if (flags & CHAIN_DEPENDS) {
+                            if (wid == 0) {
+                                bool ok = true;
+                                if (lane == 0) ok = grid_counter_wait(grid_counter, R.arrivals_needed * (unsigned)ncta);
+                                __syncwarp();
+                                if (lane == 0 && ok) mbar_arrive(dep);
+                            }
+                            if (!mbar_wait_bounded(dep, dep_phase & 1u)) { alive = false; break; }
+                            ++dep_phase;
+                        }
+                        CHAIN_STAMP(op, 1);
+                        uint32_t *act_q = reinterpret_cast<uint32_t *>(tables + (size_t)R.buf * table_bytes);
+                        float *act_s = reinterpret_cast<float *>(act_q + (size_t)G.nb_max * STREAM_ACT_WORDS);
+                        int *act_i = reinterpret_cast<int *>(act_s + (size_t)G.nb_max * 4);
+                        const float *x = static_cast<const float *>(R.x);
+                        const float *signs = R.signs;
+                        const int nfb = R.nb >> 3;
+                        // One warp per 128-element slice, G.rot_blocks 1024-blocks per round trip through
+                        // the scratch area: front butterflies, meet, back butterflies + quantiser, meet.
+                        bool ok = true;
+                        for (int fb0 = 0; fb0 < nfb && ok; fb0 += G.rot_blocks) {
+                            const int units = min(G.rot_blocks, nfb - fb0) * 8;
+                            // all of this warp's loads first (they come from L2: written by other SMs
+                            // during this launch), then the butterflies
+                            constexpr int UPW = (7 * 8 + C - 1) / C;           // units per warp and round trip
+                            float4 f[UPW];
+#pragma unroll
+                            for (int k = 0; k < UPW; ++k) {
+                                const int u = wid + k * C;
+                                if (u < units)
+                                    f[k] = __ldcg(reinterpret_cast<const float4 *>(x + (size_t)fb0 * FWHT_N + (size_t)u * 128 + 4 * lane));
+                            }
+#pragma unroll
+                            for (int k = 0; k < UPW; ++k) {
+                                const int u = wid + k * C;
+                                if (u < units) {
+                                    float v[4] = {f[k].x, f[k].y, f[k].z, f[k].w};
+                                    if (signs) {
+                                        const float4 sg = __ldg(reinterpret_cast<const float4 *>(signs + (size_t)fb0 * FWHT_N + (size_t)u * 128 + 4 * lane));
+                                        v[0] = __fmul_rn(v[0], sg.x); v[1] = __fmul_rn(v[1], sg.y);
+                                        v[2] = __fmul_rn(v[2], sg.z); v[3] = __fmul_rn(v[3], sg.w);
+                                    }
+                                    fwht_slice_front(v, lane);
+                                    scratch[u * 32 + lane] = make_float4(v[0], v[1], v[2], v[3]);
+                                }
+                            }
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(xs);
+                            ok = mbar_wait_bounded(xs, xs_phase & 1u);
+                            ++xs_phase;
+                            if (!ok) break;
+                            for (int u = wid; u < units; u += C) {
+                                float v[4];
+                                fwht_slice_back(scratch + (u >> 3) * 256, u & 7, lane, v);
+                                uint32_t word, header;
+                                quantise_chunk_8lanes(v, lane, word, header);
+                                const int chunk = fb0 * 32 + u * 4 + (lane >> 3);
+                                act_q[(chunk >> 2) * STREAM_ACT_WORDS + (chunk & 3) * 8 + (lane & 7)] = word;
+                                if ((lane & 7) == 0) {
+                                    act_s[chunk] = f16_bits_to_f32(header & 0xFFFFu);
+                                    act_i[chunk] = -64 * (int)(short)(header >> 16);
+                                }
+                            }
+                            CHAIN_STAMP(op, 3);
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(xs);
+                            ok = mbar_wait_bounded(xs, xs_phase & 1u);
+                            ++xs_phase;
+                        }
+                        if (!ok) { alive = false; break; }
+                    } else {
+                        if (!mbar_wait_bounded(&ready[R.buf], (uint32_t)R.ready_parity)) { alive = false; break; }
+                    }
+                }
+                CHAIN_STAMP(op, 2);
+            }
+            if (!alive) break;
+
+            // ---- one task of op `op`: same lanes, terms and sums as gemv_stream_kernel
+            const ChainOp &R = opring[op & (CHAIN_OP_RING - 1)];
+            const int nb = R.nb, nseg = R.nseg;
+            const int row_bytes = nb * W_BLOCK_BYTES;
+            const int local_task = task - task_base;
+            const int t = (int)fast_div((uint32_t)local_task, R.magic_tpt);
+            const int local = local_task - t * R.tpt;
+            const int quad = (int)fast_div((uint32_t)local, R.magic_nseg);
+            const int j = local - quad * nseg;
+            const int r_quad = t * R.tr + quad * 4;
+            if (r_quad >= rows_here) continue;                      // padding quad of a ragged last tile
+            const int g = g_base + t;
+            const int lap = (int)fast_div((uint32_t)g, G.magic_nslot);
+            const int slot = g - lap * G.nslot;
+            if (g >= issued_seen) {                                 // tile g must be armed: then the parity below is unambiguous
+                if (!spin_until_gt(&ctrl[0], g)) break;
+                issued_seen = ctrl[0];
+            }
+            if (lane == 0 && local == 0) TILE_STAMP(g, 2);
+            if (!mbar_wait_bounded(&full[slot], (uint32_t)(lap & 1))) break;
+            if (lane == 0 && local == 0) TILE_STAMP(g, 3);
+            const int b0 = j * R.seg_blocks;
+            const int blocks = min(R.seg_blocks, nb - b0);
+            const uint8_t *rowp = ring + (size_t)slot * G.slot_bytes + (size_t)(quad * 4 + rr) * row_bytes +
+                                  (size_t)b0 * W_BLOCK_BYTES;
+            const uint32_t *act_q = reinterpret_cast<const uint32_t *>(tables + (size_t)R.buf * table_bytes);
+            const float *act_s = reinterpret_cast<const float *>(act_q + (size_t)G.nb_max * STREAM_ACT_WORDS);
+            const int *act_i = reinterpret_cast<const int *>(act_s + (size_t)G.nb_max * 4);
+            float acc = stream_task(rowp, bl, b0, blocks, act_q, act_s, act_i, [&]() {
+                __syncwarp();
+                if (lane == 0) {
+                    __threadfence_block();                          // the loads above, before the slot is handed back
+                    atomicAdd(&done_cnt[slot], 1);
+                }
+            });
+            acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 4));
+            acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 8));
+            acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 16));
+            const int r = r_quad + rr;
+            float *y = R.y;
+            if (nseg == 1) {
+                if (bl == 0 && r < rows_here) y[row0 + r] = acc;
+            } else {
+                float *partial = partial_base + (size_t)(op & 1) * G.partial_floats;
+                int *quad_count = quad_base + (size_t)(op & 1) * G.quad_ints;
+                if (bl == 0) partial[r * nseg + j] = acc;
+                __syncwarp();
+                int last = 0;
+                if (lane == 0) {
+                    __threadfence_block();
+                    last = atomicAdd(&quad_count[r_quad >> 2], 1) == nseg - 1;
+                    if (last) quad_count[r_quad >> 2] = 0;           // left clean for the op after next
+                }
+                last = __shfl_sync(0xffffffffu, last, 0);
+                if (last) {
+                    __threadfence_block();
+                    if (bl == 0 && r < rows_here) {
+                        float total = partial[r * nseg];
+                        for (int sgm = 1; sgm < nseg; ++sgm) total = __fadd_rn(total, partial[r * nseg + sgm]);
+                        y[row0 + r] = total;
+                    }
+                }
+            }
+        }
+    } else if (wid == C) {
+        // ================================ copy warp (one lane) ================================
+        if (lane != 0) return;
+        const uint64_t pol = policy_evict_first();
+        int g = 0, slot = 0;
+        for (int op = 0; op < n_ops; ++op) {
+            if (!spin_until_gt(&ctrl[1], op)) return;
+            const ChainOp &R = opring[op & (CHAIN_OP_RING - 1)];
+            int row0, rows_here;
+            cta_rows(R, row0, rows_here);
+            const int tr = R.tr, nseg = R.nseg;
+            const size_t row_bytes = (size_t)R.nb * W_BLOCK_BYTES;
+            const uint8_t *src = R.W + (size_t)row0 * row_bytes;
+            const int ntiles = (rows_here + tr - 1) / tr;
+            for (int t = 0; t < ntiles; ++t) {
+                if (g >= G.nslot && !spin_until_eq(&done_cnt[slot], expect_cnt[slot])) return;
+                TILE_STAMP(g, 0);
+                const int r_cnt = min(tr, rows_here - t * tr);
+                done_cnt[slot] = 0;
+                expect_cnt[slot] = ((r_cnt + 3) >> 2) * nseg;
+                __threadfence_block();
+                // the slot was read through ordinary loads: order them before the asynchronous overwrite
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                uint8_t *dst = ring + (size_t)slot * G.slot_bytes;
+                const uint32_t bytes = (uint32_t)(r_cnt * row_bytes);
+                const uint32_t bulk = bytes & ~15u;
+                const uint8_t *s = src + (size_t)t * tr * row_bytes;
+                for (uint32_t o = bulk; o < bytes; o += 4) *reinterpret_cast<uint32_t *>(dst + o) = ldg_nc_u32(s + o);
+                mbar_expect_tx(&full[slot], bulk);
+                if (bulk) bulk_g2s(dst, s, bulk, &full[slot], pol);
+                __threadfence_block();
+                ctrl[0] = g + 1;                                    // tile g is armed
+                TILE_STAMP(g, 1);
+                ++g;
+                if (++slot == G.nslot) slot = 0;
+            }
+            ctrl[3] = op + 1;                                       // this op's record is no longer read here
+        }
+    } else {
+        // ================================ sequencer warp ================================
+        int gate_seen = 0;                  // every compute warp has left ops [0, gate_seen)
+        uint32_t stage_parity = 0;
+        const uint64_t pol = policy_evict_first();
+        auto see_gates = [&](int upto) {    // waits, in order, until gate_seen > upto
+            while (gate_seen <= upto) {
+                if (!mbar_wait_bounded(&gate[gate_seen & 1], (uint32_t)((gate_seen >> 1) & 1))) return false;
+                ++gate_seen;
+            }
+            return true;
+        };
+        int rec_next = 0;                   // records [0, rec_next) are in the shared ring
+        // Record r goes where record r - 8 was: every compute warp and the copy lane must be past that
+        // one.  Loads whatever is allowed without blocking, so that the copy lane can run ahead of the
+        // table preparation below; blocks only when `must` is not there yet.
+        auto load_records = [&](int must) {
+            for (;;) {
+                while (gate_seen < n_ops && mbar_test(&gate[gate_seen & 1], (uint32_t)((gate_seen >> 1) & 1))) ++gate_seen;
+                while (rec_next < n_ops &&
+                       (rec_next < CHAIN_OP_RING ||
+                        (gate_seen > rec_next - CHAIN_OP_RING && ctrl[3] > rec_next - CHAIN_OP_RING))) {
+                    reinterpret_cast<uint32_t *>(opring + (rec_next & (CHAIN_OP_RING - 1)))[lane] =
+                        __ldg(reinterpret_cast<const uint32_t *>(ops + rec_next) + lane);
+                    __syncwarp();
+                    if (lane == 0) {
+                        __threadfence_block();
+                        ctrl[1] = rec_next + 1;
+                    }
+                    __syncwarp();
+                    ++rec_next;
+                }
+                if (rec_next > must) return true;
+                if (!see_gates(must - CHAIN_OP_RING)) return false;
+                if (!spin_until_gt(&ctrl[3], must - CHAIN_OP_RING)) return false;
+            }
+        };
+        for (int op = 0; op < n_ops; ++op) {
+            if (!load_records(op)) return;
+            const ChainOp &R = opring[op & (CHAIN_OP_RING - 1)];
+            if (R.flags & (CHAIN_ROTATE | CHAIN_SAME_INPUT)) continue;
+            // Q8_1 blocks: stage the raw bytes with one bulk copy (the staging area is this warp's own, so
+            // the copy flies while the table buffer is still being read), then re-lay them into the tables
+            const int nchunks = R.nb * 4;
+            if (lane == 0) {
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                mbar_expect_tx(stage_full, (uint32_t)nchunks * A_BLOCK_BYTES);
+                bulk_g2s(stage, R.x, (uint32_t)nchunks * A_BLOCK_BYTES, stage_full, pol);
+            }
+            if (!see_gates(R.prev_user)) return;
+            if (!mbar_wait_bounded(stage_full, stage_parity)) return;
+            stage_parity ^= 1u;
+            uint32_t *act_q = reinterpret_cast<uint32_t *>(tables + (size_t)R.buf * table_bytes);
+            float *act_s = reinterpret_cast<float *>(act_q + (size_t)G.nb_max * STREAM_ACT_WORDS);
+            int *act_i = reinterpret_cast<int *>(act_s + (size_t)G.nb_max * 4);
+            for (int chunk = lane; chunk < nchunks; chunk += 32) {
+                const uint32_t *s = stage + 9 * chunk;
+                uint32_t *q = act_q + (chunk >> 2) * STREAM_ACT_WORDS + (chunk & 3) * 8;
+                const uint32_t h = s[0];
+                *reinterpret_cast<uint4 *>(q) = make_uint4(s[1], s[2], s[3], s[4]);
+                *reinterpret_cast<uint4 *>(q + 4) = make_uint4(s[5], s[6], s[7], s[8]);
+                act_s[chunk] = f16_bits_to_f32(h & 0xFFFFu);
+                act_i[chunk] = -64 * (int)(short)(h >> 16);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&ready[R.buf]);
+        }
+    }
+}
+
+}  // namespace b200

@@ -41,6 +41,111 @@ struct StreamParams {
     uint32_t magic_tpt, magic_nseg, magic_nslot;   // ceil(2^32 / d), 0 for d == 1
 };
 
+// The multiply of one task when every block lane owns exactly STEPS blocks of the segment (segment
+// length a multiple of 8 -- always the case when n_in is a multiple of 1024): no per-lane bounds, and
+// every shared-memory address is the lane's base plus a compile-time offset (block b = bl + 8k sits
+// 272 k bytes = 68 k words after block bl; its activation record 288 k words after that of bl).
+// `release` runs between the copy into registers and the multiply: it hands the ring slot back.
+// Same terms in the same order as the general loop below, so the bits do not depend on which runs.
+template <int STEPS, typename Release>
+__device__ __forceinline__ float stream_task_full(const uint8_t *rowp, int bl, int gb0, const uint32_t *act_q,
+                                                  const float *act_s, const int *act_i, Release release) {
+    const uint32_t *xw = reinterpret_cast<const uint32_t *>(rowp) + ((W_BLOCK_BYTES * bl + 2) >> 2);
+    const uint8_t *dp = rowp + W_BLOCK_BYTES * bl;
+    uint32_t x[STEPS][9];
+    float dw[STEPS];
+#pragma unroll
+    for (int k = 0; k < STEPS; ++k) {
+#pragma unroll
+        for (int i = 0; i < 9; ++i) x[k][i] = xw[68 * k + i];
+        dw[k] = f16_bits_to_f32(*reinterpret_cast<const unsigned short *>(dp + 272 * k));
+    }
+    release();
+    const uint32_t sh = (gb0 & 1) ? 0u : 16u;           // codes start two bytes into a word for even blocks
+    const uint32_t *aq = act_q + gb0 * STREAM_ACT_WORDS;
+    const float *as = act_s + 4 * gb0;
+    const int *ai = act_i + 4 * gb0;
+    float acc = 0.0f;
+#pragma unroll
+    for (int k = 0; k < STEPS; ++k) {
+        const float4 sc = *reinterpret_cast<const float4 *>(as + 32 * k);
+        const int4 in = *reinterpret_cast<const int4 *>(ai + 32 * k);
+        const float scale[4] = {sc.x, sc.y, sc.z, sc.w};
+        const int inits[4] = {in.x, in.y, in.z, in.w};
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const int4 lo = *reinterpret_cast<const int4 *>(aq + 8 * STREAM_ACT_WORDS * k + c * 8);
+            const int4 hi = *reinterpret_cast<const int4 *>(aq + 8 * STREAM_ACT_WORDS * k + c * 8 + 4);
+            const int a[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+            const uint32_t c0 = __funnelshift_r(x[k][2 * c], x[k][2 * c + 1], sh);
+            const uint32_t c1 = __funnelshift_r(x[k][2 * c + 1], x[k][2 * c + 2], sh);
+            const int sumi = chunk_sumi_scaled(c0, c1, a, inits[c]);
+            acc = __fadd_rn(acc, __fmul_rn(__fmul_rn(dw[k], scale[c]), (float)sumi));
+        }
+    }
+    return acc;
+}
+
+// The general task: a last segment of any length (a lane past the end re-reads the last block and
+// skips its terms).
+template <typename Release>
+__device__ __forceinline__ float stream_task_ragged(const uint8_t *rowp, int bl, int b0, int blocks, const uint32_t *act_q,
+                                                    const float *act_s, const int *act_i, Release release) {
+    uint32_t x[STREAM_STEPS][9];
+    float dw[STREAM_STEPS];
+#pragma unroll
+    for (int k = 0; k < STREAM_STEPS; ++k) {
+        const int b = min(bl + 8 * k, blocks - 1);
+        const uint32_t *xw = reinterpret_cast<const uint32_t *>(rowp) + ((W_BLOCK_BYTES * b + 2) >> 2);
+#pragma unroll
+        for (int i = 0; i < 9; ++i) x[k][i] = xw[i];
+        dw[k] = f16_bits_to_f32(*reinterpret_cast<const unsigned short *>(rowp + W_BLOCK_BYTES * b));
+    }
+    release();
+    float acc = 0.0f;
+#pragma unroll
+    for (int k = 0; k < STREAM_STEPS; ++k) {
+        const int b = bl + 8 * k;
+        if (b < blocks) {
+            const int gb = b0 + b;
+            const uint32_t sh = (gb & 1) ? 0u : 16u;
+            const float4 sc = *reinterpret_cast<const float4 *>(act_s + 4 * gb);
+            const int4 in = *reinterpret_cast<const int4 *>(act_i + 4 * gb);
+            const float scale[4] = {sc.x, sc.y, sc.z, sc.w};
+            const int inits[4] = {in.x, in.y, in.z, in.w};
+            const uint32_t *aq = act_q + gb * STREAM_ACT_WORDS;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int4 lo = *reinterpret_cast<const int4 *>(aq + c * 8);
+                const int4 hi = *reinterpret_cast<const int4 *>(aq + c * 8 + 4);
+                const int a[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+                const uint32_t c0 = __funnelshift_r(x[k][2 * c], x[k][2 * c + 1], sh);
+                const uint32_t c1 = __funnelshift_r(x[k][2 * c + 1], x[k][2 * c + 2], sh);
+                const int sumi = chunk_sumi_scaled(c0, c1, a, inits[c]);
+                acc = __fadd_rn(acc, __fmul_rn(__fmul_rn(dw[k], scale[c]), (float)sumi));
+            }
+        }
+    }
+    return acc;
+}
+
+// One task: dispatches on the segment length (warp-uniform).
+template <typename Release>
+__device__ __forceinline__ float stream_task(const uint8_t *rowp, int bl, int b0, int blocks, const uint32_t *act_q,
+                                             const float *act_s, const int *act_i, Release release) {
+    if ((blocks & 7) == 0) {
+        switch (blocks >> 3) {
+            case 5: return stream_task_full<5>(rowp, bl, b0 + bl, act_q, act_s, act_i, release);
+            case 4: return stream_task_full<4>(rowp, bl, b0 + bl, act_q, act_s, act_i, release);
+            case 3: return stream_task_full<3>(rowp, bl, b0 + bl, act_q, act_s, act_i, release);
+            case 2: return stream_task_full<2>(rowp, bl, b0 + bl, act_q, act_s, act_i, release);
+            case 1: return stream_task_full<1>(rowp, bl, b0 + bl, act_q, act_s, act_i, release);
+            default: break;
+        }
+    }
+    return stream_task_ragged(rowp, bl, b0, blocks, act_q, act_s, act_i, release);
+}
+
 // Shared memory: [full[256] | done[256]] [act int8: nb * 36 words] [act scale: nb * 4 floats]
 // [act -64*sum: nb * 4 ints] [partials: rows_per_cta * nseg floats] [quad counters: rows_per_cta / 4]
 // [task counter] [ring: nslot * (tr * 34 * nb + 16)].
@@ -206,50 +311,17 @@ __global__ void __launch_bounds__(512, 1) gemv_stream_kernel(const uint8_t *__re
             const uint8_t *rowp = ring + (size_t)slot * slot_bytes + (size_t)(quad * 4 + rr) * row_bytes +
                                   (size_t)b0 * W_BLOCK_BYTES;
 
-            // Phase A: pull this lane's blocks (every 8th of the segment, at most STREAM_STEPS of them)
-            // into registers and hand the slot back at once -- the ring then holds bytes in flight,
-            // not bytes being multiplied.  32 code bytes start at byte 34*b + 2 of the row: two bytes
-            // into a word for even b, word-aligned for odd b; nine words cover them either way and a
-            // funnel shift by 16 or 0 aligns them.
-            uint32_t x[STREAM_STEPS][9];
-            float dw[STREAM_STEPS];
-#pragma unroll
-            for (int k = 0; k < STREAM_STEPS; ++k) {
-                const int b = min(bl + 8 * k, blocks - 1);      // a lane past the end re-reads the last block
-                // rowp is word-aligned: rows start on a word (nb even) and so do segments (seg_blocks even)
-                const uint32_t *xw = reinterpret_cast<const uint32_t *>(rowp) + ((W_BLOCK_BYTES * b + 2) >> 2);
-#pragma unroll
-                for (int i = 0; i < 9; ++i) x[k][i] = xw[i];
-                dw[k] = f16_bits_to_f32(*reinterpret_cast<const unsigned short *>(rowp + W_BLOCK_BYTES * b));
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&done[t]);       // release: every lane's loads above are complete
-
-            // Phase B: multiply from registers against the broadcast activation words.
-            float acc = 0.0f;
-#pragma unroll
-            for (int k = 0; k < STREAM_STEPS; ++k) {
-                const int b = bl + 8 * k;
-                if (b < blocks) {
-                    const int gb = b0 + b;                                      // block index in the row
-                    const uint32_t sh = (gb & 1) ? 0u : 16u;
-                    const float4 sc = *reinterpret_cast<const float4 *>(act_s + 4 * gb);
-                    const int4 in = *reinterpret_cast<const int4 *>(act_i + 4 * gb);
-                    const float scale[4] = {sc.x, sc.y, sc.z, sc.w};
-                    const int inits[4] = {in.x, in.y, in.z, in.w};
-                    const uint32_t *aq = act_q + gb * STREAM_ACT_WORDS;
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        const int4 lo = *reinterpret_cast<const int4 *>(aq + c * 8);
-                        const int4 hi = *reinterpret_cast<const int4 *>(aq + c * 8 + 4);
-                        const int a[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-                        const uint32_t c0 = __funnelshift_r(x[k][2 * c], x[k][2 * c + 1], sh);
-                        const uint32_t c1 = __funnelshift_r(x[k][2 * c + 1], x[k][2 * c + 2], sh);
-                        const int sumi = chunk_sumi_scaled(c0, c1, a, inits[c]);
-                        acc = __fadd_rn(acc, __fmul_rn(__fmul_rn(dw[k], scale[c]), (float)sumi));
-                    }
-                }
-            }
+            // Phase A: the lane pulls its blocks (every 8th of the segment, at most STREAM_STEPS of them)
+            // into registers and the warp hands the slot back at once -- the ring then holds bytes in
+            // flight, not bytes being multiplied.  32 code bytes start at byte 34*b + 2 of the row: two
+            // bytes into a word for even b, word-aligned for odd b; nine words cover them either way and
+            // a funnel shift by 16 or 0 aligns them.  Phase B multiplies from registers against the
+            // broadcast activation words.  (rowp is word-aligned: rows start on a word since nb is even,
+            // and so do segments since seg_blocks is even.)
+            float acc = stream_task(rowp, bl, b0, blocks, act_q, act_s, act_i, [&]() {
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&done[t]);   // release: every lane's loads above are complete
+            });
             acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 4));
             acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 8));
             acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 16));

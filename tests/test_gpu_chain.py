@@ -1,0 +1,227 @@
+"""GPU parity of the one-launch list of projections (bonsai_b200_chain_*): every op's output must be
+the SAME BITS as the per-matrix entry points give (bonsai_p40_gemv after bonsai_b200_fwht_quant), which
+in turn are held to the CPU checker; dependent ops are also checked end to end against the checker."""
+import numpy as np
+import pytest
+
+from bonsai_b200 import synth
+
+pytestmark = pytest.mark.gpu
+
+REL_TOL = 1e-5
+
+
+def bits(a):
+    return np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
+
+
+def dev(a):
+    import torch
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def host(t):
+    return t.detach().cpu().numpy()
+
+
+@pytest.fixture(params=[512, 768])
+def threads(gpu, request):
+    assert gpu.set_option("chain_threads", request.param) == 0
+    yield request.param
+    gpu.set_option("chain_threads", 512)
+
+
+SHAPES = [(5, 5120), (203, 5120), (100, 17408), (37, 1024), (6000, 5120), (2500, 17408), (1500, 6144), (700, 8192),
+          (130, 2304), (5120, 5120), (1024, 5120), (4, 256)]
+
+
+def test_independent_q8_ops_equal_per_matrix_calls(gpu, port, threads):
+    import torch
+    ops, wants = [], []
+    for i, (n_out, n_in) in enumerate(SHAPES):
+        W = dev(synth.pq2_0_weights(n_out, n_in, seed=100 + i))
+        xq_h = port.quantize_q8_1(synth.activations(n_in, seed=i), True)
+        xq = dev(xq_h)
+        y_ref = torch.zeros(n_out, device="cuda")
+        assert gpu.gemv(W, xq, y_ref, n_out, n_in) == 0
+        wants.append(host(y_ref))
+        y = torch.full((n_out,), -777.0, device="cuda")
+        ops.append((W, xq, None, y, n_out, n_in, 0))
+    chain = gpu.Chain(ops)
+    info = chain.info()
+    assert info["threads"] == threads and info["nslot"] >= 3
+    for _ in range(2):                      # twice: the arrival counter and every barrier start over
+        for op in ops:
+            op[3].fill_(-777.0)
+        assert chain.run() == 0
+        torch.cuda.synchronize()
+        for op, want in zip(ops, wants):
+            assert np.array_equal(bits(host(op[3])), bits(want)), (op[4], op[5])
+    chain.close()
+    assert gpu.device_status() == 0
+
+
+def test_rotate_ops_and_shared_inputs(gpu, port, threads):
+    """fp32 inputs rotated and quantised inside the launch; k/v-style ops reuse the previous op's vector."""
+    import torch
+    n_in = 5120
+    x = synth.activations(n_in, seed=3)
+    sg = synth.signs(n_in, seed=4)
+    xd, sd = dev(x), dev(sg)
+    xq_want = port.quantize_q8_1(port.fwht_blocks(x, sg), True)
+    x2 = synth.activations(17408, seed=5)
+    x2d = dev(x2)
+    xq2_want = port.quantize_q8_1(port.fwht_blocks(x2, None), True)
+    ops, wants = [], []
+    for i, n_out in enumerate([1000, 1024, 36, 7]):
+        Wh = synth.pq2_0_weights(n_out, n_in, seed=200 + i)
+        y = torch.zeros(n_out, device="cuda")
+        ops.append((dev(Wh), xd, sd, y, n_out, n_in, gpu.OP_ROTATE | (gpu.OP_SAME_INPUT if i else 0)))
+        wants.append(port.gemv(Wh, xq_want, n_out, n_in, threads=4))
+    for i, n_out in enumerate([300, 5]):
+        Wh = synth.pq2_0_weights(n_out, 17408, seed=300 + i)
+        y = torch.zeros(n_out, device="cuda")
+        ops.append((dev(Wh), x2d, None, y, n_out, 17408, gpu.OP_ROTATE | (gpu.OP_SAME_INPUT if i else 0)))
+        wants.append(port.gemv(Wh, xq2_want, n_out, 17408, threads=4))
+    chain = gpu.Chain(ops)
+    assert chain.run() == 0
+    torch.cuda.synchronize()
+    scratch = torch.zeros(17408 // 32 * 36, dtype=torch.uint8, device="cuda")
+    for op, want in zip(ops, wants):
+        W, x_, s_, y, n_out, n_in_, _ = op
+        got = host(y)
+        scale = float(np.abs(want).max()) or 1.0
+        assert float(np.abs(got.astype(np.float64) - want).max()) <= REL_TOL * scale
+        y2 = torch.zeros(n_out, device="cuda")
+        assert gpu.linear(W, x_, s_, y2, scratch, n_out, n_in_) == 0
+        assert np.array_equal(bits(got), bits(host(y2)))
+    chain.close()
+    assert gpu.device_status() == 0
+
+
+def test_dependent_ops_flow_through_the_launch(gpu, port, threads):
+    """y of one op is the x of the next (which waits for every row of it), five ops deep, twice."""
+    import torch
+    widths = [5120, 6144, 1024, 17408, 5120, 2048]       # op i: widths[i] -> widths[i + 1]
+    x0 = synth.activations(widths[0], seed=11)
+    bufs = [dev(x0)] + [torch.zeros(w, device="cuda") for w in widths[1:]]
+    Ws = [synth.pq2_0_weights(widths[i + 1], widths[i], seed=400 + i) for i in range(5)]
+    # the second consumer of bufs[1] shares its input with op 1
+    W_side = synth.pq2_0_weights(333, widths[1], seed=499)
+    y_side = torch.zeros(333, device="cuda")
+    ops = []
+    for i in range(5):
+        ops.append((dev(Ws[i]), bufs[i], None, bufs[i + 1], widths[i + 1], widths[i],
+                    gpu.OP_ROTATE | (gpu.OP_DEPENDS if i else 0)))
+        if i == 1:
+            ops.append((dev(W_side), bufs[1], None, y_side, 333, widths[1], gpu.OP_ROTATE | gpu.OP_SAME_INPUT))
+    chain = gpu.Chain(ops)
+    # the same flow through the per-matrix entry points
+    ref = [dev(x0)] + [torch.zeros(w, device="cuda") for w in widths[1:]]
+    scratch = torch.zeros(17408 // 32 * 36, dtype=torch.uint8, device="cuda")
+    for i in range(5):
+        assert gpu.linear(dev(Ws[i]), ref[i], None, ref[i + 1], scratch, widths[i + 1], widths[i]) == 0
+    side_ref = torch.zeros(333, device="cuda")
+    assert gpu.linear(dev(W_side), ref[1], None, side_ref, scratch, 333, widths[1]) == 0
+    for _ in range(2):
+        for b in bufs[1:]:
+            b.zero_()
+        y_side.zero_()
+        assert chain.run() == 0
+        torch.cuda.synchronize()
+        for i in range(1, 6):
+            assert np.array_equal(bits(host(bufs[i])), bits(host(ref[i]))), i
+        assert np.array_equal(bits(host(y_side)), bits(host(side_ref)))
+    # and the first hop against the checker
+    want = port.gemv(Ws[0], port.quantize_q8_1(port.fwht_blocks(x0, None), True), widths[1], widths[0], threads=4)
+    got = host(bufs[1])
+    assert float(np.abs(got.astype(np.float64) - want).max()) <= REL_TOL * float(np.abs(want).max())
+    chain.close()
+    assert gpu.device_status() == 0
+
+
+def test_long_mixed_list_in_a_graph(gpu, port):
+    """60 ops (more than the record ring and many laps of the tile ring), replayed from a CUDA graph."""
+    import torch
+    rng = np.random.default_rng(7)
+    shapes = [(int(rng.integers(1, 900)), int(rng.choice([256, 1024, 2048, 5120, 6144]))) for _ in range(60)]
+    ops, wants = [], []
+    scratch = torch.zeros(6144 // 32 * 36, dtype=torch.uint8, device="cuda")
+    for i, (n_out, n_in) in enumerate(shapes):
+        W = dev(synth.pq2_0_weights(n_out, n_in, seed=500 + i))
+        y = torch.zeros(n_out, device="cuda")
+        y_ref = torch.zeros(n_out, device="cuda")
+        if i % 3 == 0 and n_in % 1024 == 0:
+            x = dev(synth.activations(n_in, seed=i))
+            assert gpu.linear(W, x, None, y_ref, scratch, n_out, n_in) == 0
+            ops.append((W, x, None, y, n_out, n_in, gpu.OP_ROTATE))
+        else:
+            xq = dev(port.quantize_q8_1(synth.activations(n_in, seed=i), True))
+            assert gpu.gemv(W, xq, y_ref, n_out, n_in) == 0
+            ops.append((W, xq, None, y, n_out, n_in, 0))
+        wants.append(host(y_ref))
+    chain = gpu.Chain(ops)
+    assert chain.run() == 0                 # warm-up outside the capture
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            assert chain.run() == 0
+    torch.cuda.current_stream().wait_stream(side)
+    for _ in range(3):
+        for op in ops:
+            op[3].zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        for op, want in zip(ops, wants):
+            assert np.array_equal(bits(host(op[3])), bits(want))
+    chain.close()
+    assert gpu.device_status() == 0
+
+
+def test_chain_rejections(gpu):
+    import torch
+    W = torch.zeros(8 * 2 * 34, dtype=torch.uint8, device="cuda")
+    x = torch.zeros(1024, device="cuda")
+    y = torch.zeros(8, device="cuda")
+    ok = (W, x, None, y, 8, 256, 0)
+    gpu.Chain([ok]).close()
+    for bad in [(W, x, None, y, 8, 128, 0),                       # odd block count
+                (W, x, None, y, 8, 256, gpu.OP_ROTATE),           # rotation needs whole 1024-blocks
+                (W, x, None, y, 8, 256, gpu.OP_DEPENDS),          # a dependent op must quantise fp32
+                (W, x, None, y, 8, 256, gpu.OP_SAME_INPUT),       # nothing before it
+                (W, x, None, y, 0, 256, 0),
+                (W, x, None, y, 8, 256, 64)]:
+        with pytest.raises(RuntimeError):
+            gpu.Chain([bad])
+    with pytest.raises(RuntimeError):
+        gpu.Chain([ok, (W, y, None, y, 8, 256, gpu.OP_SAME_INPUT)])   # not the same input
+
+
+@pytest.mark.parametrize("seg,variant", [(24, 200), (16, 300), (8, 400)])
+def test_shorter_segments_match_the_per_matrix_tiling(gpu, port, seg, variant):
+    """chain_seg changes the summation tree exactly as the per-matrix kernel's segment option does."""
+    import torch
+    ops, wants = [], []
+    try:
+        assert gpu.set_option("chain_seg", seg) == 0
+        assert gpu.set_option("gemv_variant", variant) == 0
+        for i, (n_out, n_in) in enumerate([(203, 5120), (100, 17408), (130, 2304), (64, 6144)]):
+            W = dev(synth.pq2_0_weights(n_out, n_in, seed=600 + i))
+            xq = dev(port.quantize_q8_1(synth.activations(n_in, seed=i), True))
+            y_ref = torch.zeros(n_out, device="cuda")
+            assert gpu.gemv(W, xq, y_ref, n_out, n_in) == 0
+            wants.append(host(y_ref))
+            ops.append((W, xq, None, torch.zeros(n_out, device="cuda"), n_out, n_in, 0))
+        chain = gpu.Chain(ops)
+        assert chain.run() == 0
+        torch.cuda.synchronize()
+        for op, want in zip(ops, wants):
+            assert np.array_equal(bits(host(op[3])), bits(want))
+        chain.close()
+    finally:
+        gpu.set_option("chain_seg", 40)
+        gpu.set_option("gemv_variant", -1)
+    assert gpu.device_status() == 0
