@@ -240,8 +240,10 @@ def run_b200(args):
     y_gathered = torch.zeros(world * off, dtype=torch.float32, device="cuda") if world > 1 else None
     chain = chain_e2e = None
     if use_list:
-        chain = bb.Chain([(W, xq[n_in], None, y_local[o:o + rows], rows, n_in, 0)
-                          for (n_in, n_out, rows, W, y), o in zip(mats, slice_off)])
+        # consecutive matrices that read the same resident Q8_1 vector say so (its shared-memory copy is reused)
+        chain = bb.Chain([(W, xq[n_in], None, y_local[o:o + rows], rows, n_in,
+                           bb.OP_SAME_INPUT if i and mats[i - 1][0] == n_in else 0)
+                          for i, ((n_in, n_out, rows, W, y), o) in enumerate(zip(mats, slice_off))])
         # end to end: the step's activation vectors arrive as one host block; FWHT-1024 and the quantiser
         # work on 1024- and 32-element blocks, so ONE bonsai_b200_fwht_quant call over the concatenation
         # rotates and quantises every vector (vector i's Q8_1 blocks start at byte x_off[i] / 32 * 36)

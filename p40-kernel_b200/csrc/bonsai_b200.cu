@@ -32,7 +32,7 @@ std::atomic<int> g_opt_pdl{0};
 std::atomic<int> g_opt_gemv_variant{-1};
 std::atomic<int> g_opt_gemv_order{0};
 std::atomic<int> g_opt_fuse_linear{0};         // 1: bonsai_b200_linear runs as one kernel when it can (measured slower)
-std::atomic<int> g_opt_chain_threads{512};       // threads per CTA of the chain kernel: 512 or 768
+std::atomic<int> g_opt_chain_threads{512};       // threads per CTA of the chain kernel: 512 (5 blocks per lane and task), 640 (4), 768 (3)
 std::atomic<int> g_opt_chain_tile_kb{16};
 std::atomic<int> g_opt_chain_seg{40};            // longest row segment of one task, in blocks: 8, 16, 24, 32 or 40        // target bytes of one ring slot
 std::atomic<int> g_opt_gemm_path{-1};          // -1: by token count, 0: integer SIMT kernel, 1: tensor-core kernel          // 0: streaming kernel (fixed tree order), 1: the host's sequential order
@@ -431,7 +431,9 @@ int bonsai_b200_chain_create(const bonsai_b200_op *ops, int64_t n_ops, bonsai_b2
     if (sms <= 0) return 1;
     auto round_up = [](long long v, long long m) { return (v + m - 1) / m * m; };
     const long long tile_target = (long long)g_opt_chain_tile_kb.load() * 1024;
-    const int seg_max = g_opt_chain_seg.load();
+    const int threads_opt = g_opt_chain_threads.load();
+    const int steps_max = threads_opt == 768 ? 3 : threads_opt == 640 ? 4 : STREAM_STEPS;
+    const int seg_max = g_opt_chain_seg.load() < 8 * steps_max ? g_opt_chain_seg.load() : 8 * steps_max;
 
     std::vector<ChainOp> rec((size_t)n_ops);
     ChainGeom G{};
@@ -469,15 +471,15 @@ int bonsai_b200_chain_create(const bonsai_b200_op *ops, int64_t n_ops, bonsai_b2
         if (ctas > sms) ctas = sms;
         r.rows_per_cta = (int)round_up((o.n_out + ctas - 1) / ctas, 4);
         const long long used = (o.n_out + r.rows_per_cta - 1) / r.rows_per_cta;
-        r.nseg = (r.nb + seg_max - 1) / seg_max;
-        r.seg_blocks = (int)round_up((r.nb + r.nseg - 1) / r.nseg, 8);
-        if (r.seg_blocks > seg_max) r.seg_blocks = seg_max;
-        r.nseg = (r.nb + r.seg_blocks - 1) / r.seg_blocks;
         const long long row_bytes = (long long)r.nb * W_BLOCK_BYTES;
         long long tr = (tile_target / row_bytes) & ~3ll;
         if (tr < 4) tr = 4;
         if (tr > r.rows_per_cta) tr = r.rows_per_cta;
         r.tr = (int)tr;
+        r.nseg = (r.nb + seg_max - 1) / seg_max;
+        r.seg_blocks = (int)round_up((r.nb + r.nseg - 1) / r.nseg, 8);
+        if (r.seg_blocks > seg_max) r.seg_blocks = seg_max;
+        r.nseg = (r.nb + r.seg_blocks - 1) / r.seg_blocks;
         r.tpt = (r.tr / 4) * r.nseg;
         r.magic_tpt = magic_u32((uint32_t)r.tpt);
         r.magic_nseg = magic_u32((uint32_t)r.nseg);
@@ -519,20 +521,22 @@ int bonsai_b200_chain_create(const bonsai_b200_op *ops, int64_t n_ops, bonsai_b2
     bonsai_b200_chain *c = new (std::nothrow) bonsai_b200_chain;
     if (!c) return (int)cudaErrorMemoryAllocation;
     c->n_ops = (int)n_ops;
-    c->threads = g_opt_chain_threads.load();
+    c->threads = threads_opt;
     c->grid = sms;
     c->device = dev;
     c->G = G;
     c->smem = fixed + (size_t)G.nslot * G.slot_bytes;
     // the launch is cooperative: every CTA must be resident at once
     int per_sm = 0;
-    if (c->threads == 768) {
-        e = cudaFuncSetAttribute(gemv_chain_kernel<768>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_limit);
-        if (e == cudaSuccess) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gemv_chain_kernel<768>, 768, c->smem);
-    } else {
-        e = cudaFuncSetAttribute(gemv_chain_kernel<512>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_limit);
-        if (e == cudaSuccess) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gemv_chain_kernel<512>, 512, c->smem);
-    }
+    auto prepare = [&](auto kernel) {
+        cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_limit);
+        if (err == cudaSuccess) err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, c->threads, c->smem);
+        return err;
+    };
+    if (c->threads == 768) e = prepare(gemv_chain_kernel<768, 3>);
+    else if (c->threads == 640) e = prepare(gemv_chain_kernel<640, 4>);
+    else if (c->threads == 512) e = prepare(gemv_chain_kernel<512, 5>);
+    else e = cudaErrorInvalidValue;
     if (e == cudaSuccess && per_sm < 1) e = cudaErrorLaunchOutOfResources;
     if (e == cudaSuccess) e = cudaMalloc(&c->d_ops, sizeof(ChainOp) * (size_t)n_ops);
     if (e == cudaSuccess) e = cudaMalloc(&c->d_counter, 256);
@@ -561,8 +565,10 @@ int bonsai_b200_chain_run(bonsai_b200_chain *c, bonsai_stream stream) {
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     const ChainOp *ops = c->d_ops;
-    if (c->threads == 768) e = cudaLaunchKernelEx(&cfg, gemv_chain_kernel<768>, ops, c->n_ops, c->G, c->d_counter);
-    else e = cudaLaunchKernelEx(&cfg, gemv_chain_kernel<512>, ops, c->n_ops, c->G, c->d_counter);
+    auto go = [&](auto kernel) { return cudaLaunchKernelEx(&cfg, kernel, ops, c->n_ops, c->G, c->d_counter); };
+    if (c->threads == 768) e = go(gemv_chain_kernel<768, 3>);
+    else if (c->threads == 640) e = go(gemv_chain_kernel<640, 4>);
+    else e = go(gemv_chain_kernel<512, 5>);
     return (int)e;
 }
 
@@ -702,7 +708,7 @@ int bonsai_b200_set_option(const char *key, int64_t value) {
     if (!std::strcmp(key, "gemm_path")) { g_opt_gemm_path.store((int)value); return 0; }
     if (!std::strcmp(key, "fuse_linear")) { g_opt_fuse_linear.store(value != 0); return 0; }
     if (!std::strcmp(key, "chain_threads")) {
-        if (value != 512 && value != 768) return 1;
+        if (value != 512 && value != 640 && value != 768) return 1;
         g_opt_chain_threads.store((int)value);
         return 0;
     }
@@ -732,10 +738,6 @@ int bonsai_b200_version(void) { return 100; }
 
 #ifdef BONSAI_B200_TRACE
 int bonsai_b200_set_skip(int v) { return (int)cudaMemcpyToSymbol(g_skip, &v, sizeof(int)); }
-int bonsai_b200_read_tile_trace(long long *out, int n) {
-    cudaDeviceSynchronize();
-    return (int)cudaMemcpyFromSymbol(out, g_tile_trace, sizeof(long long) * n);
-}
 int bonsai_b200_read_chain_trace(long long *out, int n) {
     cudaDeviceSynchronize();
     return (int)cudaMemcpyFromSymbol(out, g_chain_trace, sizeof(long long) * n);

@@ -56,6 +56,7 @@ enum : int { CHAIN_ROTATE = 1, CHAIN_DEPENDS = 2, CHAIN_SAME_INPUT = 4, CHAIN_SI
 
 constexpr int CHAIN_MAX_SLOTS = 16;
 constexpr int CHAIN_OP_RING = 8;
+constexpr int CHAIN_GATES = 3;           // a warp may run this many ops ahead of the slowest one
 
 struct __align__(16) ChainOp {                 // 128 bytes, one per projection, device table
     const uint8_t *W;
@@ -88,7 +89,7 @@ struct ChainGeom {
 __host__ __device__ inline size_t chain_fixed_bytes(const ChainGeom &G) {
     const size_t b = 384 + CHAIN_OP_RING * sizeof(ChainOp) + 2 * (size_t)G.nb_max * 176 + (size_t)G.stage_blocks * 144 +
                      (size_t)G.rot_blocks * 4096 +
-                     2 * (size_t)G.partial_floats * 4 + 2 * (size_t)G.quad_ints * 4;
+                     CHAIN_GATES * (size_t)G.partial_floats * 4 + CHAIN_GATES * (size_t)G.quad_ints * 4;
     return (b + 127) & ~(size_t)127;
 }
 
@@ -126,15 +127,15 @@ __device__ __forceinline__ bool grid_counter_wait(const unsigned int *counter, u
     return false;
 }
 
-template <int THREADS>
+template <int THREADS, int MAXSTEPS>
 __global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *__restrict__ ops, const int n_ops,
                                                                 const ChainGeom G, unsigned int *grid_counter) {
     constexpr int C = THREADS / 32 - 2;         // compute warps
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t *full = reinterpret_cast<uint64_t *>(smem);      // [16] tile landed in slot
     uint64_t *ready = full + CHAIN_MAX_SLOTS;                 // [2]  tables of a Q8_1 op are filled
-    uint64_t *gate = ready + 2;                               // [2]  every compute warp has finished op (index & 1)
-    uint64_t *xs = gate + 2;                                  // [1]  rotate: every warp has written its blocks
+    uint64_t *gate = ready + 2;                               // [3]  every compute warp has finished op (index % 3)
+    uint64_t *xs = gate + CHAIN_GATES;                                  // [1]  rotate: every warp has written its blocks
     uint64_t *dep = xs + 1;                                   // [1]  rotate: the producers of x have arrived
     uint64_t *stage_full = dep + 1;                           // [1]  Q8_1 staging copy landed
     int *done_cnt = reinterpret_cast<int *>(smem + 192);      // [16] tasks of the slot's tile that have copied out
@@ -150,7 +151,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *_
     float4 *scratch = reinterpret_cast<float4 *>(p);
     p += (size_t)G.rot_blocks * FWHT_N * 4;
     float *partial_base = reinterpret_cast<float *>(p);
-    p += 2 * (size_t)G.partial_floats * 4;
+    p += CHAIN_GATES * (size_t)G.partial_floats * 4;
     int *quad_base = reinterpret_cast<int *>(p);
     uint8_t *ring = smem + chain_fixed_bytes(G);
 
@@ -161,15 +162,14 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *_
         for (int s = 0; s < CHAIN_MAX_SLOTS; ++s) mbar_init(&full[s], 1);
         mbar_init(&ready[0], 1);
         mbar_init(&ready[1], 1);
-        mbar_init(&gate[0], C);
-        mbar_init(&gate[1], C);
+        for (int i = 0; i < CHAIN_GATES; ++i) mbar_init(&gate[i], C);
         mbar_init(xs, C);
         mbar_init(dep, 1);
         mbar_init(stage_full, 1);
         mbar_fence_init();
     }
     for (int i = threadIdx.x; i < 3 * CHAIN_MAX_SLOTS; i += THREADS) done_cnt[i] = 0;     // done, expect, ctrl
-    for (int i = threadIdx.x; i < 2 * G.quad_ints; i += THREADS) quad_base[i] = 0;
+    for (int i = threadIdx.x; i < CHAIN_GATES * G.quad_ints; i += THREADS) quad_base[i] = 0;
     __syncthreads();
 
     // rows of op R that this CTA owns
@@ -206,7 +206,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *_
                                 atomicAdd(grid_counter, 1u);
                             }
                         }
-                        mbar_arrive(&gate[op & 1]);
+                        mbar_arrive(&gate[op % CHAIN_GATES]);
                     }
                 }
                 task_base += ntasks;
@@ -216,7 +216,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *_
                 // ---- enter op `op`
                 CHAIN_STAMP(op, 0);
                 if (!spin_until_gt(&ctrl[1], op)) { alive = false; break; }
-                if (op >= 2 && !mbar_wait_bounded(&gate[op & 1], ((op - 2) >> 1) & 1)) { alive = false; break; }
+                if (op >= CHAIN_GATES &&
+                    !mbar_wait_bounded(&gate[op % CHAIN_GATES], ((op - CHAIN_GATES) / CHAIN_GATES) & 1)) { alive = false; break; }
                 const ChainOp &R = opring[op & (CHAIN_OP_RING - 1)];
                 flags = R.flags;
                 cta_rows(R, row0, rows_here);
@@ -225,7 +226,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *_
                 if (!(flags & CHAIN_SAME_INPUT)) {
                     if (flags & CHAIN_ROTATE) {
                         // every compute warp has left op - 1: both table buffers' readers are gone
-                        if (op >= 1 && !mbar_wait_bounded(&gate[(op - 1) & 1], ((op - 1) >> 1) & 1)) { alive = false; break; }
+                        if (op >= 1 && !mbar_wait_bounded(&gate[(op - 1) % CHAIN_GATES], ((op - 1) / CHAIN_GATES) & 1)) { alive = false; break; }
                         if (flags & CHAIN_DEPENDS) {
                             if (wid == 0) {
                                 bool ok = true;
@@ -332,7 +333,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *_
             const uint32_t *act_q = reinterpret_cast<const uint32_t *>(tables + (size_t)R.buf * table_bytes);
             const float *act_s = reinterpret_cast<const float *>(act_q + (size_t)G.nb_max * STREAM_ACT_WORDS);
             const int *act_i = reinterpret_cast<const int *>(act_s + (size_t)G.nb_max * 4);
-            float acc = stream_task(rowp, bl, b0, blocks, act_q, act_s, act_i, [&]() {
+            float acc = stream_task<MAXSTEPS>(rowp, bl, b0, blocks, act_q, act_s, act_i, [&]() {
                 __syncwarp();
                 if (lane == 0) {
                     __threadfence_block();                          // the loads above, before the slot is handed back
@@ -347,15 +348,15 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *_
             if (nseg == 1) {
                 if (bl == 0 && r < rows_here) y[row0 + r] = acc;
             } else {
-                float *partial = partial_base + (size_t)(op & 1) * G.partial_floats;
-                int *quad_count = quad_base + (size_t)(op & 1) * G.quad_ints;
+                float *partial = partial_base + (size_t)(op % CHAIN_GATES) * G.partial_floats;
+                int *quad_count = quad_base + (size_t)(op % CHAIN_GATES) * G.quad_ints;
                 if (bl == 0) partial[r * nseg + j] = acc;
                 __syncwarp();
                 int last = 0;
                 if (lane == 0) {
                     __threadfence_block();
                     last = atomicAdd(&quad_count[r_quad >> 2], 1) == nseg - 1;
-                    if (last) quad_count[r_quad >> 2] = 0;           // left clean for the op after next
+                    if (last) quad_count[r_quad >> 2] = 0;           // left clean for the next op that uses this buffer
                 }
                 last = __shfl_sync(0xffffffffu, last, 0);
                 if (last) {
@@ -413,7 +414,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *_
         const uint64_t pol = policy_evict_first();
         auto see_gates = [&](int upto) {    // waits, in order, until gate_seen > upto
             while (gate_seen <= upto) {
-                if (!mbar_wait_bounded(&gate[gate_seen & 1], (uint32_t)((gate_seen >> 1) & 1))) return false;
+                if (!mbar_wait_bounded(&gate[gate_seen % CHAIN_GATES], (uint32_t)((gate_seen / CHAIN_GATES) & 1))) return false;
                 ++gate_seen;
             }
             return true;
@@ -424,7 +425,9 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *_
         // table preparation below; blocks only when `must` is not there yet.
         auto load_records = [&](int must) {
             for (;;) {
-                while (gate_seen < n_ops && mbar_test(&gate[gate_seen & 1], (uint32_t)((gate_seen >> 1) & 1))) ++gate_seen;
+                while (gate_seen < n_ops &&
+                       mbar_test(&gate[gate_seen % CHAIN_GATES], (uint32_t)((gate_seen / CHAIN_GATES) & 1)))
+                    ++gate_seen;
                 while (rec_next < n_ops &&
                        (rec_next < CHAIN_OP_RING ||
                         (gate_seen > rec_next - CHAIN_OP_RING && ctrl[3] > rec_next - CHAIN_OP_RING))) {

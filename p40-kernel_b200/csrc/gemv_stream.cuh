@@ -88,13 +88,13 @@ __device__ __forceinline__ float stream_task_full(const uint8_t *rowp, int bl, i
 
 // The general task: a last segment of any length (a lane past the end re-reads the last block and
 // skips its terms).
-template <typename Release>
+template <int MAXSTEPS, typename Release>
 __device__ __forceinline__ float stream_task_ragged(const uint8_t *rowp, int bl, int b0, int blocks, const uint32_t *act_q,
                                                     const float *act_s, const int *act_i, Release release) {
-    uint32_t x[STREAM_STEPS][9];
-    float dw[STREAM_STEPS];
+    uint32_t x[MAXSTEPS][9];
+    float dw[MAXSTEPS];
 #pragma unroll
-    for (int k = 0; k < STREAM_STEPS; ++k) {
+    for (int k = 0; k < MAXSTEPS; ++k) {
         const int b = min(bl + 8 * k, blocks - 1);
         const uint32_t *xw = reinterpret_cast<const uint32_t *>(rowp) + ((W_BLOCK_BYTES * b + 2) >> 2);
 #pragma unroll
@@ -104,7 +104,7 @@ __device__ __forceinline__ float stream_task_ragged(const uint8_t *rowp, int bl,
     release();
     float acc = 0.0f;
 #pragma unroll
-    for (int k = 0; k < STREAM_STEPS; ++k) {
+    for (int k = 0; k < MAXSTEPS; ++k) {
         const int b = bl + 8 * k;
         if (b < blocks) {
             const int gb = b0 + b;
@@ -129,21 +129,20 @@ __device__ __forceinline__ float stream_task_ragged(const uint8_t *rowp, int bl,
     return acc;
 }
 
-// One task: dispatches on the segment length (warp-uniform).
-template <typename Release>
+// One task: dispatches on the segment length (warp-uniform).  MAXSTEPS bounds the blocks a lane
+// stages in registers (segments hold at most 8 * MAXSTEPS blocks).
+template <int MAXSTEPS, typename Release>
 __device__ __forceinline__ float stream_task(const uint8_t *rowp, int bl, int b0, int blocks, const uint32_t *act_q,
                                              const float *act_s, const int *act_i, Release release) {
     if ((blocks & 7) == 0) {
-        switch (blocks >> 3) {
-            case 5: return stream_task_full<5>(rowp, bl, b0 + bl, act_q, act_s, act_i, release);
-            case 4: return stream_task_full<4>(rowp, bl, b0 + bl, act_q, act_s, act_i, release);
-            case 3: return stream_task_full<3>(rowp, bl, b0 + bl, act_q, act_s, act_i, release);
-            case 2: return stream_task_full<2>(rowp, bl, b0 + bl, act_q, act_s, act_i, release);
-            case 1: return stream_task_full<1>(rowp, bl, b0 + bl, act_q, act_s, act_i, release);
-            default: break;
-        }
+        const int steps = blocks >> 3;
+        if (MAXSTEPS >= 5 && steps == 5) return stream_task_full<(MAXSTEPS >= 5 ? 5 : 1)>(rowp, bl, b0 + bl, act_q, act_s, act_i, release);
+        if (MAXSTEPS >= 4 && steps == 4) return stream_task_full<(MAXSTEPS >= 4 ? 4 : 1)>(rowp, bl, b0 + bl, act_q, act_s, act_i, release);
+        if (MAXSTEPS >= 3 && steps == 3) return stream_task_full<(MAXSTEPS >= 3 ? 3 : 1)>(rowp, bl, b0 + bl, act_q, act_s, act_i, release);
+        if (MAXSTEPS >= 2 && steps == 2) return stream_task_full<(MAXSTEPS >= 2 ? 2 : 1)>(rowp, bl, b0 + bl, act_q, act_s, act_i, release);
+        if (steps == 1) return stream_task_full<1>(rowp, bl, b0 + bl, act_q, act_s, act_i, release);
     }
-    return stream_task_ragged(rowp, bl, b0, blocks, act_q, act_s, act_i, release);
+    return stream_task_ragged<MAXSTEPS>(rowp, bl, b0, blocks, act_q, act_s, act_i, release);
 }
 
 // Shared memory: [full[256] | done[256]] [act int8: nb * 36 words] [act scale: nb * 4 floats]
@@ -318,7 +317,7 @@ __global__ void __launch_bounds__(512, 1) gemv_stream_kernel(const uint8_t *__re
             // a funnel shift by 16 or 0 aligns them.  Phase B multiplies from registers against the
             // broadcast activation words.  (rowp is word-aligned: rows start on a word since nb is even,
             // and so do segments since seg_blocks is even.)
-            float acc = stream_task(rowp, bl, b0, blocks, act_q, act_s, act_i, [&]() {
+            float acc = stream_task<STREAM_STEPS>(rowp, bl, b0, blocks, act_q, act_s, act_i, [&]() {
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&done[t]);   // release: every lane's loads above are complete
             });

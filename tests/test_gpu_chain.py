@@ -24,11 +24,16 @@ def host(t):
     return t.detach().cpu().numpy()
 
 
-@pytest.fixture(params=[512, 768])
+@pytest.fixture(params=[512, 640, 768])
 def threads(gpu, request):
+    """Threads per CTA of the persistent kernel; the wider ones stage fewer blocks per lane, i.e. use
+    shorter row segments -- the per-matrix kernel is given the same segment length so that both sum in
+    the same tree."""
     assert gpu.set_option("chain_threads", request.param) == 0
+    assert gpu.set_option("gemv_variant", {512: -1, 640: 100, 768: 200}[request.param]) == 0
     yield request.param
     gpu.set_option("chain_threads", 512)
+    gpu.set_option("gemv_variant", -1)
 
 
 SHAPES = [(5, 5120), (203, 5120), (100, 17408), (37, 1024), (6000, 5120), (2500, 17408), (1500, 6144), (700, 8192),
@@ -47,6 +52,14 @@ def test_independent_q8_ops_equal_per_matrix_calls(gpu, port, threads):
         wants.append(host(y_ref))
         y = torch.full((n_out,), -777.0, device="cuda")
         ops.append((W, xq, None, y, n_out, n_in, 0))
+    # two more ops that reuse the last op's quantised vector
+    last = ops[-1]
+    for i, n_out in enumerate([77, 8]):
+        W = dev(synth.pq2_0_weights(n_out, last[5], seed=900 + i))
+        y_ref = torch.zeros(n_out, device="cuda")
+        assert gpu.gemv(W, last[1], y_ref, n_out, last[5]) == 0
+        wants.append(host(y_ref))
+        ops.append((W, last[1], None, torch.full((n_out,), -777.0, device="cuda"), n_out, last[5], gpu.OP_SAME_INPUT))
     chain = gpu.Chain(ops)
     info = chain.info()
     assert info["threads"] == threads and info["nslot"] >= 3
