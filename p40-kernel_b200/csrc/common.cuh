@@ -101,24 +101,25 @@ __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 // Bounded wait: returns false (and records the status word) instead of spinning forever.  The
-// barrier is polled with the non-blocking test; between polls the thread sleeps 32, 64, ... 256 ns,
+// barrier is polled with the non-blocking test; between polls the thread sleeps first_ns, 2 first_ns, ... max_ns,
 // which keeps a waiting warp off the issue ports (the blocking form of the wait expands to a
 // software time-out loop of a couple of dozen instructions per poll).
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity, uint32_t first_ns = 32,
+                                                  uint32_t max_ns = 256) {
     uint32_t ok;
     asm volatile(
         "{\n\t"
         ".reg .pred p;\n\t"
         ".reg .u32 n, ns;\n\t"
         "mov.u32 n, %3;\n\t"
-        "mov.u32 ns, 32;\n\t"
+        "mov.u32 ns, %4;\n\t"
         "mov.u32 %0, 1;\n\t"
         "WAIT_LOOP:\n\t"
         "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
         "@p bra WAIT_DONE;\n\t"
         "nanosleep.u32 ns;\n\t"
         "add.u32 ns, ns, ns;\n\t"
-        "min.u32 ns, ns, 256;\n\t"
+        "min.u32 ns, ns, %5;\n\t"
         "sub.u32 n, n, 1;\n\t"
         "setp.ne.u32 p, n, 0;\n\t"
         "@p bra WAIT_LOOP;\n\t"
@@ -126,7 +127,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity
         "WAIT_DONE:\n\t"
         "}"
         : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity), "r"(1u << 22)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(1u << 22), "r"(first_ns), "r"(max_ns)
         : "memory");
     if (!ok) atomicExch(&g_device_status, STATUS_MBARRIER_TIMEOUT);
     return ok != 0;

@@ -22,11 +22,15 @@
 //               warps meet, wait for the producers of that vector, and rotate it together.
 //
 // Barrier discipline.  Shared-memory barriers are reused, so a waiter identifies a phase by parity;
-// that is only sound when no waiter can fall two phases behind.  Every reused barrier here is waited
-// on by every one of its waiters in every phase, in order (gate, ready, xs, dep), or is guarded by a
-// monotonic counter (full[slot]: a task first sees `issued > g`, which the copy lane publishes after
-// arming the barrier for tile g, and the slot cannot be re-armed before that task has copied out).
-// Slot release is a plain counter because the number of tasks per tile changes from op to op.
+// that is only sound when the barrier cannot complete a second phase before the waiter has seen the
+// first.  Only three kinds of barrier are waited on by parity, and each has that property by
+// construction: ready[buf] (its next phase needs every compute warp to have left an op that comes
+// after the one being waited for), xs and dep (every waiter must arrive, or pass xs, before the next
+// phase can complete), full[slot] (a task first sees `issued > g`, published after the barrier was
+// armed for tile g, and the slot cannot be re-armed before that task has copied out).  Everything
+// that a warp may fall arbitrarily far behind on is a monotonic counter instead: ops_done (every
+// compute warp has left ops [0, ops_done)), ops_loaded, issued, copy_op.  Slot release is a plain
+// counter too, because the number of tasks per tile changes from op to op.
 // Every wait is bounded; a time-out sets the status word and the warp leaves.
 #pragma once
 
@@ -56,6 +60,10 @@ enum : int { CHAIN_ROTATE = 1, CHAIN_DEPENDS = 2, CHAIN_SAME_INPUT = 4, CHAIN_SI
 
 constexpr int CHAIN_MAX_SLOTS = 16;
 constexpr int CHAIN_OP_RING = 8;
+#ifndef CHAIN_NS0                 // first and longest sleep between two polls of a wait (a stress build stretches them)
+#define CHAIN_NS0 32
+#define CHAIN_NSMAX 256
+#endif
 constexpr int CHAIN_GATES = 3;           // a warp may run this many ops ahead of the slowest one
 
 struct __align__(16) ChainOp {                 // 128 bytes, one per projection, device table
@@ -94,34 +102,34 @@ __host__ __device__ inline size_t chain_fixed_bytes(const ChainGeom &G) {
 }
 
 __device__ __forceinline__ bool spin_until_gt(volatile int *p, int v) {
-    uint32_t ns = 32;
+    uint32_t ns = CHAIN_NS0;
     for (uint32_t n = 0; n < (1u << 22); ++n) {
         if (*p > v) return true;
         __nanosleep(ns);
-        ns = min(ns * 2, 256u);
+        ns = min(ns * 2, (uint32_t)CHAIN_NSMAX);
     }
     atomicExch(&g_device_status, STATUS_MBARRIER_TIMEOUT);
     return false;
 }
 __device__ __forceinline__ bool spin_until_eq(volatile int *p, int v) {
-    uint32_t ns = 32;
+    uint32_t ns = CHAIN_NS0;
     for (uint32_t n = 0; n < (1u << 22); ++n) {
         if (*p == v) return true;
         __nanosleep(ns);
-        ns = min(ns * 2, 256u);
+        ns = min(ns * 2, (uint32_t)CHAIN_NSMAX);
     }
     atomicExch(&g_device_status, STATUS_MBARRIER_TIMEOUT);
     return false;
 }
 // Grid-wide arrival counter, polled by one lane: acquire at device scope, bounded.
 __device__ __forceinline__ bool grid_counter_wait(const unsigned int *counter, unsigned int target) {
-    uint32_t ns = 32;
+    uint32_t ns = CHAIN_NS0;
     for (uint32_t n = 0; n < (1u << 22); ++n) {
         unsigned int v;
         asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
         if (v >= target) return true;
         __nanosleep(ns);
-        ns = min(ns * 2, 256u);
+        ns = min(ns * 2, (uint32_t)CHAIN_NSMAX);
     }
     atomicExch(&g_device_status, STATUS_GRID_TIMEOUT);
     return false;
@@ -134,13 +142,13 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *_
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t *full = reinterpret_cast<uint64_t *>(smem);      // [16] tile landed in slot
     uint64_t *ready = full + CHAIN_MAX_SLOTS;                 // [2]  tables of a Q8_1 op are filled
-    uint64_t *gate = ready + 2;                               // [3]  every compute warp has finished op (index % 3)
-    uint64_t *xs = gate + CHAIN_GATES;                                  // [1]  rotate: every warp has written its blocks
+    uint64_t *xs = ready + 2;                                  // [1]  rotate: every warp has written its blocks
     uint64_t *dep = xs + 1;                                   // [1]  rotate: the producers of x have arrived
     uint64_t *stage_full = dep + 1;                           // [1]  Q8_1 staging copy landed
     int *done_cnt = reinterpret_cast<int *>(smem + 192);      // [16] tasks of the slot's tile that have copied out
     int *expect_cnt = done_cnt + CHAIN_MAX_SLOTS;             // [16] ... of how many
-    volatile int *ctrl = expect_cnt + CHAIN_MAX_SLOTS;        // [16] 0 issued, 1 ops_loaded, 2 next_task, 3 copy_op, 4-7 op_done
+    volatile int *ctrl = expect_cnt + CHAIN_MAX_SLOTS;        // [16] 0 issued, 1 ops_loaded, 2 next_task, 3 copy_op, 4-7 warps that
+                                                              //      left op (index & 3), 8 ops_done: every compute warp has left ops [0, ops_done)
     ChainOp *opring = reinterpret_cast<ChainOp *>(smem + 384);
     uint8_t *p = smem + 384 + CHAIN_OP_RING * sizeof(ChainOp);
     const size_t table_bytes = (size_t)G.nb_max * 176;
@@ -162,7 +170,6 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *_
         for (int s = 0; s < CHAIN_MAX_SLOTS; ++s) mbar_init(&full[s], 1);
         mbar_init(&ready[0], 1);
         mbar_init(&ready[1], 1);
-        for (int i = 0; i < CHAIN_GATES; ++i) mbar_init(&gate[i], C);
         mbar_init(xs, C);
         mbar_init(dep, 1);
         mbar_init(stage_full, 1);
@@ -198,15 +205,17 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *_
                     if (flags & CHAIN_SIGNAL) __threadfence();          // this warp's y rows, before its arrival below
                     __syncwarp();
                     if (lane == 0) {
-                        if (flags & CHAIN_SIGNAL) {
-                            const int old = atomicAdd(const_cast<int *>(&ctrl[4 + (op & 3)]), 1);
-                            if (old == C - 1) {                         // the CTA's rows of every op so far are written
-                                ctrl[4 + (op & 3)] = 0;
+                        __threadfence_block();                          // this warp's reads of op's tables and partial sums
+                        const int old = atomicAdd(const_cast<int *>(&ctrl[4 + (op & 3)]), 1);
+                        if (old == C - 1) {                             // last warp out: the CTA's rows of every op so far are written
+                            ctrl[4 + (op & 3)] = 0;
+                            if (flags & CHAIN_SIGNAL) {
                                 __threadfence();
                                 atomicAdd(grid_counter, 1u);
                             }
+                            __threadfence_block();
+                            ctrl[8] = op + 1;                           // monotonic: ops are left in order
                         }
-                        mbar_arrive(&gate[op % CHAIN_GATES]);
                     }
                 }
                 task_base += ntasks;
@@ -216,8 +225,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *_
                 // ---- enter op `op`
                 CHAIN_STAMP(op, 0);
                 if (!spin_until_gt(&ctrl[1], op)) { alive = false; break; }
-                if (op >= CHAIN_GATES &&
-                    !mbar_wait_bounded(&gate[op % CHAIN_GATES], ((op - CHAIN_GATES) / CHAIN_GATES) & 1)) { alive = false; break; }
+                if (op >= CHAIN_GATES && !spin_until_gt(&ctrl[8], op - CHAIN_GATES)) { alive = false; break; }
                 const ChainOp &R = opring[op & (CHAIN_OP_RING - 1)];
                 flags = R.flags;
                 cta_rows(R, row0, rows_here);
@@ -226,7 +234,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *_
                 if (!(flags & CHAIN_SAME_INPUT)) {
                     if (flags & CHAIN_ROTATE) {
                         // every compute warp has left op - 1: both table buffers' readers are gone
-                        if (op >= 1 && !mbar_wait_bounded(&gate[(op - 1) % CHAIN_GATES], ((op - 1) / CHAIN_GATES) & 1)) { alive = false; break; }
+                        if (op >= 1 && !spin_until_gt(&ctrl[8], op - 1)) { alive = false; break; }
                         if (flags & CHAIN_DEPENDS) {
                             if (wid == 0) {
                                 bool ok = true;
@@ -234,7 +242,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *_
                                 __syncwarp();
                                 if (lane == 0 && ok) mbar_arrive(dep);
                             }
-                            if (!mbar_wait_bounded(dep, dep_phase & 1u)) { alive = false; break; }
+                            if (!mbar_wait_bounded(dep, dep_phase & 1u, CHAIN_NS0, CHAIN_NSMAX)) { alive = false; break; }
                             ++dep_phase;
                         }
                         CHAIN_STAMP(op, 1);
@@ -275,7 +283,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *_
                             }
                             __syncwarp();
                             if (lane == 0) mbar_arrive(xs);
-                            ok = mbar_wait_bounded(xs, xs_phase & 1u);
+                            ok = mbar_wait_bounded(xs, xs_phase & 1u, CHAIN_NS0, CHAIN_NSMAX);
                             ++xs_phase;
                             if (!ok) break;
                             for (int u = wid; u < units; u += C) {
@@ -293,12 +301,12 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *_
                             CHAIN_STAMP(op, 3);
                             __syncwarp();
                             if (lane == 0) mbar_arrive(xs);
-                            ok = mbar_wait_bounded(xs, xs_phase & 1u);
+                            ok = mbar_wait_bounded(xs, xs_phase & 1u, CHAIN_NS0, CHAIN_NSMAX);
                             ++xs_phase;
                         }
                         if (!ok) { alive = false; break; }
                     } else {
-                        if (!mbar_wait_bounded(&ready[R.buf], (uint32_t)R.ready_parity)) { alive = false; break; }
+                        if (!mbar_wait_bounded(&ready[R.buf], (uint32_t)R.ready_parity, CHAIN_NS0, CHAIN_NSMAX)) { alive = false; break; }
                     }
                 }
                 CHAIN_STAMP(op, 2);
@@ -324,7 +332,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *_
                 issued_seen = ctrl[0];
             }
             if (lane == 0 && local == 0) TILE_STAMP(g, 2);
-            if (!mbar_wait_bounded(&full[slot], (uint32_t)(lap & 1))) break;
+            if (!mbar_wait_bounded(&full[slot], (uint32_t)(lap & 1), CHAIN_NS0, CHAIN_NSMAX)) break;
             if (lane == 0 && local == 0) TILE_STAMP(g, 3);
             const int b0 = j * R.seg_blocks;
             const int blocks = min(R.seg_blocks, nb - b0);
@@ -412,11 +420,10 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *_
         int gate_seen = 0;                  // every compute warp has left ops [0, gate_seen)
         uint32_t stage_parity = 0;
         const uint64_t pol = policy_evict_first();
-        auto see_gates = [&](int upto) {    // waits, in order, until gate_seen > upto
-            while (gate_seen <= upto) {
-                if (!mbar_wait_bounded(&gate[gate_seen % CHAIN_GATES], (uint32_t)((gate_seen / CHAIN_GATES) & 1))) return false;
-                ++gate_seen;
-            }
+        auto see_gates = [&](int upto) {    // waits until every compute warp has left ops [0, upto]
+            if (gate_seen > upto) return true;
+            if (!spin_until_gt(&ctrl[8], upto)) return false;
+            gate_seen = ctrl[8];
             return true;
         };
         int rec_next = 0;                   // records [0, rec_next) are in the shared ring
@@ -425,9 +432,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *_
         // table preparation below; blocks only when `must` is not there yet.
         auto load_records = [&](int must) {
             for (;;) {
-                while (gate_seen < n_ops &&
-                       mbar_test(&gate[gate_seen % CHAIN_GATES], (uint32_t)((gate_seen / CHAIN_GATES) & 1)))
-                    ++gate_seen;
+                gate_seen = ctrl[8];
                 while (rec_next < n_ops &&
                        (rec_next < CHAIN_OP_RING ||
                         (gate_seen > rec_next - CHAIN_OP_RING && ctrl[3] > rec_next - CHAIN_OP_RING))) {
@@ -459,7 +464,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *_
                 bulk_g2s(stage, R.x, (uint32_t)nchunks * A_BLOCK_BYTES, stage_full, pol);
             }
             if (!see_gates(R.prev_user)) return;
-            if (!mbar_wait_bounded(stage_full, stage_parity)) return;
+            if (!mbar_wait_bounded(stage_full, stage_parity, CHAIN_NS0, CHAIN_NSMAX)) return;
             stage_parity ^= 1u;
             uint32_t *act_q = reinterpret_cast<uint32_t *>(tables + (size_t)R.buf * table_bytes);
             float *act_s = reinterpret_cast<float *>(act_q + (size_t)G.nb_max * STREAM_ACT_WORDS);
