@@ -335,6 +335,19 @@ def run_b200(args):
         ms_m, launches_m, _ = timed(step_matrix, e2e_steps, max(3, args.warmup // 4), False)
         per_matrix = {"call": "bonsai_p40_gemv per matrix", "value": total_w * e2e_steps / (ms_m * 1e-3) / 1e9,
                       "unit": UNIT, "ms_per_step": ms_m / e2e_steps, "gpu_launches_per_step": launches_m // e2e_steps}
+    split = None
+    if use_list and world > 1:      # where the step's time goes: the mat-vec launch alone, the all-gather alone
+        def only_matvec():
+            assert chain.run() == 0
+            return 1
+
+        def only_gather():
+            dist.all_gather_into_tensor(y_gathered, y_local)
+            return 1
+        ms_k, _, _ = timed(only_matvec, e2e_steps, 3, False)
+        ms_g, _, _ = timed(only_gather, e2e_steps, 3, False)
+        split = {"matvec_ms_per_step": ms_k / e2e_steps, "allgather_ms_per_step": ms_g / e2e_steps,
+                 "allgather_bytes_per_rank": int(y_local.numel() * 4)}
     status = bb.device_status()
     launches_per_step = launches // args.steps
 
@@ -369,6 +382,8 @@ def run_b200(args):
     }
     if per_matrix is not None:
         line["per_matrix_abi"] = per_matrix
+    if split is not None:
+        line["split"] = split
     if world == 1 and not args.no_cpu:
         threads = os.cpu_count() or 1
         kind, sweep, wbytes = cpu_arm(args, threads)
@@ -380,6 +395,12 @@ def run_b200(args):
         dt = time.perf_counter() - t0
         line["cpu_baseline"] = {"value": wbytes * reps / dt / 1e9, "unit": UNIT, "cores": threads, "kind": kind,
                                 "sample": f"{reps} layer sweeps (4 mat-vecs each, FWHT+Q8_1 included) in {dt:.1f} s"}
+        _, sweep1, _ = cpu_arm(args, 1)             # the same code on one host thread
+        t0 = time.perf_counter()
+        sweep1()
+        dt1 = time.perf_counter() - t0
+        line["cpu_baseline"]["single_thread"] = {"value": wbytes / dt1 / 1e9, "unit": UNIT,
+                                                 "sample": f"1 layer sweep in {dt1:.2f} s"}
     if rank == 0:
         print(json.dumps(line))
     if dist is not None:

@@ -365,6 +365,39 @@ def test_gemm_bits(gpu, port, n_out, n_in, n_tok):
     assert_close_and_exact(host(Y), port.gemm(W, Xq, n_out, n_in, n_tok, threads=8))
 
 
+@pytest.mark.parametrize("n_in,n_out,n_tok", [(17408, 5120, 8), (5120, 17408, 1)])
+def test_row_partition_assembles_full_result(gpu, port, n_in, n_out, n_tok):
+    """The multi-GPU split on one device: 8 ranks' row slices (contiguous byte ranges of W), each
+    multiplied on its own, written where an all-gather would put them, equal the unsplit result bit
+    for bit (batch 8 through the mat-mul entry point, batch 1 through the mat-vec)."""
+    import torch
+    from bonsai_b200 import partition
+    W = synth.pq2_0_weights(n_out, n_in, seed=3)
+    X = synth.activations(n_in, seed=4, batch=n_tok)
+    Wd = dev(W)
+    if n_tok == 1:
+        xq = port.quantize_q8_1(X.reshape(-1), True)
+        want = port.gemv(W, xq, n_out, n_in, threads=8)
+        xqd = dev(xq)
+        y = torch.zeros(n_out, device="cuda")
+        with host_order(gpu):
+            for r in range(8):
+                lo, hi = partition.row_slice(n_out, r, 8)
+                b0, b1 = partition.byte_slice(n_out, n_in, r, 8)
+                assert gpu.gemv(Wd[b0:b1], xqd, y[lo:hi], hi - lo, n_in) == 0
+        assert_close_and_exact(host(y), want)
+    else:
+        Xq = port.quantize_batch_chunk_major(X)
+        want = port.gemm(W, Xq, n_out, n_in, n_tok, threads=8)
+        Xqd = dev(Xq)
+        Y = torch.zeros(n_out, n_tok, device="cuda")
+        for r in range(8):
+            lo, hi = partition.row_slice(n_out, r, 8)
+            b0, b1 = partition.byte_slice(n_out, n_in, r, 8)
+            assert gpu.gemm(Wd[b0:b1], Xqd, Y[lo:hi], hi - lo, n_in, n_tok) == 0
+        assert_close_and_exact(host(Y), want)
+
+
 @pytest.mark.parametrize("path", [0, 1])
 @pytest.mark.parametrize("n_out,n_in,n_tok", [(128, 128, 64), (64, 256, 5), (300, 5120, 100), (1024, 5120, 512), (200, 17408, 130),
                                               (129, 384, 65)])
