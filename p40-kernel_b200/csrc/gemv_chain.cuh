@@ -47,13 +47,8 @@ __device__ long long g_chain_trace[64 * 160 * 4];
 #define CHAIN_STAMP(op_, k_) do { if (wid == 0 && lane == 0 && (op_) < 64 && blockIdx.x < 160) { \
     long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); \
     g_chain_trace[((op_) * 160 + blockIdx.x) * 4 + (k_)] = t_; } } while (0)
-__device__ long long g_tile_trace[2 * 512 * 4];
-#define TILE_STAMP(g_, k_) do { if ((blockIdx.x == 0 || blockIdx.x == 70) && (g_) < 512) { \
-    long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); \
-    g_tile_trace[((blockIdx.x ? 1 : 0) * 512 + (g_)) * 4 + (k_)] = t_; } } while (0)
 #else
 #define CHAIN_STAMP(op_, k_) do { } while (0)
-#define TILE_STAMP(g_, k_) do { } while (0)
 #endif
 
 enum : int { CHAIN_ROTATE = 1, CHAIN_DEPENDS = 2, CHAIN_SAME_INPUT = 4, CHAIN_SIGNAL = 8 };
@@ -331,9 +326,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *_
                 if (!spin_until_gt(&ctrl[0], g)) break;
                 issued_seen = ctrl[0];
             }
-            if (lane == 0 && local == 0) TILE_STAMP(g, 2);
             if (!mbar_wait_bounded(&full[slot], (uint32_t)(lap & 1), CHAIN_NS0, CHAIN_NSMAX)) break;
-            if (lane == 0 && local == 0) TILE_STAMP(g, 3);
             const int b0 = j * R.seg_blocks;
             const int blocks = min(R.seg_blocks, nb - b0);
             const uint8_t *rowp = ring + (size_t)slot * G.slot_bytes + (size_t)(quad * 4 + rr) * row_bytes +
@@ -393,7 +386,6 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *_
             const int ntiles = (rows_here + tr - 1) / tr;
             for (int t = 0; t < ntiles; ++t) {
                 if (g >= G.nslot && !spin_until_eq(&done_cnt[slot], expect_cnt[slot])) return;
-                TILE_STAMP(g, 0);
                 const int r_cnt = min(tr, rows_here - t * tr);
                 done_cnt[slot] = 0;
                 expect_cnt[slot] = ((r_cnt + 3) >> 2) * nseg;
@@ -409,7 +401,6 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *_
                 if (bulk) bulk_g2s(dst, s, bulk, &full[slot], pol);
                 __threadfence_block();
                 ctrl[0] = g + 1;                                    // tile g is armed
-                TILE_STAMP(g, 1);
                 ++g;
                 if (++slot == G.nslot) slot = 0;
             }
