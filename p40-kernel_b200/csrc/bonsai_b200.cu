@@ -438,7 +438,8 @@ int bonsai_b200_chain_create(const bonsai_b200_op *ops, int64_t n_ops, bonsai_b2
     std::vector<ChainOp> rec((size_t)n_ops);
     ChainGeom G{};
     long long slot_payload = 0;
-    int shift = 0, buf = 1, last_user[2] = {-1, -1}, ready_uses[2] = {0, 0};
+    int shift = 0, buf = CHAIN_TABLES - 1, last_user[CHAIN_TABLES], ready_uses[CHAIN_TABLES];
+    for (int b = 0; b < CHAIN_TABLES; ++b) last_user[b] = -1, ready_uses[b] = 0;
     bool any_rotate = false, any_q8 = false;
     unsigned int signals = 0;
     for (int64_t i = 0; i < n_ops; ++i) {
@@ -446,7 +447,12 @@ int bonsai_b200_chain_create(const bonsai_b200_op *ops, int64_t n_ops, bonsai_b2
         ChainOp &r = rec[(size_t)i];
         std::memset(&r, 0, sizeof(r));
         const bool rotate = o.flags & BONSAI_B200_OP_ROTATE, depends = o.flags & BONSAI_B200_OP_DEPENDS;
-        const bool same = o.flags & BONSAI_B200_OP_SAME_INPUT;
+        bool same = o.flags & BONSAI_B200_OP_SAME_INPUT;
+        // the same vector as the op before, and no wait asked for: its tables are reused without being told
+        // (nothing may write x during the launch unless a later reader says OP_DEPENDS)
+        if (!same && i > 0 && !(o.flags & BONSAI_B200_OP_DEPENDS) && ops[i - 1].x == o.x && ops[i - 1].n_in == o.n_in &&
+            ops[i - 1].signs == o.signs && !((ops[i - 1].flags ^ o.flags) & BONSAI_B200_OP_ROTATE))
+            same = true;
         if ((o.flags & ~7u) || o.reserved) return 1;
         if (!o.W || !o.x || !o.y || o.n_out <= 0 || o.n_out > INT32_MAX || o.n_in <= 0) return 1;
         if (o.n_in % 256 != 0 || (rotate && o.n_in % FWHT_N != 0) || o.n_in / 128 > 1024) return 1;
@@ -488,7 +494,7 @@ int bonsai_b200_chain_create(const bonsai_b200_op *ops, int64_t n_ops, bonsai_b2
         r.flags = (rotate ? CHAIN_ROTATE : 0) | (depends ? CHAIN_DEPENDS : 0) | (same ? CHAIN_SAME_INPUT : 0);
         if (depends) rec[(size_t)i - 1].flags |= CHAIN_SIGNAL;     // i > 0: op 0 may not depend
         if (depends && i == 0) return 1;
-        if (!same) buf ^= 1;
+        if (!same) buf = (buf + 1) % CHAIN_TABLES;
         r.buf = buf;
         r.prev_user = same ? -1 : last_user[buf];
         last_user[buf] = (int)i;
@@ -507,6 +513,9 @@ int bonsai_b200_chain_create(const bonsai_b200_op *ops, int64_t n_ops, bonsai_b2
         if (rec[(size_t)i].flags & CHAIN_SIGNAL) ++signals;
     }
     G.stage_blocks = any_q8 ? G.nb_max : 0;
+    G.ntables = any_q8 ? CHAIN_TABLES : 1;
+    if (G.ntables == 1)
+        for (auto &r : rec) r.buf = 0;
     G.rot_blocks = any_rotate ? (G.nb_max / 8 < 7 ? G.nb_max / 8 : 7) : 0;
     G.partial_floats = (int)round_up(G.partial_floats, 4);
     G.quad_ints = (int)round_up(G.quad_ints, 4);

@@ -55,6 +55,9 @@ enum : int { CHAIN_ROTATE = 1, CHAIN_DEPENDS = 2, CHAIN_SAME_INPUT = 4, CHAIN_SI
 
 constexpr int CHAIN_MAX_SLOTS = 16;
 constexpr int CHAIN_OP_RING = 8;
+#ifndef CHAIN_TABLES
+#define CHAIN_TABLES 3             // activation-table buffers: the sequencer prepares this many inputs ahead
+#endif
 #ifndef CHAIN_NS0                 // first and longest sleep between two polls of a wait (a stress build stretches them)
 #define CHAIN_NS0 32
 #define CHAIN_NSMAX 256
@@ -84,13 +87,15 @@ struct ChainGeom {
     int nb_max;               // longest row, in blocks: sizes the tables
     int stage_blocks;         // nb_max if any op takes Q8_1 blocks (staging area of the sequencer), else 0
     int rot_blocks;           // 1024-blocks of rotation scratch (0 if no op rotates)
+    int ntables;              // table buffers in use: CHAIN_TABLES, or 1 when every op rotates its own input (the
+                              // compute warps fill the buffer themselves, after all of them have left the op before)
     int partial_floats;       // per buffer: max rows_per_cta * nseg, multiple of 4
     int quad_ints;            // per buffer: max rows_per_cta / 4, multiple of 4
 };
 
 // Shared-memory bytes before the ring (the host uses the same function).
 __host__ __device__ inline size_t chain_fixed_bytes(const ChainGeom &G) {
-    const size_t b = 384 + CHAIN_OP_RING * sizeof(ChainOp) + 2 * (size_t)G.nb_max * 176 + (size_t)G.stage_blocks * 144 +
+    const size_t b = 384 + CHAIN_OP_RING * sizeof(ChainOp) + (size_t)G.ntables * G.nb_max * 176 + (size_t)G.stage_blocks * 144 +
                      (size_t)G.rot_blocks * 4096 +
                      CHAIN_GATES * (size_t)G.partial_floats * 4 + CHAIN_GATES * (size_t)G.quad_ints * 4;
     return (b + 127) & ~(size_t)127;
@@ -137,7 +142,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *_
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t *full = reinterpret_cast<uint64_t *>(smem);      // [16] tile landed in slot
     uint64_t *ready = full + CHAIN_MAX_SLOTS;                 // [2]  tables of a Q8_1 op are filled
-    uint64_t *xs = ready + 2;                                  // [1]  rotate: every warp has written its blocks
+    uint64_t *xs = ready + CHAIN_TABLES;                                  // [1]  rotate: every warp has written its blocks
     uint64_t *dep = xs + 1;                                   // [1]  rotate: the producers of x have arrived
     uint64_t *stage_full = dep + 1;                           // [1]  Q8_1 staging copy landed
     int *done_cnt = reinterpret_cast<int *>(smem + 192);      // [16] tasks of the slot's tile that have copied out
@@ -148,7 +153,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *_
     uint8_t *p = smem + 384 + CHAIN_OP_RING * sizeof(ChainOp);
     const size_t table_bytes = (size_t)G.nb_max * 176;
     uint8_t *tables = p;
-    p += 2 * table_bytes;
+    p += (size_t)G.ntables * table_bytes;
     uint32_t *stage = reinterpret_cast<uint32_t *>(p);
     p += (size_t)G.stage_blocks * 144;
     float4 *scratch = reinterpret_cast<float4 *>(p);
@@ -163,8 +168,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *_
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < CHAIN_MAX_SLOTS; ++s) mbar_init(&full[s], 1);
-        mbar_init(&ready[0], 1);
-        mbar_init(&ready[1], 1);
+        for (int i = 0; i < CHAIN_TABLES; ++i) mbar_init(&ready[i], 1);
         mbar_init(xs, C);
         mbar_init(dep, 1);
         mbar_init(stage_full, 1);
