@@ -33,6 +33,8 @@ std::atomic<int> g_opt_gemv_variant{-1};
 std::atomic<int> g_opt_gemv_order{0};
 std::atomic<int> g_opt_fuse_linear{0};         // 1: bonsai_b200_linear runs as one kernel when it can (measured slower)
 std::atomic<int> g_opt_chain_threads{512};       // threads per CTA of the chain kernel: 512 (5 blocks per lane and task), 640 (4), 768 (3)
+std::atomic<int> g_opt_chain_spread_nb{64};      // dependent ops with at least this many blocks per row rotate their input
+                                                 // once for the grid instead of once per CTA; 0 = never
 std::atomic<int> g_opt_chain_tile_kb{16};
 std::atomic<int> g_opt_chain_seg{40};            // longest row segment of one task, in blocks: 8, 16, 24, 32 or 40        // target bytes of one ring slot
 std::atomic<int> g_opt_gemm_path{-1};          // -1: by token count, 0: integer SIMT kernel, 1: tensor-core kernel          // 0: streaming kernel (fixed tree order), 1: the host's sequential order
@@ -414,7 +416,8 @@ int bonsai_b200_linear_static(const void *W, const float *x, const float *signs,
 // ---- a list of projections in one persistent launch ------------------------------------------------
 struct bonsai_b200_chain {
     ChainOp *d_ops = nullptr;
-    unsigned int *d_counter = nullptr;
+    unsigned int *d_counter = nullptr;      // [0] arrivals of ops that others wait for, [1] rotated blocks in the image
+    uint8_t *d_image = nullptr;             // activation tables of a spread op, shared through L2
     int n_ops = 0, threads = 0, grid = 0, device = 0;
     size_t smem = 0;
     ChainGeom G{};
@@ -440,7 +443,9 @@ int bonsai_b200_chain_create(const bonsai_b200_op *ops, int64_t n_ops, bonsai_b2
     long long slot_payload = 0;
     int shift = 0, buf = CHAIN_TABLES - 1, last_user[CHAIN_TABLES], ready_uses[CHAIN_TABLES];
     for (int b = 0; b < CHAIN_TABLES; ++b) last_user[b] = -1, ready_uses[b] = 0;
-    bool any_rotate = false, any_q8 = false;
+    bool any_rotate = false, any_q8 = false, any_spread = false;
+    unsigned int spread_total = 0;
+    const int spread_nb = g_opt_chain_spread_nb.load();
     unsigned int signals = 0;
     for (int64_t i = 0; i < n_ops; ++i) {
         const bonsai_b200_op &o = ops[i];
@@ -500,6 +505,12 @@ int bonsai_b200_chain_create(const bonsai_b200_op *ops, int64_t n_ops, bonsai_b2
         last_user[buf] = (int)i;
         if (!same && !rotate) r.ready_parity = ready_uses[buf]++ & 1;
         if (rotate) any_rotate = true; else any_q8 = true;
+        if (rotate && depends && !same && spread_nb > 0 && r.nb >= spread_nb && r.nb / 8 <= sms) {
+            r.flags |= CHAIN_SPREAD;
+            spread_total += (unsigned)(r.nb / 8);
+            r.spread_blocks = spread_total;
+            any_spread = true;
+        }
         if (r.nb > G.nb_max) G.nb_max = r.nb;
         if (r.nseg > 1) {        // only rows in several segments are joined through shared memory
             if (r.rows_per_cta * r.nseg > G.partial_floats) G.partial_floats = r.rows_per_cta * r.nseg;
@@ -549,6 +560,7 @@ int bonsai_b200_chain_create(const bonsai_b200_op *ops, int64_t n_ops, bonsai_b2
     if (e == cudaSuccess && per_sm < 1) e = cudaErrorLaunchOutOfResources;
     if (e == cudaSuccess) e = cudaMalloc(&c->d_ops, sizeof(ChainOp) * (size_t)n_ops);
     if (e == cudaSuccess) e = cudaMalloc(&c->d_counter, 256);
+    if (e == cudaSuccess && any_spread) e = cudaMalloc(&c->d_image, (size_t)G.nb_max * 176);
     if (e == cudaSuccess) e = cudaMemcpy(c->d_ops, rec.data(), sizeof(ChainOp) * (size_t)n_ops, cudaMemcpyHostToDevice);
     if (e != cudaSuccess) {
         bonsai_b200_chain_destroy(c);
@@ -561,7 +573,7 @@ int bonsai_b200_chain_create(const bonsai_b200_op *ops, int64_t n_ops, bonsai_b2
 int bonsai_b200_chain_run(bonsai_b200_chain *c, bonsai_stream stream) {
     if (!c || !c->d_ops) return 1;
     cudaStream_t st = as_stream(stream);
-    cudaError_t e = cudaMemsetAsync(c->d_counter, 0, sizeof(unsigned int), st);
+    cudaError_t e = cudaMemsetAsync(c->d_counter, 0, 2 * sizeof(unsigned int), st);
     if (e != cudaSuccess) return (int)e;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)c->grid);
@@ -574,7 +586,7 @@ int bonsai_b200_chain_run(bonsai_b200_chain *c, bonsai_stream stream) {
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     const ChainOp *ops = c->d_ops;
-    auto go = [&](auto kernel) { return cudaLaunchKernelEx(&cfg, kernel, ops, c->n_ops, c->G, c->d_counter); };
+    auto go = [&](auto kernel) { return cudaLaunchKernelEx(&cfg, kernel, ops, c->n_ops, c->G, c->d_counter, c->d_image); };
     if (c->threads == 768) e = go(gemv_chain_kernel<768, 3>);
     else if (c->threads == 640) e = go(gemv_chain_kernel<640, 4>);
     else e = go(gemv_chain_kernel<512, 5>);
@@ -585,6 +597,7 @@ int bonsai_b200_chain_destroy(bonsai_b200_chain *c) {
     if (!c) return 0;
     cudaError_t e1 = c->d_ops ? cudaFree(c->d_ops) : cudaSuccess;
     cudaError_t e2 = c->d_counter ? cudaFree(c->d_counter) : cudaSuccess;
+    if (c->d_image) cudaFree(c->d_image);
     delete c;
     return (int)(e1 != cudaSuccess ? e1 : e2);
 }
@@ -724,6 +737,11 @@ int bonsai_b200_set_option(const char *key, int64_t value) {
     if (!std::strcmp(key, "chain_seg")) {
         if (value < 8 || value > 8 * STREAM_STEPS || value % 8 != 0) return 1;
         g_opt_chain_seg.store((int)value);
+        return 0;
+    }
+    if (!std::strcmp(key, "chain_spread_nb")) {
+        if (value < 0) return 1;
+        g_opt_chain_spread_nb.store((int)value);
         return 0;
     }
     if (!std::strcmp(key, "chain_tile_kb")) {

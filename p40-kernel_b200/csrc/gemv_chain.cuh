@@ -51,7 +51,7 @@ __device__ long long g_chain_trace[64 * 160 * 4];
 #define CHAIN_STAMP(op_, k_) do { } while (0)
 #endif
 
-enum : int { CHAIN_ROTATE = 1, CHAIN_DEPENDS = 2, CHAIN_SAME_INPUT = 4, CHAIN_SIGNAL = 8 };
+enum : int { CHAIN_ROTATE = 1, CHAIN_DEPENDS = 2, CHAIN_SAME_INPUT = 4, CHAIN_SIGNAL = 8, CHAIN_SPREAD = 16 };
 
 constexpr int CHAIN_MAX_SLOTS = 16;
 constexpr int CHAIN_OP_RING = 8;
@@ -77,7 +77,8 @@ struct __align__(16) ChainOp {                 // 128 bytes, one per projection,
     int buf;                                   // table buffer (0 / 1) this op reads
     int ready_parity;                          // phase parity of ready[buf] (Q8_1 ops that fill a buffer)
     int prev_user;                             // last op that read the previous contents of buf, or -1
-    int pad[9];
+    uint32_t spread_blocks;                    // CHAIN_SPREAD: 1024-blocks rotated by spread ops up to and including this one
+    int pad[8];
 };
 static_assert(sizeof(ChainOp) == 128, "op records are copied as 32 words");
 
@@ -137,7 +138,8 @@ __device__ __forceinline__ bool grid_counter_wait(const unsigned int *counter, u
 
 template <int THREADS, int MAXSTEPS>
 __global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *__restrict__ ops, const int n_ops,
-                                                                const ChainGeom G, unsigned int *grid_counter) {
+                                                                const ChainGeom G, unsigned int *grid_counter,
+                                                                uint8_t *table_image) {
     constexpr int C = THREADS / 32 - 2;         // compute warps
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t *full = reinterpret_cast<uint64_t *>(smem);      // [16] tile landed in slot
@@ -245,17 +247,25 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *_
                             ++dep_phase;
                         }
                         CHAIN_STAMP(op, 1);
-                        uint32_t *act_q = reinterpret_cast<uint32_t *>(tables + (size_t)R.buf * table_bytes);
+                        // Wide inputs of dependent ops are rotated ONCE for the whole grid instead of once per CTA
+                        // (every CTA repeating 17 blocks costs ~10 us): block fb is rotated by CTA fb, which writes
+                        // its part of the tables to an image in global memory; a second arrival counter tells
+                        // everybody when all blocks are there, and every CTA copies the image into its tables.
+                        const bool spread = flags & CHAIN_SPREAD;
+                        uint8_t *own = tables + (size_t)R.buf * table_bytes;
+                        uint32_t *act_q = reinterpret_cast<uint32_t *>(spread ? table_image : own);
                         float *act_s = reinterpret_cast<float *>(act_q + (size_t)G.nb_max * STREAM_ACT_WORDS);
                         int *act_i = reinterpret_cast<int *>(act_s + (size_t)G.nb_max * 4);
                         const float *x = static_cast<const float *>(R.x);
                         const float *signs = R.signs;
                         const int nfb = R.nb >> 3;
+                        const int fb_lo = spread ? min((int)blockIdx.x, nfb) : 0;
+                        const int fb_hi = spread ? min((int)blockIdx.x + 1, nfb) : nfb;
                         // One warp per 128-element slice, G.rot_blocks 1024-blocks per round trip through
                         // the scratch area: front butterflies, meet, back butterflies + quantiser, meet.
                         bool ok = true;
-                        for (int fb0 = 0; fb0 < nfb && ok; fb0 += G.rot_blocks) {
-                            const int units = min(G.rot_blocks, nfb - fb0) * 8;
+                        for (int fb0 = fb_lo; fb0 < fb_hi && ok; fb0 += G.rot_blocks) {
+                            const int units = min(G.rot_blocks, fb_hi - fb0) * 8;
                             // all of this warp's loads first (they come from L2: written by other SMs
                             // during this launch), then the butterflies
                             constexpr int UPW = (7 * 8 + C - 1) / C;           // units per warp and round trip
@@ -298,12 +308,38 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *_
                                 }
                             }
                             CHAIN_STAMP(op, 3);
+                            if (spread) __threadfence();                // the image rows written above, before the arrival below
                             __syncwarp();
                             if (lane == 0) mbar_arrive(xs);
                             ok = mbar_wait_bounded(xs, xs_phase & 1u, CHAIN_NS0, CHAIN_NSMAX);
                             ++xs_phase;
                         }
                         if (!ok) { alive = false; break; }
+                        if (spread) {
+                            if (wid == 0) {
+                                bool there = true;
+                                if (lane == 0) {
+                                    if (fb_lo < fb_hi) {                // this CTA's block is in the image (every warp has fenced)
+                                        __threadfence();
+                                        atomicAdd(grid_counter + 1, (unsigned)(fb_hi - fb_lo));
+                                    }
+                                    there = grid_counter_wait(grid_counter + 1, R.spread_blocks);
+                                }
+                                __syncwarp();
+                                if (lane == 0 && there) mbar_arrive(dep);
+                            }
+                            if (!mbar_wait_bounded(dep, dep_phase & 1u, CHAIN_NS0, CHAIN_NSMAX)) { alive = false; break; }
+                            ++dep_phase;
+                            // image -> this CTA's tables (written by other SMs during this launch: read at L2)
+                            const uint4 *src16 = reinterpret_cast<const uint4 *>(table_image);
+                            uint4 *dst16 = reinterpret_cast<uint4 *>(own);
+                            const int n16 = (int)(table_bytes >> 4);
+                            for (int i = wid * 32 + lane; i < n16; i += C * 32) dst16[i] = __ldcg(src16 + i);
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(xs);
+                            if (!mbar_wait_bounded(xs, xs_phase & 1u, CHAIN_NS0, CHAIN_NSMAX)) { alive = false; break; }
+                            ++xs_phase;
+                        }
                     } else {
                         if (!mbar_wait_bounded(&ready[R.buf], (uint32_t)R.ready_parity, CHAIN_NS0, CHAIN_NSMAX)) { alive = false; break; }
                     }
