@@ -441,7 +441,19 @@ int bonsai_b200_chain_create(const bonsai_b200_op *ops, int64_t n_ops, bonsai_b2
     std::vector<ChainOp> rec((size_t)n_ops);
     ChainGeom G{};
     long long slot_payload = 0;
-    int shift = 0, buf = CHAIN_TABLES - 1, last_user[CHAIN_TABLES], ready_uses[CHAIN_TABLES];
+    // Table buffers: a third one lets the sequencer prepare two inputs ahead, which pays when most ops bring
+    // their own Q8_1 vector; lists whose ops mostly share inputs keep the shared memory for the ring instead.
+    int q8_ops = 0, q8_fills = 0;
+    for (int64_t i = 0; i < n_ops; ++i) {
+        if (ops[i].flags & BONSAI_B200_OP_ROTATE) continue;
+        ++q8_ops;
+        const bool shared = (ops[i].flags & BONSAI_B200_OP_SAME_INPUT) ||
+                            (i > 0 && ops[i - 1].x == ops[i].x && ops[i - 1].n_in == ops[i].n_in &&
+                             !(ops[i - 1].flags & BONSAI_B200_OP_ROTATE));
+        if (!shared) ++q8_fills;
+    }
+    const int ntables = q8_ops == 0 ? 1 : (2 * q8_fills > q8_ops ? CHAIN_TABLES : 2);
+    int shift = 0, buf = ntables - 1, last_user[CHAIN_TABLES], ready_uses[CHAIN_TABLES];
     for (int b = 0; b < CHAIN_TABLES; ++b) last_user[b] = -1, ready_uses[b] = 0;
     bool any_rotate = false, any_q8 = false, any_spread = false;
     unsigned int spread_total = 0;
@@ -499,7 +511,7 @@ int bonsai_b200_chain_create(const bonsai_b200_op *ops, int64_t n_ops, bonsai_b2
         r.flags = (rotate ? CHAIN_ROTATE : 0) | (depends ? CHAIN_DEPENDS : 0) | (same ? CHAIN_SAME_INPUT : 0);
         if (depends) rec[(size_t)i - 1].flags |= CHAIN_SIGNAL;     // i > 0: op 0 may not depend
         if (depends && i == 0) return 1;
-        if (!same) buf = (buf + 1) % CHAIN_TABLES;
+        if (!same) buf = (buf + 1) % ntables;
         r.buf = buf;
         r.prev_user = same ? -1 : last_user[buf];
         last_user[buf] = (int)i;
@@ -524,9 +536,7 @@ int bonsai_b200_chain_create(const bonsai_b200_op *ops, int64_t n_ops, bonsai_b2
         if (rec[(size_t)i].flags & CHAIN_SIGNAL) ++signals;
     }
     G.stage_blocks = any_q8 ? G.nb_max : 0;
-    G.ntables = any_q8 ? CHAIN_TABLES : 1;
-    if (G.ntables == 1)
-        for (auto &r : rec) r.buf = 0;
+    G.ntables = ntables;
     G.rot_blocks = any_rotate ? (G.nb_max / 8 < 7 ? G.nb_max / 8 : 7) : 0;
     G.partial_floats = (int)round_up(G.partial_floats, 4);
     G.quad_ints = (int)round_up(G.quad_ints, 4);
