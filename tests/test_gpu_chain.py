@@ -238,3 +238,58 @@ def test_shorter_segments_match_the_per_matrix_tiling(gpu, port, seg, variant):
         gpu.set_option("chain_seg", 40)
         gpu.set_option("gemv_variant", -1)
     assert gpu.device_status() == 0
+
+
+@pytest.mark.parametrize("seed", [1, 2])
+def test_random_lists_with_dependencies(gpu, port, threads, seed):
+    """Random lists: Q8_1 and fp32 inputs, shared inputs, ops that read earlier ops' outputs (of any
+    width, so wide inputs take the rotate-once-for-the-grid path too).  Dependencies only point
+    backwards, so the same ops issued one by one through the per-matrix entry points are the answer."""
+    import torch
+    rng = np.random.default_rng(seed)
+    widths = [1024, 2048, 5120, 6144, 9216, 17408]
+    ext = {w: dev(synth.activations(w, seed=seed * 100 + w)) for w in widths}          # vectors from outside the list
+    ext_q = {w: dev(port.quantize_q8_1(synth.activations(w, seed=seed * 100 + w + 1), True)) for w in widths}
+    produced = {}                                   # width -> (chain buffer, reference buffer) written by an earlier op
+    scratch = torch.zeros(max(widths) // 32 * 36, dtype=torch.uint8, device="cuda")
+    ops, refs = [], []
+    prev = None
+    for i in range(40):
+        if prev is not None and rng.random() < 0.2:
+            kind, n_in, x, x_ref = prev                                  # same input as the op before
+            flags = (gpu.OP_ROTATE if kind != "q8" else 0) | gpu.OP_SAME_INPUT
+        else:
+            n_in = int(rng.choice(list(produced) if produced and rng.random() < 0.5 else [1024, 1024, 2048, 2048, 5120, 6144]))
+            if n_in in produced and rng.random() < 0.7:
+                kind, (x, x_ref), flags = "dep", produced[n_in], gpu.OP_ROTATE | gpu.OP_DEPENDS
+            elif rng.random() < 0.5:
+                kind, x, x_ref, flags = "q8", ext_q[n_in], ext_q[n_in], 0
+            else:
+                kind, x, x_ref, flags = "rot", ext[n_in], ext[n_in], gpu.OP_ROTATE
+        if n_in <= 2048 and rng.random() < 0.5:
+            n_out = int(rng.choice([9216, 17408]))                       # wide outputs only from narrow inputs: small matrices
+        elif rng.random() < 0.5:
+            n_out = int(rng.choice([1024, 2048, 5120, 6144]))
+        else:
+            n_out = int(rng.integers(1, 700))
+        W = dev(synth.pq2_0_weights(n_out, n_in, seed=seed * 1000 + i))
+        y, y_ref = torch.zeros(n_out, device="cuda"), torch.zeros(n_out, device="cuda")
+        if kind == "q8":
+            assert gpu.gemv(W, x_ref, y_ref, n_out, n_in) == 0
+        else:
+            assert gpu.linear(W, x_ref, None, y_ref, scratch, n_out, n_in) == 0
+        ops.append((W, x, None, y, n_out, n_in, flags))
+        refs.append(y_ref)
+        if n_out in widths:
+            produced[n_out] = (y, y_ref)
+        prev = (kind, n_in, x, x_ref)
+    chain = gpu.Chain(ops)
+    for _ in range(2):
+        for op in ops:
+            op[3].fill_(-3.0)
+        assert chain.run() == 0
+        torch.cuda.synchronize()
+        for i, (op, want) in enumerate(zip(ops, refs)):
+            assert np.array_equal(bits(host(op[3])), bits(host(want))), (i, op[4], op[5], op[6])
+    chain.close()
+    assert gpu.device_status() == 0
