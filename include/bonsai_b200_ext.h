@@ -113,7 +113,9 @@ int bonsai_b200_device_status(void);
  *                              only when every row of every earlier op is in memory.  Needs OP_ROTATE
  *                              (ops write fp32).  Without this flag an op may start at any time, so x
  *                              must not be an output of the list.
- *   BONSAI_B200_OP_SAME_INPUT  same x (and kind) as the previous op: its quantised vector is reused.
+ *   BONSAI_B200_OP_SAME_INPUT  same x (and kind) as the previous op: its quantised vector is reused.  An op that
+ *                              names the same x, n_in, signs and kind as the op before it and does not say
+ *                              OP_DEPENDS is treated this way without the flag.
  * Shapes: n_in a multiple of 256 (of 1024 with OP_ROTATE), W and x 16-byte aligned.
  * create() allocates a small device table (cudaMalloc) and copies the list; run() allocates nothing,
  * launches one cooperative kernel of one CTA per SM on `stream` (plus a 4-byte memset) and can be
