@@ -62,6 +62,10 @@ constexpr int CHAIN_OP_RING = 8;
 #define CHAIN_NS0 32
 #define CHAIN_NSMAX 256
 #endif
+#ifndef CHAIN_GATE_NS0            // ... of the waits that usually last microseconds (a warp that ran ahead of the others, a
+#define CHAIN_GATE_NS0 32         // table buffer still being read): every poll costs issue slots the working warps want
+#define CHAIN_GATE_NSMAX 256
+#endif
 constexpr int CHAIN_GATES = 3;           // a warp may run this many ops ahead of the slowest one
 
 struct __align__(16) ChainOp {                 // 128 bytes, one per projection, device table
@@ -102,12 +106,13 @@ __host__ __device__ inline size_t chain_fixed_bytes(const ChainGeom &G) {
     return (b + 127) & ~(size_t)127;
 }
 
-__device__ __forceinline__ bool spin_until_gt(volatile int *p, int v) {
-    uint32_t ns = CHAIN_NS0;
+__device__ __forceinline__ bool spin_until_gt(volatile int *p, int v, uint32_t first_ns = CHAIN_NS0,
+                                              uint32_t max_ns = CHAIN_NSMAX) {
+    uint32_t ns = first_ns;
     for (uint32_t n = 0; n < (1u << 22); ++n) {
         if (*p > v) return true;
         __nanosleep(ns);
-        ns = min(ns * 2, (uint32_t)CHAIN_NSMAX);
+        ns = min(ns * 2, max_ns);
     }
     atomicExch(&g_device_status, STATUS_MBARRIER_TIMEOUT);
     return false;
@@ -225,8 +230,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *_
                 if (op >= n_ops) { alive = false; break; }
                 // ---- enter op `op`
                 CHAIN_STAMP(op, 0);
-                if (!spin_until_gt(&ctrl[1], op)) { alive = false; break; }
-                if (op >= CHAIN_GATES && !spin_until_gt(&ctrl[8], op - CHAIN_GATES)) { alive = false; break; }
+                if (!spin_until_gt(&ctrl[1], op, CHAIN_GATE_NS0, CHAIN_GATE_NSMAX)) { alive = false; break; }
+                if (op >= CHAIN_GATES && !spin_until_gt(&ctrl[8], op - CHAIN_GATES, CHAIN_GATE_NS0, CHAIN_GATE_NSMAX)) { alive = false; break; }
                 const ChainOp &R = opring[op & (CHAIN_OP_RING - 1)];
                 flags = R.flags;
                 cta_rows(R, row0, rows_here);
@@ -341,7 +346,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *_
                             ++xs_phase;
                         }
                     } else {
-                        if (!mbar_wait_bounded(&ready[R.buf], (uint32_t)R.ready_parity, CHAIN_NS0, CHAIN_NSMAX)) { alive = false; break; }
+                        if (!mbar_wait_bounded(&ready[R.buf], (uint32_t)R.ready_parity, CHAIN_GATE_NS0, CHAIN_GATE_NSMAX)) { alive = false; break; }
                     }
                 }
                 CHAIN_STAMP(op, 2);
@@ -453,7 +458,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *_
         const uint64_t pol = policy_evict_first();
         auto see_gates = [&](int upto) {    // waits until every compute warp has left ops [0, upto]
             if (gate_seen > upto) return true;
-            if (!spin_until_gt(&ctrl[8], upto)) return false;
+            if (!spin_until_gt(&ctrl[8], upto, CHAIN_GATE_NS0, CHAIN_GATE_NSMAX)) return false;
             gate_seen = ctrl[8];
             return true;
         };
