@@ -521,28 +521,42 @@ def _graph_time(torch, fn, steps, warmup):
 
 
 def run_decode_step(args):
-    """BASELINE config 2: the chain of 401 projections of one decoded token, each the rotation +
-    Q8_1 quantiser of a resident fp32 vector of its input width followed by the mat-vec (one fused kernel) (the values do not flow from one mat-vec to
-    the next; stream order does), replayed as one CUDA graph.  Reports tokens/s and weight GB/s."""
+    """BASELINE config 2: the 401 projections of one decoded token, each the rotation + Q8_1 quantiser of a
+    resident fp32 vector of its input width followed by the mat-vec (the values do not flow from one
+    projection to the next; the waits do), replayed as one CUDA graph.  Reports tokens/s and weight GB/s.
+    With N > 1 every matrix is split by output rows and every projection is followed by the all-gather of
+    its output (per-matrix calls: a list launch cannot span a collective, and one launch per group of
+    projections that share an input measured slower, 82 against 127 tokens/s at N = 2)."""
     import torch
     import bonsai_b200 as bb
-    torch.cuda.set_device(0)
+    from bonsai_b200 import partition
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     bb.lib()
     bb.set_option("pdl", max(args.pdl, 0))
     shapes = model_gemvs()
-    ws, first = [], 0
+    ws, rows_of, first = [], [], 0
     for n_in, n_out in shapes:
-        nblk = n_out * (n_in // 128)
-        W = torch.empty(nblk * 34, dtype=torch.uint8, device="cuda")
-        assert bb.synth_pq2_0(W, first, nblk, args.seed) == 0
-        first += nblk
+        lo, hi = partition.row_slice(n_out, rank, world)
+        nblk_row = n_in // 128
+        W = torch.empty((hi - lo) * nblk_row * 34, dtype=torch.uint8, device="cuda")
+        assert bb.synth_pq2_0(W, first + lo * nblk_row, (hi - lo) * nblk_row, args.seed) == 0
+        first += n_out * nblk_row
         ws.append(W)
-    xs = {k: torch.randn(k, device="cuda") for k in {a for a, _ in shapes}}
+        rows_of.append(hi - lo)
+    g = torch.Generator(device="cpu").manual_seed(args.seed)
+    xs = {k: torch.randn(k, generator=g).cuda() for k in sorted({a for a, _ in shapes})}
     xq = {k: torch.empty(k // 32 * 36, dtype=torch.uint8, device="cuda") for k in xs}
     ys = {n: torch.empty(n, device="cuda") for n in {b for _, b in shapes}}
 
     launches_per_token = len(shapes)
-    if args.call == "list":
+    if args.call == "list" and world == 1:
         # one launch per token: projections that read the same vector share its quantised form, every
         # other projection waits for all rows of the projections before it (its input is an output
         # of the step in the real model; here the values do not flow, the waits do)
@@ -558,28 +572,46 @@ def run_decode_step(args):
             assert chain.run() == 0
     else:
         def token():
-            for (n_in, n_out), W in zip(shapes, ws):
-                bb.linear(W, xs[n_in], None, ys[n_out], xq[n_in], n_out, n_in)   # rotation + quantiser + mat-vec
+            for i, ((n_in, n_out), W) in enumerate(zip(shapes, ws)):
+                r = rows_of[i]
+                ysl = ys[n_out][rank * r:(rank + 1) * r]
+                bb.linear(W, xs[n_in], None, ysl, xq[n_in], r, n_in)    # rotation + quantiser + mat-vec
+                if world > 1:
+                    dist.all_gather_into_tensor(ys[n_out], ysl)
 
     steps = max(3, min(args.steps, 50))
-    sampler = ClockSampler(0)
+    warm = max(3, min(args.warmup, 5))
+    sampler = ClockSampler(local)
     sampler.start()
-    ms = _graph_time(torch, token, steps, max(3, min(args.warmup, 5)))
+    if dist is not None:
+        dist.barrier()
+        torch.cuda.synchronize()
+    ms = _graph_time(torch, token, steps, warm)
     clocks = sampler.result()
+    if dist is not None:
+        t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
     wbytes = sum(weight_bytes(a, b) for a, b in shapes)
     peak, peak_kind = measured_peak_gbs()
     gbs = wbytes / (ms * 1e-3) / 1e9
-    print(json.dumps({
-        "metric": "decode_tokens_per_s", "value": 1e3 / ms, "unit": "tokens/s", "n_gpus": 1, "steps": steps,
-        "warmup": max(3, min(args.warmup, 5)), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "int8xint2->int32, fp32 scale", "data": "synthetic",
-        "config": {"workload": "decode_step", "matvecs": len(shapes), "weight_bytes": wbytes, "batch": 1, "pdl": args.pdl,
-                   "l2": "inputs larger than L2", "launch": "cuda_graph_per_step",
-                   "call": "bonsai_b200_chain_run, one launch per token" if args.call == "list" else "bonsai_b200_linear per matrix"},
-        "gpu_launches": launches_per_token * steps, "clocks": clocks,
-        "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak,
-                     "peak_kind": peak_kind, "traffic": None},
-        "device_status": bb.device_status()}))
+    status = bb.device_status()
+    if rank == 0:
+        call = ("bonsai_b200_chain_run, one launch per token" if args.call == "list" and world == 1 else
+                "bonsai_b200_linear per matrix" + (", then an all-gather" if world > 1 else ""))
+        print(json.dumps({
+            "metric": "decode_tokens_per_s", "value": 1e3 / ms, "unit": "tokens/s", "n_gpus": world, "steps": steps,
+            "warmup": warm, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong" if world > 1 else "weak",
+            "vs_baseline": None, "dtype": "int8xint2->int32, fp32 scale", "data": "synthetic",
+            "config": {"workload": "decode_step", "matvecs": len(shapes), "weight_bytes": wbytes, "batch": 1, "pdl": args.pdl,
+                       "l2": "inputs larger than L2", "launch": "cuda_graph_per_step", "call": call,
+                       "parallelism": f"rows/{world}+allgather" if world > 1 else "single"},
+            "gpu_launches": launches_per_token * steps, "clocks": clocks,
+            "roofline": {"bound": "hbm", "achieved": gbs / world, "peak": peak, "unit": "GB/s", "frac": gbs / world / peak,
+                         "peak_kind": peak_kind, "traffic": None},
+            "device_status": status}))
+    if dist is not None:
+        dist.destroy_process_group()
 
 
 def run_prefill(args):
@@ -614,9 +646,29 @@ def run_prefill(args):
     tops = ops / (ms * 1e-3) / 1e12
     try:
         bf16 = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"])
-        peak, kind = 2.0 * bf16, "2 x measured dense bf16 (no int8 figure is measured on this pool)"
+        peak, kind = 2.0 * bf16, "2 x measured dense bf16"
     except Exception:
         peak, kind = 2.0 * 1590.0, "2 x fallback dense bf16"
+    # a dense int8 figure measured here, for reference beside the denominator above: the library's int8
+    # mat-mul (cuBLASLt through torch._int_mm) on 8192^3, best of 10 -- a measuring stick, not on the path
+    int8_lib = None
+    try:
+        n = 8192
+        a = torch.randint(-3, 4, (n, n), dtype=torch.int8, device="cuda")
+        b = torch.randint(-3, 4, (n, n), dtype=torch.int8, device="cuda").t()
+        for _ in range(3):
+            torch._int_mm(a, b)
+        best = 1e9
+        for _ in range(10):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            torch._int_mm(a, b)
+            e1.record()
+            torch.cuda.synchronize()
+            best = min(best, e0.elapsed_time(e1))
+        int8_lib = 2.0 * n ** 3 / (best * 1e-3) / 1e12
+    except Exception:
+        pass
     print(json.dumps({
         "metric": "pq2_0_prefill_gemm", "value": tops, "unit": "TOPS", "n_gpus": 1, "steps": steps,
         "warmup": max(3, min(args.warmup, 5)), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
@@ -625,7 +677,7 @@ def run_prefill(args):
                    "launch": "cuda_graph_per_step"},
         "gpu_launches": 4 * steps, "clocks": clocks,
         "roofline": {"bound": "tensor", "achieved": tops, "peak": peak, "unit": "TOPS", "frac": tops / peak,
-                     "peak_kind": kind, "traffic": None},
+                     "peak_kind": kind, "traffic": None, "library_int8_dense_tops_measured": int8_lib},
         "device_status": bb.device_status()}))
 
 
