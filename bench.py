@@ -238,7 +238,16 @@ def run_b200(args):
         off += m[2]
     y_local = torch.zeros(off, dtype=torch.float32, device="cuda")
     y_gathered = torch.zeros(world * off, dtype=torch.float32, device="cuda") if world > 1 else None
-    chain = chain_e2e = None
+    chain = chain_e2e = chain_tp = peer_buf = None
+    if use_list and world > 1 and args.gather == "peer":
+        # the gathered outputs live in a buffer that every rank has mapped (CUDA IPC): the kernel's epilogue stores
+        # each y element into every rank's copy, so there is no collective at all
+        from bonsai_b200.peer import PeerBuffer
+        peer_buf = PeerBuffer(world * off * 4, dist, rank, world)
+        y_peer = peer_buf.tensor.view(torch.float32)
+        chain_tp = bb.Chain([(W, xq[n_in], None, y_peer[rank * off + o:rank * off + o + rows], rows, n_in,
+                              bb.OP_SAME_INPUT if i and mats[i - 1][0] == n_in else 0)
+                             for i, ((n_in, n_out, rows, W, y), o) in enumerate(zip(mats, slice_off))], peers=peer_buf)
     if use_list:
         # consecutive matrices that read the same resident Q8_1 vector say so (its shared-memory copy is reused)
         chain = bb.Chain([(W, xq[n_in], None, y_local[o:o + rows], rows, n_in,
@@ -252,6 +261,9 @@ def run_b200(args):
                               for (n_in, n_out, rows, W, y), o, xo in zip(mats, slice_off, x_off)])
 
     def step_list():
+        if chain_tp is not None:
+            assert chain_tp.run() == 0
+            return 1
         assert chain.run() == 0
         if world > 1:
             dist.all_gather_into_tensor(y_gathered, y_local)
@@ -411,7 +423,7 @@ def run_b200(args):
         per_matrix = {"call": "bonsai_p40_gemv per matrix", "value": total_w * e2e_steps / (ms_m * 1e-3) / 1e9,
                       "unit": UNIT, "ms_per_step": ms_m / e2e_steps, "gpu_launches_per_step": launches_m // e2e_steps}
     split = None
-    if use_list and world > 1:      # where the step's time goes: the mat-vec launch alone, the all-gather alone
+    if use_list and world > 1 and chain_tp is None:      # where the step's time goes: the mat-vec launch alone, the all-gather alone
         def only_matvec():
             assert chain.run() == 0
             return 1
@@ -440,7 +452,9 @@ def run_b200(args):
         "vs_baseline": None, "dtype": "int8xint2->int32, fp32 scale", "data": "synthetic",
         "config": {"workload": "layer_sweep", "shapes_nin_nout": LAYER_SHAPES, "batch": 1, "sets": sets,
                    "resident_weight_bytes": total_w, "l2": "inputs larger than L2" if total_w > 126e6 else "fits L2",
-                   "parallelism": f"rows/{world}+allgather" if world > 1 else "single", "pdl": args.pdl,
+                   "parallelism": ("single" if world == 1 else f"rows/{world}, outputs stored into every rank's buffer by the "
+                                   "kernel (peer-mapped memory, no collective)" if chain_tp is not None
+                                   else f"rows/{world}+allgather"), "pdl": args.pdl,
                    "fp32_order": "host-sequential" if args.order == 1 else "fixed-tree", "variant": args.variant,
                    "launch": "eager" if args.no_graph else "cuda_graph_per_step",
                    "call": "bonsai_b200_chain_run: the step's mat-vecs as one persistent launch" if use_list
@@ -479,6 +493,9 @@ def run_b200(args):
                                                  "sample": f"1 layer sweep in {dt1:.2f} s"}
     if rank == 0:
         print(json.dumps(line))
+    if peer_buf is not None:
+        chain_tp.close()
+        peer_buf.close(dist)
     if dist is not None:
         dist.destroy_process_group()
 
@@ -556,7 +573,30 @@ def run_decode_step(args):
     ys = {n: torch.empty(n, device="cuda") for n in {b for _, b in shapes}}
 
     launches_per_token = len(shapes)
-    if args.call == "list" and world == 1:
+    peer_buf = None
+    if args.call == "list" and world > 1 and args.gather == "peer":
+        # one launch per token and rank: every rank multiplies its rows of every projection and stores them into
+        # every rank's copy of the output vectors; a projection that waits, waits for the rows of every rank
+        from bonsai_b200.peer import PeerBuffer
+        outs = sorted({b for _, b in shapes})
+        base, off = {}, 0
+        for n in outs:
+            base[n] = off
+            off += n
+        peer_buf = PeerBuffer(off * 4, dist, rank, world)
+        y_peer = peer_buf.tensor.view(torch.float32)
+        ops, prev = [], None
+        for i, ((n_in, n_out), W) in enumerate(zip(shapes, ws)):
+            r = rows_of[i]
+            fl = bb.OP_ROTATE | (bb.OP_SAME_INPUT if prev == n_in and i else (bb.OP_DEPENDS if i else 0))
+            ops.append((W, xs[n_in], None, y_peer[base[n_out] + rank * r:base[n_out] + (rank + 1) * r], r, n_in, fl))
+            prev = n_in
+        chain = bb.Chain(ops, peers=peer_buf)
+        launches_per_token = 1
+
+        def token():
+            assert chain.run() == 0
+    elif args.call == "list" and world == 1:
         # one launch per token: projections that read the same vector share its quantised form, every
         # other projection waits for all rows of the projections before it (its input is an output
         # of the step in the real model; here the values do not flow, the waits do)
@@ -597,7 +637,8 @@ def run_decode_step(args):
     gbs = wbytes / (ms * 1e-3) / 1e9
     status = bb.device_status()
     if rank == 0:
-        call = ("bonsai_b200_chain_run, one launch per token" if args.call == "list" and world == 1 else
+        call = ("bonsai_b200_chain_run, one launch per token" + (" and rank, outputs stored into every rank's buffer "
+                "by the kernel" if world > 1 else "") if launches_per_token == 1 else
                 "bonsai_b200_linear per matrix" + (", then an all-gather" if world > 1 else ""))
         print(json.dumps({
             "metric": "decode_tokens_per_s", "value": 1e3 / ms, "unit": "tokens/s", "n_gpus": world, "steps": steps,
@@ -610,6 +651,9 @@ def run_decode_step(args):
             "roofline": {"bound": "hbm", "achieved": gbs / world, "peak": peak, "unit": "GB/s", "frac": gbs / world / peak,
                          "peak_kind": peak_kind, "traffic": None},
             "device_status": status}))
+    if peer_buf is not None:
+        chain.close()
+        peer_buf.close(dist)
     if dist is not None:
         dist.destroy_process_group()
 
@@ -724,6 +768,9 @@ def main():
     ap.add_argument("--call", default="list", choices=["list", "matrix"],
                     help="list (default): the step's mat-vecs as one persistent launch (bonsai_b200_chain_run); "
                          "matrix: one bonsai_p40_gemv launch per matrix")
+    ap.add_argument("--gather", default="peer", choices=["peer", "nccl"],
+                    help="N > 1, list mode: peer = the kernel stores its outputs into every rank's buffer (CUDA IPC "
+                         "mapping, no collective); nccl = one all-gather per step")
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--pdl", type=int, default=1, help="0 plain launches, 1 programmatic launches (weights of the next "
                     "mat-vec stream while the previous kernel drains)")

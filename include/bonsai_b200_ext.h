@@ -137,6 +137,19 @@ typedef struct bonsai_b200_chain bonsai_b200_chain;
 int bonsai_b200_chain_create(const bonsai_b200_op *ops, int64_t n_ops, bonsai_b200_chain **out);
 int bonsai_b200_chain_run(bonsai_b200_chain *chain, bonsai_stream stream);
 int bonsai_b200_chain_destroy(bonsai_b200_chain *chain);
+/* The same list over the row slices of several GPUs (one process and one chain per GPU; no reference counterpart,
+ * the reference is single-GPU).  Every rank passes the same list with ITS rows of every matrix (W, n_out of the
+ * slice) and y pointing at its slice inside a buffer that every rank has allocated with the same layout and mapped
+ * into every other rank (CUDA IPC or any other peer mapping): peer_base[q] is rank q's buffer as addressed from
+ * this process (peer_base[rank] is the local one).  The kernel stores every y element it produces into all `world`
+ * buffers, so each rank ends up with the whole vector without a collective, and OP_DEPENDS waits for every row of
+ * every rank.  64 bytes at counter_offset (a multiple of 64) inside the buffer are the kernel's arrival counters:
+ * zero them once after allocation and never touch them again.  All ranks must call run() the same number of times;
+ * the launches of different ranks wait for each other (bounded: a rank that never comes makes the others give up
+ * after about a second and set the status word), so each rank needs its own GPU.  Reading the outputs on the host
+ * needs the usual ordering between ranks: a peer's next run() overwrites them. */
+int bonsai_b200_chain_create_tp(const bonsai_b200_op *ops, int64_t n_ops, int rank, int world,
+                                const void *const *peer_base, int64_t counter_offset, bonsai_b200_chain **out);
 /* kernels launched so far by run() on this chain's behalf, and its geometry (threads per CTA, ring
  * slots, bytes per slot, CTAs): for benchmarks and tests. */
 int bonsai_b200_chain_info(const bonsai_b200_chain *chain, int64_t out[4]);

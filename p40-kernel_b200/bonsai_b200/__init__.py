@@ -42,6 +42,7 @@ SIGNATURES = {
     "bonsai_b200_synth_pq2_0": (_INT, [_VP, _I64, _I64, _U64, _VP]),
     "bonsai_b200_stream_probe": (_INT, [_VP, _I64, _INT, _VP, _VP]),
     "bonsai_b200_chain_create": (_INT, [_VP, _I64, _VP]),
+    "bonsai_b200_chain_create_tp": (_INT, [_VP, _I64, _INT, _INT, _VP, _I64, _VP]),
     "bonsai_b200_chain_run": (_INT, [_VP, _VP]),
     "bonsai_b200_chain_destroy": (_INT, [_VP]),
     "bonsai_b200_chain_info": (_INT, [_VP, _VP]),
@@ -165,10 +166,11 @@ class Op(C.Structure):
 
 
 class Chain:
-    """bonsai_b200_chain_create / _run / _destroy.  `ops` is a list of (W, x, signs, y, n_out, n_in, flags)
-    with CUDA tensors; the tensors are kept alive by the object."""
+    """bonsai_b200_chain_create / _create_tp / _run / _destroy.  `ops` is a list of (W, x, signs, y, n_out, n_in,
+    flags) with CUDA tensors; the tensors are kept alive by the object.  With `peers` (a peer.PeerBuffer whose
+    tensor holds every y) the list runs over the row slices of several ranks."""
 
-    def __init__(self, ops):
+    def __init__(self, ops, peers=None):
         self._keep = [t for op in ops for t in op[:4] if t is not None]
         arr = (Op * len(ops))()
         for o, (W, x, signs, y, n_out, n_in, flags) in zip(arr, ops):
@@ -176,7 +178,13 @@ class Chain:
             o.signs = _dev(signs, "signs").value if signs is not None else None
             o.n_out, o.n_in, o.flags, o.reserved = n_out, n_in, flags, 0
         self._h = C.c_void_p()
-        rc = lib().bonsai_b200_chain_create(C.cast(arr, C.c_void_p), len(ops), C.byref(self._h))
+        if peers is None:
+            rc = lib().bonsai_b200_chain_create(C.cast(arr, C.c_void_p), len(ops), C.byref(self._h))
+        else:       # several ranks: `peers` is a bonsai_b200.peer.PeerBuffer that holds every y of the list
+            self._keep.append(peers)
+            bases = (C.c_void_p * peers.world)(*peers.ptrs)
+            rc = lib().bonsai_b200_chain_create_tp(C.cast(arr, C.c_void_p), len(ops), peers.rank, peers.world,
+                                                  C.cast(bases, C.c_void_p), peers.counter_offset, C.byref(self._h))
         if rc != 0:
             self._h = C.c_void_p()
             raise RuntimeError(f"bonsai_b200_chain_create returned {rc}")

@@ -418,14 +418,21 @@ struct bonsai_b200_chain {
     ChainOp *d_ops = nullptr;
     unsigned int *d_counter = nullptr;      // [0] arrivals of ops that others wait for, [1] rotated blocks in the image
     uint8_t *d_image = nullptr;             // activation tables of a spread op, shared through L2
+    bool tp = false;                        // several ranks: counters live in the caller's peer-mapped buffer, never reset
+    ChainPeers peers{};
     int n_ops = 0, threads = 0, grid = 0, device = 0;
     size_t smem = 0;
     ChainGeom G{};
 };
 
-int bonsai_b200_chain_create(const bonsai_b200_op *ops, int64_t n_ops, bonsai_b200_chain **out) {
+static int chain_create_impl(const bonsai_b200_op *ops, int64_t n_ops, int tp_rank, int tp_world,
+                             const void *const *peer_base, int64_t counter_offset, bonsai_b200_chain **out) {
     if (!ops || !out || n_ops <= 0 || n_ops > (1 << 20)) return 1;
     *out = nullptr;
+    const bool tp = tp_world > 1;
+    if (tp && (tp_world > CHAIN_MAX_RANKS || tp_rank < 0 || tp_rank >= tp_world || !peer_base || counter_offset < 0 ||
+               (counter_offset & 63)))
+        return 1;
     int dev = 0, sms = 0, smem_limit = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return (int)e;
@@ -530,6 +537,7 @@ int bonsai_b200_chain_create(const bonsai_b200_op *ops, int64_t n_ops, bonsai_b2
         }
         if (tr * row_bytes > slot_payload) slot_payload = tr * row_bytes;
     }
+    if (tp) rec[(size_t)n_ops - 1].flags |= CHAIN_SIGNAL;       // the closing arrival of a run
     // arrivals a dependent op must see: one per CTA for every signalling op before it
     for (int64_t i = 0; i < n_ops; ++i) {
         rec[(size_t)i].arrivals_needed = signals;
@@ -538,6 +546,9 @@ int bonsai_b200_chain_create(const bonsai_b200_op *ops, int64_t n_ops, bonsai_b2
     G.stage_blocks = any_q8 ? G.nb_max : 0;
     G.ntables = ntables;
     G.rot_blocks = any_rotate ? (G.nb_max / 8 < 7 ? G.nb_max / 8 : 7) : 0;
+    if (tp)
+        for (const auto &r : rec)
+            if (r.rows_per_cta > G.rows_stage) G.rows_stage = r.rows_per_cta;
     G.partial_floats = (int)round_up(G.partial_floats, 4);
     G.quad_ints = (int)round_up(G.quad_ints, 4);
     G.slot_bytes = (int)round_up(slot_payload + 16, 128);
@@ -552,6 +563,19 @@ int bonsai_b200_chain_create(const bonsai_b200_op *ops, int64_t n_ops, bonsai_b2
     if (!c) return (int)cudaErrorMemoryAllocation;
     c->n_ops = (int)n_ops;
     c->threads = threads_opt;
+    c->tp = tp;
+    if (tp) {
+        if (threads_opt != 512) { delete c; return 1; }             // the several-rank kernel is built for 512 threads
+        c->peers.rank = tp_rank;
+        c->peers.world = tp_world;
+        c->peers.arrivals_per_run = signals;
+        c->peers.spread_per_run = spread_total;
+        for (int q = 0; q < tp_world; ++q) {
+            if (!peer_base[q]) { delete c; return 1; }
+            c->peers.y_delta[q] = (long long)(static_cast<const char *>(peer_base[q]) - static_cast<const char *>(peer_base[tp_rank]));
+            c->peers.counter[q] = reinterpret_cast<unsigned int *>(const_cast<char *>(static_cast<const char *>(peer_base[q])) + counter_offset);
+        }
+    }
     c->grid = sms;
     c->device = dev;
     c->G = G;
@@ -563,13 +587,15 @@ int bonsai_b200_chain_create(const bonsai_b200_op *ops, int64_t n_ops, bonsai_b2
         if (err == cudaSuccess) err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, c->threads, c->smem);
         return err;
     };
-    if (c->threads == 768) e = prepare(gemv_chain_kernel<768, 3>);
-    else if (c->threads == 640) e = prepare(gemv_chain_kernel<640, 4>);
-    else if (c->threads == 512) e = prepare(gemv_chain_kernel<512, 5>);
+    if (tp) e = prepare(gemv_chain_kernel<512, 5, true>);
+    else if (c->threads == 768) e = prepare(gemv_chain_kernel<768, 3, false>);
+    else if (c->threads == 640) e = prepare(gemv_chain_kernel<640, 4, false>);
+    else if (c->threads == 512) e = prepare(gemv_chain_kernel<512, 5, false>);
     else e = cudaErrorInvalidValue;
     if (e == cudaSuccess && per_sm < 1) e = cudaErrorLaunchOutOfResources;
     if (e == cudaSuccess) e = cudaMalloc(&c->d_ops, sizeof(ChainOp) * (size_t)n_ops);
-    if (e == cudaSuccess) e = cudaMalloc(&c->d_counter, 256);
+    if (e == cudaSuccess && tp) c->d_counter = c->peers.counter[tp_rank];
+    if (e == cudaSuccess && !tp) e = cudaMalloc(&c->d_counter, 256);
     if (e == cudaSuccess && any_spread) e = cudaMalloc(&c->d_image, (size_t)G.nb_max * 176);
     if (e == cudaSuccess) e = cudaMemcpy(c->d_ops, rec.data(), sizeof(ChainOp) * (size_t)n_ops, cudaMemcpyHostToDevice);
     if (e != cudaSuccess) {
@@ -580,10 +606,21 @@ int bonsai_b200_chain_create(const bonsai_b200_op *ops, int64_t n_ops, bonsai_b2
     return 0;
 }
 
+int bonsai_b200_chain_create(const bonsai_b200_op *ops, int64_t n_ops, bonsai_b200_chain **out) {
+    return chain_create_impl(ops, n_ops, 0, 1, nullptr, 0, out);
+}
+
+int bonsai_b200_chain_create_tp(const bonsai_b200_op *ops, int64_t n_ops, int rank, int world, const void *const *peer_base,
+                                int64_t counter_offset, bonsai_b200_chain **out) {
+    if (world < 2) return 1;
+    return chain_create_impl(ops, n_ops, rank, world, peer_base, counter_offset, out);
+}
+
 int bonsai_b200_chain_run(bonsai_b200_chain *c, bonsai_stream stream) {
     if (!c || !c->d_ops) return 1;
     cudaStream_t st = as_stream(stream);
-    cudaError_t e = cudaMemsetAsync(c->d_counter, 0, 2 * sizeof(unsigned int), st);
+    cudaError_t e = cudaSuccess;
+    if (!c->tp) e = cudaMemsetAsync(c->d_counter, 0, 2 * sizeof(unsigned int), st);
     if (e != cudaSuccess) return (int)e;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)c->grid);
@@ -596,17 +633,20 @@ int bonsai_b200_chain_run(bonsai_b200_chain *c, bonsai_stream stream) {
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     const ChainOp *ops = c->d_ops;
-    auto go = [&](auto kernel) { return cudaLaunchKernelEx(&cfg, kernel, ops, c->n_ops, c->G, c->d_counter, c->d_image); };
-    if (c->threads == 768) e = go(gemv_chain_kernel<768, 3>);
-    else if (c->threads == 640) e = go(gemv_chain_kernel<640, 4>);
-    else e = go(gemv_chain_kernel<512, 5>);
+    auto go = [&](auto kernel) {
+        return cudaLaunchKernelEx(&cfg, kernel, ops, c->n_ops, c->G, c->d_counter, c->d_image, c->peers);
+    };
+    if (c->tp) e = go(gemv_chain_kernel<512, 5, true>);
+    else if (c->threads == 768) e = go(gemv_chain_kernel<768, 3, false>);
+    else if (c->threads == 640) e = go(gemv_chain_kernel<640, 4, false>);
+    else e = go(gemv_chain_kernel<512, 5, false>);
     return (int)e;
 }
 
 int bonsai_b200_chain_destroy(bonsai_b200_chain *c) {
     if (!c) return 0;
     cudaError_t e1 = c->d_ops ? cudaFree(c->d_ops) : cudaSuccess;
-    cudaError_t e2 = c->d_counter ? cudaFree(c->d_counter) : cudaSuccess;
+    cudaError_t e2 = (c->d_counter && !c->tp) ? cudaFree(c->d_counter) : cudaSuccess;
     if (c->d_image) cudaFree(c->d_image);
     delete c;
     return (int)(e1 != cudaSuccess ? e1 : e2);

@@ -92,6 +92,7 @@ struct ChainGeom {
     int nb_max;               // longest row, in blocks: sizes the tables
     int stage_blocks;         // nb_max if any op takes Q8_1 blocks (staging area of the sequencer), else 0
     int rot_blocks;           // 1024-blocks of rotation scratch (0 if no op rotates)
+    int rows_stage;           // several ranks: max rows per CTA (finished rows are staged in shared memory for the peer warp), else 0
     int ntables;              // table buffers in use: CHAIN_TABLES, or 1 when every op rotates its own input (the
                               // compute warps fill the buffer themselves, after all of them have left the op before)
     int partial_floats;       // per buffer: max rows_per_cta * nseg, multiple of 4
@@ -102,7 +103,8 @@ struct ChainGeom {
 __host__ __device__ inline size_t chain_fixed_bytes(const ChainGeom &G) {
     const size_t b = 384 + CHAIN_OP_RING * sizeof(ChainOp) + (size_t)G.ntables * G.nb_max * 176 + (size_t)G.stage_blocks * 144 +
                      (size_t)G.rot_blocks * 4096 +
-                     CHAIN_GATES * (size_t)G.partial_floats * 4 + CHAIN_GATES * (size_t)G.quad_ints * 4;
+                     CHAIN_GATES * (size_t)G.partial_floats * 4 + CHAIN_GATES * (size_t)G.quad_ints * 4 +
+                     CHAIN_GATES * (size_t)G.rows_stage * 4;
     return (b + 127) & ~(size_t)127;
 }
 
@@ -127,13 +129,17 @@ __device__ __forceinline__ bool spin_until_eq(volatile int *p, int v) {
     atomicExch(&g_device_status, STATUS_MBARRIER_TIMEOUT);
     return false;
 }
-// Grid-wide arrival counter, polled by one lane: acquire at device scope, bounded.
+// Arrival counter, polled by one lane, bounded.  Counters only grow (several ranks' launches may add to them, and a
+// rank that is already in its next run may add early), so "reached" is a wrap-safe signed difference.  SYS: the
+// counter is also written by other GPUs (acquire at system scope).
+template <bool SYS>
 __device__ __forceinline__ bool grid_counter_wait(const unsigned int *counter, unsigned int target) {
     uint32_t ns = CHAIN_NS0;
     for (uint32_t n = 0; n < (1u << 22); ++n) {
         unsigned int v;
-        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
-        if (v >= target) return true;
+        if (SYS) asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
+        else asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
+        if ((int)(v - target) >= 0) return true;
         __nanosleep(ns);
         ns = min(ns * 2, (uint32_t)CHAIN_NSMAX);
     }
@@ -141,11 +147,28 @@ __device__ __forceinline__ bool grid_counter_wait(const unsigned int *counter, u
     return false;
 }
 
-template <int THREADS, int MAXSTEPS>
+// Row-partitioned lists over several GPUs (one process and one launch per GPU, same list on every rank over its
+// own row slices).  The rows a CTA writes are also copied into the same place of every peer's buffer when the CTA
+// leaves the op (coalesced stores to peer-mapped memory over NVLink), so each rank ends up with the whole vector; "every row of every earlier op
+// is there" then means on every rank: the last warp of a CTA to leave such an op fences at system scope and adds 1
+// to the arrival counter of EVERY rank (peer atomics), and a dependent op polls its own counter for
+// arrivals x CTAs x ranks.  Counters are never reset: a launch reads its run number from counter word 2 and the
+// last CTA to leave adds 1 to it; every launch ends with one more arrival + wait, so that no rank starts its next
+// run (and writes into its peers' outputs) before every rank has finished this one.
+constexpr int CHAIN_MAX_RANKS = 8;
+struct ChainPeers {
+    int rank, world;
+    unsigned int arrivals_per_run;              // signalling ops + 1 (the closing one), per CTA and rank
+    unsigned int spread_per_run;                // 1024-blocks rotated by spread ops in one run
+    long long y_delta[CHAIN_MAX_RANKS];         // byte offset from this rank's buffer to rank p's mapping of its own
+    unsigned int *counter[CHAIN_MAX_RANKS];     // rank p's counter block: [0] arrivals [1] spread blocks [2] run [3] CTAs out
+};
+
+template <int THREADS, int MAXSTEPS, bool TP>
 __global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *__restrict__ ops, const int n_ops,
                                                                 const ChainGeom G, unsigned int *grid_counter,
-                                                                uint8_t *table_image) {
-    constexpr int C = THREADS / 32 - 2;         // compute warps
+                                                                uint8_t *table_image, const ChainPeers PE) {
+    constexpr int C = THREADS / 32 - 2 - (TP ? 1 : 0);      // compute warps (several ranks: one warp talks to the peers)
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t *full = reinterpret_cast<uint64_t *>(smem);      // [16] tile landed in slot
     uint64_t *ready = full + CHAIN_MAX_SLOTS;                 // [2]  tables of a Q8_1 op are filled
@@ -155,7 +178,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *_
     int *done_cnt = reinterpret_cast<int *>(smem + 192);      // [16] tasks of the slot's tile that have copied out
     int *expect_cnt = done_cnt + CHAIN_MAX_SLOTS;             // [16] ... of how many
     volatile int *ctrl = expect_cnt + CHAIN_MAX_SLOTS;        // [16] 0 issued, 1 ops_loaded, 2 next_task, 3 copy_op, 4-7 warps that
-                                                              //      left op (index & 3), 8 ops_done: every compute warp has left ops [0, ops_done)
+                                                              //      left op (index & 3), 8 ops_done: every compute warp has left ops [0, ops_done),
+                                                              //      9 (several ranks) ops whose rows the peer warp has sent
     ChainOp *opring = reinterpret_cast<ChainOp *>(smem + 384);
     uint8_t *p = smem + 384 + CHAIN_OP_RING * sizeof(ChainOp);
     const size_t table_bytes = (size_t)G.nb_max * 176;
@@ -168,6 +192,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *_
     float *partial_base = reinterpret_cast<float *>(p);
     p += CHAIN_GATES * (size_t)G.partial_floats * 4;
     int *quad_base = reinterpret_cast<int *>(p);
+    p += CHAIN_GATES * (size_t)G.quad_ints * 4;
+    float *ystage = reinterpret_cast<float *>(p);
     uint8_t *ring = smem + chain_fixed_bytes(G);
 
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
@@ -184,6 +210,24 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *_
     for (int i = threadIdx.x; i < 3 * CHAIN_MAX_SLOTS; i += THREADS) done_cnt[i] = 0;     // done, expect, ctrl
     for (int i = threadIdx.x; i < CHAIN_GATES * G.quad_ints; i += THREADS) quad_base[i] = 0;
     __syncthreads();
+
+    // several ranks: counters are never reset, this launch's targets start at run * (what one run adds)
+    unsigned int arrive_base = 0, spread_base = 0;
+    if (TP) {
+        const unsigned int run = __ldcg(grid_counter + 2);          // written by the previous launch on this stream
+        arrive_base = run * PE.arrivals_per_run * (unsigned)ncta * (unsigned)PE.world;
+        spread_base = run * PE.spread_per_run;
+    }
+    // a finished y element (several ranks: the CTA's rows go to the peers in one piece when it leaves the op)
+    auto store_y = [&](float *p, float v, int op_, int r_) {
+        *p = v;
+        if (TP) ystage[(size_t)(op_ % CHAIN_GATES) * G.rows_stage + r_] = v;
+    };
+    // this CTA's rows of every op so far are written: tell the grid
+    auto arrive_all = [&]() {
+        __threadfence();
+        atomicAdd(grid_counter, 1u);
+    };
 
     // rows of op R that this CTA owns
     auto cta_rows = [&](const ChainOp &R, int &row0, int &rows_here) {
@@ -208,17 +252,16 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *_
             while (task >= task_base + ntasks) {
                 // ---- leave op `op`
                 if (op >= 0) {
-                    if (flags & CHAIN_SIGNAL) __threadfence();          // this warp's y rows, before its arrival below
+                    // this warp's y rows are in memory (device scope) before it is counted out below: other CTAs read them
+                    // once everybody has arrived (several ranks: the peer warp reads its copy in shared memory)
+                    if (flags & CHAIN_SIGNAL) __threadfence();
                     __syncwarp();
                     if (lane == 0) {
                         __threadfence_block();                          // this warp's reads of op's tables and partial sums
                         const int old = atomicAdd(const_cast<int *>(&ctrl[4 + (op & 3)]), 1);
                         if (old == C - 1) {                             // last warp out: the CTA's rows of every op so far are written
                             ctrl[4 + (op & 3)] = 0;
-                            if (flags & CHAIN_SIGNAL) {
-                                __threadfence();
-                                atomicAdd(grid_counter, 1u);
-                            }
+                            if (!TP && (flags & CHAIN_SIGNAL)) arrive_all();
                             __threadfence_block();
                             ctrl[8] = op + 1;                           // monotonic: ops are left in order
                         }
@@ -232,6 +275,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *_
                 CHAIN_STAMP(op, 0);
                 if (!spin_until_gt(&ctrl[1], op, CHAIN_GATE_NS0, CHAIN_GATE_NSMAX)) { alive = false; break; }
                 if (op >= CHAIN_GATES && !spin_until_gt(&ctrl[8], op - CHAIN_GATES, CHAIN_GATE_NS0, CHAIN_GATE_NSMAX)) { alive = false; break; }
+                // several ranks: the peer warp has sent the rows staged where this op will stage its own
+                if (TP && op >= CHAIN_GATES && !spin_until_gt(&ctrl[9], op - CHAIN_GATES)) { alive = false; break; }
                 const ChainOp &R = opring[op & (CHAIN_OP_RING - 1)];
                 flags = R.flags;
                 cta_rows(R, row0, rows_here);
@@ -244,7 +289,9 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *_
                         if (flags & CHAIN_DEPENDS) {
                             if (wid == 0) {
                                 bool ok = true;
-                                if (lane == 0) ok = grid_counter_wait(grid_counter, R.arrivals_needed * (unsigned)ncta);
+                                if (lane == 0)
+                                    ok = grid_counter_wait<TP>(grid_counter, arrive_base + R.arrivals_needed * (unsigned)ncta *
+                                                                                   (unsigned)(TP ? PE.world : 1));
                                 __syncwarp();
                                 if (lane == 0 && ok) mbar_arrive(dep);
                             }
@@ -328,7 +375,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *_
                                         __threadfence();
                                         atomicAdd(grid_counter + 1, (unsigned)(fb_hi - fb_lo));
                                     }
-                                    there = grid_counter_wait(grid_counter + 1, R.spread_blocks);
+                                    there = grid_counter_wait<false>(grid_counter + 1, spread_base + R.spread_blocks);
                                 }
                                 __syncwarp();
                                 if (lane == 0 && there) mbar_arrive(dep);
@@ -392,7 +439,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *_
             const int r = r_quad + rr;
             float *y = R.y;
             if (nseg == 1) {
-                if (bl == 0 && r < rows_here) y[row0 + r] = acc;
+                if (bl == 0 && r < rows_here) store_y(&y[row0 + r], acc, op, r);
             } else {
                 float *partial = partial_base + (size_t)(op % CHAIN_GATES) * G.partial_floats;
                 int *quad_count = quad_base + (size_t)(op % CHAIN_GATES) * G.quad_ints;
@@ -410,7 +457,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *_
                     if (bl == 0 && r < rows_here) {
                         float total = partial[r * nseg];
                         for (int sgm = 1; sgm < nseg; ++sgm) total = __fadd_rn(total, partial[r * nseg + sgm]);
-                        y[row0 + r] = total;
+                        store_y(&y[row0 + r], total, op, r);
                     }
                 }
             }
@@ -450,6 +497,53 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *_
                 if (++slot == G.nslot) slot = 0;
             }
             ctrl[3] = op + 1;                                       // this op's record is no longer read here
+        }
+    } else if (TP && wid == C + 2) {
+        // ================================ peer warp (several ranks) ================================
+        // Follows ops_done: when every compute warp has left op k, copies the CTA's rows of op k (contiguous in y)
+        // into every peer's buffer, 128 bytes per store; after an op that others wait for it fences at system scope
+        // and adds 1 to the arrival counter of every rank.  All traffic to the peers comes from this one warp, so
+        // its own program order and fences cover it, and the compute warps never wait for NVLink.
+        bool good = true;
+        for (int k = 0; k < n_ops && good; ++k) {
+            good = spin_until_gt(&ctrl[8], k);
+            if (!good) break;
+            const ChainOp *Rk = ops + k;                    // the device table: the shared ring may be past op k by now
+            const int rpc = __ldg(&Rk->rows_per_cta), n_out = __ldg(&Rk->n_out), kflags = __ldg(&Rk->flags);
+            int c = (int)blockIdx.x + __ldg(&Rk->cta_shift);
+            if (c >= ncta) c -= ncta;
+            const int r0 = c * rpc, rows = max(0, min(rpc, n_out - r0));
+            if (rows > 0) {
+                float *home = reinterpret_cast<float *>(__ldg(reinterpret_cast<const unsigned long long *>(&Rk->y))) + r0;
+                const float *staged = ystage + (size_t)(k % CHAIN_GATES) * G.rows_stage;
+#pragma unroll 1
+                for (int q = 0; q < PE.world; ++q) {
+                    if (q == PE.rank) continue;
+                    float *dst = reinterpret_cast<float *>(reinterpret_cast<char *>(home) + PE.y_delta[q]);
+                    for (int i = lane; i < rows; i += 32) dst[i] = staged[i];
+                }
+            }
+            __syncwarp();
+            if (lane == 0) {
+                __threadfence_block();
+                ctrl[9] = k + 1;                            // the staging rows of op k may be reused
+            }
+            if (kflags & CHAIN_SIGNAL) {
+                __threadfence_system();
+                __syncwarp();
+                if (lane == 0)
+                    for (int q = 0; q < PE.world; ++q) atomicAdd_system(PE.counter[q], 1u);
+            }
+        }
+        // the closing wait: every CTA of every rank has arrived for the last op (the host marks it as one that others
+        // wait for), so nobody is still reading this run's vectors when a rank starts its next run
+        if (good && lane == 0 &&
+            grid_counter_wait<true>(grid_counter, arrive_base + PE.arrivals_per_run * (unsigned)ncta * (unsigned)PE.world)) {
+            if (atomicAdd(grid_counter + 3, 1u) == (unsigned)ncta - 1u) {        // last CTA out: the next launch is run + 1
+                grid_counter[3] = 0u;
+                __threadfence();
+                atomicAdd(grid_counter + 2, 1u);
+            }
         }
     } else {
         // ================================ sequencer warp ================================
