@@ -768,9 +768,9 @@ def main():
     ap.add_argument("--call", default="list", choices=["list", "matrix"],
                     help="list (default): the step's mat-vecs as one persistent launch (bonsai_b200_chain_run); "
                          "matrix: one bonsai_p40_gemv launch per matrix")
-    ap.add_argument("--gather", default="peer", choices=["peer", "nccl"],
-                    help="N > 1, list mode: peer = the kernel stores its outputs into every rank's buffer (CUDA IPC "
-                         "mapping, no collective); nccl = one all-gather per step")
+    ap.add_argument("--gather", default="nccl", choices=["peer", "nccl"],
+                    help="N > 1, list mode: nccl = one all-gather per step; peer = the kernel stores its outputs into "
+                         "every rank's buffer (CUDA IPC mapping, no collective)")
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--pdl", type=int, default=1, help="0 plain launches, 1 programmatic launches (weights of the next "
                     "mat-vec stream while the previous kernel drains)")
