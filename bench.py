@@ -239,7 +239,8 @@ def run_b200(args):
     y_local = torch.zeros(off, dtype=torch.float32, device="cuda")
     y_gathered = torch.zeros(world * off, dtype=torch.float32, device="cuda") if world > 1 else None
     chain = chain_e2e = chain_tp = peer_buf = None
-    if use_list and world > 1 and args.gather == "peer":
+    gather = args.gather if args.gather != "auto" else ("peer" if world >= 4 else "nccl")
+    if use_list and world > 1 and gather == "peer":
         # the gathered outputs live in a buffer that every rank has mapped (CUDA IPC): the kernel's epilogue stores
         # each y element into every rank's copy, so there is no collective at all
         from bonsai_b200.peer import PeerBuffer
@@ -574,7 +575,7 @@ def run_decode_step(args):
 
     launches_per_token = len(shapes)
     peer_buf = None
-    if args.call == "list" and world > 1 and args.gather == "peer":
+    if args.call == "list" and world > 1 and args.gather in ("auto", "peer"):
         # one launch per token and rank: every rank multiplies its rows of every projection and stores them into
         # every rank's copy of the output vectors; a projection that waits, waits for the rows of every rank
         from bonsai_b200.peer import PeerBuffer
@@ -646,7 +647,8 @@ def run_decode_step(args):
             "vs_baseline": None, "dtype": "int8xint2->int32, fp32 scale", "data": "synthetic",
             "config": {"workload": "decode_step", "matvecs": len(shapes), "weight_bytes": wbytes, "batch": 1, "pdl": args.pdl,
                        "l2": "inputs larger than L2", "launch": "cuda_graph_per_step", "call": call,
-                       "parallelism": f"rows/{world}+allgather" if world > 1 else "single"},
+                       "parallelism": ("single" if world == 1 else f"rows/{world}, peer stores in the kernel" if peer_buf is not None
+                                       else f"rows/{world}+allgather")},
             "gpu_launches": launches_per_token * steps, "clocks": clocks,
             "roofline": {"bound": "hbm", "achieved": gbs / world, "peak": peak, "unit": "GB/s", "frac": gbs / world / peak,
                          "peak_kind": peak_kind, "traffic": None},
@@ -768,9 +770,10 @@ def main():
     ap.add_argument("--call", default="list", choices=["list", "matrix"],
                     help="list (default): the step's mat-vecs as one persistent launch (bonsai_b200_chain_run); "
                          "matrix: one bonsai_p40_gemv launch per matrix")
-    ap.add_argument("--gather", default="nccl", choices=["peer", "nccl"],
+    ap.add_argument("--gather", default="auto", choices=["auto", "peer", "nccl"],
                     help="N > 1, list mode: nccl = one all-gather per step; peer = the kernel stores its outputs into "
-                         "every rank's buffer (CUDA IPC mapping, no collective)")
+                         "every rank's buffer (CUDA IPC mapping, no collective); auto = what measured faster: peer for "
+                         "the decode step and for the layer sweep at N >= 4, nccl for the layer sweep at N = 2")
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--pdl", type=int, default=1, help="0 plain launches, 1 programmatic launches (weights of the next "
                     "mat-vec stream while the previous kernel drains)")
