@@ -240,6 +240,11 @@ def run_b200(args):
     y_gathered = torch.zeros(world * off, dtype=torch.float32, device="cuda") if world > 1 else None
     chain = chain_e2e = chain_tp = peer_buf = None
     gather = args.gather if args.gather != "auto" else ("peer" if world >= 4 else "nccl")
+    if args.gather == "auto" and gather == "peer":
+        try:                                    # the peer mapping needs the CUDA runtime bindings (same on every rank)
+            import cuda.bindings.runtime       # noqa: F401
+        except Exception:
+            gather = "nccl"
     if use_list and world > 1 and gather == "peer":
         # the gathered outputs live in a buffer that every rank has mapped (CUDA IPC): the kernel's epilogue stores
         # each y element into every rank's copy, so there is no collective at all
@@ -575,7 +580,14 @@ def run_decode_step(args):
 
     launches_per_token = len(shapes)
     peer_buf = None
-    if args.call == "list" and world > 1 and args.gather in ("auto", "peer"):
+    peer_ok = args.gather == "peer"
+    if args.gather == "auto":
+        try:
+            import cuda.bindings.runtime       # noqa: F401
+            peer_ok = True
+        except Exception:
+            peer_ok = False
+    if args.call == "list" and world > 1 and peer_ok:
         # one launch per token and rank: every rank multiplies its rows of every projection and stores them into
         # every rank's copy of the output vectors; a projection that waits, waits for the rows of every rank
         from bonsai_b200.peer import PeerBuffer
