@@ -293,3 +293,33 @@ def test_random_lists_with_dependencies(gpu, port, threads, seed):
             assert np.array_equal(bits(host(op[3])), bits(host(want))), (i, op[4], op[5], op[6])
     chain.close()
     assert gpu.device_status() == 0
+
+
+def test_several_rank_form_checks_its_arguments(gpu):
+    """bonsai_b200_chain_create_tp on one device: creation only (nothing is launched, so the second
+    'rank' can be the same buffer); bad rank counts, ranks and counter offsets are refused."""
+    import ctypes as C
+    import torch
+    W = torch.zeros(8 * 2 * 34, dtype=torch.uint8, device="cuda")
+    x = torch.zeros(1024, device="cuda")
+    buf = torch.zeros(4096, dtype=torch.uint8, device="cuda")
+    y = buf[:32].view(torch.float32)
+    op = (gpu.Op * 1)()
+    op[0].W, op[0].x, op[0].signs, op[0].y = W.data_ptr(), x.data_ptr(), None, y.data_ptr()
+    op[0].n_out, op[0].n_in, op[0].flags, op[0].reserved = 8, 256, 0, 0
+    bases = (C.c_void_p * 2)(buf.data_ptr(), buf.data_ptr())
+    lib = gpu.lib()
+
+    def create(rank, world, offset):
+        h = C.c_void_p()
+        rc = lib.bonsai_b200_chain_create_tp(C.cast(op, C.c_void_p), 1, rank, world, C.cast(bases, C.c_void_p), offset, C.byref(h))
+        if rc == 0:
+            assert lib.bonsai_b200_chain_destroy(h) == 0
+        return rc
+    assert create(0, 2, 2048) == 0
+    assert create(1, 2, 2048) == 0
+    assert create(0, 1, 2048) == 1          # one rank: use bonsai_b200_chain_create
+    assert create(2, 2, 2048) == 1          # rank out of range
+    assert create(0, 9, 2048) == 1          # more ranks than the kernel addresses
+    assert create(0, 2, 2050) == 1          # counters must sit on a 64-byte boundary
+    assert create(0, 2, -64) == 1
