@@ -11,10 +11,11 @@
 // a projection that reads an earlier projection's output waits on a grid-wide arrival counter
 // (bounded) while the ring keeps filling behind it.
 //
-// Warp roles (THREADS / 32 - 2 compute warps, 1 copy warp, 1 sequencer warp):
+// Warp roles (THREADS / 32 - 2 compute warps, 1 copy warp, 1 sequencer warp; the several-rank form
+// gives one compute warp's place to a peer warp, described further down):
 //   sequencer : copies op records into a shared ring of 8, and for ops whose activations arrive as
-//               Q8_1 blocks stages them (one bulk copy) and re-lays them into one of two table
-//               buffers while the compute warps are still on the previous op;
+//               Q8_1 blocks stages them (one bulk copy) and re-lays them into one of up to three
+//               table buffers while the compute warps are still on earlier ops;
 //   copy      : tile g of the CTA (whole rows of one op, <= slot bytes, one contiguous bulk copy)
 //               goes to slot g % nslot once every task of tile g - nslot has copied its blocks out;
 //   compute   : tasks are handed out in order across ops; entering an op a warp waits for its
@@ -78,7 +79,7 @@ struct __align__(16) ChainOp {                 // 128 bytes, one per projection,
     uint32_t magic_tpt, magic_nseg;
     int cta_shift;                             // CTA c takes the rows of CTA (c + shift) % grid
     uint32_t arrivals_needed;                  // CHAIN_DEPENDS: signalling ops before this one
-    int buf;                                   // table buffer (0 / 1) this op reads
+    int buf;                                   // table buffer this op reads
     int ready_parity;                          // phase parity of ready[buf] (Q8_1 ops that fill a buffer)
     int prev_user;                             // last op that read the previous contents of buf, or -1
     uint32_t spread_blocks;                    // CHAIN_SPREAD: 1024-blocks rotated by spread ops up to and including this one
