@@ -41,7 +41,8 @@ int bonsai_b200_linear(const void *W, const float *x, const float *signs, float 
  *     launches nothing.  Other shape errors return 1 as in bonsai_b200_linear.
  *   - it calls no cudaMalloc / cudaFree nor any allocating library routine, on any call.
  *   - the first call on each device looks up the array's device address (cudaGetSymbolAddress) and
- *     remembers it; make that first call outside of any stream capture.
+ *     remembers it for the life of the process; make that first call outside of any stream capture, and
+ *     do not call cudaDeviceReset() afterwards (the remembered address would belong to the old context).
  *   - every call on a device uses the same array and leaves its Q8_1 bytes there.  Nothing has to be
  *     cleared between calls (each call overwrites the n_in / 32 blocks it then reads), but two calls
  *     whose kernels overlap on the GPU -- different streams, or concurrent host threads -- race on it:
@@ -93,11 +94,15 @@ int bonsai_b200_stream_probe(const void *buf, int64_t bytes, int mode, void *sin
  * Returns 0, or 1 for an unknown key. */
 int bonsai_b200_set_option(const char *key, int64_t value);
 
-/* Sticky status word written by device-side bounded waits: 0 = no kernel of this library has
- * given up on a wait on the current device.  Synchronises the device. */
+/* Status word written by device-side bounded waits: 0 = no kernel of this library has given up on a
+ * wait on the current device since the word was last cleared; 1 = a wait on a shared-memory barrier or
+ * counter ran out; 2 = a wait for other CTAs or other ranks ran out (the launch still ends by itself and
+ * the context stays usable; the outputs of that launch are incomplete).  Both calls synchronise the device
+ * (cudaDeviceSynchronize), so neither may be made while a stream of the device is being captured.
+ * Failures of the calls themselves come back as 1000 + the CUDA error code. */
 int bonsai_b200_device_status(void);
+int bonsai_b200_clear_status(void);
 
-/* Version of this build as major * 10000 + minor * 100 + patch. */
 /* ---- a list of projections in one persistent launch (no counterpart in the reference) ---------
  * The reference launches one kernel per matrix (bonsai_p40_gemv, include/bonsai_p40.h:26-28).  On a
  * B200 a decode projection streams for 0.2 - 4 us, about as long as a kernel takes to start and drain,
@@ -105,7 +110,7 @@ int bonsai_b200_device_status(void);
  * one is multiplied, and only a projection that reads an earlier projection's output waits.
  *
  * Each op computes y = W . q(x): W as for bonsai_p40_gemv; x is either the permuted Q8_1 blocks of
- * the activation vector (as bonsai_p40_quantize_q8_1 / bonsai_b200_fwht_quant write them), or, with
+ * the activation vector (as bonsai_p40_quant_activations / bonsai_b200_fwht_quant write them), or, with
  * BONSAI_B200_OP_ROTATE, the fp32 vector itself, which the kernel rotates (FWHT-1024, optional signs)
  * and quantises exactly as bonsai_b200_fwht_quant does.  y is bit-identical to bonsai_p40_gemv with
  * the default kernel.
@@ -143,17 +148,24 @@ int bonsai_b200_chain_destroy(bonsai_b200_chain *chain);
  * into every other rank (CUDA IPC or any other peer mapping): peer_base[q] is rank q's buffer as addressed from
  * this process (peer_base[rank] is the local one).  The kernel stores every y element it produces into all `world`
  * buffers, so each rank ends up with the whole vector without a collective, and OP_DEPENDS waits for every row of
- * every rank.  64 bytes at counter_offset (a multiple of 64) inside the buffer are the kernel's arrival counters:
- * zero them once after allocation and never touch them again.  All ranks must call run() the same number of times;
- * the launches of different ranks wait for each other (bounded: a rank that never comes makes the others give up
- * after about a second and set the status word), so each rank needs its own GPU.  Reading the outputs on the host
- * needs the usual ordering between ranks: a peer's next run() overwrites them. */
+ * every rank.  The buffer is buffer_bytes long on every rank; BONSAI_B200_TP_COUNTER_BYTES bytes at counter_offset
+ * (a multiple of 64, behind every output) are the kernel's counters and flags: zero them once after allocation and
+ * never touch them again.  Refused (1): an output that does not lie inside [buffer, buffer + counter_offset), a
+ * counter block that does not fit in buffer_bytes, a mapping that is not 16-byte aligned.  Every rank must run on a
+ * GPU with the same number of SMs.  All ranks must call run() the same number of times; the launches of different
+ * ranks wait for each other, so each rank needs its own GPU.  The waits are bounded by wait_limit_us microseconds
+ * (0 = one second): a rank that never comes makes the others give up, set the status word to 2 and return; a
+ * chain that has given up must be destroyed and its counter block zeroed again before the buffer is reused.
+ * Reading the outputs on the host needs the usual ordering between ranks: a peer's next run() overwrites them. */
+#define BONSAI_B200_TP_COUNTER_BYTES 64
 int bonsai_b200_chain_create_tp(const bonsai_b200_op *ops, int64_t n_ops, int rank, int world,
-                                const void *const *peer_base, int64_t counter_offset, bonsai_b200_chain **out);
+                                const void *const *peer_base, int64_t buffer_bytes, int64_t counter_offset,
+                                int64_t wait_limit_us, bonsai_b200_chain **out);
 /* kernels launched so far by run() on this chain's behalf, and its geometry (threads per CTA, ring
  * slots, bytes per slot, CTAs): for benchmarks and tests. */
 int bonsai_b200_chain_info(const bonsai_b200_chain *chain, int64_t out[4]);
 
+/* Version of this build as major * 100 + minor. */
 int bonsai_b200_version(void);
 
 #ifdef __cplusplus

@@ -18,7 +18,9 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ORACLE_SO = os.path.join(HERE, "libbonsai_oracle.so")
 REF_DIR = os.path.join(HERE, "_ref")
 REF_SO = os.path.join(REF_DIR, "libbonsai_ref.so")
-DEFAULT_REFERENCE = os.environ.get("BONSAI_REFERENCE_DIR", "/root/reference")
+# where a checkout of the reference is looked for: $BONSAI_REFERENCE_DIR, else a directory named "reference"
+# beside this repository; when neither holds the headers, a prebuilt oracle/_ref is used as it is
+DEFAULT_REFERENCE = os.environ.get("BONSAI_REFERENCE_DIR") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 
 FP_FLAGS = ["-O2", "-ffp-contract=off", "-fno-fast-math", "-fPIC", "-shared"]
 

@@ -42,12 +42,13 @@ SIGNATURES = {
     "bonsai_b200_synth_pq2_0": (_INT, [_VP, _I64, _I64, _U64, _VP]),
     "bonsai_b200_stream_probe": (_INT, [_VP, _I64, _INT, _VP, _VP]),
     "bonsai_b200_chain_create": (_INT, [_VP, _I64, _VP]),
-    "bonsai_b200_chain_create_tp": (_INT, [_VP, _I64, _INT, _INT, _VP, _I64, _VP]),
+    "bonsai_b200_chain_create_tp": (_INT, [_VP, _I64, _INT, _INT, _VP, _I64, _I64, _I64, _VP]),
     "bonsai_b200_chain_run": (_INT, [_VP, _VP]),
     "bonsai_b200_chain_destroy": (_INT, [_VP]),
     "bonsai_b200_chain_info": (_INT, [_VP, _VP]),
     "bonsai_b200_set_option": (_INT, [C.c_char_p, _I64]),
     "bonsai_b200_device_status": (_INT, []),
+    "bonsai_b200_clear_status": (_INT, []),
     "bonsai_b200_version": (_INT, []),
 }
 
@@ -89,6 +90,10 @@ def set_option(key, value):
 
 def device_status():
     return lib().bonsai_b200_device_status()
+
+
+def clear_status():
+    return lib().bonsai_b200_clear_status()
 
 
 def version():
@@ -170,7 +175,7 @@ class Chain:
     flags) with CUDA tensors; the tensors are kept alive by the object.  With `peers` (a peer.PeerBuffer whose
     tensor holds every y) the list runs over the row slices of several ranks."""
 
-    def __init__(self, ops, peers=None):
+    def __init__(self, ops, peers=None, wait_limit_us=0):
         self._keep = [t for op in ops for t in op[:4] if t is not None]
         arr = (Op * len(ops))()
         for o, (W, x, signs, y, n_out, n_in, flags) in zip(arr, ops):
@@ -184,7 +189,8 @@ class Chain:
             self._keep.append(peers)
             bases = (C.c_void_p * peers.world)(*peers.ptrs)
             rc = lib().bonsai_b200_chain_create_tp(C.cast(arr, C.c_void_p), len(ops), peers.rank, peers.world,
-                                                  C.cast(bases, C.c_void_p), peers.counter_offset, C.byref(self._h))
+                                                  C.cast(bases, C.c_void_p), peers.total_bytes,
+                                                  peers.counter_offset, wait_limit_us, C.byref(self._h))
         if rc != 0:
             self._h = C.c_void_p()
             raise RuntimeError(f"bonsai_b200_chain_create returned {rc}")

@@ -37,6 +37,7 @@ class PeerBuffer:
         self.nbytes = (int(nbytes) + 255) // 256 * 256
         self.counter_offset = self.nbytes
         total = self.nbytes + COUNTER_BYTES
+        self.total_bytes = total
         self._rt, self.rank, self.world = rt, rank, world
         self._ptr = int(_check(rt.cudaMalloc(total), "cudaMalloc"))
         _check(rt.cudaMemset(self._ptr, 0, total), "cudaMemset")

@@ -52,8 +52,22 @@ __device__ __forceinline__ void quantise_chunk_8lanes(const float (&v)[4], int l
     header = f32_to_f16_bits_ties_away(d) | (((uint32_t)sum & 0xFFFFu) << 16);
 }
 
+// Four consecutive floats: one 16-byte access when the caller's pointer allows it (VEC), else four 4-byte
+// accesses -- the reference takes any float pointer (src/kernels/elementwise_p40.cu:75-80, gemv_p40.cu:200-208).
+template <bool VEC>
+__device__ __forceinline__ float4 load_f4(const float *p) {
+    if (VEC) return *reinterpret_cast<const float4 *>(p);
+    return make_float4(p[0], p[1], p[2], p[3]);
+}
+template <bool VEC>
+__device__ __forceinline__ void store_f4(float *p, float4 v) {
+    if (VEC) { *reinterpret_cast<float4 *>(p) = v; return; }
+    p[0] = v.x; p[1] = v.y; p[2] = v.z; p[3] = v.w;
+}
+
 // One thread per four inputs.  X is [n_tok][n_in]; output block index = chunk * tok_stride + tok
 // (tok_stride = 1 with n_tok = 1 gives the plain vector layout).
+template <bool VEC>
 __global__ void __launch_bounds__(256) quant_q8_1_kernel(const float *__restrict__ X, uint32_t *__restrict__ out,
                                                          int n_in, int n_tok) {
     pdl_launch_dependents();
@@ -69,7 +83,7 @@ __global__ void __launch_bounds__(256) quant_q8_1_kernel(const float *__restrict
         const long long ic = live ? i : total - 1;
         const int tok = (int)(ic / per_tok);
         const int g4 = (int)(ic - (long long)tok * per_tok);
-        const float4 f = *reinterpret_cast<const float4 *>(X + (size_t)tok * n_in + 4 * (size_t)g4);
+        const float4 f = load_f4<VEC>(X + (size_t)tok * n_in + 4 * (size_t)g4);
         const float v[4] = {f.x, f.y, f.z, f.w};
         uint32_t word, header;
         quantise_chunk_8lanes(v, lane, word, header);
@@ -176,6 +190,7 @@ __device__ __forceinline__ void fwht_slice_back(const float4 *block, int r, int 
 
 // blocks = n_tok * (n_in / 1024) warps.  X [n_tok][n_in] read-only; x_rot (nullable, may alias X)
 // receives the rotated values; xq (nullable) the Q8_1 blocks at chunk * n_tok + tok.
+template <bool VEC>
 __global__ void __launch_bounds__(128) fwht_quant_kernel(const float *X, const float *__restrict__ signs, float *x_rot,
                                                          uint32_t *__restrict__ xq, int n_in, int n_tok) {
     pdl_launch_dependents();
@@ -192,13 +207,13 @@ __global__ void __launch_bounds__(128) fwht_quant_kernel(const float *X, const f
     float v[8][4];
 #pragma unroll
     for (int r = 0; r < 8; ++r) {
-        const float4 f = *reinterpret_cast<const float4 *>(X + base + r * 128 + 4 * lane);
+        const float4 f = load_f4<VEC>(X + base + r * 128 + 4 * lane);
         v[r][0] = f.x; v[r][1] = f.y; v[r][2] = f.z; v[r][3] = f.w;
     }
     if (signs) {
 #pragma unroll
         for (int r = 0; r < 8; ++r) {
-            const float4 s = *reinterpret_cast<const float4 *>(signs + (size_t)blk * FWHT_N + r * 128 + 4 * lane);
+            const float4 s = load_f4<VEC>(signs + (size_t)blk * FWHT_N + r * 128 + 4 * lane);
             v[r][0] = __fmul_rn(v[r][0], s.x); v[r][1] = __fmul_rn(v[r][1], s.y);
             v[r][2] = __fmul_rn(v[r][2], s.z); v[r][3] = __fmul_rn(v[r][3], s.w);
         }
@@ -207,7 +222,7 @@ __global__ void __launch_bounds__(128) fwht_quant_kernel(const float *X, const f
     if (x_rot) {
 #pragma unroll
         for (int r = 0; r < 8; ++r)
-            *reinterpret_cast<float4 *>(x_rot + base + r * 128 + 4 * lane) = make_float4(v[r][0], v[r][1], v[r][2], v[r][3]);
+            store_f4<VEC>(x_rot + base + r * 128 + 4 * lane, make_float4(v[r][0], v[r][1], v[r][2], v[r][3]));
     }
     if (xq) {
 #pragma unroll

@@ -41,6 +41,7 @@ std::atomic<int> g_opt_gemm_path{-1};          // -1: by token count, 0: integer
 
 inline cudaStream_t as_stream(bonsai_stream s) { return reinterpret_cast<cudaStream_t>(s); }
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+inline bool aligned4(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 3u) == 0; }
 
 // cudaFuncSetAttribute is per device; remember which devices have been configured per kernel.
 struct SmemOptIn {
@@ -270,29 +271,37 @@ extern "C" {
 
 int bonsai_p40_quant_activations(const float *x, void *out, int64_t n, bonsai_stream stream) {
     if (n <= 0 || n % 32 != 0) return 1;
-    if (!aligned16(x) || (reinterpret_cast<uintptr_t>(out) & 3u)) return 1;
+    if (!aligned4(x) || !aligned4(out) || n > INT32_MAX) return 1;
     const long long threads = n / 4;
     const int blocks = (int)((threads + 255) / 256);
-    quant_q8_1_kernel<<<blocks, 256, 0, as_stream(stream)>>>(x, static_cast<uint32_t *>(out), (int)n, 1);
+    // any float pointer is taken, as by the reference; 16-byte aligned ones get 16-byte loads
+    if (aligned16(x)) quant_q8_1_kernel<true><<<blocks, 256, 0, as_stream(stream)>>>(x, static_cast<uint32_t *>(out), (int)n, 1);
+    else quant_q8_1_kernel<false><<<blocks, 256, 0, as_stream(stream)>>>(x, static_cast<uint32_t *>(out), (int)n, 1);
     return (int)cudaGetLastError();
 }
 
 int bonsai_p40_fwht(float *x, const float *signs, int64_t n, bonsai_stream stream) {
     if (n <= 0 || n % FWHT_N != 0) return 1;
-    if (!aligned16(x) || (signs && !aligned16(signs))) return 1;
+    if (!aligned4(x) || (signs && !aligned4(signs)) || n > INT32_MAX) return 1;
     const int warps = (int)(n / FWHT_N);
-    fwht_quant_kernel<<<(warps + 3) / 4, 128, 0, as_stream(stream)>>>(x, signs, x, nullptr, (int)n, 1);
+    if (aligned16(x) && (!signs || aligned16(signs)))
+        fwht_quant_kernel<true><<<(warps + 3) / 4, 128, 0, as_stream(stream)>>>(x, signs, x, nullptr, (int)n, 1);
+    else
+        fwht_quant_kernel<false><<<(warps + 3) / 4, 128, 0, as_stream(stream)>>>(x, signs, x, nullptr, (int)n, 1);
     return (int)cudaGetLastError();
 }
 
 int bonsai_b200_fwht_quant(const float *x, const float *signs, void *xq, float *x_rot, int64_t n,
                            bonsai_stream stream) {
-    if (n <= 0 || n % FWHT_N != 0) return 1;
-    if (!aligned16(x) || (signs && !aligned16(signs)) || (x_rot && !aligned16(x_rot))) return 1;
-    if (reinterpret_cast<uintptr_t>(xq) & 3u) return 1;
+    if (n <= 0 || n % FWHT_N != 0 || n > INT32_MAX) return 1;
+    if (!aligned4(x) || (signs && !aligned4(signs)) || (x_rot && !aligned4(x_rot)) || !aligned4(xq)) return 1;
     const int warps = (int)(n / FWHT_N);
-    fwht_quant_kernel<<<(warps + 3) / 4, 128, 0, as_stream(stream)>>>(x, signs, x_rot, static_cast<uint32_t *>(xq),
-                                                                      (int)n, 1);
+    if (aligned16(x) && (!signs || aligned16(signs)) && (!x_rot || aligned16(x_rot)))
+        fwht_quant_kernel<true><<<(warps + 3) / 4, 128, 0, as_stream(stream)>>>(x, signs, x_rot, static_cast<uint32_t *>(xq),
+                                                                                (int)n, 1);
+    else
+        fwht_quant_kernel<false><<<(warps + 3) / 4, 128, 0, as_stream(stream)>>>(x, signs, x_rot, static_cast<uint32_t *>(xq),
+                                                                                 (int)n, 1);
     return (int)cudaGetLastError();
 }
 
@@ -300,18 +309,20 @@ int bonsai_b200_quant_batch(const float *X, const float *signs, void *Xq, int64_
                             bonsai_stream stream) {
     if (n_in <= 0 || n_tok <= 0 || n_in % 32 != 0) return 1;
     if (rotate && n_in % FWHT_N != 0) return 1;
-    if (!aligned16(X) || (signs && !aligned16(signs)) || (reinterpret_cast<uintptr_t>(Xq) & 3u)) return 1;
+    if (!aligned4(X) || (signs && !aligned4(signs)) || !aligned4(Xq)) return 1;
     if (n_in > INT32_MAX || n_tok > INT32_MAX) return 1;
+    const bool vec = aligned16(X) && (!signs || aligned16(signs));
     if (rotate) {
         const long long warps = (n_in / FWHT_N) * n_tok;
-        fwht_quant_kernel<<<(unsigned)((warps + 3) / 4), 128, 0, as_stream(stream)>>>(
-            X, signs, nullptr, static_cast<uint32_t *>(Xq), (int)n_in, (int)n_tok);
+        const unsigned blocks = (unsigned)((warps + 3) / 4);
+        if (vec) fwht_quant_kernel<true><<<blocks, 128, 0, as_stream(stream)>>>(X, signs, nullptr, static_cast<uint32_t *>(Xq), (int)n_in, (int)n_tok);
+        else fwht_quant_kernel<false><<<blocks, 128, 0, as_stream(stream)>>>(X, signs, nullptr, static_cast<uint32_t *>(Xq), (int)n_in, (int)n_tok);
     } else {
         const long long threads = n_in / 4 * n_tok;
         long long blocks = (threads + 255) / 256;
         if (blocks > 8 * SM_COUNT * 4) blocks = 8 * SM_COUNT * 4;
-        quant_q8_1_kernel<<<(unsigned)blocks, 256, 0, as_stream(stream)>>>(X, static_cast<uint32_t *>(Xq), (int)n_in,
-                                                                           (int)n_tok);
+        if (vec) quant_q8_1_kernel<true><<<(unsigned)blocks, 256, 0, as_stream(stream)>>>(X, static_cast<uint32_t *>(Xq), (int)n_in, (int)n_tok);
+        else quant_q8_1_kernel<false><<<(unsigned)blocks, 256, 0, as_stream(stream)>>>(X, static_cast<uint32_t *>(Xq), (int)n_in, (int)n_tok);
     }
     return (int)cudaGetLastError();
 }
@@ -365,12 +376,12 @@ int bonsai_p40_gemv(const void *W, const void *xq, float *y, int64_t n_out, int6
 int bonsai_b200_linear(const void *W, const float *x, const float *signs, float *y, void *xq_scratch, int64_t n_out,
                        int64_t n_in, bonsai_stream stream) {
     if (n_out <= 0 || n_in <= 0 || n_in % FWHT_N != 0 || !xq_scratch) return 1;
-    if (n_out > INT32_MAX || !aligned16(x) || (signs && !aligned16(signs)) || (reinterpret_cast<uintptr_t>(xq_scratch) & 3u))
-        return 1;
+    if (n_out > INT32_MAX || !aligned4(x) || (signs && !aligned4(signs)) || !aligned4(xq_scratch)) return 1;
     // one launch when the streaming mat-vec takes the shape: rotation and quantiser run in its prologue
     StreamParams sp;
     int threads = 0, smem_bytes = 0;
-    if (g_opt_gemv_order.load() == 0 && g_opt_fuse_linear.load() != 0 && aligned16(W) &&
+    if (g_opt_gemv_order.load() == 0 && g_opt_fuse_linear.load() != 0 && aligned16(W) && aligned16(x) &&
+        (!signs || aligned16(signs)) &&
         plan_stream(n_out, (int)(n_in / 128), g_opt_gemv_variant.load(), sp, threads, smem_bytes)) {
         static SmemOptIn opt;
         cudaError_t err = opt.ensure(gemv_stream_kernel<true>);
@@ -426,13 +437,27 @@ struct bonsai_b200_chain {
 };
 
 static int chain_create_impl(const bonsai_b200_op *ops, int64_t n_ops, int tp_rank, int tp_world,
-                             const void *const *peer_base, int64_t counter_offset, bonsai_b200_chain **out) {
+                             const void *const *peer_base, int64_t buffer_bytes, int64_t counter_offset,
+                             int64_t wait_limit_us, bonsai_b200_chain **out) {
     if (!ops || !out || n_ops <= 0 || n_ops > (1 << 20)) return 1;
     *out = nullptr;
     const bool tp = tp_world > 1;
-    if (tp && (tp_world > CHAIN_MAX_RANKS || tp_rank < 0 || tp_rank >= tp_world || !peer_base || counter_offset < 0 ||
-               (counter_offset & 63)))
-        return 1;
+    if (tp) {
+        if (tp_world > CHAIN_MAX_RANKS || tp_rank < 0 || tp_rank >= tp_world || !peer_base || counter_offset < 0 ||
+            (counter_offset & 63) || wait_limit_us < 0)
+            return 1;
+        // the counter block lies inside the buffer, behind every output; every mapping is 16-byte aligned
+        if (buffer_bytes < counter_offset + BONSAI_B200_TP_COUNTER_BYTES) return 1;
+        for (int q = 0; q < tp_world; ++q)
+            if (!peer_base[q] || !aligned16(peer_base[q])) return 1;
+        // every output must lie inside [buffer, counters): the kernel stores it at the same offset of every
+        // rank's mapping, so an output outside the buffer would be a store into memory that is not ours
+        const char *lo = static_cast<const char *>(peer_base[tp_rank]);
+        for (int64_t i = 0; i < n_ops; ++i) {
+            const char *y = reinterpret_cast<const char *>(ops[i].y);
+            if (!y || ops[i].n_out <= 0 || y < lo || y + ops[i].n_out * 4 > lo + counter_offset) return 1;
+        }
+    }
     int dev = 0, sms = 0, smem_limit = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return (int)e;
@@ -570,8 +595,8 @@ static int chain_create_impl(const bonsai_b200_op *ops, int64_t n_ops, int tp_ra
         c->peers.world = tp_world;
         c->peers.arrivals_per_run = signals;
         c->peers.spread_per_run = spread_total;
+        c->peers.wait_limit_ns = (unsigned long long)(wait_limit_us > 0 ? wait_limit_us : 1000000) * 1000ull;
         for (int q = 0; q < tp_world; ++q) {
-            if (!peer_base[q]) { delete c; return 1; }
             c->peers.y_delta[q] = (long long)(static_cast<const char *>(peer_base[q]) - static_cast<const char *>(peer_base[tp_rank]));
             c->peers.counter[q] = reinterpret_cast<unsigned int *>(const_cast<char *>(static_cast<const char *>(peer_base[q])) + counter_offset);
         }
@@ -607,13 +632,14 @@ static int chain_create_impl(const bonsai_b200_op *ops, int64_t n_ops, int tp_ra
 }
 
 int bonsai_b200_chain_create(const bonsai_b200_op *ops, int64_t n_ops, bonsai_b200_chain **out) {
-    return chain_create_impl(ops, n_ops, 0, 1, nullptr, 0, out);
+    return chain_create_impl(ops, n_ops, 0, 1, nullptr, 0, 0, 0, out);
 }
 
 int bonsai_b200_chain_create_tp(const bonsai_b200_op *ops, int64_t n_ops, int rank, int world, const void *const *peer_base,
-                                int64_t counter_offset, bonsai_b200_chain **out) {
+                                int64_t buffer_bytes, int64_t counter_offset, int64_t wait_limit_us,
+                                bonsai_b200_chain **out) {
     if (world < 2) return 1;
-    return chain_create_impl(ops, n_ops, rank, world, peer_base, counter_offset, out);
+    return chain_create_impl(ops, n_ops, rank, world, peer_base, buffer_bytes, counter_offset, wait_limit_us, out);
 }
 
 int bonsai_b200_chain_run(bonsai_b200_chain *c, bonsai_stream stream) {
@@ -724,22 +750,28 @@ int bonsai_p40_gemv_repack(const void *W, const float *x, float *y, int64_t n_ou
     // the reference refuses vectors whose Q8_1 image exceeds 48 KiB; this build takes anything that
     // leaves room for four rows beside the activation records
     if (GEMV_BAR_BYTES + act_bytes + 4 * row_bytes + 64 > (size_t)111 * 1024) return 1;
-    if (!aligned16(W) || !aligned16(x)) return 1;
+    if (!aligned16(W) || !aligned4(x)) return 1;        // dst of bonsai_p40_repack is 16-byte aligned; x is any float pointer
     const bool pdl = g_opt_pdl.load() != 0;
     GemvPlan p = plan_rows(n_out, row_bytes, act_bytes, 1, g_opt_gemv_variant.load());
     if (p.threads > 256) p.threads = 256;
     const dim3 grid((unsigned)p.ctas);
-    static SmemOptIn opt1, opt2, opt4;
-    auto go = [&](auto kernel, SmemOptIn &opt) -> cudaError_t {
-        cudaError_t err = opt.ensure(kernel);
+    static SmemOptIn opt[6];
+    auto go = [&](auto kernel, SmemOptIn &o) -> cudaError_t {
+        cudaError_t err = o.ensure(kernel);
         if (err != cudaSuccess) return err;
         return launch(kernel, grid, dim3(p.threads), (size_t)p.smem_bytes, as_stream(stream), pdl,
                       static_cast<const uint8_t *>(W), x, y, (int)n_out, nb, p.rows_per_cta, p.rows_per_stage);
     };
     cudaError_t e;
-    if (p.rr == 1) e = go(gemv_repack_kernel<1>, opt1);
-    else if (p.rr == 2) e = go(gemv_repack_kernel<2>, opt2);
-    else e = go(gemv_repack_kernel<4>, opt4);
+    if (aligned16(x)) {
+        if (p.rr == 1) e = go(gemv_repack_kernel<1, true>, opt[0]);
+        else if (p.rr == 2) e = go(gemv_repack_kernel<2, true>, opt[1]);
+        else e = go(gemv_repack_kernel<4, true>, opt[2]);
+    } else {
+        if (p.rr == 1) e = go(gemv_repack_kernel<1, false>, opt[3]);
+        else if (p.rr == 2) e = go(gemv_repack_kernel<2, false>, opt[4]);
+        else e = go(gemv_repack_kernel<4, false>, opt[5]);
+    }
     return (int)e;
 }
 
@@ -811,19 +843,15 @@ int bonsai_b200_device_status(void) {
     return v;
 }
 
-int bonsai_b200_version(void) { return 100; }
+int bonsai_b200_clear_status(void) {
+    const int zero = 0;
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return (int)e + 1000;
+    e = cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int));
+    return e == cudaSuccess ? 0 : (int)e + 1000;
+}
 
-#ifdef BONSAI_B200_TRACE
-int bonsai_b200_set_skip(int v) { return (int)cudaMemcpyToSymbol(g_skip, &v, sizeof(int)); }
-int bonsai_b200_read_chain_trace(long long *out, int n) {
-    cudaDeviceSynchronize();
-    return (int)cudaMemcpyFromSymbol(out, g_chain_trace, sizeof(long long) * n);
-}
-int bonsai_b200_read_trace(long long *out, int n) {
-    cudaDeviceSynchronize();
-    return (int)cudaMemcpyFromSymbol(out, g_trace, sizeof(long long) * n);
-}
-#endif
+int bonsai_b200_version(void) { return 200; }
 
 // Not on the PQ2_0 mat-vec / mat-mul path: exported so that programs written against the reference
 // link; each refuses without touching its arguments (reference: include/bonsai_p40.h:44-56).

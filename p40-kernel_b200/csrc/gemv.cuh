@@ -34,17 +34,6 @@
 
 namespace b200 {
 
-#ifdef BONSAI_B200_TRACE
-// Development aid (not in the shipped build): per-CTA time stamps of the mat-vec phases.
-__device__ long long g_trace[4096 * 8];
-__device__ int g_skip = 0;
-#define TRACE_STAMP(slot) do { if (blockIdx.x < 4096) { \
-    long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); \
-    g_trace[blockIdx.x * 8 + (slot)] = t_; } } while (0)
-#else
-#define TRACE_STAMP(slot) do { } while (0)
-#endif
-
 constexpr int GEMV_MAX_STAGES = 64;
 constexpr int GEMV_BAR_BYTES = 2 * GEMV_MAX_STAGES * 8;   // full[] + done[]
 constexpr int ACT_REC_WORDS = 84;   // 64 words int8 + 8 fp32 scales + 8 int32 (-64*s) + 4 pad
@@ -272,7 +261,6 @@ __global__ void __launch_bounds__(RR == 4 ? 512 : 1024, 1) gemv_ring_kernel(cons
         __syncwarp();
         for (int t = 0; t < min(2, first_fill); ++t) issue_tile(t);
     }
-    if (threadIdx.x == 0) TRACE_STAMP(0);
     pdl_launch_dependents();
     pdl_wait_prior_grid();              // activations (and y) belong to the previous kernel until here
     {
@@ -289,7 +277,6 @@ __global__ void __launch_bounds__(RR == 4 ? 512 : 1024, 1) gemv_ring_kernel(cons
         }
     }
     __syncthreads();                    // records and barrier inits visible to all
-    if (threadIdx.x == 0) TRACE_STAMP(1);
 
     if (wid < compute_warps) {
         // ---- compute warps: items in tile order; a warp keeps one parity of the block pairs -------
@@ -321,15 +308,11 @@ __global__ void __launch_bounds__(RR == 4 ? 512 : 1024, 1) gemv_ring_kernel(cons
                 const uint32_t *pair_words = ring + (size_t)slot * slot_words + (g * RR) * P.sw + 17 * ql;
                 const uint32_t *pair_rec = act + (q0 + ql) * ACT_REC_WORDS;
                 float *pair_terms = terms + (size_t)tb * tb_floats + (g * RR) * P.ts + 8 * ql;
-#ifdef BONSAI_B200_TRACE
-                if (g_skip & 1) { pair_terms[0] = __uint_as_float(pair_rec[0] + pair_words[0]); } else
-#endif
                 if (half == 0) gemv_item<RR, 0>(pair_words, P.sw, pair_rec, pair_terms, P.ts, ql);
                 else gemv_item<RR, 1>(pair_words, P.sw, pair_rec, pair_terms, P.ts, ql);
             }
             mbar_arrive(&done[t]);      // release: the loads and the terms above are complete
         }
-        if (threadIdx.x == 0) TRACE_STAMP(2);
     } else if (wid < producer_warp) {
         // ---- adding warps: one lane per row of a row block, running sum kept across its segments --
         const int cw = wid - compute_warps;
@@ -343,16 +326,12 @@ __global__ void __launch_bounds__(RR == 4 ? 512 : 1024, 1) gemv_ring_kernel(cons
                 const int tb = t - (int)fast_div((uint32_t)t, P.magic_ntb) * P.ntb;
                 const int q0 = j * P.seg_base;
                 const int pairs = (j == P.nseg - 1) ? P.npairs - q0 : P.seg_base;
-#ifdef BONSAI_B200_TRACE
-                if (!(g_skip & 2))
-#endif
                 acc = ordered_terms_sum(acc, terms + (size_t)tb * tb_floats + r * P.ts, 0, pairs);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&freed[t]);
             }
             if (lane < r_cnt) y[row0 + rb * P.rs + lane] = acc;
         }
-        if (wid == compute_warps && lane == 0) TRACE_STAMP(3);
     } else {
         // ---- copy warp: a slot is refilled as soon as every item of its previous tile is done ------
         for (int t = first_fill; t < ntiles; ++t) {

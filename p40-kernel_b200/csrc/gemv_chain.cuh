@@ -42,31 +42,13 @@
 
 namespace b200 {
 
-#ifdef BONSAI_B200_TRACE
-// Development aid (not in the shipped build): time stamps of warp 0 at the op boundaries of the first 64 ops.
-__device__ long long g_chain_trace[64 * 160 * 4];
-#define CHAIN_STAMP(op_, k_) do { if (wid == 0 && lane == 0 && (op_) < 64 && blockIdx.x < 160) { \
-    long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); \
-    g_chain_trace[((op_) * 160 + blockIdx.x) * 4 + (k_)] = t_; } } while (0)
-#else
-#define CHAIN_STAMP(op_, k_) do { } while (0)
-#endif
-
 enum : int { CHAIN_ROTATE = 1, CHAIN_DEPENDS = 2, CHAIN_SAME_INPUT = 4, CHAIN_SIGNAL = 8, CHAIN_SPREAD = 16 };
 
 constexpr int CHAIN_MAX_SLOTS = 16;
 constexpr int CHAIN_OP_RING = 8;
-#ifndef CHAIN_TABLES
-#define CHAIN_TABLES 3             // activation-table buffers: the sequencer prepares this many inputs ahead
-#endif
-#ifndef CHAIN_NS0                 // first and longest sleep between two polls of a wait (a stress build stretches them)
-#define CHAIN_NS0 32
-#define CHAIN_NSMAX 256
-#endif
-#ifndef CHAIN_GATE_NS0            // ... of the waits that usually last microseconds (a warp that ran ahead of the others, a
-#define CHAIN_GATE_NS0 32         // table buffer still being read): every poll costs issue slots the working warps want
-#define CHAIN_GATE_NSMAX 256
-#endif
+constexpr int CHAIN_TABLES = 3;          // activation-table buffers: the sequencer prepares this many inputs ahead
+constexpr uint32_t CHAIN_NS0 = 32, CHAIN_NSMAX = 256;             // first and longest sleep between two polls of a wait
+constexpr uint32_t CHAIN_GATE_NS0 = 32, CHAIN_GATE_NSMAX = 256;   // ... of the waits that usually last microseconds
 constexpr int CHAIN_GATES = 3;           // a warp may run this many ops ahead of the slowest one
 
 struct __align__(16) ChainOp {                 // 128 bytes, one per projection, device table
@@ -130,39 +112,69 @@ __device__ __forceinline__ bool spin_until_eq(volatile int *p, int v) {
     atomicExch(&g_device_status, STATUS_MBARRIER_TIMEOUT);
     return false;
 }
-// Arrival counter, polled by one lane, bounded.  Counters only grow (several ranks' launches may add to them, and a
-// rank that is already in its next run may add early), so "reached" is a wrap-safe signed difference.  SYS: the
-// counter is also written by other GPUs (acquire at system scope).
-template <bool SYS>
+// Arrival counter of this GPU's own CTAs, polled by one lane, bounded by an iteration count.  Counters only grow,
+// so "reached" is a wrap-safe signed difference.
 __device__ __forceinline__ bool grid_counter_wait(const unsigned int *counter, unsigned int target) {
     uint32_t ns = CHAIN_NS0;
     for (uint32_t n = 0; n < (1u << 22); ++n) {
         unsigned int v;
-        if (SYS) asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
-        else asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
         if ((int)(v - target) >= 0) return true;
         __nanosleep(ns);
-        ns = min(ns * 2, (uint32_t)CHAIN_NSMAX);
+        ns = min(ns * 2, CHAIN_NSMAX);
     }
     atomicExch(&g_device_status, STATUS_GRID_TIMEOUT);
+    return false;
+}
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Several ranks: flag word q of this rank's counter block is written by rank q (one store over NVLink per signal).
+// Lane q < world polls flag q (acquire at system scope) until it has reached `target`; the wait ends for the whole
+// warp when every flag is there, or when `limit_ns` nanoseconds have passed (status word, false).  Called by a
+// whole warp.
+__device__ __forceinline__ bool rank_flags_wait(const unsigned int *flags, int world, unsigned int target,
+                                                unsigned long long limit_ns, int lane) {
+    const unsigned long long t0 = global_timer_ns();
+    uint32_t ns = CHAIN_NS0;
+    for (uint32_t n = 0; n < (1u << 26); ++n) {
+        bool here = true;
+        if (lane < world) {
+            unsigned int v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + lane) : "memory");
+            here = (int)(v - target) >= 0;
+        }
+        if (__all_sync(0xffffffffu, here)) return true;
+        if (global_timer_ns() - t0 > limit_ns) break;
+        __nanosleep(ns);
+        ns = min(ns * 2, CHAIN_NSMAX);
+    }
+    if (lane == 0) atomicExch(&g_device_status, STATUS_GRID_TIMEOUT);
     return false;
 }
 
 // Row-partitioned lists over several GPUs (one process and one launch per GPU, same list on every rank over its
 // own row slices).  The rows a CTA writes are also copied into the same place of every peer's buffer when the CTA
-// leaves the op (coalesced stores to peer-mapped memory over NVLink), so each rank ends up with the whole vector; "every row of every earlier op
-// is there" then means on every rank: the last warp of a CTA to leave such an op fences at system scope and adds 1
-// to the arrival counter of EVERY rank (peer atomics), and a dependent op polls its own counter for
-// arrivals x CTAs x ranks.  Counters are never reset: a launch reads its run number from counter word 2 and the
-// last CTA to leave adds 1 to it; every launch ends with one more arrival + wait, so that no rank starts its next
-// run (and writes into its peers' outputs) before every rank has finished this one.
+// leaves the op (coalesced stores to peer-mapped memory over NVLink), so each rank ends up with the whole vector.
+// "Every row of every earlier op is there" then means on every rank.  Signalling costs ONE store per peer and
+// signal: after an op that others wait for, each CTA's peer warp fences at system scope and adds 1 to a counter in
+// LOCAL memory; the CTA that completes the count (all CTAs of this GPU have sent their rows) writes the signal's
+// sequence number into flag word `rank` of every rank's counter block, and a dependent op polls the `world` flag
+// words of its own block.  Sequence numbers are never reset: a launch reads its run number from counter word 2 and
+// the last CTA to leave adds 1 to it; every launch ends with one more signal + wait, so that no rank starts its
+// next run (and writes into its peers' outputs) before every rank has finished this one.
+// Counter block (16 words): [0] arrivals of dependent-op producers (one-rank form) [1] spread blocks [2] run
+// [3] CTAs out [4] CTAs of this GPU that have sent their rows, all signals so far [8 + q] last signal of rank q.
 constexpr int CHAIN_MAX_RANKS = 8;
 struct ChainPeers {
     int rank, world;
-    unsigned int arrivals_per_run;              // signalling ops + 1 (the closing one), per CTA and rank
+    unsigned int arrivals_per_run;              // signalling ops (the closing one included) of one run
     unsigned int spread_per_run;                // 1024-blocks rotated by spread ops in one run
+    unsigned long long wait_limit_ns;           // longest wait for the other ranks
     long long y_delta[CHAIN_MAX_RANKS];         // byte offset from this rank's buffer to rank p's mapping of its own
-    unsigned int *counter[CHAIN_MAX_RANKS];     // rank p's counter block: [0] arrivals [1] spread blocks [2] run [3] CTAs out
+    unsigned int *counter[CHAIN_MAX_RANKS];     // rank p's counter block
 };
 
 template <int THREADS, int MAXSTEPS, bool TP>
@@ -216,7 +228,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *_
     unsigned int arrive_base = 0, spread_base = 0;
     if (TP) {
         const unsigned int run = __ldcg(grid_counter + 2);          // written by the previous launch on this stream
-        arrive_base = run * PE.arrivals_per_run * (unsigned)ncta * (unsigned)PE.world;
+        arrive_base = run * PE.arrivals_per_run;                    // signals before this run
         spread_base = run * PE.spread_per_run;
     }
     // a finished y element (several ranks: the CTA's rows go to the peers in one piece when it leaves the op)
@@ -273,7 +285,6 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *_
                 ++op;
                 if (op >= n_ops) { alive = false; break; }
                 // ---- enter op `op`
-                CHAIN_STAMP(op, 0);
                 if (!spin_until_gt(&ctrl[1], op, CHAIN_GATE_NS0, CHAIN_GATE_NSMAX)) { alive = false; break; }
                 if (op >= CHAIN_GATES && !spin_until_gt(&ctrl[8], op - CHAIN_GATES, CHAIN_GATE_NS0, CHAIN_GATE_NSMAX)) { alive = false; break; }
                 // several ranks: the peer warp has sent the rows staged where this op will stage its own
@@ -290,16 +301,15 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *_
                         if (flags & CHAIN_DEPENDS) {
                             if (wid == 0) {
                                 bool ok = true;
-                                if (lane == 0)
-                                    ok = grid_counter_wait<TP>(grid_counter, arrive_base + R.arrivals_needed * (unsigned)ncta *
-                                                                                   (unsigned)(TP ? PE.world : 1));
+                                if (TP) ok = rank_flags_wait(grid_counter + 8, PE.world, arrive_base + R.arrivals_needed,
+                                                             PE.wait_limit_ns, lane);
+                                else if (lane == 0) ok = grid_counter_wait(grid_counter, R.arrivals_needed * (unsigned)ncta);
                                 __syncwarp();
                                 if (lane == 0 && ok) mbar_arrive(dep);
                             }
                             if (!mbar_wait_bounded(dep, dep_phase & 1u, CHAIN_NS0, CHAIN_NSMAX)) { alive = false; break; }
                             ++dep_phase;
                         }
-                        CHAIN_STAMP(op, 1);
                         // Wide inputs of dependent ops are rotated ONCE for the whole grid instead of once per CTA
                         // (every CTA repeating 17 blocks costs ~10 us): block fb is rotated by CTA fb, which writes
                         // its part of the tables to an image in global memory; a second arrival counter tells
@@ -360,7 +370,6 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *_
                                     act_i[chunk] = -64 * (int)(short)(header >> 16);
                                 }
                             }
-                            CHAIN_STAMP(op, 3);
                             if (spread) __threadfence();                // the image rows written above, before the arrival below
                             __syncwarp();
                             if (lane == 0) mbar_arrive(xs);
@@ -376,7 +385,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *_
                                         __threadfence();
                                         atomicAdd(grid_counter + 1, (unsigned)(fb_hi - fb_lo));
                                     }
-                                    there = grid_counter_wait<false>(grid_counter + 1, spread_base + R.spread_blocks);
+                                    there = grid_counter_wait(grid_counter + 1, spread_base + R.spread_blocks);
                                 }
                                 __syncwarp();
                                 if (lane == 0 && there) mbar_arrive(dep);
@@ -397,7 +406,6 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *_
                         if (!mbar_wait_bounded(&ready[R.buf], (uint32_t)R.ready_parity, CHAIN_GATE_NS0, CHAIN_GATE_NSMAX)) { alive = false; break; }
                     }
                 }
-                CHAIN_STAMP(op, 2);
             }
             if (!alive) break;
 
@@ -530,16 +538,25 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *_
                 ctrl[9] = k + 1;                            // the staging rows of op k may be reused
             }
             if (kflags & CHAIN_SIGNAL) {
+                // this CTA's rows are on their way to every rank: count it in local memory; whoever completes the
+                // count for this signal tells every rank (one store each), ordered behind every CTA's stores
                 __threadfence_system();
                 __syncwarp();
-                if (lane == 0)
-                    for (int q = 0; q < PE.world; ++q) atomicAdd_system(PE.counter[q], 1u);
+                if (lane == 0) {
+                    const unsigned int seq = arrive_base + __ldg(&Rk->arrivals_needed) + 1u;    // this signal, counted from 1
+                    const unsigned int old = atomicAdd(grid_counter + 4, 1u);
+                    if (old + 1u == seq * (unsigned)ncta) {
+                        __threadfence_system();
+                        for (int q = 0; q < PE.world; ++q)
+                            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(PE.counter[q] + 8 + PE.rank), "r"(seq) : "memory");
+                    }
+                }
             }
         }
-        // the closing wait: every CTA of every rank has arrived for the last op (the host marks it as one that others
-        // wait for), so nobody is still reading this run's vectors when a rank starts its next run
-        if (good && lane == 0 &&
-            grid_counter_wait<true>(grid_counter, arrive_base + PE.arrivals_per_run * (unsigned)ncta * (unsigned)PE.world)) {
+        // the closing wait: every rank has sent the rows of its last op (the host marks it as one that others wait
+        // for), so nobody is still reading this run's vectors when a rank starts its next run
+        if (good) good = rank_flags_wait(grid_counter + 8, PE.world, arrive_base + PE.arrivals_per_run, PE.wait_limit_ns, lane);
+        if (good && lane == 0) {
             if (atomicAdd(grid_counter + 3, 1u) == (unsigned)ncta - 1u) {        // last CTA out: the next launch is run + 1
                 grid_counter[3] = 0u;
                 __threadfence();

@@ -137,12 +137,10 @@ __device__ __forceinline__ float stream_task(const uint8_t *rowp, int bl, int b0
     if ((blocks & 7) == 0) {
         const int steps = blocks >> 3;
         if (MAXSTEPS >= 5 && steps == 5) return stream_task_full<(MAXSTEPS >= 5 ? 5 : 1)>(rowp, bl, b0 + bl, act_q, act_s, act_i, release);
-#ifndef STREAM_ONLY_LONGEST
         if (MAXSTEPS >= 4 && steps == 4) return stream_task_full<(MAXSTEPS >= 4 ? 4 : 1)>(rowp, bl, b0 + bl, act_q, act_s, act_i, release);
         if (MAXSTEPS >= 3 && steps == 3) return stream_task_full<(MAXSTEPS >= 3 ? 3 : 1)>(rowp, bl, b0 + bl, act_q, act_s, act_i, release);
         if (MAXSTEPS >= 2 && steps == 2) return stream_task_full<(MAXSTEPS >= 2 ? 2 : 1)>(rowp, bl, b0 + bl, act_q, act_s, act_i, release);
         if (steps == 1) return stream_task_full<1>(rowp, bl, b0 + bl, act_q, act_s, act_i, release);
-#endif
     }
     return stream_task_ragged<MAXSTEPS>(rowp, bl, b0, blocks, act_q, act_s, act_i, release);
 }

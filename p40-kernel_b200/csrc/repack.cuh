@@ -37,7 +37,7 @@ __global__ void __launch_bounds__(256) repack_kernel(const uint8_t *__restrict__
     }
 }
 
-template <int RR>
+template <int RR, bool VEC>
 __global__ void __launch_bounds__(256) gemv_repack_kernel(const uint8_t *__restrict__ W, const float *__restrict__ x,
                                                           float *__restrict__ y, int n_out, int nb, int rows_per_cta,
                                                           int rows_per_stage) {
@@ -78,7 +78,7 @@ __global__ void __launch_bounds__(256) gemv_repack_kernel(const uint8_t *__restr
 #pragma unroll
             for (int b = 0; b < 4; ++b) {
                 const int i = i0 + b * blockDim.x + lane;
-                f[b] = i < ngroups4 ? *reinterpret_cast<const float4 *>(x + 4 * (size_t)i) : make_float4(0, 0, 0, 0);
+                f[b] = i < ngroups4 ? load_f4<VEC>(x + 4 * (size_t)i) : make_float4(0, 0, 0, 0);
             }
 #pragma unroll
             for (int b = 0; b < 4; ++b) {

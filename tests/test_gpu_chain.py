@@ -295,31 +295,95 @@ def test_random_lists_with_dependencies(gpu, port, threads, seed):
     assert gpu.device_status() == 0
 
 
-def test_several_rank_form_checks_its_arguments(gpu):
-    """bonsai_b200_chain_create_tp on one device: creation only (nothing is launched, so the second
-    'rank' can be the same buffer); bad rank counts, ranks and counter offsets are refused."""
+def _one_op_chain_tp(gpu, y_ptr, bases, rank, world, total, offset, limit=0, n_out=8):
     import ctypes as C
     import torch
-    W = torch.zeros(8 * 2 * 34, dtype=torch.uint8, device="cuda")
+    W = torch.zeros(n_out * 2 * 34, dtype=torch.uint8, device="cuda")
     x = torch.zeros(1024, device="cuda")
-    buf = torch.zeros(4096, dtype=torch.uint8, device="cuda")
-    y = buf[:32].view(torch.float32)
     op = (gpu.Op * 1)()
-    op[0].W, op[0].x, op[0].signs, op[0].y = W.data_ptr(), x.data_ptr(), None, y.data_ptr()
-    op[0].n_out, op[0].n_in, op[0].flags, op[0].reserved = 8, 256, 0, 0
-    bases = (C.c_void_p * 2)(buf.data_ptr(), buf.data_ptr())
-    lib = gpu.lib()
+    op[0].W, op[0].x, op[0].signs, op[0].y = W.data_ptr(), x.data_ptr(), None, y_ptr
+    op[0].n_out, op[0].n_in, op[0].flags, op[0].reserved = n_out, 256, 0, 0
+    arr = (C.c_void_p * len(bases))(*bases)
+    h = C.c_void_p()
+    rc = gpu.lib().bonsai_b200_chain_create_tp(C.cast(op, C.c_void_p), 1, rank, world, C.cast(arr, C.c_void_p), total,
+                                              offset, limit, C.byref(h))
+    if rc == 0:
+        assert gpu.lib().bonsai_b200_chain_destroy(h) == 0
+    return rc
 
-    def create(rank, world, offset):
-        h = C.c_void_p()
-        rc = lib.bonsai_b200_chain_create_tp(C.cast(op, C.c_void_p), 1, rank, world, C.cast(bases, C.c_void_p), offset, C.byref(h))
-        if rc == 0:
-            assert lib.bonsai_b200_chain_destroy(h) == 0
-        return rc
+
+def test_several_rank_form_checks_its_arguments(gpu):
+    """bonsai_b200_chain_create_tp on one device: creation only (nothing is launched, so the second
+    'rank' can be the same buffer).  Refused: bad rank counts, ranks and counter offsets; a counter block
+    that does not fit in the buffer; a mapping that is not 16-byte aligned; an output that does not lie
+    inside the peer-mapped buffer in front of the counters (the kernel stores it into every other GPU at
+    the same offset, so it would leave the mapping there)."""
+    import torch
+    buf = torch.zeros(4096, dtype=torch.uint8, device="cuda")
+    other = torch.zeros(4096, dtype=torch.uint8, device="cuda")
+    base = buf.data_ptr()
+
+    def create(rank, world, offset, y=base, total=2048 + 64, bases=(base, base), n_out=8):
+        return _one_op_chain_tp(gpu, y, list(bases), rank, world, total, offset, n_out=n_out)
     assert create(0, 2, 2048) == 0
     assert create(1, 2, 2048) == 0
+    assert create(0, 2, 2048, y=base + 2048 - 32) == 0      # the last 8 floats in front of the counters
     assert create(0, 1, 2048) == 1          # one rank: use bonsai_b200_chain_create
     assert create(2, 2, 2048) == 1          # rank out of range
     assert create(0, 9, 2048) == 1          # more ranks than the kernel addresses
     assert create(0, 2, 2050) == 1          # counters must sit on a 64-byte boundary
     assert create(0, 2, -64) == 1
+    assert create(0, 2, 2048, total=2048 + 63) == 1                      # counter block runs past the buffer
+    assert create(0, 2, 2048, y=base + 2048 - 28) == 1                   # output overlaps the counters
+    assert create(0, 2, 2048, y=base + 2048) == 1                        # output behind the buffer's payload
+    assert create(0, 2, 2048, y=other.data_ptr()) == 1                   # output in another allocation
+    assert create(0, 2, 2048, y=base, n_out=520) == 1                    # 2080 bytes do not fit in 2048
+    assert create(0, 2, 2048, bases=(base, base + 8)) == 1               # unaligned mapping of a peer
+    assert create(1, 2, 2048, y=base + 8 + 64, bases=(base, base + 8)) == 1
+
+
+def test_a_rank_that_never_comes_makes_the_wait_run_out(gpu, port):
+    """Failure detection without a fault: a two-rank list whose second 'rank' is a second buffer on the same GPU that
+    no kernel ever signals.  The launch must end by itself within the wait limit (3 ms), the status word must
+    say that a wait for other ranks ran out, clearing must work, and a normal list must pass parity afterwards."""
+    import time
+    import torch
+    n_in, n_out = 1024, 64
+    W = synth.pq2_0_weights(n_out, n_in, seed=5)
+    x = synth.activations(n_in, seed=5)
+    Wd, xd = dev(W), dev(x)
+    payload = 4096
+
+    class TwoBuffers:            # what bonsai_b200.peer.PeerBuffer provides, without a second process
+        rank, world, counter_offset, total_bytes = 0, 2, payload, payload + 64
+
+    mine = torch.zeros(payload + 64, dtype=torch.uint8, device="cuda")
+    nobody = torch.zeros(payload + 64, dtype=torch.uint8, device="cuda")
+    TwoBuffers.ptrs = [mine.data_ptr(), nobody.data_ptr()]
+    y = mine[:n_out * 4].view(torch.float32)
+    assert gpu.device_status() == 0
+    chain = gpu.Chain([(Wd, xd, None, y, n_out, n_in, gpu.OP_ROTATE)], peers=TwoBuffers, wait_limit_us=3000)
+    t0 = time.perf_counter()
+    assert chain.run() == 0
+    torch.cuda.synchronize()
+    assert time.perf_counter() - t0 < 5.0
+    assert gpu.device_status() == 2                      # STATUS_GRID_TIMEOUT: the wait for the other rank ran out
+    # the rows were computed and also stored into the other buffer before the wait
+    scratch = torch.zeros(n_in // 32 * 36, dtype=torch.uint8, device="cuda")
+    ref = torch.zeros(n_out, device="cuda")
+    assert gpu.linear(Wd, xd, None, ref, scratch, n_out, n_in) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(y, ref) and torch.equal(nobody[:n_out * 4].view(torch.float32), ref)
+    chain.close()
+    assert gpu.clear_status() == 0
+    assert gpu.device_status() == 0
+    # the context is intact: a one-rank list gives the per-matrix bits
+    y2 = torch.zeros(n_out, device="cuda")
+    chain = gpu.Chain([(Wd, xd, None, y2, n_out, n_in, gpu.OP_ROTATE)])
+    assert chain.run() == 0
+    torch.cuda.synchronize()
+    assert torch.equal(y2, ref)
+    want = port.gemv(W, port.quantize_q8_1(port.fwht_blocks(x), True), n_out, n_in)
+    assert float(np.abs(host(y2).astype(np.float64) - want).max()) <= REL_TOL * float(np.abs(want).max())
+    chain.close()
+    assert gpu.device_status() == 0

@@ -459,6 +459,51 @@ def test_synthetic_weights_distribution_and_slices(gpu):
     assert not np.array_equal(host(other), host(part))
 
 
+@pytest.mark.parametrize("offset", [1, 2, 3])
+def test_float_vectors_at_odd_offsets(gpu, port, offset):
+    """The reference takes any float pointer (src/kernels/elementwise_p40.cu:75-80, gemv_p40.cu:200-208,
+    gemv_repack_p40.cu:209-220): a vector that starts `offset` floats into an allocation is only 4-byte aligned
+    and must give the same bytes as an aligned one."""
+    import torch
+    n = 5120
+    x = synth.activations(n, seed=31)
+    sg = synth.signs(n, seed=31)
+    holder = torch.zeros(n + 8, dtype=torch.float32, device="cuda")
+    sholder = torch.zeros(n + 8, dtype=torch.float32, device="cuda")
+    xv, sv = holder[offset:offset + n], sholder[offset:offset + n]
+    xv.copy_(dev(x)); sv.copy_(dev(sg))
+    assert xv.data_ptr() % 16 != 0
+    # quantiser
+    out = torch.zeros(n // 32 * 36, dtype=torch.uint8, device="cuda")
+    assert gpu.quant_activations(xv, out, n) == 0
+    assert np.array_equal(host(out), port.quantize_q8_1(x, True))
+    # rotation in place, with signs
+    assert gpu.fwht(xv, sv, n) == 0
+    assert np.array_equal(bits(host(xv)), bits(port.fwht_blocks(x, sg)))
+    assert holder[offset - 1].item() == 0.0 and holder[offset + n].item() == 0.0      # neighbours untouched
+    # rotation + quantiser in one launch, rotated copy at an odd offset too
+    xv.copy_(dev(x))
+    rot = torch.zeros(n + 8, dtype=torch.float32, device="cuda")
+    assert gpu.fwht_quant(xv, sv, out, rot[offset:offset + n], n) == 0
+    want_rot = port.fwht_blocks(x, sg)
+    assert np.array_equal(bits(host(rot[offset:offset + n])), bits(want_rot))
+    assert np.array_equal(host(out), port.quantize_q8_1(want_rot, True))
+    # repacked mat-vec takes the fp32 vector itself
+    n_out = 96
+    W = synth.pq2_0_weights(n_out, n, seed=32)
+    Wr = torch.zeros(W.size, dtype=torch.uint8, device="cuda")
+    assert gpu.repack(dev(W), Wr, n_out, n) == 0
+    y = torch.zeros(n_out, device="cuda")
+    assert gpu.gemv_repack(Wr, xv, y, n_out, n) == 0
+    y_al = torch.zeros(n_out, device="cuda")
+    assert gpu.gemv_repack(Wr, dev(x), y_al, n_out, n) == 0
+    assert np.array_equal(bits(host(y)), bits(host(y_al)))
+    # a pointer that is not even float-aligned is refused
+    raw = torch.zeros(4 * n + 64, dtype=torch.uint8, device="cuda")
+    assert gpu.lib().bonsai_p40_fwht(raw.data_ptr() + 2, None, 1024, None) == 1
+    assert gpu.lib().bonsai_p40_quant_activations(raw.data_ptr() + 2, out.data_ptr(), 1024, None) == 1
+
+
 def test_rejections_and_stubs_on_device(gpu):
     import torch
     z = torch.zeros(4096, dtype=torch.float32, device="cuda")

@@ -46,6 +46,24 @@ def test_static_scratch_projection_two_calls_in_a_row(gpu, port):
     assert gpu.device_status() == 0
 
 
+def test_static_scratch_projection_takes_no_device_memory(gpu):
+    """What the name promises: device memory in use is the same before and after a call (the first call on the
+    device has happened above or happens here, before the measurement; nothing else allocates in between)."""
+    import torch
+    n_out, n_in = 256, 17408
+    Wd = torch.from_numpy(synth.pq2_0_weights(n_out, n_in, seed=24)).cuda()
+    xd = torch.from_numpy(synth.activations(n_in, seed=24)).cuda()
+    y = torch.zeros(n_out, dtype=torch.float32, device="cuda")
+    assert gpu.linear_static(Wd, xd, None, y, n_out, n_in) == 0         # set-up call: resolves the array's address
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    for _ in range(2):
+        assert gpu.linear_static(Wd, xd, None, y, n_out, n_in) == 0
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before, (free_before, free_after)
+
+
 def test_static_scratch_projection_rejects_what_does_not_fit(gpu):
     import torch
     z = torch.zeros(8, dtype=torch.float32, device="cuda")
