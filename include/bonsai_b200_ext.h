@@ -66,6 +66,19 @@ int bonsai_b200_quant_batch(const float *X, const float *signs, void *Xq, int64_
 int bonsai_b200_gemv_chunk_sums(const void *W, const void *xq, int32_t *out, int64_t row0, int64_t n_rows,
                                 int64_t n_in, bonsai_stream stream);
 
+/* The tensor-core mat-vec with its integers written out: y as bonsai_p40_gemv computes it, and in sums[n_out][n_in/32]
+ * the int32 chunk sums (sum of code * activation - sum of activation) that THIS kernel formed on the way -- the
+ * parity probe of the production arithmetic (src/pq2_0.h:149-169).  Shapes: n_in / 128 even. */
+int bonsai_b200_gemv_dump(const void *W, const void *xq, float *y, int32_t *sums, int64_t n_out, int64_t n_in,
+                          bonsai_stream stream);
+
+/* The tensor-core mat-mul with its integers written out: Y as bonsai_p40_gemm computes it on the tensor-core path,
+ * and in sums[(row * n_tok + tok) * (n_in / 32) + chunk] the int32 value (sum of code * activation - sum of
+ * activation) that the tensor core produced for that row, token and chunk -- the host loop's integers
+ * (tests/test_p40.cpp:460-467).  For small cases: the dump is n_out * n_tok * n_in / 32 words. */
+int bonsai_b200_gemm_dump(const void *W, const void *Xq, float *Y, int32_t *sums, int64_t n_out, int64_t n_in,
+                          int64_t n_tok, bonsai_stream stream);
+
 /* Synthetic PQ2_0 weights written on the device: n_blocks blocks whose codes are drawn per
  * element from {0,1,2} with p = {0.33,0.34,0.33} plus code 3 at p = 0.001, and whose fp16
  * scale is |z| * 0.02 with z approximately standard normal.  Counter-based: block i of a
@@ -85,8 +98,9 @@ int bonsai_b200_stream_probe(const void *buf, int64_t bytes, int mode, void *sin
  * bit and are added in a fixed tree order (outputs within 1e-5 of the host's, identical from launch
  * to launch); 1 = the mat-vec that also adds them in the host's sequential order (outputs
  * bit-identical to src/pq2_0.h:183-191, slower).
- * key "gemm_path": -1 (default) = the mat-mul picks its kernel by token count (tensor cores from 16
- * tokens up), 0 = integer SIMT kernel, 1 = tcgen05 tensor-core kernel.  Both give the same bits.
+ * key "gemm_path": -1 (default) = the mat-mul picks its kernel by token count (tensor cores from 48
+ * tokens up), 0 = integer SIMT kernel (Y bit-identical to the host loop), 1 = tcgen05 tensor-core kernel (same
+ * integers; fp32 side within 1e-5 of max |Y|, see csrc/gemm_tc.cuh).
  * key "fuse_linear": 0 (default) = bonsai_b200_linear is two launches, 1 = one kernel when it can (saves a
  * launch, but every CTA then waits for its own rotation before its first multiply: measured ~6 % slower
  * on the 401-projection decode chain).

@@ -39,6 +39,8 @@ SIGNATURES = {
     "bonsai_b200_linear_static": (_INT, [_VP, _VP, _VP, _VP, _I64, _I64, _VP]),
     "bonsai_b200_quant_batch": (_INT, [_VP, _VP, _VP, _I64, _I64, _INT, _VP]),
     "bonsai_b200_gemv_chunk_sums": (_INT, [_VP, _VP, _VP, _I64, _I64, _I64, _VP]),
+    "bonsai_b200_gemv_dump": (_INT, [_VP, _VP, _VP, _VP, _I64, _I64, _VP]),
+    "bonsai_b200_gemm_dump": (_INT, [_VP, _VP, _VP, _VP, _I64, _I64, _I64, _VP]),
     "bonsai_b200_synth_pq2_0": (_INT, [_VP, _I64, _I64, _U64, _VP]),
     "bonsai_b200_stream_probe": (_INT, [_VP, _I64, _INT, _VP, _VP]),
     "bonsai_b200_chain_create": (_INT, [_VP, _I64, _VP]),
@@ -139,6 +141,15 @@ def quant_batch(X, signs, Xq, n_in, n_tok, rotate):
 def gemv_chunk_sums(W, xq, out, row0, n_rows, n_in):
     return lib().bonsai_b200_gemv_chunk_sums(_dev(W, "W"), _dev(xq, "xq"), _dev(out, "out"), row0, n_rows, n_in,
                                              _stream())
+
+
+def gemv_dump(W, xq, y, sums, n_out, n_in):
+    return lib().bonsai_b200_gemv_dump(_dev(W, "W"), _dev(xq, "xq"), _dev(y, "y"), _dev(sums, "sums"), n_out, n_in, _stream())
+
+
+def gemm_dump(W, Xq, Y, sums, n_out, n_in, n_tok):
+    return lib().bonsai_b200_gemm_dump(_dev(W, "W"), _dev(Xq, "Xq"), _dev(Y, "Y"), _dev(sums, "sums"), n_out, n_in, n_tok,
+                                       _stream())
 
 
 def synth_pq2_0(W, first_block, n_blocks, seed):

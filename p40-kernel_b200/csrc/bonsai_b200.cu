@@ -12,6 +12,7 @@
 #include "gemv.cuh"
 #include "gemv_stream.cuh"
 #include "gemv_chain.cuh"
+#include "gemv_mma.cuh"
 #include "probe.cuh"
 #include "repack.cuh"
 #include "synth.cuh"
@@ -141,6 +142,52 @@ bool plan_stream(long long n_out, int nb, int variant, StreamParams &p, int &thr
         smem_bytes = (int)(fixed + (size_t)p.nslot * ((size_t)tr * row_bytes + 16) + 64);
         return true;
     }
+}
+
+// Geometry of the tensor-core mat-vec (gemv_mma.cuh): tiles of 16 rows x one row segment, a ring of slots as deep
+// as `cap_kb` of shared memory allows.  Rows must start on a word (nb even); rows longer than one segment are cut at
+// multiples of 8 blocks (16-byte aligned pieces), which needs nb % 8 == 0.
+bool plan_mma(long long n_out, int nb, int cap_kb, MmaGeom &P, int &smem_bytes, int &grid) {
+    if (nb <= 0 || nb % 2 != 0) return false;
+    P = MmaGeom{};
+    P.n_out = (int)n_out;
+    P.nb = nb;
+    P.ngroups = (int)((n_out + 15) / 16);
+    int seg_max;
+    if (nb % 8 == 0) {
+        const int units = nb / 8;
+        P.nseg = (nb + MMA_SEG_MAX - 1) / MMA_SEG_MAX;
+        P.seg_q = units / P.nseg;
+        P.seg_r = units % P.nseg;
+        seg_max = 8 * (P.seg_q + (P.seg_r ? 1 : 0));
+    } else {
+        if (nb > MMA_SEG_MAX + 8) return false;
+        P.nseg = 1;
+        seg_max = nb;
+    }
+    P.pairs_max = seg_max / 2;
+    const int row_bytes = nb * W_BLOCK_BYTES;
+    if (nb % 8 == 0) {
+        // rows of a tile 16 * (odd) bytes apart: the 8 rows a load instruction touches fall into 8 different bank groups
+        int stride = seg_max * W_BLOCK_BYTES;
+        if ((stride / 16) % 2 == 0) stride += 16;
+        P.contiguous = (P.nseg == 1 && stride == row_bytes) ? 1 : 0;
+        P.stride = stride;
+    } else {
+        P.contiguous = 1;
+        P.stride = row_bytes;
+    }
+    P.slot_bytes = (16 * P.stride + 127) & ~127;
+    int nslot = MMA_MAX_SLOTS;
+    while (nslot >= 2 && mma_fixed_bytes(P, nslot) + (size_t)nslot * P.slot_bytes > (size_t)cap_kb * 1024) --nslot;
+    if (nslot < 2) return false;
+    P.nslot = nslot;
+    P.magic_pairs = magic_u32((uint32_t)P.pairs_max);
+    P.magic_nseg = magic_u32((uint32_t)P.nseg);
+    P.magic_nslot = magic_u32((uint32_t)P.nslot);
+    smem_bytes = (int)(mma_fixed_bytes(P, nslot) + (size_t)nslot * P.slot_bytes);
+    grid = P.ngroups < SM_COUNT ? P.ngroups : SM_COUNT;
+    return true;
 }
 
 // Geometry of the ring mat-vec: one CTA per SM, tiles of about 16 rows by one row segment, a ring that
@@ -336,7 +383,19 @@ int bonsai_p40_gemv(const void *W, const void *xq, float *y, int64_t n_out, int6
     const int variant = g_opt_gemv_variant.load();
     const bool base_ok = (nblocks % 2 == 0) && aligned16(W) && !(reinterpret_cast<uintptr_t>(xq) & 3u);
     int threads = 0, smem_bytes = 0, rr = 2;
-    if (g_opt_gemv_order.load() == 0) {
+    if (g_opt_gemv_order.load() == 2) {
+        MmaGeom mp;
+        int grid = 0;
+        if (base_ok && plan_mma(n_out, nblocks, 200, mp, smem_bytes, grid)) {
+            static SmemOptIn opt;
+            cudaError_t err = opt.ensure(gemv_mma_kernel<false>);
+            if (err != cudaSuccess) return (int)err;
+            return (int)launch(gemv_mma_kernel<false>, dim3((unsigned)grid), dim3(MMA_THREADS), (size_t)smem_bytes,
+                               as_stream(stream), pdl, static_cast<const uint8_t *>(W), static_cast<const uint32_t *>(xq), y,
+                               mp, static_cast<int32_t *>(nullptr));
+        }
+    }
+    if (g_opt_gemv_order.load() != 1) {
         StreamParams sp;
         if (base_ok && plan_stream(n_out, nblocks, variant, sp, threads, smem_bytes)) {
             static SmemOptIn opt;
@@ -350,7 +409,7 @@ int bonsai_p40_gemv(const void *W, const void *xq, float *y, int64_t n_out, int6
         }
     }
     RingParams rp;
-    const bool ring = base_ok && g_opt_gemv_order.load() != 0 &&
+    const bool ring = base_ok && g_opt_gemv_order.load() == 1 &&
                       plan_ring(n_out, nblocks / 2, variant, rp, threads, smem_bytes, rr);
     if (!ring) {
         // odd block count, unaligned weights or a row too long for the rings: plain loads, host order
@@ -700,30 +759,88 @@ int bonsai_b200_gemv_chunk_sums(const void *W, const void *xq, int32_t *out, int
     return (int)cudaGetLastError();
 }
 
+int bonsai_b200_gemv_dump(const void *W, const void *xq, float *y, int32_t *sums, int64_t n_out, int64_t n_in,
+                          bonsai_stream stream) {
+    if (n_in <= 0 || n_in % 128 != 0 || n_out <= 0 || n_out > INT32_MAX || !sums) return 1;
+    const int nblocks = (int)(n_in / 128);
+    MmaGeom mp;
+    int smem_bytes = 0, grid = 0;
+    if (!aligned16(W) || !aligned4(xq) || !plan_mma(n_out, nblocks, 200, mp, smem_bytes, grid)) return 1;
+    static SmemOptIn opt;
+    cudaError_t err = opt.ensure(gemv_mma_kernel<true>);
+    if (err != cudaSuccess) return (int)err;
+    return (int)launch(gemv_mma_kernel<true>, dim3((unsigned)grid), dim3(MMA_THREADS), (size_t)smem_bytes, as_stream(stream),
+                       false, static_cast<const uint8_t *>(W), static_cast<const uint32_t *>(xq), y, mp, sums);
+}
+
+// The tensor-core mat-mul: one CTA per SM walks its share of the (tile, weight block) iterations.
+static int launch_gemm_tc(const void *W, const void *Xq, float *Y, int64_t n_out, int64_t n_in, int64_t n_tok,
+                          int32_t *dump, cudaStream_t st) {
+    static std::atomic<unsigned int> epoch{0};
+    TcParams P{};
+    P.n_out = (int)n_out;
+    P.nblocks = (int)(n_in / 128);
+    P.n_tok = (int)n_tok;
+    P.tiles_tok = (int)((n_tok + TC_N - 1) / TC_N);
+    const long long tiles = (long long)((n_out + TC_M - 1) / TC_M) * P.tiles_tok;
+    if (tiles > INT32_MAX) return 1;
+    P.n_tiles = (int)tiles;
+    P.total_it = tiles * P.nblocks;
+    int dev = 0, sms = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return (int)e;
+    if (sms > TC_MAX_CTAS - 1) sms = TC_MAX_CTAS - 1;
+    const int grid = (int)(tiles < sms ? tiles : sms);
+    // contiguous ranges when they are at least one tile long (then a tile is cut at most once); whole tiles otherwise
+    P.stream_k = (tiles % grid != 0 && P.total_it / grid >= P.nblocks) ? 1 : 0;
+    P.epoch = epoch.fetch_add(1) + 1u;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(TC_THREADS);
+    cfg.dynamicSmemBytes = TC_SMEM_BYTES;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeCooperative;        // a CTA may wait for its neighbour's partial tile: all must be resident
+    attr[0].val.cooperative = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const uint8_t *w8 = static_cast<const uint8_t *>(W);
+    const uint32_t *x32 = static_cast<const uint32_t *>(Xq);
+    // bulk-copy staging of the raw bytes needs 16-byte multiples everywhere; other shapes load from global memory
+    const bool tma = P.nblocks % 8 == 0 && n_tok % 4 == 0 && aligned16(W) && aligned16(Xq);
+    static SmemOptIn opt[4];
+    auto go = [&](auto kernel, SmemOptIn &o, int smem) -> int {
+        cudaError_t err = o.ensure(kernel);
+        if (err != cudaSuccess) return (int)err;
+        cfg.dynamicSmemBytes = (size_t)smem;
+        return (int)cudaLaunchKernelEx(&cfg, kernel, w8, x32, Y, P, dump);
+    };
+    if (dump) return tma ? go(gemm_tc_kernel<true, true>, opt[0], TC_SMEM_BYTES_TMA) : go(gemm_tc_kernel<true, false>, opt[1], TC_SMEM_BYTES);
+    return tma ? go(gemm_tc_kernel<false, true>, opt[2], TC_SMEM_BYTES_TMA) : go(gemm_tc_kernel<false, false>, opt[3], TC_SMEM_BYTES);
+}
+
 int bonsai_p40_gemm(const void *W, const void *Xq, float *Y, int64_t n_out, int64_t n_in, int64_t n_tok,
                     bonsai_stream stream) {
     if (n_in <= 0 || n_in % 128 != 0) return 1;
     if (n_out <= 0 || n_tok <= 0) return 0;
-    if (n_out > INT32_MAX || n_tok > INT32_MAX || (reinterpret_cast<uintptr_t>(Xq) & 3u)) return 1;
+    if (n_out > INT32_MAX || n_tok > INT32_MAX || !aligned4(Xq)) return 1;
     const int path = g_opt_gemm_path.load();
-    const bool tensor = path == 1 || (path < 0 && n_tok >= 16);       // a 64-token tile needs tokens to fill it
-    if (tensor) {
-        const dim3 grid((unsigned)((n_out + TC_M - 1) / TC_M), (unsigned)((n_tok + TC_N - 1) / TC_N));
-        if (grid.y > 65535) return 1;
-        static SmemOptIn opt;
-        cudaError_t err = opt.ensure(gemm_tc_kernel);
-        if (err != cudaSuccess) return (int)err;
-        gemm_tc_kernel<<<grid, TC_THREADS, TC_SMEM_BYTES, as_stream(stream)>>>(
-            static_cast<const uint8_t *>(W), static_cast<const uint32_t *>(Xq), Y, (int)n_out, (int)(n_in / 128),
-            (int)n_tok);
-        return (int)cudaGetLastError();
-    }
+    const bool tensor = path == 1 || (path < 0 && n_tok >= 48);       // a 128-token tile needs tokens to fill it
+    if (tensor) return launch_gemm_tc(W, Xq, Y, n_out, n_in, n_tok, nullptr, as_stream(stream));
     const dim3 grid((unsigned)((n_out + GS_ROWS - 1) / GS_ROWS), (unsigned)((n_tok + GS_TOKS - 1) / GS_TOKS));
     if (grid.y > 65535) return 1;
     gemm_simt_kernel<<<grid, 256, 0, as_stream(stream)>>>(static_cast<const uint8_t *>(W),
                                                           static_cast<const uint32_t *>(Xq), Y, (int)n_out,
                                                           (int)(n_in / 128), (int)n_tok);
     return (int)cudaGetLastError();
+}
+
+int bonsai_b200_gemm_dump(const void *W, const void *Xq, float *Y, int32_t *sums, int64_t n_out, int64_t n_in,
+                          int64_t n_tok, bonsai_stream stream) {
+    if (n_in <= 0 || n_in % 128 != 0 || n_out <= 0 || n_tok <= 0 || !sums) return 1;
+    if (n_out > INT32_MAX || n_tok > INT32_MAX || !aligned4(Xq)) return 1;
+    return launch_gemm_tc(W, Xq, Y, n_out, n_in, n_tok, sums, as_stream(stream));
 }
 
 int bonsai_p40_repack(const void *src, void *dst, int64_t n_out, int64_t n_in, bonsai_stream stream) {
@@ -808,7 +925,11 @@ int bonsai_b200_set_option(const char *key, int64_t value) {
     if (!key) return 1;
     if (!std::strcmp(key, "pdl")) { g_opt_pdl.store(value != 0); return 0; }
     if (!std::strcmp(key, "gemv_variant")) { g_opt_gemv_variant.store((int)value); return 0; }
-    if (!std::strcmp(key, "gemv_order")) { g_opt_gemv_order.store(value != 0); return 0; }
+    if (!std::strcmp(key, "gemv_order")) {
+        if (value < 0 || value > 2) return 1;
+        g_opt_gemv_order.store((int)value);
+        return 0;
+    }
     if (!std::strcmp(key, "gemm_path")) { g_opt_gemm_path.store((int)value); return 0; }
     if (!std::strcmp(key, "fuse_linear")) { g_opt_fuse_linear.store(value != 0); return 0; }
     if (!std::strcmp(key, "chain_threads")) {

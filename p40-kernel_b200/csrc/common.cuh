@@ -132,6 +132,32 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity
     if (!ok) atomicExch(&g_device_status, STATUS_MBARRIER_TIMEOUT);
     return ok != 0;
 }
+// The same wait for a barrier that is expected within a fraction of a microsecond (a tensor-core result, a stage a
+// neighbouring role is about to hand over): polls back to back first, and sleeps between polls only when that did
+// not help.  Bounded like the one above.
+__device__ __forceinline__ bool mbar_wait_hot(uint64_t *bar, uint32_t parity) {
+    uint32_t ok = 0;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        ".reg .u32 n;\n\t"
+        "mov.u32 n, 512;\n\t"
+        "mov.u32 %0, 1;\n\t"
+        "HOT_LOOP:\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "@p bra HOT_DONE;\n\t"
+        "sub.u32 n, n, 1;\n\t"
+        "setp.ne.u32 p, n, 0;\n\t"
+        "@p bra HOT_LOOP;\n\t"
+        "mov.u32 %0, 0;\n\t"
+        "HOT_DONE:\n\t"
+        "}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    if (ok) return true;
+    return mbar_wait_bounded(bar, parity, 32, 128);
+}
 // One non-blocking poll: has the phase with this parity completed?
 __device__ __forceinline__ bool mbar_test(uint64_t *bar, uint32_t parity) {
     uint32_t ok;
@@ -157,6 +183,12 @@ __device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t by
 __device__ __forceinline__ uint64_t policy_evict_first() {
     uint64_t p;
     asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+// Cache policy for data that many CTAs re-read (activation blocks of a token tile): keep it in L2.
+__device__ __forceinline__ uint64_t policy_evict_last_or_default() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
     return p;
 }
 // Programmatic dependent launch: both are no-ops unless the launch carries the attribute.

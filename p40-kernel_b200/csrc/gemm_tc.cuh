@@ -1,25 +1,40 @@
 // gemm_tc.cuh -- prefill mat-mul Y[n_out][n_tok] = W . X on the 5th-generation tensor cores.
 //
-// Replaces, for sm_100a, gemm_pq2_0_p40_kernel (src/kernels/gemm_p40.cu:44-139).  The contraction is
-// a real dense one, so the integer dot products run as tcgen05.mma.kind::i8 with int32 accumulators
-// in tensor memory.  Every 32-weight chunk has its own fp16 x fp16 scale, so chunks cannot be summed
-// inside the tensor core: each K = 32 MMA writes its own TMEM columns (accumulate off), and the
-// epilogue warps read the int32 tile back (tcgen05.ld), subtract the activation sum, convert, scale
-// with (dw * da) and add into fp32 registers -- chunk by chunk, in the order of the reference's host
-// loop (tests/test_p40.cpp:460-467), so Y is bit-identical to it.
+// Replaces, for sm_100a, gemm_pq2_0_p40_kernel (src/kernels/gemm_p40.cu:44-139).  The contraction is a real dense
+// one, so the integer dot products run as tcgen05.mma.kind::i8 with int32 accumulators in tensor memory.  Every
+// 32-weight chunk has its own fp16 x fp16 scale, so chunks cannot be summed inside the tensor core: each K = 32 MMA
+// writes its own TMEM columns (accumulate off) and the epilogue warps read the int32 tile back (tcgen05.ld) and
+// fold it into fp32 registers.  The integers are exact: weights are expanded to signed bytes code - 1, so one MMA
+// gives sum(code * a) - sum(a) of the chunk, the very int32 of the host loop (tests/test_p40.cpp:460-467,
+// src/pq2_0.h:149-169).  The fp32 side uses the tolerance the path states (1e-5 of max |Y|) to spend two
+// instructions per output and chunk instead of five: per block  s = da0*v0 + da1*v1 + da2*v2 + da3*v3  by fused
+// multiply-adds, then  acc += dw * s  -- the host computes (dw*da_c)*v_c term by term; same sums, other roundings.
+// (The integer SIMT kernel, gemm_simt.cuh, keeps the host's bits; bonsai_b200_set_option("gemm_path", 0).)
 //
-// CTA tile: 128 weight rows x 64 tokens, K stepped one weight block (128 weights = 4 MMAs) at a time.
-//   warps 0-7  : epilogue; warp w owns TMEM lanes 32 * (w & 3) .. (one weight row per thread) and
-//                tokens 32 * (w >> 2) .. + 31 (32 fp32 accumulators per thread)
-//   warps 8-11 : producers; expand the 2-bit codes of 128 rows x 1 block to int8 in the K-major
-//                core-matrix layout the MMA reads (8 rows x 16 bytes per core matrix), copy the
-//                int8 activations of 64 tokens x 4 chunks into the same layout, and set up the scale /
-//                sum tables of the block
-//   warp 12    : one thread issues the MMAs and commits them to an mbarrier; the warp owns the TMEM
-//                allocation (512 columns = 2 stages x 4 chunks x 64 tokens)
-// The byte order inside a chunk is the permuted one on both sides: extracting field k of a 16-code
-// word gives the four codes that the activation quantiser stored as word k (src/pq2_0.h:120-125,
-// 158-166), so no shuffle is needed on either operand.
+// CTA tile: 128 weight rows x 128 tokens, one CTA per SM (it owns the SM's 512 TMEM columns: 4 stages x 128), K
+// stepped one weight block (4 chunks = 4 MMAs of M 128 x N 128 x K 32) at a time:
+//   warps 0-15  : epilogue; warp w owns TMEM lanes 32 * (w % 4) .. (one weight row per thread) and tokens
+//                 32 * (w / 4) .. + 31: 32 accumulators per thread, block sums 16 tokens at a time
+//   warps 16-19 : producers; thread p expands the 2-bit codes of row p of the block to int8 (code - 1) in the
+//                 K-major core-matrix layout the MMA reads (8 rows x 16 bytes per core matrix) and copies the int8
+//                 activations and the scale of token p for the block's four chunks
+//   warp 20     : one thread issues the MMAs and commits them to mbarriers; the warp owns the TMEM allocation
+//   warp 21     : (TMA form) bulk async copies of the raw bytes into shared memory, two buffers each: the weight
+//                 rows 8 blocks (272 bytes, a 16-byte multiple) at a time, the Q8_1 blocks of the tile's tokens one
+//                 weight block at a time -- the producers then read shared memory instead of issuing a 2-byte
+//                 global load per halfword of a 34-byte block (which made them the bottleneck: 1.8 us per block).
+//                 Needs n_in / 128 a multiple of 8, n_tok a multiple of 4, 16-byte aligned W and Xq; every other
+//                 shape takes the form whose producers load from global memory themselves.
+// The byte order inside a chunk is the permuted one on both sides: field k of a 16-code word holds the four codes
+// that the activation quantiser stored as word k (src/pq2_0.h:120-125, 158-166).
+//
+// Work split ("stream-K"): the (tile, weight block) iterations of the whole problem are cut into one contiguous
+// range per CTA, so every SM gets the same work whatever the tile count (160 tiles on 148 SMs would otherwise take
+// two rounds).  A tile cut in two has its later K part computed FIRST by the CTA whose range starts inside it: that
+// CTA writes its partial sums to Y and raises a flag; the CTA whose range ends inside the tile computes the earlier
+// K part LAST, waits for the flag (bounded; normally long since raised) and stores early + late.  One fixed order,
+// so Y does not depend on timing.  Flags live in a small static array, one set per launch in flight (8 sets, chosen
+// by the launch number); the reader lowers a flag once it has seen it.
 // Every wait is bounded; on a time-out the CTA still reaches the common exit and frees its TMEM.
 #pragma once
 
@@ -27,13 +42,22 @@
 
 namespace b200 {
 
-constexpr int TC_M = 128, TC_N = 64;
-constexpr int TC_SMEM_STAGES = 4, TC_TMEM_STAGES = 2;
-constexpr int TC_A_BYTES = 4 * TC_M * 32;                 // 4 chunks x 128 rows x 32 bytes
+constexpr int TC_M = 128, TC_N = 128;
+constexpr int TC_STAGES = 3;                               // shared-memory stages (one weight block each)
+constexpr int TC_A_BYTES = 4 * TC_M * 32;                  // 4 chunks x 128 rows x 32 bytes
 constexpr int TC_B_BYTES = 4 * TC_N * 32;
-constexpr int TC_STAGE_BYTES = TC_A_BYTES + TC_B_BYTES + TC_M * 4 + 4 * TC_N * 4 + 4 * TC_N * 4;
-constexpr int TC_EPI_THREADS = 256, TC_PROD_THREADS = 128, TC_THREADS = TC_EPI_THREADS + TC_PROD_THREADS + 32;
-constexpr int TC_SMEM_BYTES = 1024 + TC_SMEM_STAGES * TC_STAGE_BYTES + 8192;   // > half an SM: one CTA (one TMEM owner) per SM
+constexpr int TC_STAGE_BYTES = TC_A_BYTES + TC_B_BYTES + TC_M * 4 + 4 * TC_N * 4;
+constexpr int TC_EPI_WARPS = 16, TC_PROD_WARPS = 4;
+constexpr int TC_EPI_THREADS = TC_EPI_WARPS * 32, TC_PROD_THREADS = TC_PROD_WARPS * 32;
+constexpr int TC_THREADS = TC_EPI_THREADS + TC_PROD_THREADS + 64;       // + issuer warp + loader warp
+constexpr int TC_WRAW_BYTES = TC_M * 272;                  // raw PQ2_0 bytes of 8 consecutive blocks of 128 rows
+constexpr int TC_XRAW_BYTES = 4 * TC_N * A_BLOCK_BYTES;    // raw Q8_1 blocks of 4 chunks x 128 tokens
+constexpr int TC_SMEM_BYTES = 1024 + TC_STAGES * TC_STAGE_BYTES;
+constexpr int TC_SMEM_BYTES_TMA = TC_SMEM_BYTES + 2 * TC_WRAW_BYTES + 2 * TC_XRAW_BYTES;
+constexpr int TC_FLAG_SETS = 8, TC_MAX_CTAS = 256;
+
+// Partial-tile flags: set `epoch % 8`, word = CTA that wrote the partial; raised by the writer, lowered by the reader.
+__device__ unsigned int g_gemm_flags[TC_FLAG_SETS][TC_MAX_CTAS];
 
 // Shared-memory matrix descriptor, K-major, no swizzle: core matrices of 8 rows x 16 bytes; the two
 // core matrices along K are 128 bytes apart (leading offset), 8-row groups 256 bytes apart (stride).
@@ -41,8 +65,7 @@ __device__ __forceinline__ uint64_t tc_smem_desc(uint32_t smem_addr) {
     return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | ((uint64_t)(128 >> 4) << 16) | ((uint64_t)(256 >> 4) << 32) |
            (1ull << 46);
 }
-// Instruction descriptor: D = int32, A and B signed 8-bit (codes 0..3 are the same numbers signed),
-// both K-major, N = 64, M = 128.
+// Instruction descriptor: D = int32, A and B signed 8-bit, both K-major, N = 128, M = 128.
 constexpr uint32_t TC_IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((TC_N >> 3) << 17) | ((TC_M >> 4) << 24);
 
 __device__ __forceinline__ void tc_mma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc) {
@@ -61,25 +84,22 @@ __device__ __forceinline__ void tc_commit(uint64_t *bar) {
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, int (&v)[32]) {
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, int (&v)[16]) {
     asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
         : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
-          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
-          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
         : "r"(taddr)
         : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+__device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_epi_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(TC_EPI_THREADS) : "memory"); }
 
 struct TcStage {
-    uint8_t *a, *b;      // 4 x (128 x 32) and 4 x (64 x 32) int8, core-matrix layout
+    uint8_t *a, *b;      // 4 x (128 x 32) int8 each, core-matrix layout
     float *dw;           // [128] weight scale of the block, per row
-    float *da;           // [4][64] activation scale per chunk and token
-    int *sn;             // [4][64] activation sum per chunk and token
+    float *da;           // [4][128] activation scale per chunk and token
 };
 __device__ __forceinline__ TcStage tc_stage(uint8_t *base, int s) {
     uint8_t *p = base + (size_t)s * TC_STAGE_BYTES;
@@ -88,29 +108,79 @@ __device__ __forceinline__ TcStage tc_stage(uint8_t *base, int s) {
     st.b = p + TC_A_BYTES;
     st.dw = reinterpret_cast<float *>(p + TC_A_BYTES + TC_B_BYTES);
     st.da = st.dw + TC_M;
-    st.sn = reinterpret_cast<int *>(st.da + 4 * TC_N);
     return st;
 }
 
+struct TcParams {
+    int n_out, nblocks, n_tok;
+    int tiles_tok, n_tiles;          // token tiles per row tile, tiles in all (token tile runs fastest)
+    int stream_k;                    // 1: contiguous ranges of (tile, block) iterations; 0: whole tiles, round-robin
+    unsigned int epoch;              // launch number, never 0 (flag set = epoch % 8)
+    long long total_it;              // n_tiles * nblocks
+};
+
+// The CTA's next piece of work: blocks [kb0, kb1) of `tile`.  Every role walks the same sequence.
+struct TcWalk {
+    long long it, it_end;
+    int tile_rr;
+    __device__ __forceinline__ void start(const TcParams &P) {
+        if (P.stream_k) {
+            it = P.total_it * (long long)blockIdx.x / (long long)gridDim.x;
+            it_end = P.total_it * ((long long)blockIdx.x + 1) / (long long)gridDim.x;
+        } else {
+            tile_rr = (int)blockIdx.x;
+        }
+    }
+    __device__ __forceinline__ bool next(const TcParams &P, int &tile, int &kb0, int &kb1) {
+        if (P.stream_k) {
+            if (it >= it_end) return false;
+            tile = (int)(it / P.nblocks);
+            kb0 = (int)(it - (long long)tile * P.nblocks);
+            const long long left = it_end - it;
+            kb1 = (int)min((long long)P.nblocks, (long long)kb0 + left);
+            it += kb1 - kb0;
+            return true;
+        }
+        if (tile_rr >= P.n_tiles) return false;
+        tile = tile_rr;
+        kb0 = 0;
+        kb1 = P.nblocks;
+        tile_rr += (int)gridDim.x;
+        return true;
+    }
+};
+
+// DUMP: also writes the int32 value of every (row, token, chunk) to dump[(row * n_tok + tok) * (4 * nblocks) + chunk].
+template <bool DUMP, bool TMA>
 __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const uint8_t *__restrict__ W, const uint32_t *__restrict__ Xq,
-                                                                float *__restrict__ Y, int n_out, int nblocks, int n_tok) {
+                                                                float *Y, const TcParams P, int32_t *__restrict__ dump) {
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t *full = reinterpret_cast<uint64_t *>(smem);               // [4] producers -> issuer
-    uint64_t *released = full + TC_SMEM_STAGES;                         // [4] epilogue -> producers
-    uint64_t *mma_done = released + TC_SMEM_STAGES;                     // [2] tensor core -> epilogue
-    uint64_t *tmem_empty = mma_done + TC_TMEM_STAGES;                   // [2] epilogue -> issuer
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tmem_empty + TC_TMEM_STAGES);
+    uint64_t *released = full + TC_STAGES;                              // [4] tensor core + epilogue -> producers
+    uint64_t *mma_done = released + TC_STAGES;                          // [4] tensor core -> epilogue (one per chunk of a block)
+    uint64_t *tmem_empty = mma_done + 4;                                // [4] epilogue -> issuer
+    uint64_t *wfull = tmem_empty + 4;                                   // [2] loader -> producers: 8 blocks of weight rows landed
+    uint64_t *wfree = wfull + 2;                                        // [2] producers -> loader
+    uint64_t *xfull = wfree + 2;                                        // [2] loader -> producers: a block's Q8_1 blocks landed
+    uint64_t *xfree = xfull + 2;                                        // [2] producers -> loader
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(xfree + 2);
     uint8_t *stages = smem + 1024;
+    uint8_t *wraw = stages + TC_STAGES * TC_STAGE_BYTES;
+    uint8_t *xraw = wraw + 2 * TC_WRAW_BYTES;
 
     const int wid = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int row0 = blockIdx.x * TC_M, tok0 = blockIdx.y * TC_N;
+    const int nblocks = P.nblocks, n_tok = P.n_tok, n_out = P.n_out;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < TC_SMEM_STAGES; ++s) { mbar_init(&full[s], TC_PROD_THREADS); mbar_init(&released[s], TC_EPI_THREADS); }
-        for (int s = 0; s < TC_TMEM_STAGES; ++s) { mbar_init(&mma_done[s], 1); mbar_init(&tmem_empty[s], TC_EPI_THREADS); }
+        for (int s = 0; s < TC_STAGES; ++s) { mbar_init(&full[s], TC_PROD_THREADS); mbar_init(&released[s], 1 + TC_EPI_WARPS); }
+        for (int s = 0; s < 4; ++s) { mbar_init(&mma_done[s], 1); mbar_init(&tmem_empty[s], TC_EPI_WARPS); }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&wfull[s], 1); mbar_init(&wfree[s], TC_PROD_THREADS);
+            mbar_init(&xfull[s], 1); mbar_init(&xfree[s], TC_PROD_THREADS);
+        }
         mbar_fence_init();
     }
-    if (wid == 12) {
+    if (wid == TC_EPI_WARPS + TC_PROD_WARPS) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -119,123 +189,259 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const uint8_t *_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    TcWalk walk;
+    walk.start(P);
+    int tile, kb0, kb1;
 
-    if (wid < 8) {
+    if (wid < TC_EPI_WARPS) {
         // ---------------- epilogue: one weight row per thread, 32 tokens ----------------
-        const int q = wid & 3, hf = wid >> 2;
+        const int q = wid & 3, cg = wid >> 2;
         const int row_l = 32 * q + lane;
-        float acc[32];
+        unsigned int *flags = g_gemm_flags[P.epoch & (TC_FLAG_SETS - 1)];
+        bool ok = true;
+        int n = 0;                              // weight blocks consumed by this CTA so far
+        while (ok && walk.next(P, tile, kb0, kb1)) {
+            const int rt = tile / P.tiles_tok, tt = tile - rt * P.tiles_tok;
+            const int row = rt * TC_M + row_l, tokb = tt * TC_N + 32 * cg;
+            float acc[32];
 #pragma unroll
-        for (int t = 0; t < 32; ++t) acc[t] = 0.0f;
-        for (int b = 0; b < nblocks; ++b) {
-            const int s = b % TC_SMEM_STAGES, ts = b % TC_TMEM_STAGES;
-            if (!mbar_wait_bounded(&mma_done[ts], (uint32_t)((b / TC_TMEM_STAGES) & 1))) break;
-            tc_fence_after();
-            const TcStage st = tc_stage(stages, s);
-            const float dw = st.dw[row_l];
-#pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                int v[32];
-                tc_ld32(tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(ts * 256 + c * TC_N + 32 * hf), v);
-                if (c == 3) {           // the tile of this stage is in registers: the tensor core may reuse it
-                    tc_fence_before();
-                    mbar_arrive(&tmem_empty[ts]);
+            for (int j = 0; j < 32; ++j) acc[j] = 0.0f;
+            for (int kb = kb0; kb < kb1 && ok; ++kb, ++n) {
+                const int s = n % TC_STAGES;
+                const TcStage st = tc_stage(stages, s);
+                // two passes of 16 tokens over the block's four chunks (32 accumulators + 16 block sums + 16 integers live)
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    float accb[16];
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        if (h == 0) {
+                            if (!mbar_wait_hot(&mma_done[c], (uint32_t)(n & 1))) { ok = false; break; }
+                            tc_fence_after();
+                        }
+                        int v[16];
+                        tc_ld16(tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(c * TC_N + 32 * cg + 16 * h), v);
+                        tc_ld_wait();
+                        if (h == 1) {           // both halves of this chunk are in registers: the tensor core may overwrite it
+                            tc_fence_before();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(&tmem_empty[c]);
+                        }
+                        const float4 *da4 = reinterpret_cast<const float4 *>(st.da + c * TC_N + 32 * cg + 16 * h);
+#pragma unroll
+                        for (int g4 = 0; g4 < 4; ++g4) {
+                            const float4 d = da4[g4];
+                            const float dd[4] = {d.x, d.y, d.z, d.w};
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const float f = (float)v[4 * g4 + e];
+                                accb[4 * g4 + e] = (c == 0) ? __fmul_rn(dd[e], f) : __fmaf_rn(dd[e], f, accb[4 * g4 + e]);
+                            }
+                        }
+                        if (DUMP && row < n_out) {
+#pragma unroll
+                            for (int e = 0; e < 16; ++e) {
+                                const int tok = tokb + 16 * h + e;
+                                if (tok < n_tok) dump[((size_t)row * n_tok + tok) * (4 * (size_t)nblocks) + 4 * kb + c] = v[e];
+                            }
+                        }
+                    }
+                    if (!ok) break;
+                    const float dw = st.dw[row_l];          // written by the producers: read behind the waits above
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) acc[16 * h + j] = __fmaf_rn(dw, accb[j], acc[16 * h + j]);
                 }
-                const float4 *da4 = reinterpret_cast<const float4 *>(st.da + c * TC_N + 32 * hf);
-                const int4 *sn4 = reinterpret_cast<const int4 *>(st.sn + c * TC_N + 32 * hf);
+                if (!ok) break;
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&released[s]);          // the scale tables of this stage are free
+            }
+            if (!ok) break;
+            // ---- the tile (or this CTA's part of it) is done
+            const bool late_part = kb0 > 0, early_part = kb1 < nblocks;
+            float *yrow = Y + (size_t)row * n_tok + tokb;
+            const bool vec = (n_tok & 3) == 0 && (reinterpret_cast<uintptr_t>(Y) & 15u) == 0;
+            if (early_part) {
+                // the CTA after this one computed the later blocks of this tile first and left them in Y
+                if (threadIdx.x == 0) {
+                    const unsigned int *f = flags + blockIdx.x + 1;
+                    uint32_t ns = 64;
+                    bool there = false;
+                    for (uint32_t k = 0; k < (1u << 22); ++k) {
+                        unsigned int v;
+                        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+                        if (v != 0u) { there = true; break; }
+                        __nanosleep(ns);
+                        ns = min(ns * 2, 1024u);
+                    }
+                    if (!there) atomicExch(&g_device_status, STATUS_GRID_TIMEOUT);
+                    // this CTA is the flag's only reader: lowered here, it is down again for the next launch that uses
+                    // the set (a replayed CUDA graph carries the same launch number every time)
+                    *const_cast<volatile unsigned int *>(f) = 0u;
+                }
+                tc_epi_barrier();
+                if (row < n_out) {
 #pragma unroll
-                for (int g = 0; g < 8; ++g) {
-                    const float4 d = da4[g];
-                    const int4 sm = sn4[g];
-                    acc[4 * g + 0] = __fadd_rn(acc[4 * g + 0], __fmul_rn(__fmul_rn(dw, d.x), (float)(v[4 * g + 0] - sm.x)));
-                    acc[4 * g + 1] = __fadd_rn(acc[4 * g + 1], __fmul_rn(__fmul_rn(dw, d.y), (float)(v[4 * g + 1] - sm.y)));
-                    acc[4 * g + 2] = __fadd_rn(acc[4 * g + 2], __fmul_rn(__fmul_rn(dw, d.z), (float)(v[4 * g + 2] - sm.z)));
-                    acc[4 * g + 3] = __fadd_rn(acc[4 * g + 3], __fmul_rn(__fmul_rn(dw, d.w), (float)(v[4 * g + 3] - sm.w)));
+                    for (int j = 0; j < 32; ++j)
+                        if (tokb + j < n_tok) acc[j] = __fadd_rn(acc[j], __ldcg(yrow + j));
                 }
             }
-            mbar_arrive(&released[s]);          // the scale tables (and A/B) of this stage are free
-        }
-        const int row = row0 + row_l;
-        if (row < n_out) {
+            if (row < n_out) {
+                if (vec) {
 #pragma unroll
-            for (int t = 0; t < 32; ++t) {
-                const int tok = tok0 + 32 * hf + t;
-                if (tok < n_tok) Y[(size_t)row * n_tok + tok] = acc[t];
-            }
-        }
-    } else if (wid < 12) {
-        // ---------------- producers: expand codes, lay out activations ----------------
-        const int p = threadIdx.x - TC_EPI_THREADS;            // 0..127 = weight row of the tile
-        const int row = min(row0 + p, n_out - 1);               // rows past the end repeat the last one (never stored)
-        const uint8_t *wrow = W + (size_t)row * nblocks * W_BLOCK_BYTES;
-        const uint32_t a_off = (uint32_t)((p >> 3) * 256 + (p & 7) * 16);
-        for (int b = 0; b < nblocks; ++b) {
-            const int s = b % TC_SMEM_STAGES;
-            if (!mbar_wait_bounded(&released[s], (uint32_t)(((b / TC_SMEM_STAGES) & 1) ^ 1))) break;
-            const TcStage st = tc_stage(stages, s);
-            const uint8_t *wb = wrow + (size_t)b * W_BLOCK_BYTES;
-            // all 17 + 18 loads of this thread are issued before anything is stored: one memory round
-            // trip per block instead of one per word
-            uint32_t h[17];
-#pragma unroll
-            for (int i = 0; i < 17; ++i) h[i] = ldg_nc_u16(wb + 2 * i);
-            constexpr int ACT_WORDS = 4 * TC_N * 9 / TC_PROD_THREADS;       // 18 words of Q8_1 per thread and block
-            uint32_t av[ACT_WORDS];
-#pragma unroll
-            for (int j = 0; j < ACT_WORDS; ++j) {
-                const int i = p + j * TC_PROD_THREADS;
-                const int c = i / (TC_N * 9), rem = i - c * (TC_N * 9);
-                const int t = rem / 9, w = rem - t * 9;
-                av[j] = (tok0 + t < n_tok) ? __ldg(Xq + 9 * ((size_t)(4 * b + c) * n_tok + tok0 + t) + w) : 0u;
-            }
-            st.dw[p] = f16_bits_to_f32(h[0]);
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                const uint32_t w0 = h[1 + 4 * c] | (h[2 + 4 * c] << 16), w1 = h[3 + 4 * c] | (h[4 + 4 * c] << 16);
-                uint4 lo, hi;
-                lo.x = w0 & 0x03030303u; lo.y = (w0 >> 2) & 0x03030303u; lo.z = (w0 >> 4) & 0x03030303u; lo.w = (w0 >> 6) & 0x03030303u;
-                hi.x = w1 & 0x03030303u; hi.y = (w1 >> 2) & 0x03030303u; hi.z = (w1 >> 4) & 0x03030303u; hi.w = (w1 >> 6) & 0x03030303u;
-                uint8_t *ac = st.a + c * (TC_M * 32) + a_off;
-                *reinterpret_cast<uint4 *>(ac) = lo;             // bytes 0..15 of the chunk: first K core matrix
-                *reinterpret_cast<uint4 *>(ac + 128) = hi;       // bytes 16..31: second K core matrix
-            }
-#pragma unroll
-            for (int j = 0; j < ACT_WORDS; ++j) {
-                const int i = p + j * TC_PROD_THREADS;
-                const int c = i / (TC_N * 9), rem = i - c * (TC_N * 9);
-                const int t = rem / 9, w = rem - t * 9;
-                const uint32_t v = av[j];
-                if (w == 0) {
-                    st.da[c * TC_N + t] = f16_bits_to_f32(v & 0xFFFFu);
-                    st.sn[c * TC_N + t] = (int)(short)(v >> 16);
+                    for (int j = 0; j < 32; j += 4)
+                        if (tokb + j < n_tok) *reinterpret_cast<float4 *>(yrow + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
                 } else {
-                    const int k = w - 1;
-                    *reinterpret_cast<uint32_t *>(st.b + c * (TC_N * 32) + (t >> 3) * 256 + (k >> 2) * 128 + (t & 7) * 16 +
-                                                  (k & 3) * 4) = v;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (tokb + j < n_tok) yrow[j] = acc[j];
                 }
             }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");    // the tensor core reads through the async proxy
-            mbar_arrive(&full[s]);
+            if (late_part) {
+                __threadfence();
+                tc_epi_barrier();
+                if (threadIdx.x == 0) asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(flags + blockIdx.x), "r"(P.epoch) : "memory");
+            }
+        }
+    } else if (wid < TC_EPI_WARPS + TC_PROD_WARPS) {
+        // ---------------- producers: expand codes (thread = weight row), lay out activations (thread = token) --------
+        const int p = threadIdx.x - TC_EPI_THREADS;            // 0..127
+        const uint32_t a_off = (uint32_t)((p >> 3) * 256 + (p & 7) * 16);
+        bool ok = true;
+        int n = 0, oct = 0;                     // weight blocks / groups of 8 blocks handled so far
+        while (ok && walk.next(P, tile, kb0, kb1)) {
+            const int rt = tile / P.tiles_tok, tt = tile - rt * P.tiles_tok;
+            const int row = min(rt * TC_M + p, n_out - 1);      // rows past the end repeat the last one (never stored)
+            const int tok = tt * TC_N + p;
+            const bool tok_ok = tok < n_tok;
+            const uint8_t *wrow = W + (size_t)row * nblocks * W_BLOCK_BYTES;
+            for (int kb = kb0; kb < kb1; ++kb, ++n) {
+                const int s = n % TC_STAGES;
+                uint32_t h[17];
+                uint32_t av[4][9];
+                int wbuf = 0;
+                if (TMA) {
+                    // raw bytes from shared memory: the loader warp copied them there
+                    if (kb == kb0 || (kb & 7) == 0) {
+                        if (!mbar_wait_bounded(&wfull[oct & 1], (uint32_t)((oct >> 1) & 1))) { ok = false; break; }
+                        ++oct;
+                    }
+                    wbuf = (oct - 1) & 1;
+                    if (!mbar_wait_bounded(&xfull[n & 1], (uint32_t)((n >> 1) & 1))) { ok = false; break; }
+                    const unsigned short *wr = reinterpret_cast<const unsigned short *>(wraw + (size_t)wbuf * TC_WRAW_BYTES + (size_t)p * 272 +
+                                                                                        (size_t)(kb & 7) * W_BLOCK_BYTES);
+#pragma unroll
+                    for (int i = 0; i < 17; ++i) h[i] = wr[i];
+                    const uint32_t *xr = reinterpret_cast<const uint32_t *>(xraw + (size_t)(n & 1) * TC_XRAW_BYTES) + 9 * p;
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+#pragma unroll
+                        for (int w = 0; w < 9; ++w) av[c][w] = tok_ok ? xr[c * (TC_N * 9) + w] : 0u;
+                } else {
+                    // all loads of this thread are issued before the wait and before anything is stored
+                    const uint8_t *wb = wrow + (size_t)kb * W_BLOCK_BYTES;
+#pragma unroll
+                    for (int i = 0; i < 17; ++i) h[i] = ldg_nc_u16(wb + 2 * i);
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+#pragma unroll
+                        for (int w = 0; w < 9; ++w)
+                            av[c][w] = tok_ok ? __ldg(Xq + 9 * ((size_t)(4 * kb + c) * n_tok + tok) + w) : 0u;
+                }
+                if (!mbar_wait_bounded(&released[s], (uint32_t)(((n / TC_STAGES) & 1) ^ 1))) { ok = false; break; }
+                const TcStage st = tc_stage(stages, s);
+                st.dw[p] = f16_bits_to_f32(h[0]);
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const uint32_t w0 = h[1 + 4 * c] | (h[2 + 4 * c] << 16), w1 = h[3 + 4 * c] | (h[4 + 4 * c] << 16);
+                    // field k of a word -> four codes 0..3 -> signed bytes code - 1 (add 0x7F per byte, flip the top bit)
+                    uint4 lo, hi;
+                    lo.x = ((w0 & 0x03030303u) + 0x7F7F7F7Fu) ^ 0x80808080u;
+                    lo.y = (((w0 >> 2) & 0x03030303u) + 0x7F7F7F7Fu) ^ 0x80808080u;
+                    lo.z = (((w0 >> 4) & 0x03030303u) + 0x7F7F7F7Fu) ^ 0x80808080u;
+                    lo.w = (((w0 >> 6) & 0x03030303u) + 0x7F7F7F7Fu) ^ 0x80808080u;
+                    hi.x = ((w1 & 0x03030303u) + 0x7F7F7F7Fu) ^ 0x80808080u;
+                    hi.y = (((w1 >> 2) & 0x03030303u) + 0x7F7F7F7Fu) ^ 0x80808080u;
+                    hi.z = (((w1 >> 4) & 0x03030303u) + 0x7F7F7F7Fu) ^ 0x80808080u;
+                    hi.w = (((w1 >> 6) & 0x03030303u) + 0x7F7F7F7Fu) ^ 0x80808080u;
+                    uint8_t *ac = st.a + c * (TC_M * 32) + a_off;
+                    *reinterpret_cast<uint4 *>(ac) = lo;             // bytes 0..15 of the chunk: first K core matrix
+                    *reinterpret_cast<uint4 *>(ac + 128) = hi;       // bytes 16..31: second K core matrix
+                    uint8_t *bc = st.b + c * (TC_N * 32) + a_off;
+                    *reinterpret_cast<uint4 *>(bc) = make_uint4(av[c][1], av[c][2], av[c][3], av[c][4]);
+                    *reinterpret_cast<uint4 *>(bc + 128) = make_uint4(av[c][5], av[c][6], av[c][7], av[c][8]);
+                    st.da[c * TC_N + p] = f16_bits_to_f32(av[c][0] & 0xFFFFu);
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");    // the tensor core reads through the async proxy
+                mbar_arrive(&full[s]);
+                if (TMA) {
+                    mbar_arrive(&xfree[n & 1]);                                  // the raw bytes are in registers / the stage
+                    if ((kb & 7) == 7 || kb == kb1 - 1) mbar_arrive(&wfree[wbuf]);
+                }
+            }
+        }
+    } else if (wid == TC_EPI_WARPS + TC_PROD_WARPS + 1) {
+        // ---------------- loader (TMA form): raw weight rows and raw Q8_1 blocks into shared memory ----------------
+        if (TMA) {
+            const uint64_t pol = policy_evict_first();
+            const size_t row_bytes = (size_t)nblocks * W_BLOCK_BYTES;
+            bool ok = true;
+            int n = 0, oct = 0;
+            while (ok && walk.next(P, tile, kb0, kb1)) {
+                const int rt = tile / P.tiles_tok, tt = tile - rt * P.tiles_tok;
+                const int rows_valid = min(TC_M, n_out - rt * TC_M), toks_valid = min(TC_N, n_tok - tt * TC_N);
+                for (int kb = kb0; kb < kb1; ++kb, ++n) {
+                    if (kb == kb0 || (kb & 7) == 0) {
+                        const int wb = oct & 1;
+                        if (!mbar_wait_bounded(&wfree[wb], (uint32_t)(((oct >> 1) & 1) ^ 1))) { ok = false; break; }
+                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                        if (lane == 0) mbar_expect_tx(&wfull[wb], (uint32_t)rows_valid * 272u);
+                        __syncwarp();
+                        const uint8_t *src = W + (size_t)rt * TC_M * row_bytes + (size_t)(kb >> 3) * 272;
+                        for (int r = lane; r < rows_valid; r += 32)
+                            bulk_g2s(wraw + (size_t)wb * TC_WRAW_BYTES + (size_t)r * 272, src + (size_t)r * row_bytes, 272u, &wfull[wb], pol);
+                        ++oct;
+                    }
+                    const int xb = n & 1;
+                    if (!mbar_wait_bounded(&xfree[xb], (uint32_t)(((n >> 1) & 1) ^ 1))) { ok = false; break; }
+                    if (lane == 0) {
+                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                        const uint32_t bytes = (uint32_t)toks_valid * A_BLOCK_BYTES;       // a multiple of 16: n_tok % 4 == 0
+                        mbar_expect_tx(&xfull[xb], 4u * bytes);
+                        for (int c = 0; c < 4; ++c)
+                            bulk_g2s(xraw + (size_t)xb * TC_XRAW_BYTES + (size_t)c * (TC_N * A_BLOCK_BYTES),
+                                     reinterpret_cast<const uint8_t *>(Xq) + ((size_t)(4 * kb + c) * n_tok + (size_t)tt * TC_N) * A_BLOCK_BYTES,
+                                     bytes, &xfull[xb], policy_evict_last_or_default());
+                    }
+                    __syncwarp();
+                }
+            }
         }
     } else if (lane == 0) {
-        // ---------------- issuer: four K = 32 MMAs per weight block, one commit ----------------
-        for (int b = 0; b < nblocks; ++b) {
-            const int s = b % TC_SMEM_STAGES, ts = b % TC_TMEM_STAGES;
-            if (!mbar_wait_bounded(&full[s], (uint32_t)((b / TC_SMEM_STAGES) & 1))) break;
-            if (!mbar_wait_bounded(&tmem_empty[ts], (uint32_t)(((b / TC_TMEM_STAGES) & 1) ^ 1))) break;
-            tc_fence_after();
-            const TcStage st = tc_stage(stages, s);
+        // ---------------- issuer: four K = 32 MMAs per weight block ----------------
+        bool ok = true;
+        int n = 0;
+        while (ok && walk.next(P, tile, kb0, kb1)) {
+            for (int kb = kb0; kb < kb1; ++kb, ++n) {
+                const int s = n % TC_STAGES;
+                if (!mbar_wait_hot(&full[s], (uint32_t)((n / TC_STAGES) & 1))) { ok = false; break; }
+                const TcStage st = tc_stage(stages, s);
 #pragma unroll
-            for (int c = 0; c < 4; ++c)
-                tc_mma_i8(tmem_base + (uint32_t)(ts * 256 + c * TC_N), tc_smem_desc(smem_u32(st.a + c * (TC_M * 32))),
-                          tc_smem_desc(smem_u32(st.b + c * (TC_N * 32))));
-            tc_commit(&mma_done[ts]);
+                for (int c = 0; c < 4; ++c) {
+                    if (!mbar_wait_hot(&tmem_empty[c], (uint32_t)((n & 1) ^ 1))) { ok = false; break; }
+                    tc_fence_after();
+                    tc_mma_i8(tmem_base + (uint32_t)(c * TC_N), tc_smem_desc(smem_u32(st.a + c * (TC_M * 32))),
+                              tc_smem_desc(smem_u32(st.b + c * (TC_N * 32))));
+                    tc_commit(&mma_done[c]);
+                }
+                if (!ok) break;
+                tc_commit(&released[s]);        // arrives when the four MMAs above have read the stage
+            }
         }
     }
     // common exit: every role arrives here, also after a time-out, so the TMEM columns are always freed
     tc_fence_before();
     __syncthreads();
-    if (wid == 12) {
+    if (wid == TC_EPI_WARPS + TC_PROD_WARPS) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
     }

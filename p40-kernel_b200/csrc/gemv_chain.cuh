@@ -139,15 +139,18 @@ __device__ __forceinline__ bool rank_flags_wait(const unsigned int *flags, int w
                                                 unsigned long long limit_ns, int lane) {
     const unsigned long long t0 = global_timer_ns();
     uint32_t ns = CHAIN_NS0;
-    for (uint32_t n = 0; n < (1u << 26); ++n) {
+    for (uint32_t n = 1; n < (1u << 26); ++n) {
         bool here = true;
         if (lane < world) {
             unsigned int v;
-            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + lane) : "memory");
+            asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + lane) : "memory");
             here = (int)(v - target) >= 0;
         }
-        if (__all_sync(0xffffffffu, here)) return true;
-        if (global_timer_ns() - t0 > limit_ns) break;
+        if (__all_sync(0xffffffffu, here)) {
+            __threadfence_system();         // acquire: what the other ranks wrote before their flags is visible from here on
+            return true;
+        }
+        if ((n & 15u) == 0 && global_timer_ns() - t0 > limit_ns) break;      // the clock is read now and then, not per poll
         __nanosleep(ns);
         ns = min(ns * 2, CHAIN_NSMAX);
     }
@@ -540,15 +543,17 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *_
             if (kflags & CHAIN_SIGNAL) {
                 // this CTA's rows are on their way to every rank: count it in local memory; whoever completes the
                 // count for this signal tells every rank (one store each), ordered behind every CTA's stores
-                __threadfence_system();
+                // (the warp's stores are ordered before lane 0's fence by the warp barrier; one fence per CTA, then,
+                // in the CTA that completes the count, one more behind the count and plain stores of the flags)
                 __syncwarp();
                 if (lane == 0) {
+                    __threadfence_system();
                     const unsigned int seq = arrive_base + __ldg(&Rk->arrivals_needed) + 1u;    // this signal, counted from 1
                     const unsigned int old = atomicAdd(grid_counter + 4, 1u);
                     if (old + 1u == seq * (unsigned)ncta) {
                         __threadfence_system();
                         for (int q = 0; q < PE.world; ++q)
-                            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(PE.counter[q] + 8 + PE.rank), "r"(seq) : "memory");
+                            asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(PE.counter[q] + 8 + PE.rank), "r"(seq) : "memory");
                     }
                 }
             }

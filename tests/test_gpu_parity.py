@@ -213,6 +213,47 @@ def test_gemv_programmatic_launch_same_bits(gpu, port, order):
         gpu.set_option("gemv_order", 0)
 
 
+MMA_SHAPES = [(5, 5120), (16, 256), (203, 5120), (100, 17408), (37, 1024), (2400, 5120), (700, 17408), (1500, 6144),
+              (130, 2304), (33, 8192), (4, 256), (250, 10240)]
+
+
+@pytest.mark.parametrize("n_out,n_in", MMA_SHAPES)
+def test_gemv_tensor_core_body_ints_and_bound(gpu, port, n_out, n_in):
+    """The mat-vec whose integer products run on mma.sync (gemv_order = 2): the int32 chunk sums that the kernel
+    itself formed (bonsai_b200_gemv_dump) equal the host's bit for bit on every row and chunk; y stays within the
+    bound; the plain entry point gives the same bits as the dumping one; rows give the same bits wherever they sit
+    in the matrix (a row slice, as a rank of a row-partitioned run would hold it)."""
+    import torch
+    W = synth.pq2_0_weights(n_out, n_in, seed=n_out + 3)
+    x = synth.activations(n_in, seed=n_out + 3)
+    xq = port.quantize_q8_1(port.fwht_blocks(x) if n_in % 1024 == 0 else x, True)
+    Wd, xqd = dev(W), dev(xq)
+    y = torch.full((n_out,), 7.0, dtype=torch.float32, device="cuda")
+    sums = torch.full((n_out, n_in // 32), -12345, dtype=torch.int32, device="cuda")
+    assert gpu.gemv_dump(Wd, xqd, y, sums, n_out, n_in) == 0
+    want = port.gemv(W, xq, n_out, n_in)
+    assert_close(host(y), want)
+    row_bytes = n_in // 128 * 34
+    got_sums = host(sums)
+    for r in sorted({r for r in (0, 1, 7, 8, 15, 16, n_out // 2, n_out - 1) if r < n_out}):
+        want_sums = port.row_chunk_sums(W[r * row_bytes:(r + 1) * row_bytes], xq, n_in)
+        assert np.array_equal(got_sums[r], want_sums), r
+    try:
+        assert gpu.set_option("gemv_order", 2) == 0
+        y2 = torch.zeros(n_out, dtype=torch.float32, device="cuda")
+        assert gpu.gemv(Wd, xqd, y2, n_out, n_in) == 0
+        assert np.array_equal(bits(host(y2)), bits(host(y)))
+        if n_out >= 40:
+            lo, hi = 16 + 3, n_out - 2          # a slice that starts in the middle of a 16-row group
+            ys = torch.zeros(hi - lo, dtype=torch.float32, device="cuda")
+            Ws = dev(W[lo * row_bytes:hi * row_bytes]) if (lo * row_bytes) % 16 else Wd[lo * row_bytes:hi * row_bytes]
+            assert gpu.gemv(Ws, xqd, ys, hi - lo, n_in) == 0
+            assert np.array_equal(bits(host(ys)), bits(host(y)[lo:hi]))
+    finally:
+        gpu.set_option("gemv_order", 0)
+    assert gpu.device_status() == 0
+
+
 def test_gemv_unaligned_weights_take_the_generic_kernel(gpu, port):
     import torch
     n_out, n_in = 19, 1024
@@ -361,7 +402,11 @@ def test_gemm_bits(gpu, port, n_out, n_in, n_tok):
     X = synth.activations(n_in, seed=n_out, batch=n_tok)
     Xq = port.quantize_batch_chunk_major(X)
     Y = torch.full((n_out, n_tok), 777.0, dtype=torch.float32, device="cuda")
-    assert gpu.gemm(dev(W), dev(Xq), Y, n_out, n_in, n_tok) == 0
+    try:
+        assert gpu.set_option("gemm_path", 0) == 0          # the integer SIMT kernel: the host loop's bits
+        assert gpu.gemm(dev(W), dev(Xq), Y, n_out, n_in, n_tok) == 0
+    finally:
+        gpu.set_option("gemm_path", -1)
     assert_close_and_exact(host(Y), port.gemm(W, Xq, n_out, n_in, n_tok, threads=8))
 
 
@@ -398,25 +443,90 @@ def test_row_partition_assembles_full_result(gpu, port, n_in, n_out, n_tok):
         assert_close_and_exact(host(Y), want)
 
 
-@pytest.mark.parametrize("path", [0, 1])
 @pytest.mark.parametrize("n_out,n_in,n_tok", [(128, 128, 64), (64, 256, 5), (300, 5120, 100), (1024, 5120, 512), (200, 17408, 130),
                                               (129, 384, 65)])
-def test_gemm_both_kernels_same_bits(gpu, port, path, n_out, n_in, n_tok):
-    """Integer SIMT kernel (path 0) and tcgen05 tensor-core kernel (path 1): both bit-identical to the host
-    loop, on full tiles, ragged rows, ragged tokens and odd block counts."""
+def test_gemm_simt_kernel_keeps_the_host_bits(gpu, port, n_out, n_in, n_tok):
+    """Integer SIMT kernel (gemm_path 0): bit-identical to the host loop, on full tiles, ragged rows, ragged
+    tokens and odd block counts."""
     import torch
-    W = synth.pq2_0_weights(n_out, n_in, seed=n_tok + path)
+    W = synth.pq2_0_weights(n_out, n_in, seed=n_tok)
     X = synth.activations(n_in, seed=n_out, batch=n_tok)
     Xq = port.quantize_batch_chunk_major(X)
     Y = torch.full((n_out, n_tok), 777.0, dtype=torch.float32, device="cuda")
     try:
-        assert gpu.set_option("gemm_path", path) == 0
+        assert gpu.set_option("gemm_path", 0) == 0
         assert gpu.gemm(dev(W), dev(Xq), Y, n_out, n_in, n_tok) == 0
         torch.cuda.synchronize()
     finally:
         gpu.set_option("gemm_path", -1)
     assert_close_and_exact(host(Y), port.gemm(W, Xq, n_out, n_in, n_tok, threads=8))
     assert gpu.device_status() == 0
+
+
+def _chunk_ints(port, W, Xq, n_out, n_in, n_tok, rows, toks):
+    """The host loop's int32 (sum code * a - sum a) for the given rows and tokens: [len(rows)][len(toks)][n_in/32]."""
+    nch = n_in // 32
+    row_bytes = n_in // 128 * 34
+    xb = Xq.reshape(nch, n_tok, 36)
+    out = np.zeros((len(rows), len(toks), nch), dtype=np.int32)
+    for j, t in enumerate(toks):
+        xq_t = np.ascontiguousarray(xb[:, t, :]).reshape(-1)
+        for i, r in enumerate(rows):
+            out[i, j] = port.row_chunk_sums(W[r * row_bytes:(r + 1) * row_bytes], xq_t, n_in)
+    return out
+
+
+@pytest.mark.parametrize("n_out,n_in,n_tok", [(128, 128, 64), (64, 256, 5), (300, 1024, 100), (256, 5120, 128), (129, 384, 65),
+                                              (6400, 256, 384), (19072, 256, 130)])
+def test_gemm_tensor_core_ints_and_bound(gpu, port, n_out, n_in, n_tok):
+    """tcgen05 kernel (gemm_path 1): the int32 the tensor core produced for every (row, token, chunk) -- written out
+    by bonsai_b200_gemm_dump -- equals the host loop's integer bit for bit on sampled rows and tokens, and Y is
+    within 1e-5 of max |Y| of the host loop (fp32 side: fused multiply-adds per block, see csrc/gemm_tc.cuh); the
+    plain entry point gives the same Y bits as the dumping one.  Full tiles, ragged rows and tokens, odd block
+    counts, and tile counts that do not divide over the SMs (tiles cut in two between neighbouring CTAs)."""
+    import torch
+    W = synth.pq2_0_weights(n_out, n_in, seed=n_tok + 1)
+    X = synth.activations(n_in, seed=n_out, batch=n_tok)
+    Xq = port.quantize_batch_chunk_major(X)
+    Wd, Xqd = dev(W), dev(Xq)
+    nch = n_in // 32
+    Y = torch.full((n_out, n_tok), 777.0, dtype=torch.float32, device="cuda")
+    sums = torch.full((n_out, n_tok, nch), -12345, dtype=torch.int32, device="cuda")
+    assert gpu.gemm_dump(Wd, Xqd, Y, sums, n_out, n_in, n_tok) == 0
+    torch.cuda.synchronize()
+    want = port.gemm(W, Xq, n_out, n_in, n_tok, threads=8)
+    assert_close(host(Y), want)
+    rows = sorted({0, 1, 31, 32, 127 % n_out, 128 % n_out, n_out // 2, n_out - 1})
+    toks = sorted({0, 1, 15, 16, 31, 32, 63, 127, 128, n_tok // 2, n_tok - 1} & set(range(n_tok)))
+    got = host(sums)[np.ix_(rows, toks)]
+    assert np.array_equal(got, _chunk_ints(port, W, Xq, n_out, n_in, n_tok, rows, toks))
+    assert not (host(sums) == -12345).any()          # every (row, token, chunk) was produced
+    Y2 = torch.full((n_out, n_tok), 555.0, dtype=torch.float32, device="cuda")
+    try:
+        assert gpu.set_option("gemm_path", 1) == 0
+        assert gpu.gemm(Wd, Xqd, Y2, n_out, n_in, n_tok) == 0
+        torch.cuda.synchronize()
+    finally:
+        gpu.set_option("gemm_path", -1)
+    assert np.array_equal(bits(host(Y2)), bits(host(Y)))
+    assert gpu.device_status() == 0
+
+
+def test_gemm_default_dispatch(gpu, port):
+    """By token count: few tokens take the kernel that keeps the host's bits, a prefill batch the tensor cores."""
+    import torch
+    n_out, n_in = 256, 1024
+    W = synth.pq2_0_weights(n_out, n_in, seed=9)
+    for n_tok, exact in ((8, True), (512, False)):
+        X = synth.activations(n_in, seed=n_tok, batch=n_tok)
+        Xq = port.quantize_batch_chunk_major(X)
+        Y = torch.zeros((n_out, n_tok), dtype=torch.float32, device="cuda")
+        assert gpu.gemm(dev(W), dev(Xq), Y, n_out, n_in, n_tok) == 0
+        want = port.gemm(W, Xq, n_out, n_in, n_tok, threads=8)
+        if exact:
+            assert_close_and_exact(host(Y), want)
+        else:
+            assert_close(host(Y), want)
 
 
 def test_gemm_golden(gpu, golden):
