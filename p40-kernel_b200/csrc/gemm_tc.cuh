@@ -7,7 +7,7 @@
 // fold it into fp32 registers.  The integers are exact: weights are expanded to signed bytes code - 1, so one MMA
 // gives sum(code * a) - sum(a) of the chunk, the very int32 of the host loop (tests/test_p40.cpp:460-467,
 // src/pq2_0.h:149-169).  The fp32 side uses the tolerance the path states (1e-5 of max |Y|) to spend two
-// instructions per output and chunk instead of five: per block  s = da0*v0 + da1*v1 + da2*v2 + da3*v3  by fused
+// instructions per output and chunk instead of five: per pair of chunks  s = da0*v0 + da1*v1  by fused
 // multiply-adds, then  acc += dw * s  -- the host computes (dw*da_c)*v_c term by term; same sums, other roundings.
 // (The integer SIMT kernel, gemm_simt.cuh, keeps the host's bits; bonsai_b200_set_option("gemm_path", 0).)
 //
@@ -43,7 +43,8 @@
 namespace b200 {
 
 constexpr int TC_M = 128, TC_N = 128;
-constexpr int TC_STAGES = 3;                               // shared-memory stages (one weight block each)
+constexpr int TC_STAGES = 2;                               // shared-memory stages (one weight block each)
+constexpr int TC_XBUFS = 4;                                // raw Q8_1 buffers in flight (TMA form): bulk copies take ~1 us to land
 constexpr int TC_A_BYTES = 4 * TC_M * 32;                  // 4 chunks x 128 rows x 32 bytes
 constexpr int TC_B_BYTES = 4 * TC_N * 32;
 constexpr int TC_STAGE_BYTES = TC_A_BYTES + TC_B_BYTES + TC_M * 4 + 4 * TC_N * 4;
@@ -53,7 +54,7 @@ constexpr int TC_THREADS = TC_EPI_THREADS + TC_PROD_THREADS + 64;       // + iss
 constexpr int TC_WRAW_BYTES = TC_M * 272;                  // raw PQ2_0 bytes of 8 consecutive blocks of 128 rows
 constexpr int TC_XRAW_BYTES = 4 * TC_N * A_BLOCK_BYTES;    // raw Q8_1 blocks of 4 chunks x 128 tokens
 constexpr int TC_SMEM_BYTES = 1024 + TC_STAGES * TC_STAGE_BYTES;
-constexpr int TC_SMEM_BYTES_TMA = TC_SMEM_BYTES + 2 * TC_WRAW_BYTES + 2 * TC_XRAW_BYTES;
+constexpr int TC_SMEM_BYTES_TMA = TC_SMEM_BYTES + 2 * TC_WRAW_BYTES + TC_XBUFS * TC_XRAW_BYTES;
 constexpr int TC_FLAG_SETS = 8, TC_MAX_CTAS = 256;
 
 // Partial-tile flags: set `epoch % 8`, word = CTA that wrote the partial; raised by the writer, lowered by the reader.
@@ -94,6 +95,12 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, int (&v)[16]) {
         : "memory");
 }
 __device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_ld8(uint32_t taddr, int (&v)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];\n"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+                 : "r"(taddr)
+                 : "memory");
+}
 __device__ __forceinline__ void tc_epi_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(TC_EPI_THREADS) : "memory"); }
 
 struct TcStage {
@@ -161,9 +168,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const uint8_t *_
     uint64_t *tmem_empty = mma_done + 4;                                // [4] epilogue -> issuer
     uint64_t *wfull = tmem_empty + 4;                                   // [2] loader -> producers: 8 blocks of weight rows landed
     uint64_t *wfree = wfull + 2;                                        // [2] producers -> loader
-    uint64_t *xfull = wfree + 2;                                        // [2] loader -> producers: a block's Q8_1 blocks landed
-    uint64_t *xfree = xfull + 2;                                        // [2] producers -> loader
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(xfree + 2);
+    uint64_t *xfull = wfree + 2;                                        // [4] loader -> producers: a block's Q8_1 blocks landed
+    uint64_t *xfree = xfull + TC_XBUFS;                                 // [4] producers -> loader
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(xfree + TC_XBUFS);
     uint8_t *stages = smem + 1024;
     uint8_t *wraw = stages + TC_STAGES * TC_STAGE_BYTES;
     uint8_t *xraw = wraw + 2 * TC_WRAW_BYTES;
@@ -174,10 +181,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const uint8_t *_
     if (threadIdx.x == 0) {
         for (int s = 0; s < TC_STAGES; ++s) { mbar_init(&full[s], TC_PROD_THREADS); mbar_init(&released[s], 1 + TC_EPI_WARPS); }
         for (int s = 0; s < 4; ++s) { mbar_init(&mma_done[s], 1); mbar_init(&tmem_empty[s], TC_EPI_WARPS); }
-        for (int s = 0; s < 2; ++s) {
-            mbar_init(&wfull[s], 1); mbar_init(&wfree[s], TC_PROD_THREADS);
-            mbar_init(&xfull[s], 1); mbar_init(&xfree[s], TC_PROD_THREADS);
-        }
+        for (int s = 0; s < 2; ++s) { mbar_init(&wfull[s], 1); mbar_init(&wfree[s], TC_PROD_THREADS); }
+        for (int s = 0; s < TC_XBUFS; ++s) { mbar_init(&xfull[s], 1); mbar_init(&xfree[s], TC_PROD_THREADS); }
         mbar_fence_init();
     }
     if (wid == TC_EPI_WARPS + TC_PROD_WARPS) {
@@ -209,47 +214,67 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const uint8_t *_
             for (int kb = kb0; kb < kb1 && ok; ++kb, ++n) {
                 const int s = n % TC_STAGES;
                 const TcStage st = tc_stage(stages, s);
-                // two passes of 16 tokens over the block's four chunks (32 accumulators + 16 block sums + 16 integers live)
+                // The block's four chunks are folded in as two pairs, each pair in two passes of 16 tokens (32 accumulators
+                // + 16 pair sums live): a pair's tensor-memory columns are released as soon as its second pass has them in
+                // registers, i.e. in the middle of the block, so the tensor core works on the next block's first pair
+                // while this block's second pair is folded in.  (Held to the end of the block, every block would wait
+                // for the round trip issue -> MMA -> commit: measured 1.8 us per block whatever the epilogue did.)
+                // A pass is four loads of 8 columns; the next load is in flight while the current one is folded in.
 #pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    float accb[16];
+                for (int pr = 0; pr < 2; ++pr) {
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) {
+                    for (int h = 0; h < 2; ++h) {
+                        float accb[16];
+                        int v[2][8];
+                        const uint32_t tbase = tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(32 * cg + 16 * h);
                         if (h == 0) {
-                            if (!mbar_wait_hot(&mma_done[c], (uint32_t)(n & 1))) { ok = false; break; }
+                            if (!mbar_wait_hot(&mma_done[2 * pr], (uint32_t)(n & 1))) { ok = false; break; }
                             tc_fence_after();
                         }
-                        int v[16];
-                        tc_ld16(tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(c * TC_N + 32 * cg + 16 * h), v);
-                        tc_ld_wait();
-                        if (h == 1) {           // both halves of this chunk are in registers: the tensor core may overwrite it
-                            tc_fence_before();
-                            __syncwarp();
-                            if (lane == 0) mbar_arrive(&tmem_empty[c]);
-                        }
-                        const float4 *da4 = reinterpret_cast<const float4 *>(st.da + c * TC_N + 32 * cg + 16 * h);
+                        tc_ld8(tbase + (uint32_t)(2 * pr * TC_N), v[0]);
 #pragma unroll
-                        for (int g4 = 0; g4 < 4; ++g4) {
-                            const float4 d = da4[g4];
-                            const float dd[4] = {d.x, d.y, d.z, d.w};
+                        for (int k = 0; k < 4; ++k) {
+                            const int cc = k >> 1, q8 = k & 1, c = 2 * pr + cc;
+                            tc_ld_wait();
+                            if (h == 1 && q8 == 1) {    // all of this chunk is in registers: the tensor core may overwrite it
+                                tc_fence_before();
+                                __syncwarp();
+                                if (lane == 0) mbar_arrive(&tmem_empty[c]);
+                            }
+                            if (k < 3) {
+                                const int cn = 2 * pr + ((k + 1) >> 1);
+                                if (h == 0 && q8 == 1) {
+                                    if (!mbar_wait_hot(&mma_done[cn], (uint32_t)(n & 1))) { ok = false; break; }
+                                    tc_fence_after();
+                                }
+                                tc_ld8(tbase + (uint32_t)(cn * TC_N + 8 * ((k + 1) & 1)), v[(k + 1) & 1]);
+                            }
+                            const float4 *da4 = reinterpret_cast<const float4 *>(st.da + c * TC_N + 32 * cg + 16 * h + 8 * q8);
 #pragma unroll
-                            for (int e = 0; e < 4; ++e) {
-                                const float f = (float)v[4 * g4 + e];
-                                accb[4 * g4 + e] = (c == 0) ? __fmul_rn(dd[e], f) : __fmaf_rn(dd[e], f, accb[4 * g4 + e]);
+                            for (int g4 = 0; g4 < 2; ++g4) {
+                                const float4 d = da4[g4];
+                                const float dd[4] = {d.x, d.y, d.z, d.w};
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) {
+                                    const int jj = 8 * q8 + 4 * g4 + e;
+                                    const float f = (float)v[k & 1][4 * g4 + e];
+                                    accb[jj] = (cc == 0) ? __fmul_rn(dd[e], f) : __fmaf_rn(dd[e], f, accb[jj]);
+                                }
+                            }
+                            if (DUMP && row < n_out) {
+#pragma unroll
+                                for (int e = 0; e < 8; ++e) {
+                                    const int tok = tokb + 16 * h + 8 * q8 + e;
+                                    if (tok < n_tok) dump[((size_t)row * n_tok + tok) * (4 * (size_t)nblocks) + 4 * kb + c] = v[k & 1][e];
+                                }
                             }
                         }
-                        if (DUMP && row < n_out) {
+                        if (!ok) break;
+                        const float dw = st.dw[row_l];          // written by the producers: read behind the waits above
 #pragma unroll
-                            for (int e = 0; e < 16; ++e) {
-                                const int tok = tokb + 16 * h + e;
-                                if (tok < n_tok) dump[((size_t)row * n_tok + tok) * (4 * (size_t)nblocks) + 4 * kb + c] = v[e];
-                            }
-                        }
+                        for (int jj = 0; jj < 16; ++jj) acc[16 * h + jj] = __fmaf_rn(dw, accb[jj], acc[16 * h + jj]);
                     }
                     if (!ok) break;
-                    const float dw = st.dw[row_l];          // written by the producers: read behind the waits above
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) acc[16 * h + j] = __fmaf_rn(dw, accb[j], acc[16 * h + j]);
                 }
                 if (!ok) break;
                 __syncwarp();
@@ -326,12 +351,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const uint8_t *_
                         ++oct;
                     }
                     wbuf = (oct - 1) & 1;
-                    if (!mbar_wait_bounded(&xfull[n & 1], (uint32_t)((n >> 1) & 1))) { ok = false; break; }
+                    if (!mbar_wait_bounded(&xfull[n % TC_XBUFS], (uint32_t)((n / TC_XBUFS) & 1))) { ok = false; break; }
                     const unsigned short *wr = reinterpret_cast<const unsigned short *>(wraw + (size_t)wbuf * TC_WRAW_BYTES + (size_t)p * 272 +
                                                                                         (size_t)(kb & 7) * W_BLOCK_BYTES);
 #pragma unroll
                     for (int i = 0; i < 17; ++i) h[i] = wr[i];
-                    const uint32_t *xr = reinterpret_cast<const uint32_t *>(xraw + (size_t)(n & 1) * TC_XRAW_BYTES) + 9 * p;
+                    const uint32_t *xr = reinterpret_cast<const uint32_t *>(xraw + (size_t)(n % TC_XBUFS) * TC_XRAW_BYTES) + 9 * p;
 #pragma unroll
                     for (int c = 0; c < 4; ++c)
 #pragma unroll
@@ -374,7 +399,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const uint8_t *_
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");    // the tensor core reads through the async proxy
                 mbar_arrive(&full[s]);
                 if (TMA) {
-                    mbar_arrive(&xfree[n & 1]);                                  // the raw bytes are in registers / the stage
+                    mbar_arrive(&xfree[n % TC_XBUFS]);                                  // the raw bytes are in registers / the stage
                     if ((kb & 7) == 7 || kb == kb1 - 1) mbar_arrive(&wfree[wbuf]);
                 }
             }
@@ -401,8 +426,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const uint8_t *_
                             bulk_g2s(wraw + (size_t)wb * TC_WRAW_BYTES + (size_t)r * 272, src + (size_t)r * row_bytes, 272u, &wfull[wb], pol);
                         ++oct;
                     }
-                    const int xb = n & 1;
-                    if (!mbar_wait_bounded(&xfree[xb], (uint32_t)(((n >> 1) & 1) ^ 1))) { ok = false; break; }
+                    const int xb = n % TC_XBUFS;
+                    if (!mbar_wait_bounded(&xfree[xb], (uint32_t)(((n / TC_XBUFS) & 1) ^ 1))) { ok = false; break; }
                     if (lane == 0) {
                         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                         const uint32_t bytes = (uint32_t)toks_valid * A_BLOCK_BYTES;       // a multiple of 16: n_tok % 4 == 0
