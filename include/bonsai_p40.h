@@ -69,16 +69,24 @@ int bonsai_p40_gemv_repack(const void *W, const float *x, float *y, int64_t n_ou
  * Replaces include/bonsai_p40.h:41 / src/kernels/elementwise_p40.cu:75. */
 int bonsai_p40_fwht(float *x, const float *signs, int64_t n, bonsai_stream stream);
 
-/* The three entry points below are not part of the PQ2_0 mat-vec / mat-mul path.  They are
- * exported so that programs written against the reference link; this build returns
- * BONSAI_P40_ENOTIMPL from each without touching its arguments.
- * (reference: include/bonsai_p40.h:44-56) */
-#define BONSAI_P40_ENOTIMPL 38
+/* RMSNorm over n_rows rows of length n: y = x * (1 / sqrt(mean(x^2) + eps)) * w.  Returns 1 if n <= 0, 0 without
+ * a launch if n_rows <= 0.  Within 1e-5 of the host formula (src/ops.h:13-22): the sum of squares is added in a
+ * fixed tree order, not sequentially.  Replaces include/bonsai_p40.h:44 / src/kernels/elementwise_p40.cu:82. */
 int bonsai_p40_rmsnorm(const float *x, const float *w, float *y, int64_t n_rows, int64_t n, float eps,
                        bonsai_stream stream);
+
+/* One gated delta-net step for n_v_heads value heads (state [n_v_heads][K][V], updated in place; q, k per key head,
+ * value head vh reads key head vh / (n_v_heads / n_k_heads); v, out [n_v_heads][V]; g, beta [n_v_heads]).  Returns 1
+ * unless V > 0, V % 32 == 0, 0 < K <= 128 and n_v_heads % n_k_heads == 0.  Arithmetic in the order of src/ops.h:66-92;
+ * exp(g) is the device's.  Replaces include/bonsai_p40.h:49 / src/kernels/attn_p40.cu:119. */
 int bonsai_p40_gdn_step(float *state, const float *q, const float *k, const float *v, const float *g,
                         const float *beta, float *out, int n_k_heads, int n_v_heads, int K, int V,
                         bonsai_stream stream);
+
+/* Causal attention, head_dim 256, grouped-query heads: q, out [n_tok][n_head][256]; k, v [n_tok][n_head_kv][256]
+ * (16-byte aligned).  Returns 1 if head_dim != 256 or n_head % n_head_kv != 0; 0 without a launch if n_tok <= 0.
+ * Online softmax, one key at a time (src/kernels/attn_p40.cu:92-118).  Replaces include/bonsai_p40.h:54 /
+ * src/kernels/attn_p40.cu:131. */
 int bonsai_p40_attn(const float *q, const float *k, const float *v, float *out, int n_tok, int n_head,
                     int n_head_kv, int head_dim, float scale, bonsai_stream stream);
 

@@ -348,3 +348,76 @@ int bo_gemm_mt(const uint8_t *W, const uint8_t *Xq, float *Y, int64_t n_out, int
                int nthreads) {
     return bo_run_mt(W, Xq, Y, n_out, n_in, n_tok, nthreads);
 }
+
+/* ---- the operators beside the mat-vec path ------------------------------------------------------
+ * RMSNorm and SwiGLU follow src/ops.h:13-31, the gated delta-net step src/ops.h:66-92 with the head
+ * mapping of src/kernels/attn_p40.cu:36-38; attention is the online-softmax recurrence of
+ * tests/test_p40.cpp:240-262 applied to every (query, head) under the causal mask of
+ * src/kernels/attn_p40.cu:101. */
+void bo_rmsnorm(const float *x, const float *w, float *y, int64_t n_rows, int64_t n, float eps) {
+    for (int64_t r = 0; r < n_rows; ++r) {
+        const float *xr = x + r * n;
+        float ss = 0.0f;
+        for (int64_t i = 0; i < n; ++i) ss += xr[i] * xr[i];
+        const float s = 1.0f / sqrtf(ss / (float)n + eps);
+        for (int64_t i = 0; i < n; ++i) y[r * n + i] = xr[i] * s * w[i];
+    }
+}
+
+void bo_swiglu(const float *gate, const float *up, float *y, int64_t n) {
+    for (int64_t i = 0; i < n; ++i) y[i] = gate[i] / (1.0f + expf(-gate[i])) * up[i];
+}
+
+void bo_gdn_step(float *state, const float *q, const float *k, const float *v, const float *g, const float *beta,
+                 float *out, int n_k_heads, int n_v_heads, int K, int V) {
+    for (int vh = 0; vh < n_v_heads; ++vh) {
+        const int kh = vh / (n_v_heads / n_k_heads);
+        float *S = state + (size_t)vh * K * V;
+        const float *kk = k + (size_t)kh * K, *qq = q + (size_t)kh * K, *vv = v + (size_t)vh * V;
+        float *o = out + (size_t)vh * V;
+        const float decay = expf(g[vh]);
+        for (int i = 0; i < K; ++i)
+            for (int j = 0; j < V; ++j) S[i * V + j] *= decay;
+        for (int j = 0; j < V; ++j) {
+            float acc = 0.0f;
+            for (int i = 0; i < K; ++i) acc += kk[i] * S[i * V + j];
+            o[j] = acc;
+        }
+        for (int i = 0; i < K; ++i) {
+            const float bk = beta[vh] * kk[i];
+            for (int j = 0; j < V; ++j) S[i * V + j] += bk * (vv[j] - o[j]);
+        }
+        for (int j = 0; j < V; ++j) {
+            float acc = 0.0f;
+            for (int i = 0; i < K; ++i) acc += qq[i] * S[i * V + j];
+            o[j] = acc;
+        }
+    }
+}
+
+void bo_attn(const float *q, const float *k, const float *v, float *out, int n_tok, int n_head, int n_head_kv, int D,
+             float scale) {
+    float *acc = (float *)malloc(sizeof(float) * (size_t)D);
+    for (int qi = 0; qi < n_tok; ++qi)
+        for (int head = 0; head < n_head; ++head) {
+            const int kvh = head / (n_head / n_head_kv);
+            const float *qp = q + ((size_t)qi * n_head + head) * D;
+            float m = -INFINITY, l = 0.0f;
+            for (int d = 0; d < D; ++d) acc[d] = 0.0f;
+            for (int j = 0; j <= qi; ++j) {
+                const float *kp = k + ((size_t)j * n_head_kv + kvh) * D;
+                const float *vp = v + ((size_t)j * n_head_kv + kvh) * D;
+                float s = 0.0f;
+                for (int d = 0; d < D; ++d) s += qp[d] * kp[d];
+                s *= scale;
+                const float m_new = fmaxf(m, s);
+                const float alpha = expf(m - m_new), p = expf(s - m_new);
+                l = l * alpha + p;
+                for (int d = 0; d < D; ++d) acc[d] = acc[d] * alpha + p * vp[d];
+                m = m_new;
+            }
+            for (int d = 0; d < D; ++d) out[((size_t)qi * n_head + head) * D + d] = acc[d] / l;
+        }
+    free(acc);
+}
+

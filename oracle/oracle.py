@@ -58,7 +58,11 @@ class Oracle:
         f("unpack_row", None, [C.c_void_p, C.c_int, C.c_void_p])
         f("repack_unit_sumi", C.c_int32, [C.c_void_p, C.c_void_p, C.c_int, C.c_int])
         f("repack_row_dot", C.c_float, [C.c_void_p, C.c_void_p, C.c_int])
+        f("rmsnorm", None, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_float])
+        f("swiglu", None, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64])
+        f("gdn_step", None, [C.c_void_p] * 7 + [C.c_int] * 4)
         if kind == "port":
+            f("attn", None, [C.c_void_p] * 4 + [C.c_int] * 4 + [C.c_float])
             f("chunk_sumi", C.c_int32, [C.c_void_p, C.c_void_p, C.c_int])
             f("row_chunk_sums", None, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p])
 
@@ -178,3 +182,33 @@ class Oracle:
         xq = self.quantize_q8_1(x)
         Wr = np.ascontiguousarray(Wr, dtype=np.uint8).reshape(n_out, W_BYTES * nb)
         return np.array([self.repack_row_dot(Wr[r], xq, nb) for r in range(n_out)], dtype=np.float32)
+
+    # ---- the operators beside the mat-vec path ---------------------------------------------------------
+    def rmsnorm(self, x, w, eps):
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        w = np.ascontiguousarray(w, dtype=np.float32)
+        x2 = x.reshape(-1, w.size)
+        y = np.zeros_like(x2)
+        self._rmsnorm(_p(x2), _p(w), _p(y), x2.shape[0], x2.shape[1], float(eps))
+        return y.reshape(x.shape)
+
+    def swiglu(self, gate, up):
+        gate = np.ascontiguousarray(gate, dtype=np.float32)
+        up = np.ascontiguousarray(up, dtype=np.float32)
+        y = np.zeros_like(gate)
+        self._swiglu(_p(gate), _p(up), _p(y), gate.size)
+        return y
+
+    def gdn_step(self, state, q, k, v, g, beta, n_k_heads, n_v_heads, K, V):
+        """Returns (new state, out); `state` is not modified."""
+        S = np.array(state, dtype=np.float32, copy=True)
+        a = [np.ascontiguousarray(t, dtype=np.float32) for t in (q, k, v, g, beta)]
+        out = np.zeros(n_v_heads * V, dtype=np.float32)
+        self._gdn_step(_p(S), _p(a[0]), _p(a[1]), _p(a[2]), _p(a[3]), _p(a[4]), _p(out), n_k_heads, n_v_heads, K, V)
+        return S, out
+
+    def attn(self, q, k, v, n_tok, n_head, n_head_kv, D, scale):
+        a = [np.ascontiguousarray(t, dtype=np.float32) for t in (q, k, v)]
+        out = np.zeros(n_tok * n_head * D, dtype=np.float32)
+        self._attn(_p(a[0]), _p(a[1]), _p(a[2]), _p(out), n_tok, n_head, n_head_kv, D, float(scale))
+        return out

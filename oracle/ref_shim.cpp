@@ -9,6 +9,7 @@
 // Compiled with g++ (never nvcc), so the headers take their non-CUDA branches: software
 // f32_to_f16 / f16_to_f32 and the dp4a emulation.
 #include "fwht.h"
+#include "ops.h"
 #include "pq2_0.h"
 #include "pq2_0_repack.h"
 
@@ -94,6 +95,22 @@ int32_t ref_repack_unit_sumi(const uint8_t *row, const void *xq, int nb, int u) 
 }
 float ref_repack_row_dot(const uint8_t *row, const void *xq, int nb) {
     return repack_row_dot(row, (const block_q8_1 *)xq, nb);
+}
+
+// ---- the operators beside the mat-vec path (src/ops.h) ---------------------------------------------------------
+void ref_rmsnorm(const float *x, const float *w, float *y, int64_t n_rows, int64_t n, float eps) {
+    for (int64_t r = 0; r < n_rows; ++r) rmsnorm(x + r * n, w, y + r * n, (int)n, eps);
+}
+void ref_swiglu(const float *gate, const float *up, float *y, int64_t n) { swiglu(gate, up, y, (int)n); }
+// One recurrent step for every value head, with the grouped-query mapping of the reference's wrapper
+// (src/kernels/attn_p40.cu:36-38): value head vh reads key head vh / (n_v_heads / n_k_heads).
+void ref_gdn_step(float *state, const float *q, const float *k, const float *v, const float *g, const float *beta,
+                  float *out, int n_k_heads, int n_v_heads, int K, int V) {
+    for (int vh = 0; vh < n_v_heads; ++vh) {
+        const int kh = vh / (n_v_heads / n_k_heads);
+        gdn_step(state + (size_t)vh * K * V, q + (size_t)kh * K, k + (size_t)kh * K, v + (size_t)vh * V, g[vh], beta[vh],
+                 out + (size_t)vh * V, K, V);
+    }
 }
 
 }  // extern "C"

@@ -17,7 +17,6 @@ LIB_PATH = os.path.join(_ROOT, "libbonsai_p40.so")
 
 W_BLOCK_BYTES = 34
 A_BLOCK_BYTES = 36
-ENOTIMPL = 38
 
 _lib = None
 
@@ -121,6 +120,20 @@ def repack(src, dst, n_out, n_in):
 
 def gemv_repack(W, x, y, n_out, n_in):
     return lib().bonsai_p40_gemv_repack(_dev(W, "W"), _dev(x, "x"), _dev(y, "y"), n_out, n_in, _stream())
+
+
+def rmsnorm(x, w, y, n_rows, n, eps):
+    return lib().bonsai_p40_rmsnorm(_dev(x, "x"), _dev(w, "w"), _dev(y, "y"), n_rows, n, eps, _stream())
+
+
+def gdn_step(state, q, k, v, g, beta, out, n_k_heads, n_v_heads, K, V):
+    return lib().bonsai_p40_gdn_step(_dev(state, "state"), _dev(q, "q"), _dev(k, "k"), _dev(v, "v"), _dev(g, "g"),
+                                     _dev(beta, "beta"), _dev(out, "out"), n_k_heads, n_v_heads, K, V, _stream())
+
+
+def attn(q, k, v, out, n_tok, n_head, n_head_kv, head_dim, scale):
+    return lib().bonsai_p40_attn(_dev(q, "q"), _dev(k, "k"), _dev(v, "v"), _dev(out, "out"), n_tok, n_head, n_head_kv,
+                                 head_dim, scale, _stream())
 
 
 def fwht(x, signs, n):

@@ -13,6 +13,7 @@
 #include "gemv_stream.cuh"
 #include "gemv_chain.cuh"
 #include "gemv_mma.cuh"
+#include "ops.cuh"
 #include "probe.cuh"
 #include "repack.cuh"
 #include "synth.cuh"
@@ -974,17 +975,37 @@ int bonsai_b200_clear_status(void) {
 
 int bonsai_b200_version(void) { return 200; }
 
-// Not on the PQ2_0 mat-vec / mat-mul path: exported so that programs written against the reference
-// link; each refuses without touching its arguments (reference: include/bonsai_p40.h:44-56).
-int bonsai_p40_rmsnorm(const float *, const float *, float *, int64_t, int64_t, float, bonsai_stream) {
-    return BONSAI_P40_ENOTIMPL;
+// ---- the operators beside the mat-vec path (reference: include/bonsai_p40.h:44-56) ---------------------------
+int bonsai_p40_rmsnorm(const float *x, const float *w, float *y, int64_t n_rows, int64_t n, float eps,
+                       bonsai_stream stream) {
+    // return convention of src/kernels/elementwise_p40.cu:82-88
+    if (n <= 0 || n_rows <= 0) return (n <= 0) ? 1 : 0;
+    if (n > INT32_MAX || n_rows > INT32_MAX || !aligned4(x) || !aligned4(w) || !aligned4(y)) return 1;
+    if (n % 4 == 0 && aligned16(x)) rmsnorm_kernel<true><<<(unsigned)n_rows, 256, 0, as_stream(stream)>>>(x, w, y, (int)n, eps);
+    else rmsnorm_kernel<false><<<(unsigned)n_rows, 256, 0, as_stream(stream)>>>(x, w, y, (int)n, eps);
+    return (int)cudaGetLastError();
 }
-int bonsai_p40_gdn_step(float *, const float *, const float *, const float *, const float *, const float *, float *,
-                        int, int, int, int, bonsai_stream) {
-    return BONSAI_P40_ENOTIMPL;
+
+int bonsai_p40_gdn_step(float *state, const float *q, const float *k, const float *v, const float *g, const float *beta,
+                        float *out, int n_k_heads, int n_v_heads, int K, int V, bonsai_stream stream) {
+    // rejections of src/kernels/attn_p40.cu:121-124
+    if (V <= 0 || V % 32 != 0 || K <= 0 || K > GDN_KMAX) return 1;
+    if (n_v_heads <= 0 || n_k_heads <= 0 || n_v_heads % n_k_heads != 0) return 1;
+    const int blocks = n_v_heads * ((V + 63) / 64);
+    gdn_step_kernel<<<blocks, 64, 0, as_stream(stream)>>>(state, q, k, v, g, beta, out, n_k_heads, n_v_heads, K, V);
+    return (int)cudaGetLastError();
 }
-int bonsai_p40_attn(const float *, const float *, const float *, float *, int, int, int, int, float, bonsai_stream) {
-    return BONSAI_P40_ENOTIMPL;
+
+int bonsai_p40_attn(const float *q, const float *k, const float *v, float *out, int n_tok, int n_head, int n_head_kv,
+                    int head_dim, float scale, bonsai_stream stream) {
+    // rejections of src/kernels/attn_p40.cu:134-136
+    if (head_dim != ATT_D || n_head_kv == 0 || (n_head % n_head_kv) != 0) return 1;
+    if (n_tok <= 0 || n_head <= 0 || n_head_kv <= 0) return (n_tok <= 0) ? 0 : 1;
+    if (!aligned16(k) || !aligned16(v) || !aligned4(q) || !aligned4(out)) return 1;    // rows of 256 floats: 16-byte loads
+    const long long blocks = (long long)n_head * ((n_tok + ATT_WARPS - 1) / ATT_WARPS);
+    if (blocks > INT32_MAX) return 1;
+    attn_kernel<<<(unsigned)blocks, ATT_WARPS * 32, 0, as_stream(stream)>>>(q, k, v, out, n_tok, n_head, n_head_kv, scale);
+    return (int)cudaGetLastError();
 }
 
 }  // extern "C"

@@ -65,4 +65,12 @@ def test_shape_rejections_need_no_gpu():
     assert L.bonsai_p40_gemv_repack(None, None, None, 8, 640, None) == 1
     assert L.bonsai_p40_fwht(None, None, 1000, None) == 1
     assert L.bonsai_p40_fwht(None, None, 0, None) == 1
-    assert L.bonsai_p40_rmsnorm(None, None, None, 1, 8, 1e-6, None) == bonsai_b200.ENOTIMPL
+    # the operators beside the path (reference: elementwise_p40.cu:82-84, attn_p40.cu:121-124, 134-136)
+    assert L.bonsai_p40_rmsnorm(None, None, None, 1, 0, 1e-6, None) == 1
+    assert L.bonsai_p40_rmsnorm(None, None, None, 0, 8, 1e-6, None) == 0
+    assert L.bonsai_p40_gdn_step(None, None, None, None, None, None, None, 4, 8, 128, 33, None) == 1
+    assert L.bonsai_p40_gdn_step(None, None, None, None, None, None, None, 4, 8, 129, 128, None) == 1
+    assert L.bonsai_p40_gdn_step(None, None, None, None, None, None, None, 3, 8, 128, 128, None) == 1
+    assert L.bonsai_p40_attn(None, None, None, None, 4, 24, 4, 128, 0.1, None) == 1
+    assert L.bonsai_p40_attn(None, None, None, None, 4, 24, 5, 256, 0.1, None) == 1
+    assert L.bonsai_p40_attn(None, None, None, None, 0, 24, 4, 256, 0.1, None) == 0

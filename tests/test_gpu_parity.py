@@ -625,7 +625,6 @@ def test_rejections_and_stubs_on_device(gpu):
     assert gpu.repack(b, b, 4, 128) == 1
     assert gpu.gemv_repack(b, z, z, 4, 640) == 1
     assert gpu.gemm(b, b, z, 4, 100, 2) == 1
-    assert gpu.lib().bonsai_p40_rmsnorm(None, None, None, 1, 8, 1e-6, None) == gpu.ENOTIMPL
 
 
 def test_no_bounded_wait_gave_up(gpu):
