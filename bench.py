@@ -650,56 +650,82 @@ def model_gemvs():
     return out
 
 
-def decode_step_leg(args, torch, bb, dist):
-    """The 401 projections of one decoded token (6.8 GB of PQ2_0 weights), each the rotation + Q8_1 quantiser of
-    a resident fp32 vector of its input width followed by the mat-vec, replayed as one CUDA graph: tokens/s and
-    weight GB/s.  One launch per token (bonsai_b200_chain_run): projections that read the same vector share its
-    quantised form, every other projection waits for all rows of the projections before it.  With N > 1 every
-    matrix is split by output rows; the outputs reach every rank either by peer stores inside the kernel or
-    (per-matrix calls) by an all-gather behind every projection.  Parity: every projection's output of the
-    timed launch against the per-matrix call on the same input, bit for bit."""
+def decode_ops(torch, bb, shapes, seed, flow, rank=0, world=1, y_all=None):
+    """The op list of one decoded token.  flow=True (one rank): op i reads the output of op i - 1 through the exact
+    power-of-two glue (x_i[j] = y_{i-1}[j mod N_{i-1}] * 2^-e, e = floor(log2(max |y_{i-1}|))), projections of equal
+    input width that follow each other share one input.  flow=False: every op rotates and quantises a resident
+    vector of its input width; the waits between the ops are the same.  Returns (ops, outputs, weights)."""
     from bonsai_b200 import partition
-    rank, world, local = env_ranks()
-    if dist is None:
-        world, rank = 1, 0
-    bb.set_option("pdl", max(args.pdl, 0))
-    shapes = model_gemvs()
     ws, rows_of, first = [], [], 0
     for n_in, n_out in shapes:
         lo, hi = partition.row_slice(n_out, rank, world)
         nblk_row = n_in // 128
         W = torch.empty((hi - lo) * nblk_row * 34, dtype=torch.uint8, device="cuda")
-        assert bb.synth_pq2_0(W, first + lo * nblk_row, (hi - lo) * nblk_row, args.seed) == 0
+        assert bb.synth_pq2_0(W, first + lo * nblk_row, (hi - lo) * nblk_row, seed) == 0
         first += n_out * nblk_row
         ws.append(W)
         rows_of.append(hi - lo)
-    g = torch.Generator(device="cpu").manual_seed(args.seed)
+    g = torch.Generator(device="cpu").manual_seed(seed)
     xs = {k: torch.randn(k, generator=g).cuda() for k in sorted({a for a, _ in shapes})}
-    xq = {k: torch.empty(k // 32 * 36, dtype=torch.uint8, device="cuda") for k in xs}
-    # every projection keeps its own output vector, so that all of them can be checked after the run
     y_off, off = [], 0
     for _, n_out in shapes:
         y_off.append(off)
         off += n_out
-    peer_buf, chain = None, None
+    if y_all is None:
+        y_all = torch.zeros(off, dtype=torch.float32, device="cuda")
+    ys = [y_all[o:o + n] for o, (_, n) in zip(y_off, shapes)]
+    ops = []
+    for i, ((n_in, n_out), W) in enumerate(zip(shapes, ws)):
+        r = rows_of[i]
+        same = i > 0 and shapes[i - 1][0] == n_in
+        fl = bb.OP_ROTATE | (bb.OP_SAME_INPUT if same else (bb.OP_DEPENDS if i else 0))
+        ysl = ys[i][rank * r:(rank + 1) * r]
+        if flow and same:           # the previous op's input, prepared the same way
+            ops.append((W, ops[i - 1][1], None, ysl, r, n_in, fl | (ops[i - 1][6] & bb.OP_RESCALE), None, 0.0, ops[i - 1][9]))
+        elif flow and i > 0:
+            ops.append((W, ys[i - 1], None, ysl, r, n_in, fl | bb.OP_RESCALE, None, 0.0, shapes[i - 1][1]))
+        else:
+            ops.append((W, xs[n_in], None, ysl, r, n_in, fl, None, 0.0, 0))
+    return ops, ys, ws
+
+
+def glue_vector(torch, y_prev, n_in):
+    """The glue of decode_ops(flow=True), with torch on the device: exact (a power-of-two factor, an index map)."""
+    m = y_prev.abs().max()
+    scale = torch.ones((), device=y_prev.device)
+    if float(m.item()) >= 1.1754943508222875e-38:
+        _, ex = torch.frexp(m)
+        scale = torch.ldexp(scale, -(ex - 1))
+    idx = torch.arange(n_in, device=y_prev.device) % y_prev.numel()
+    return (y_prev[idx] * scale).contiguous()
+
+
+def decode_step_leg(args, torch, bb, dist):
+    """The 401 projections of one decoded token (6.8 GB of PQ2_0 weights) as ONE list launch per token
+    (bonsai_b200_chain_run), replayed as one CUDA graph: tokens/s and weight GB/s.  On one GPU the values flow: each
+    projection rotates and quantises the previous projection's output (exact power-of-two glue), projections that read
+    the same vector share its quantised form, every other projection waits for all rows of the projections before
+    it.  With N > 1 every matrix is split by output rows; the outputs reach every rank by peer stores inside the kernel
+    (list) or by an all-gather behind every projection (per-matrix calls), and every projection reads a resident
+    vector (the glue needs the maximum over all ranks' rows, which the kernel records on one rank only).
+    Parity: every projection's output of the timed launch against the per-matrix call (bonsai_b200_linear) on the
+    unsplit matrix and the same input vector -- for flowing values the glue'd previous output -- bit for bit."""
+    rank, world, local = env_ranks()
+    if dist is None:
+        world, rank = 1, 0
+    bb.set_option("pdl", max(args.pdl, 0))
+    shapes = model_gemvs()
     use_list = args.call == "list"
+    flow = use_list and world == 1
+    peer_buf, chain, y_all = None, None, None
     if use_list and world > 1:
         from bonsai_b200.peer import PeerBuffer
-        peer_buf = PeerBuffer(off * 4, dist, rank, world)
+        peer_buf = PeerBuffer(sum(n for _, n in shapes) * 4, dist, rank, world)
         y_all = peer_buf.tensor.view(torch.float32)
-    else:
-        y_all = torch.zeros(off, dtype=torch.float32, device="cuda")
-
-    def flags_of(i):
-        prev = shapes[i - 1][0] if i else None
-        return bb.OP_ROTATE | (bb.OP_SAME_INPUT if i and prev == shapes[i][0] else (bb.OP_DEPENDS if i else 0))
-
+    ops, ys, ws = decode_ops(torch, bb, shapes, args.seed, flow, rank, world, y_all)
+    xq = {k: torch.empty(k // 32 * 36, dtype=torch.uint8, device="cuda") for k in sorted({a for a, _ in shapes})}
     launches_per_token = len(shapes)
     if use_list:
-        ops = []
-        for i, ((n_in, n_out), W) in enumerate(zip(shapes, ws)):
-            r = rows_of[i]
-            ops.append((W, xs[n_in], None, y_all[y_off[i] + rank * r:y_off[i] + (rank + 1) * r], r, n_in, flags_of(i)))
         chain = bb.Chain(ops, peers=peer_buf)
         launches_per_token = 1
 
@@ -707,11 +733,8 @@ def decode_step_leg(args, torch, bb, dist):
             assert chain.run() == 0
     else:
         def token():
-            for i, ((n_in, n_out), W) in enumerate(zip(shapes, ws)):
-                r = rows_of[i]
-                yv = y_all[y_off[i]:y_off[i] + n_out]
-                ysl = yv[rank * r:(rank + 1) * r]
-                assert bb.linear(W, xs[n_in], None, ysl, xq[n_in], r, n_in) == 0    # rotation + quantiser + mat-vec
+            for (W, x, _, ysl, r, n_in, *_), yv in zip(ops, ys):
+                assert bb.linear(W, x, None, ysl, xq[n_in], r, n_in) == 0    # rotation + quantiser + mat-vec
                 if world > 1:
                     dist.all_gather_into_tensor(yv, ysl)
 
@@ -724,7 +747,7 @@ def decode_step_leg(args, torch, bb, dist):
     torch.cuda.synchronize()
     if dist is not None:
         dist.barrier()
-    first = 0
+    first, x_cur = 0, None
     for i, (n_in, n_out) in enumerate(shapes):
         nblk = n_out * (n_in // 128)
         if world == 1:
@@ -733,9 +756,13 @@ def decode_step_leg(args, torch, bb, dist):
             Wf = torch.empty(nblk * 34, dtype=torch.uint8, device="cuda")
             assert bb.synth_pq2_0(Wf, first, nblk, args.seed) == 0
         first += nblk
+        if not flow or i == 0:
+            x_cur = ops[i][1]
+        elif not (ops[i][6] & bb.OP_SAME_INPUT):
+            x_cur = glue_vector(torch, ys[i - 1], n_in)
         want = torch.empty(n_out, dtype=torch.float32, device="cuda")
-        assert bb.linear(Wf, xs[n_in], None, want, xq[n_in], n_out, n_in) == 0
-        got = y_all[y_off[i]:y_off[i] + n_out]
+        assert bb.linear(Wf, x_cur, None, want, xq[n_in], n_out, n_in) == 0
+        got = ys[i]
         if not torch.equal(got.view(torch.int32), want.view(torch.int32)):
             bad += 1
             worst = max(worst, float((got - want).abs().max().item()))
@@ -752,7 +779,7 @@ def decode_step_leg(args, torch, bb, dist):
             "by the kernel" if world > 1 else "") if launches_per_token == 1 else
             "bonsai_b200_linear per matrix" + (", then an all-gather" if world > 1 else ""))
     out = {"metric": "decode_tokens_per_s", "value": 1e3 / ms_tok, "unit": "tokens/s", "ms_per_token": ms_tok,
-           "weight_gbs": gbs, "matvecs": len(shapes), "weight_bytes": wbytes, "call": call,
+           "weight_gbs": gbs, "matvecs": len(shapes), "weight_bytes": wbytes, "call": call, "values_flow": flow,
            "gpu_launches": launches_per_token * steps * reps, "steps": steps, "tokens_per_step": reps,
            "frac": gbs / world / peak, "frac_nominal": gbs / world / NOMINAL_HBM_GBS, "peak_kind": peak_kind,
            "parity": {"checked": len(shapes), "mismatches": bad, "max_abs": worst,
@@ -784,6 +811,7 @@ def run_decode_step(args):
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": DTYPE, "data": "synthetic",
             "config": {"workload": "decode_step", "matvecs": leg["matvecs"], "weight_bytes": leg["weight_bytes"], "batch": 1,
                        "pdl": args.pdl, "l2": "inputs larger than L2", "launch": "cuda_graph_per_token", "call": leg["call"],
+                       "values_flow": leg["values_flow"],
                        "tokens_per_step": leg["tokens_per_step"],
                        "parallelism": "single" if world == 1 else f"rows/{world}"},
             "gpu_launches": leg["gpu_launches"], "clocks": leg["clocks"], "parity": leg["parity"],

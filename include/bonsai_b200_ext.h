@@ -52,6 +52,10 @@ int bonsai_b200_linear(const void *W, const float *x, const float *signs, float 
 int bonsai_b200_linear_static(const void *W, const float *x, const float *signs, float *y, int64_t n_out,
                               int64_t n_in, bonsai_stream stream);
 
+/* y = silu(gate) * up, elementwise (src/ops.h:27-31; the reference has no entry point for it).  The unfused form of
+ * BONSAI_B200_OP_SWIGLU below. */
+int bonsai_b200_swiglu(const float *gate, const float *up, float *y, int64_t n, bonsai_stream stream);
+
 /* Token batch for the mat-mul: X is fp32 [n_tok][n_in] (token-major); Xq receives the
  * chunk-major [n_in/32][n_tok] Q8_1 layout that bonsai_p40_gemm reads (the reference has no
  * entry point that produces it; its test builds it by hand, tests/test_p40.cpp:438-447).
@@ -140,9 +144,24 @@ int bonsai_b200_clear_status(void);
  * launches one cooperative kernel of one CTA per SM on `stream` (plus a 4-byte memset) and can be
  * captured in a CUDA graph; a chain object must not run on two streams at once.  Errors: 1 for a bad
  * argument, otherwise the CUDA error code. */
+/* Producers (with OP_ROTATE, at most one per op): what turns the fp32 vector at x into the vector that is rotated and
+ * quantised, fused into the op's prologue -- the step that precedes every projection of a decode step
+ * (reference: src/ops.h:13-31; its device code runs them as kernels of their own, src/kernels/elementwise_p40.cu:48-88).
+ *   BONSAI_B200_OP_RMSNORM     input = x * (1 / sqrt(mean(x^2) + eps)) * aux[0 .. n_in); n_in <= 7168.  Same bits as
+ *                              bonsai_p40_rmsnorm followed by the op without the flag.
+ *   BONSAI_B200_OP_SWIGLU      input = silu(x) * aux  (x = gate, aux = up, both n_in floats).  Same bits as
+ *                              bonsai_b200_swiglu followed by the op without the flag.
+ *   BONSAI_B200_OP_RESCALE     x is the whole output (src_len floats) of an earlier op of the list;
+ *                              input[j] = x[j mod src_len] * 2^-e with e = floor(log2(max |x|)) (x unscaled if that
+ *                              maximum is zero or subnormal): an exact, order-independent glue between the ops of a
+ *                              synthetic decode step.  Needs OP_DEPENDS (or OP_SAME_INPUT after such an op); one-rank
+ *                              lists only. */
 #define BONSAI_B200_OP_ROTATE 1u
 #define BONSAI_B200_OP_DEPENDS 2u
 #define BONSAI_B200_OP_SAME_INPUT 4u
+#define BONSAI_B200_OP_RMSNORM 8u
+#define BONSAI_B200_OP_SWIGLU 16u
+#define BONSAI_B200_OP_RESCALE 32u
 typedef struct bonsai_b200_op {
     const void *W;
     const void *x;
@@ -151,6 +170,9 @@ typedef struct bonsai_b200_op {
     int64_t n_out, n_in;
     uint32_t flags;
     uint32_t reserved;      /* 0 */
+    const float *aux;       /* OP_RMSNORM: norm weights, OP_SWIGLU: the second vector; else NULL */
+    float eps;              /* OP_RMSNORM; else 0 */
+    uint32_t src_len;       /* OP_RESCALE: floats at x; else 0 */
 } bonsai_b200_op;
 typedef struct bonsai_b200_chain bonsai_b200_chain;
 int bonsai_b200_chain_create(const bonsai_b200_op *ops, int64_t n_ops, bonsai_b200_chain **out);

@@ -36,6 +36,7 @@ SIGNATURES = {
     "bonsai_b200_fwht_quant": (_INT, [_VP, _VP, _VP, _VP, _I64, _VP]),
     "bonsai_b200_linear": (_INT, [_VP, _VP, _VP, _VP, _VP, _I64, _I64, _VP]),
     "bonsai_b200_linear_static": (_INT, [_VP, _VP, _VP, _VP, _I64, _I64, _VP]),
+    "bonsai_b200_swiglu": (_INT, [_VP, _VP, _VP, _I64, _VP]),
     "bonsai_b200_quant_batch": (_INT, [_VP, _VP, _VP, _I64, _I64, _INT, _VP]),
     "bonsai_b200_gemv_chunk_sums": (_INT, [_VP, _VP, _VP, _I64, _I64, _I64, _VP]),
     "bonsai_b200_gemv_dump": (_INT, [_VP, _VP, _VP, _VP, _I64, _I64, _VP]),
@@ -146,6 +147,10 @@ def fwht_quant(x, signs, xq, x_rot, n):
                                         _stream())
 
 
+def swiglu(gate, up, y, n):
+    return lib().bonsai_b200_swiglu(_dev(gate, "gate"), _dev(up, "up"), _dev(y, "y"), n, _stream())
+
+
 def quant_batch(X, signs, Xq, n_in, n_tok, rotate):
     return lib().bonsai_b200_quant_batch(_dev(X, "X"), _dev(signs, "signs"), _dev(Xq, "Xq"), n_in, n_tok,
                                          int(bool(rotate)), _stream())
@@ -185,26 +190,32 @@ def linear_static(W, x, signs, y, n_out, n_in):
 
 
 # ---- a list of projections in one launch -------------------------------------------------------------
-OP_ROTATE, OP_DEPENDS, OP_SAME_INPUT = 1, 2, 4
+OP_ROTATE, OP_DEPENDS, OP_SAME_INPUT, OP_RMSNORM, OP_SWIGLU, OP_RESCALE = 1, 2, 4, 8, 16, 32
 
 
 class Op(C.Structure):
     """struct bonsai_b200_op"""
     _fields_ = [("W", C.c_void_p), ("x", C.c_void_p), ("signs", C.c_void_p), ("y", C.c_void_p),
-                ("n_out", C.c_int64), ("n_in", C.c_int64), ("flags", C.c_uint32), ("reserved", C.c_uint32)]
+                ("n_out", C.c_int64), ("n_in", C.c_int64), ("flags", C.c_uint32), ("reserved", C.c_uint32),
+                ("aux", C.c_void_p), ("eps", C.c_float), ("src_len", C.c_uint32)]
 
 
 class Chain:
     """bonsai_b200_chain_create / _create_tp / _run / _destroy.  `ops` is a list of (W, x, signs, y, n_out, n_in,
-    flags) with CUDA tensors; the tensors are kept alive by the object.  With `peers` (a peer.PeerBuffer whose
+    flags[, aux[, eps[, src_len]]]) with CUDA tensors; the tensors are kept alive by the object.  With `peers` (a peer.PeerBuffer whose
     tensor holds every y) the list runs over the row slices of several ranks."""
 
     def __init__(self, ops, peers=None, wait_limit_us=0):
-        self._keep = [t for op in ops for t in op[:4] if t is not None]
+        self._keep = [t for op in ops for t in (*op[:4], *op[7:8]) if t is not None]
         arr = (Op * len(ops))()
-        for o, (W, x, signs, y, n_out, n_in, flags) in zip(arr, ops):
+        for o, op in zip(arr, ops):
+            W, x, signs, y, n_out, n_in, flags = op[:7]
+            aux = op[7] if len(op) > 7 else None
             o.W, o.x, o.y = _dev(W, "W").value, _dev(x, "x").value, _dev(y, "y").value
             o.signs = _dev(signs, "signs").value if signs is not None else None
+            o.aux = _dev(aux, "aux").value if aux is not None else None
+            o.eps = float(op[8]) if len(op) > 8 else 0.0
+            o.src_len = int(op[9]) if len(op) > 9 else 0
             o.n_out, o.n_in, o.flags, o.reserved = n_out, n_in, flags, 0
         self._h = C.c_void_p()
         if peers is None:

@@ -492,7 +492,7 @@ struct bonsai_b200_chain {
     bool tp = false;                        // several ranks: counters live in the caller's peer-mapped buffer, never reset
     ChainPeers peers{};
     int n_ops = 0, threads = 0, grid = 0, device = 0;
-    size_t smem = 0;
+    size_t smem = 0, counter_bytes = 0;
     ChainGeom G{};
 };
 
@@ -547,7 +547,7 @@ static int chain_create_impl(const bonsai_b200_op *ops, int64_t n_ops, int tp_ra
     const int ntables = q8_ops == 0 ? 1 : (2 * q8_fills > q8_ops ? CHAIN_TABLES : 2);
     int shift = 0, buf = ntables - 1, last_user[CHAIN_TABLES], ready_uses[CHAIN_TABLES];
     for (int b = 0; b < CHAIN_TABLES; ++b) last_user[b] = -1, ready_uses[b] = 0;
-    bool any_rotate = false, any_q8 = false, any_spread = false;
+    bool any_rotate = false, any_q8 = false, any_spread = false, any_rescale = false;
     unsigned int spread_total = 0;
     const int spread_nb = g_opt_chain_spread_nb.load();
     unsigned int signals = 0;
@@ -557,24 +557,42 @@ static int chain_create_impl(const bonsai_b200_op *ops, int64_t n_ops, int tp_ra
         std::memset(&r, 0, sizeof(r));
         const bool rotate = o.flags & BONSAI_B200_OP_ROTATE, depends = o.flags & BONSAI_B200_OP_DEPENDS;
         bool same = o.flags & BONSAI_B200_OP_SAME_INPUT;
+        const uint32_t producer = o.flags & (BONSAI_B200_OP_RMSNORM | BONSAI_B200_OP_SWIGLU | BONSAI_B200_OP_RESCALE);
+        // two ops read the same prepared input: same vector, width, signs, kind and producer (with its arguments)
+        auto same_input = [](const bonsai_b200_op &a, const bonsai_b200_op &b) {
+            const uint32_t kind = BONSAI_B200_OP_ROTATE | BONSAI_B200_OP_RMSNORM | BONSAI_B200_OP_SWIGLU | BONSAI_B200_OP_RESCALE;
+            return a.x == b.x && a.n_in == b.n_in && a.signs == b.signs && !((a.flags ^ b.flags) & kind) && a.aux == b.aux &&
+                   a.eps == b.eps && a.src_len == b.src_len;
+        };
         // the same vector as the op before, and no wait asked for: its tables are reused without being told
         // (nothing may write x during the launch unless a later reader says OP_DEPENDS)
-        if (!same && i > 0 && !(o.flags & BONSAI_B200_OP_DEPENDS) && ops[i - 1].x == o.x && ops[i - 1].n_in == o.n_in &&
-            ops[i - 1].signs == o.signs && !((ops[i - 1].flags ^ o.flags) & BONSAI_B200_OP_ROTATE))
-            same = true;
-        if ((o.flags & ~7u) || o.reserved) return 1;
+        if (!same && i > 0 && !depends && same_input(ops[i - 1], o)) same = true;
+        if ((o.flags & ~63u) || o.reserved) return 1;
         if (!o.W || !o.x || !o.y || o.n_out <= 0 || o.n_out > INT32_MAX || o.n_in <= 0) return 1;
         if (o.n_in % 256 != 0 || (rotate && o.n_in % FWHT_N != 0) || o.n_in / 128 > 1024) return 1;
         if (!aligned16(o.W) || !aligned16(o.x) || (o.signs && !aligned16(o.signs)) || (reinterpret_cast<uintptr_t>(o.y) & 3u))
             return 1;
         if (depends && !rotate) return 1;               // outputs are fp32: a dependent op must quantise
         if (o.signs && !rotate) return 1;
+        // producers work on the fp32 vector, one at a time
+        if (producer && (!rotate || (producer & (producer - 1)))) return 1;
+        if ((producer & (BONSAI_B200_OP_RMSNORM | BONSAI_B200_OP_SWIGLU)) && (!o.aux || !aligned16(o.aux))) return 1;
+        if (!(producer & (BONSAI_B200_OP_RMSNORM | BONSAI_B200_OP_SWIGLU)) && o.aux) return 1;
+        if ((producer & BONSAI_B200_OP_RMSNORM) && o.n_in / FWHT_N > 7) return 1;      // the whole vector must fit one pass
+        if (!(producer & BONSAI_B200_OP_RMSNORM) && o.eps != 0.0f) return 1;
+        int src_op = -1;
+        if (producer & BONSAI_B200_OP_RESCALE) {
+            // x is the output of an earlier op of the list (all of it), whose largest magnitude the kernel records
+            if (tp || o.src_len == 0 || o.src_len % 4 != 0 || o.src_len > INT32_MAX) return 1;
+            for (int64_t pidx = i - 1; pidx >= 0 && src_op < 0; --pidx)
+                if (ops[pidx].y == o.x && ops[pidx].n_out == (int64_t)o.src_len) src_op = (int)pidx;
+            if (src_op < 0) return 1;
+        } else if (o.src_len != 0) {
+            return 1;
+        }
         if (same) {
             if (i == 0 || depends) return 1;
-            const bonsai_b200_op &q = ops[i - 1];
-            if (q.x != o.x || q.n_in != o.n_in || q.signs != o.signs ||
-                ((q.flags ^ o.flags) & BONSAI_B200_OP_ROTATE))
-                return 1;
+            if (!same_input(ops[i - 1], o)) return 1;
         }
         r.W = static_cast<const uint8_t *>(o.W);
         r.x = o.x;
@@ -600,7 +618,17 @@ static int chain_create_impl(const bonsai_b200_op *ops, int64_t n_ops, int tp_ra
         r.magic_nseg = magic_u32((uint32_t)r.nseg);
         r.cta_shift = shift;
         shift = (int)((shift + used) % sms);            // the next op starts on the CTA after this one's last
-        r.flags = (rotate ? CHAIN_ROTATE : 0) | (depends ? CHAIN_DEPENDS : 0) | (same ? CHAIN_SAME_INPUT : 0);
+        r.flags = (rotate ? CHAIN_ROTATE : 0) | (depends ? CHAIN_DEPENDS : 0) | (same ? CHAIN_SAME_INPUT : 0) |
+                  ((producer & BONSAI_B200_OP_RMSNORM) ? CHAIN_RMSNORM : 0) | ((producer & BONSAI_B200_OP_SWIGLU) ? CHAIN_SWIGLU : 0) |
+                  ((producer & BONSAI_B200_OP_RESCALE) ? CHAIN_RESCALE : 0);
+        r.aux = o.aux;
+        r.eps = o.eps;
+        r.src_len = (int)o.src_len;
+        r.src_op = src_op;
+        if (src_op >= 0) {
+            rec[(size_t)src_op].flags |= CHAIN_MAXSRC;
+            any_rescale = true;
+        }
         if (depends) rec[(size_t)i - 1].flags |= CHAIN_SIGNAL;     // i > 0: op 0 may not depend
         if (depends && i == 0) return 1;
         if (!same) buf = (buf + 1) % ntables;
@@ -680,7 +708,8 @@ static int chain_create_impl(const bonsai_b200_op *ops, int64_t n_ops, int tp_ra
     if (e == cudaSuccess && per_sm < 1) e = cudaErrorLaunchOutOfResources;
     if (e == cudaSuccess) e = cudaMalloc(&c->d_ops, sizeof(ChainOp) * (size_t)n_ops);
     if (e == cudaSuccess && tp) c->d_counter = c->peers.counter[tp_rank];
-    if (e == cudaSuccess && !tp) e = cudaMalloc(&c->d_counter, 256);
+    c->counter_bytes = 256 + (any_rescale ? 4 * (size_t)n_ops : 0);        // counters, then the largest |y| of every op
+    if (e == cudaSuccess && !tp) e = cudaMalloc(&c->d_counter, c->counter_bytes);
     if (e == cudaSuccess && any_spread) e = cudaMalloc(&c->d_image, (size_t)G.nb_max * 176);
     if (e == cudaSuccess) e = cudaMemcpy(c->d_ops, rec.data(), sizeof(ChainOp) * (size_t)n_ops, cudaMemcpyHostToDevice);
     if (e != cudaSuccess) {
@@ -706,7 +735,7 @@ int bonsai_b200_chain_run(bonsai_b200_chain *c, bonsai_stream stream) {
     if (!c || !c->d_ops) return 1;
     cudaStream_t st = as_stream(stream);
     cudaError_t e = cudaSuccess;
-    if (!c->tp) e = cudaMemsetAsync(c->d_counter, 0, 2 * sizeof(unsigned int), st);
+    if (!c->tp) e = cudaMemsetAsync(c->d_counter, 0, c->counter_bytes > 256 ? c->counter_bytes : 2 * sizeof(unsigned int), st);
     if (e != cudaSuccess) return (int)e;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)c->grid);
@@ -983,6 +1012,12 @@ int bonsai_p40_rmsnorm(const float *x, const float *w, float *y, int64_t n_rows,
     if (n > INT32_MAX || n_rows > INT32_MAX || !aligned4(x) || !aligned4(w) || !aligned4(y)) return 1;
     if (n % 4 == 0 && aligned16(x)) rmsnorm_kernel<true><<<(unsigned)n_rows, 256, 0, as_stream(stream)>>>(x, w, y, (int)n, eps);
     else rmsnorm_kernel<false><<<(unsigned)n_rows, 256, 0, as_stream(stream)>>>(x, w, y, (int)n, eps);
+    return (int)cudaGetLastError();
+}
+
+int bonsai_b200_swiglu(const float *gate, const float *up, float *y, int64_t n, bonsai_stream stream) {
+    if (n <= 0 || n > INT32_MAX || !aligned4(gate) || !aligned4(up) || !aligned4(y)) return 1;
+    swiglu_kernel<<<(unsigned)((n + 255) / 256), 256, 0, as_stream(stream)>>>(gate, up, y, (int)n);
     return (int)cudaGetLastError();
 }
 

@@ -39,10 +39,19 @@
 #include "common.cuh"
 #include "gemv.cuh"
 #include "gemv_stream.cuh"
+#include "ops.cuh"
 
 namespace b200 {
 
-enum : int { CHAIN_ROTATE = 1, CHAIN_DEPENDS = 2, CHAIN_SAME_INPUT = 4, CHAIN_SIGNAL = 8, CHAIN_SPREAD = 16 };
+// Bits 0-5 are the caller's (bonsai_b200_ext.h); the others are set while the list is laid out.
+enum : int {
+    CHAIN_ROTATE = 1, CHAIN_DEPENDS = 2, CHAIN_SAME_INPUT = 4,
+    CHAIN_RMSNORM = 8,        // input = RMSNorm(x; aux = weights, eps)   (src/ops.h:13-22), then signs, rotation, quantiser
+    CHAIN_SWIGLU = 16,        // input = silu(x) * aux                     (src/ops.h:27-31)
+    CHAIN_RESCALE = 32,       // input[j] = x[j mod src_len] * 2^-e, e = floor(log2(max |x|)): the exact glue of the synthetic decode step
+    CHAIN_SIGNAL = 64, CHAIN_SPREAD = 128,
+    CHAIN_MAXSRC = 256        // a later CHAIN_RESCALE op reads this op's output: its largest magnitude is recorded
+};
 
 constexpr int CHAIN_MAX_SLOTS = 16;
 constexpr int CHAIN_OP_RING = 8;
@@ -65,7 +74,11 @@ struct __align__(16) ChainOp {                 // 128 bytes, one per projection,
     int ready_parity;                          // phase parity of ready[buf] (Q8_1 ops that fill a buffer)
     int prev_user;                             // last op that read the previous contents of buf, or -1
     uint32_t spread_blocks;                    // CHAIN_SPREAD: 1024-blocks rotated by spread ops up to and including this one
-    int pad[8];
+    const float *aux;                          // CHAIN_RMSNORM: norm weights; CHAIN_SWIGLU: the second vector
+    float eps;                                 // CHAIN_RMSNORM
+    int src_len;                               // CHAIN_RESCALE: floats at x
+    int src_op;                                // CHAIN_RESCALE: the op whose output x is
+    int pad[3];
 };
 static_assert(sizeof(ChainOp) == 128, "op records are copied as 32 words");
 
@@ -84,7 +97,7 @@ struct ChainGeom {
 
 // Shared-memory bytes before the ring (the host uses the same function).
 __host__ __device__ inline size_t chain_fixed_bytes(const ChainGeom &G) {
-    const size_t b = 384 + CHAIN_OP_RING * sizeof(ChainOp) + (size_t)G.ntables * G.nb_max * 176 + (size_t)G.stage_blocks * 144 +
+    const size_t b = 640 + CHAIN_OP_RING * sizeof(ChainOp) + (size_t)G.ntables * G.nb_max * 176 + (size_t)G.stage_blocks * 144 +
                      (size_t)G.rot_blocks * 4096 +
                      CHAIN_GATES * (size_t)G.partial_floats * 4 + CHAIN_GATES * (size_t)G.quad_ints * 4 +
                      CHAIN_GATES * (size_t)G.rows_stage * 4;
@@ -195,9 +208,11 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *_
     int *expect_cnt = done_cnt + CHAIN_MAX_SLOTS;             // [16] ... of how many
     volatile int *ctrl = expect_cnt + CHAIN_MAX_SLOTS;        // [16] 0 issued, 1 ops_loaded, 2 next_task, 3 copy_op, 4-7 warps that
                                                               //      left op (index & 3), 8 ops_done: every compute warp has left ops [0, ops_done),
-                                                              //      9 (several ranks) ops whose rows the peer warp has sent
-    ChainOp *opring = reinterpret_cast<ChainOp *>(smem + 384);
-    uint8_t *p = smem + 384 + CHAIN_OP_RING * sizeof(ChainOp);
+                                                              //      9 (several ranks) ops whose rows the peer warp has sent,
+                                                              //      10-13 largest |y| of op (index & 3) so far, as float bits
+    float *ssum = reinterpret_cast<float *>(smem + 384);     // [56] sums of squares of the slices of an RMSNorm input
+    ChainOp *opring = reinterpret_cast<ChainOp *>(smem + 640);
+    uint8_t *p = smem + 640 + CHAIN_OP_RING * sizeof(ChainOp);
     const size_t table_bytes = (size_t)G.nb_max * 176;
     uint8_t *tables = p;
     p += (size_t)G.ntables * table_bytes;
@@ -235,10 +250,13 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *_
         spread_base = run * PE.spread_per_run;
     }
     // a finished y element (several ranks: the CTA's rows go to the peers in one piece when it leaves the op)
+    float ymax = 0.0f;          // largest |y| this lane has stored in the current op (kept only for CHAIN_MAXSRC ops)
     auto store_y = [&](float *p, float v, int op_, int r_) {
         *p = v;
+        ymax = fmaxf(ymax, fabsf(v));
         if (TP) ystage[(size_t)(op_ % CHAIN_GATES) * G.rows_stage + r_] = v;
     };
+    unsigned int *opmax = grid_counter + 64;     // one word per op behind the counters (one-rank form)
     // this CTA's rows of every op so far are written: tell the grid
     auto arrive_all = [&]() {
         __threadfence();
@@ -271,12 +289,21 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *_
                     // this warp's y rows are in memory (device scope) before it is counted out below: other CTAs read them
                     // once everybody has arrived (several ranks: the peer warp reads its copy in shared memory)
                     if (flags & CHAIN_SIGNAL) __threadfence();
+                    if (!TP && (flags & CHAIN_MAXSRC)) {                // the warp's largest |y|, then the CTA's (float bits order as ints)
+#pragma unroll
+                        for (int o = 16; o > 0; o >>= 1) ymax = fmaxf(ymax, __shfl_xor_sync(0xffffffffu, ymax, o));
+                        if (lane == 0) atomicMax(const_cast<int *>(&ctrl[10 + (op & 3)]), __float_as_int(ymax));
+                    }
                     __syncwarp();
                     if (lane == 0) {
                         __threadfence_block();                          // this warp's reads of op's tables and partial sums
                         const int old = atomicAdd(const_cast<int *>(&ctrl[4 + (op & 3)]), 1);
                         if (old == C - 1) {                             // last warp out: the CTA's rows of every op so far are written
                             ctrl[4 + (op & 3)] = 0;
+                            if (!TP && (flags & CHAIN_MAXSRC)) {        // ... and the largest of them is known: to the grid, before the arrival
+                                atomicMax(opmax + op, (unsigned int)ctrl[10 + (op & 3)]);
+                                ctrl[10 + (op & 3)] = 0;
+                            }
                             if (!TP && (flags & CHAIN_SIGNAL)) arrive_all();
                             __threadfence_block();
                             ctrl[8] = op + 1;                           // monotonic: ops are left in order
@@ -297,6 +324,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *_
                 cta_rows(R, row0, rows_here);
                 ntiles = (rows_here + R.tr - 1) / R.tr;
                 ntasks = ntiles * R.tpt;
+                ymax = 0.0f;
                 if (!(flags & CHAIN_SAME_INPUT)) {
                     if (flags & CHAIN_ROTATE) {
                         // every compute warp has left op - 1: both table buffers' readers are gone
@@ -324,9 +352,18 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *_
                         int *act_i = reinterpret_cast<int *>(act_s + (size_t)G.nb_max * 4);
                         const float *x = static_cast<const float *>(R.x);
                         const float *signs = R.signs;
+                        const float *aux = R.aux;
                         const int nfb = R.nb >> 3;
                         const int fb_lo = spread ? min((int)blockIdx.x, nfb) : 0;
                         const int fb_hi = spread ? min((int)blockIdx.x + 1, nfb) : nfb;
+                        // the exact power-of-two rescale of the synthetic decode step: the producer recorded max |x|
+                        float rescale = 1.0f;
+                        const int src_len = R.src_len;
+                        if (flags & CHAIN_RESCALE) {
+                            const unsigned int mb = __ldcg(opmax + R.src_op);
+                            const int e8 = (int)(mb >> 23);                     // biased exponent of the largest magnitude
+                            if (e8 >= 1) rescale = __int_as_float(max(1, 254 - e8) << 23);      // 2^-(e8 - 127); zero / subnormal: unscaled
+                        }
                         // One warp per 128-element slice, G.rot_blocks 1024-blocks per round trip through
                         // the scratch area: front butterflies, meet, back butterflies + quantiser, meet.
                         bool ok = true;
@@ -339,8 +376,54 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *_
 #pragma unroll
                             for (int k = 0; k < UPW; ++k) {
                                 const int u = wid + k * C;
-                                if (u < units)
-                                    f[k] = __ldcg(reinterpret_cast<const float4 *>(x + (size_t)fb0 * FWHT_N + (size_t)u * 128 + 4 * lane));
+                                if (u < units) {
+                                    int idx = fb0 * FWHT_N + u * 128 + 4 * lane;
+                                    if (flags & CHAIN_RESCALE) idx %= src_len;
+                                    f[k] = __ldcg(reinterpret_cast<const float4 *>(x + idx));
+                                }
+                            }
+                            if (flags & (CHAIN_SWIGLU | CHAIN_RESCALE)) {
+#pragma unroll
+                                for (int k = 0; k < UPW; ++k) {
+                                    const int u = wid + k * C;
+                                    if (u < units) {
+                                        if (flags & CHAIN_SWIGLU) {
+                                            const float4 up = __ldcg(reinterpret_cast<const float4 *>(aux + (size_t)fb0 * FWHT_N + (size_t)u * 128 + 4 * lane));
+                                            f[k] = make_float4(swiglu1(f[k].x, up.x), swiglu1(f[k].y, up.y), swiglu1(f[k].z, up.z), swiglu1(f[k].w, up.w));
+                                        } else {
+                                            f[k] = make_float4(__fmul_rn(f[k].x, rescale), __fmul_rn(f[k].y, rescale), __fmul_rn(f[k].z, rescale), __fmul_rn(f[k].w, rescale));
+                                        }
+                                    }
+                                }
+                            }
+                            if (flags & CHAIN_RMSNORM) {
+                                // the whole vector is in the registers of this round (the host refuses longer ones): slice sums
+                                // of squares, meet, every warp adds them in slice order, scales and applies the weights
+#pragma unroll
+                                for (int k = 0; k < UPW; ++k) {
+                                    const int u = wid + k * C;
+                                    if (u < units) {
+                                        const float sq = slice_sumsq(f[k]);
+                                        if (lane == 0) ssum[u] = sq;
+                                    }
+                                }
+                                __syncwarp();
+                                if (lane == 0) mbar_arrive(xs);
+                                ok = mbar_wait_bounded(xs, xs_phase & 1u, CHAIN_NS0, CHAIN_NSMAX);
+                                ++xs_phase;
+                                if (!ok) break;
+                                float ss = 0.0f;
+                                for (int u = 0; u < units; ++u) ss = __fadd_rn(ss, ssum[u]);
+                                const float sc = rms_scale(ss, R.nb * 128, R.eps);
+#pragma unroll
+                                for (int k = 0; k < UPW; ++k) {
+                                    const int u = wid + k * C;
+                                    if (u < units) {
+                                        const float4 wv = __ldg(reinterpret_cast<const float4 *>(aux + (size_t)u * 128 + 4 * lane));
+                                        f[k] = make_float4(__fmul_rn(__fmul_rn(f[k].x, sc), wv.x), __fmul_rn(__fmul_rn(f[k].y, sc), wv.y),
+                                                           __fmul_rn(__fmul_rn(f[k].z, sc), wv.z), __fmul_rn(__fmul_rn(f[k].w, sc), wv.w));
+                                    }
+                                }
                             }
 #pragma unroll
                             for (int k = 0; k < UPW; ++k) {

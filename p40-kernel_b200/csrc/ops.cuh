@@ -34,6 +34,12 @@ __device__ __forceinline__ float swiglu1(float g, float u) {
     return __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))), u);
 }
 
+__global__ void __launch_bounds__(256) swiglu_kernel(const float *__restrict__ gate, const float *__restrict__ up,
+                                                     float *__restrict__ y, int n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) y[i] = swiglu1(gate[i], up[i]);
+}
+
 // One CTA per row, n % 128 == 0 handled by whole slices (VEC: 16-byte loads), any n by the scalar tail path.
 template <bool VEC>
 __global__ void __launch_bounds__(256) rmsnorm_kernel(const float *__restrict__ x, const float *__restrict__ w,
