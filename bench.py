@@ -26,8 +26,8 @@ parity  : after the timed loop every output vector of the last sweep (on every r
 N > 1   : every matrix is split by output rows over the ranks (strong scaling: the total work is fixed); the
           slices are assembled either by one NCCL all-gather per sweep or by the kernel itself (stores into
           every rank's peer-mapped buffer); --gather auto times both here and keeps the faster.
-secondary (N = 1): decode step (401 mat-vecs of one token), prefill mat-mul (512 tokens), repacked-layout
-          mat-vec, each with its own parity check.
+secondary: row-partitioned batch of 8 (every N); on one GPU also the decode step (401 mat-vecs of one token, values
+          flowing), the prefill mat-mul (512 tokens) and the repacked-layout mat-vec; each with its own parity check.
 --impl reference : the reference's own host implementation of the same path on this box's CPU
           cores (oracle/_ref when it was built, else the C restatement in oracle/).
 """
@@ -578,7 +578,9 @@ def run_b200(args):
         "vs_baseline": None, "dtype": DTYPE, "data": "synthetic",
         "config": {"workload": "layer_sweep", "shapes_nin_nout": LAYER_SHAPES, "batch": 1, "sets": sets,
                    "sweeps_per_step": reps, "us_per_sweep": ms * 1e3 / sweeps,
-                   "resident_weight_bytes": total_w, "l2": "inputs larger than L2" if total_w > 126e6 else "fits L2",
+                   "resident_weight_bytes": total_w,
+                   "l2": ("inputs larger than L2" if total_w / world > 126e6 else
+                          f"the rank's slice ({total_w / world / 1e6:.0f} MB) is smaller than the 126 MB L2: weights may be served from it"),
                    "parallelism": par, "gather": gather, "gather_probe_us_per_sweep": gather_probe, "pdl": args.pdl,
                    "fp32_order": "host-sequential" if args.order == 1 else "fixed-tree",
                    "launch": "eager" if args.no_graph else "cuda_graph_per_sweep",
@@ -598,12 +600,17 @@ def run_b200(args):
         line["per_matrix_abi"] = per_matrix
     if split is not None:
         line["split"] = split
-    if world == 1 and not args.no_secondary:
+    if not args.no_secondary:
         sec = {}
-        for name, leg in (("decode_step", decode_step_leg), ("prefill", prefill_leg), ("repack_gemv", repack_leg)):
+        legs = [("batch8", batch_leg)]              # at every N; the others on one GPU
+        if world == 1:
+            legs += [("decode_step", decode_step_leg), ("prefill", prefill_leg), ("repack_gemv", repack_leg)]
+        for name, leg in legs:
             try:
-                sec[name] = leg(args, torch, bb, None)
+                sec[name] = leg(args, torch, bb, dist)
             except Exception as e:                 # a failing secondary leg must not hide the headline
+                if dist is not None:
+                    raise                          # several ranks: an exception on one rank must not leave the others waiting
                 sec[name] = {"error": f"{type(e).__name__}: {e}"[:300]}
         line["secondary"] = sec
     if world == 1 and not args.no_cpu:
@@ -977,6 +984,71 @@ def repack_leg(args, torch, bb, dist):
             "peak_kind": kind, "call": "bonsai_p40_gemv_repack per matrix (quantiser fused)",
             "parity": {"checked": 4, "mismatches": bad, "max_rel_to_max_abs": worst, "bound": 1e-5,
                        "against": "bonsai_p40_gemv on the un-repacked matrix"},
+            "device_status": bb.device_status()}
+
+
+# ---- row-partitioned small batch -----------------------------------------------------------------------
+def batch_leg(args, torch, bb, dist, n_tok=8):
+    """The two large projections (5120 -> 17408, 17408 -> 5120) with a batch of 8 activation vectors: every rank
+    multiplies its row slice through bonsai_p40_gemm (2 .. 8 tokens: the kernel that streams the weights once for all
+    tokens), an NCCL all-gather assembles Y[n_out][8].  `--sets` copies of each matrix are resident.  Reports weight
+    GB/s (weight bytes of all launches / time) and token-weight GB/s (x 8).  Parity: the assembled Y of the last sweep
+    against the same entry point on the unsplit matrix, bit for bit (a row's sum does not depend on the split)."""
+    from bonsai_b200 import partition
+    rank, world, local = env_ranks()
+    if dist is None:
+        world, rank = 1, 0
+    shapes = [(5120, 17408), (17408, 5120)]
+    mats, total_w, first = [], 0, 0
+    for s_ in range(args.sets):
+        for n_in, n_out in shapes:
+            lo, hi = partition.row_slice(n_out, rank, world)
+            nblk_row = n_in // 128
+            W = torch.empty((hi - lo) * nblk_row * 34, dtype=torch.uint8, device="cuda")
+            assert bb.synth_pq2_0(W, first + lo * nblk_row, (hi - lo) * nblk_row, args.seed + 17) == 0
+            mats.append((n_in, n_out, lo, hi, W, first))
+            first += n_out * nblk_row
+            total_w += n_out * nblk_row * 34
+    g = torch.Generator(device="cpu").manual_seed(args.seed + 8)
+    Xq = {}
+    for n_in in sorted({a for a, _ in shapes}):
+        X = torch.randn(n_tok, n_in, generator=g).cuda()
+        Xq[n_in] = torch.empty(n_in // 32 * n_tok * 36, dtype=torch.uint8, device="cuda")
+        assert bb.quant_batch(X, None, Xq[n_in], n_in, n_tok, True) == 0
+    Y = {n_out: torch.zeros(n_out, n_tok, device="cuda") for _, n_out in shapes}
+
+    def sweep():
+        for n_in, n_out, lo, hi, W, _ in mats:
+            assert bb.gemm(W, Xq[n_in], Y[n_out][lo:hi], hi - lo, n_in, n_tok) == 0
+            if world > 1:
+                dist.all_gather_into_tensor(Y[n_out], Y[n_out][lo:hi])
+
+    steps = max(3, min(args.steps, 50))
+    ms, reps, _ = timed(torch, sweep, steps, 3, dist, None, True)
+    us = ms * 1e3 / (steps * reps)
+    gbs = total_w / (us * 1e-6) / 1e9
+    bad, worst = 0, 0.0
+    torch.cuda.synchronize()
+    for n_in, n_out, lo, hi, W, first_blk in mats[-2:]:             # the copies the last sweep left in Y
+        nblk = n_out * (n_in // 128)
+        Wf = torch.empty(nblk * 34, dtype=torch.uint8, device="cuda")
+        assert bb.synth_pq2_0(Wf, first_blk, nblk, args.seed + 17) == 0
+        want = torch.zeros(n_out, n_tok, device="cuda")
+        assert bb.gemm(Wf, Xq[n_in], want, n_out, n_in, n_tok) == 0
+        if not torch.equal(Y[n_out].view(torch.int32), want.view(torch.int32)):
+            bad += 1
+            worst = max(worst, float((Y[n_out] - want).abs().max().item()))
+    if dist is not None:
+        t = torch.tensor([bad, worst], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        bad, worst = int(t[0].item()), float(t[1].item())
+    peak, _, kind = measured_peaks()
+    return {"metric": "pq2_0_gemm_batch8_weight_stream", "value": gbs, "unit": UNIT, "n_tok": n_tok, "us_per_sweep": us,
+            "token_weight_gbs": gbs * n_tok, "gpu_launches": len(mats) * steps * reps,
+            "frac": gbs / world / peak, "peak_kind": kind, "resident_weight_bytes": total_w,
+            "call": "bonsai_p40_gemm (8 tokens) per matrix slice" + (" + NCCL all-gather" if world > 1 else ""),
+            "parity": {"checked": 2, "mismatches": bad, "max_abs": worst,
+                       "against": "bonsai_p40_gemm on the unsplit matrix, bit for bit, every rank"},
             "device_status": bb.device_status()}
 
 

@@ -102,9 +102,11 @@ int bonsai_b200_stream_probe(const void *buf, int64_t bytes, int mode, void *sin
  * bit and are added in a fixed tree order (outputs within 1e-5 of the host's, identical from launch
  * to launch); 1 = the mat-vec that also adds them in the host's sequential order (outputs
  * bit-identical to src/pq2_0.h:183-191, slower).
- * key "gemm_path": -1 (default) = the mat-mul picks its kernel by token count (tensor cores from 48
- * tokens up), 0 = integer SIMT kernel (Y bit-identical to the host loop), 1 = tcgen05 tensor-core kernel (same
- * integers; fp32 side within 1e-5 of max |Y|, see csrc/gemm_tc.cuh).
+ * key "gemm_path": -1 (default) = the mat-mul picks its kernel by token count (2 .. 8 tokens: the streaming
+ * small-batch kernel; 48 tokens and more: tcgen05; else the integer SIMT kernel), 0 = integer SIMT kernel (Y
+ * bit-identical to the host loop), 1 = tcgen05 tensor-core kernel, 2 = the small-batch kernel where it takes the
+ * shape.  All give the host's int32 chunk sums; 1 and 2 hold fp32 Y to 1e-5 of max |Y| (csrc/gemm_tc.cuh,
+ * csrc/gemv_mma.cuh).
  * key "fuse_linear": 0 (default) = bonsai_b200_linear is two launches, 1 = one kernel when it can (saves a
  * launch, but every CTA then waits for its own rotation before its first multiply: measured ~6 % slower
  * on the 401-projection decode chain).

@@ -148,7 +148,7 @@ bool plan_stream(long long n_out, int nb, int variant, StreamParams &p, int &thr
 // Geometry of the tensor-core mat-vec (gemv_mma.cuh): tiles of 16 rows x one row segment, a ring of slots as deep
 // as `cap_kb` of shared memory allows.  Rows must start on a word (nb even); rows longer than one segment are cut at
 // multiples of 8 blocks (16-byte aligned pieces), which needs nb % 8 == 0.
-bool plan_mma(long long n_out, int nb, int cap_kb, MmaGeom &P, int &smem_bytes, int &grid) {
+bool plan_mma(long long n_out, int nb, int cap_kb, MmaGeom &P, int &smem_bytes, int &grid, bool batched = false) {
     if (nb <= 0 || nb % 2 != 0) return false;
     P = MmaGeom{};
     P.n_out = (int)n_out;
@@ -179,14 +179,15 @@ bool plan_mma(long long n_out, int nb, int cap_kb, MmaGeom &P, int &smem_bytes, 
         P.stride = row_bytes;
     }
     P.slot_bytes = (16 * P.stride + 127) & ~127;
+    auto fixed = [&](int n) { return batched ? mmab_fixed_bytes(P, n) : mma_fixed_bytes(P, n); };
     int nslot = MMA_MAX_SLOTS;
-    while (nslot >= 2 && mma_fixed_bytes(P, nslot) + (size_t)nslot * P.slot_bytes > (size_t)cap_kb * 1024) --nslot;
+    while (nslot >= 2 && fixed(nslot) + (size_t)nslot * P.slot_bytes > (size_t)cap_kb * 1024) --nslot;
     if (nslot < 2) return false;
     P.nslot = nslot;
     P.magic_pairs = magic_u32((uint32_t)P.pairs_max);
     P.magic_nseg = magic_u32((uint32_t)P.nseg);
     P.magic_nslot = magic_u32((uint32_t)P.nslot);
-    smem_bytes = (int)(mma_fixed_bytes(P, nslot) + (size_t)nslot * P.slot_bytes);
+    smem_bytes = (int)(fixed(nslot) + (size_t)nslot * P.slot_bytes);
     grid = P.ngroups < SM_COUNT ? P.ngroups : SM_COUNT;
     return true;
 }
@@ -850,6 +851,28 @@ static int launch_gemm_tc(const void *W, const void *Xq, float *Y, int64_t n_out
     return tma ? go(gemm_tc_kernel<false, true>, opt[2], TC_SMEM_BYTES_TMA) : go(gemm_tc_kernel<false, false>, opt[3], TC_SMEM_BYTES);
 }
 
+// The streaming small-batch mat-mul (gemv_mma.cuh).  -1: shape not taken (more than 8 tokens, odd block count, rows
+// too long for the activations of 8 tokens to stay resident beside two ring slots, unaligned W).
+static int launch_gemm_small(const void *W, const void *Xq, float *Y, int64_t n_out, int64_t n_in, int64_t n_tok,
+                             int32_t *dump, cudaStream_t st) {
+    if (n_tok < 1 || n_tok > 8 || !aligned16(W)) return -1;
+    MmaGeom mp;
+    int smem_bytes = 0, grid = 0;
+    if (!plan_mma(n_out, (int)(n_in / 128), 224, mp, smem_bytes, grid, true)) return -1;
+    static SmemOptIn opt, opt_dump;
+    const bool pdl = g_opt_pdl.load() != 0;
+    if (dump) {
+        cudaError_t err = opt_dump.ensure(gemm_mma_kernel<true>);
+        if (err != cudaSuccess) return (int)err;
+        return (int)launch(gemm_mma_kernel<true>, dim3((unsigned)grid), dim3(MMA_THREADS), (size_t)smem_bytes, st, false,
+                           static_cast<const uint8_t *>(W), static_cast<const uint32_t *>(Xq), Y, mp, (int)n_tok, dump);
+    }
+    cudaError_t err = opt.ensure(gemm_mma_kernel<false>);
+    if (err != cudaSuccess) return (int)err;
+    return (int)launch(gemm_mma_kernel<false>, dim3((unsigned)grid), dim3(MMA_THREADS), (size_t)smem_bytes, st, pdl,
+                       static_cast<const uint8_t *>(W), static_cast<const uint32_t *>(Xq), Y, mp, (int)n_tok, dump);
+}
+
 int bonsai_p40_gemm(const void *W, const void *Xq, float *Y, int64_t n_out, int64_t n_in, int64_t n_tok,
                     bonsai_stream stream) {
     if (n_in <= 0 || n_in % 128 != 0) return 1;
@@ -858,6 +881,10 @@ int bonsai_p40_gemm(const void *W, const void *Xq, float *Y, int64_t n_out, int6
     const int path = g_opt_gemm_path.load();
     const bool tensor = path == 1 || (path < 0 && n_tok >= 48);       // a 128-token tile needs tokens to fill it
     if (tensor) return launch_gemm_tc(W, Xq, Y, n_out, n_in, n_tok, nullptr, as_stream(stream));
+    if (path == 2 || (path < 0 && n_tok >= 2 && n_tok <= 8)) {        // a handful of tokens: weights streamed once for all of them
+        const int rc = launch_gemm_small(W, Xq, Y, n_out, n_in, n_tok, nullptr, as_stream(stream));
+        if (rc >= 0) return rc;                                       // -1: the shape does not fit, the kernel below takes it
+    }
     const dim3 grid((unsigned)((n_out + GS_ROWS - 1) / GS_ROWS), (unsigned)((n_tok + GS_TOKS - 1) / GS_TOKS));
     if (grid.y > 65535) return 1;
     gemm_simt_kernel<<<grid, 256, 0, as_stream(stream)>>>(static_cast<const uint8_t *>(W),
@@ -870,6 +897,10 @@ int bonsai_b200_gemm_dump(const void *W, const void *Xq, float *Y, int32_t *sums
                           int64_t n_tok, bonsai_stream stream) {
     if (n_in <= 0 || n_in % 128 != 0 || n_out <= 0 || n_tok <= 0 || !sums) return 1;
     if (n_out > INT32_MAX || n_tok > INT32_MAX || !aligned4(Xq)) return 1;
+    if (n_tok <= 8) {           // the streaming small-batch kernel, when it takes the shape
+        const int rc = launch_gemm_small(W, Xq, Y, n_out, n_in, n_tok, sums, as_stream(stream));
+        if (rc >= 0) return rc;
+    }
     return launch_gemm_tc(W, Xq, Y, n_out, n_in, n_tok, sums, as_stream(stream));
 }
 

@@ -156,7 +156,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) gemv_mma_kernel(const uint8_t 
                                                                  int32_t *__restrict__ dump) {
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t *full = reinterpret_cast<uint64_t *>(smem);       // [12] tile landed in slot
-    uint64_t *done = full + MMA_MAX_SLOTS;                      // [12] every pair of the slot's tile has stored its sums
+    uint64_t *done = full + MMA_MAX_SLOTS;                      // [12] every compute warp is through with the slot's tile
     uint64_t *freeb = done + MMA_MAX_SLOTS;                     // [12] the adder warp has read them: the slot may be refilled
     uint32_t *actw = reinterpret_cast<uint32_t *>(smem + 512);
     uint32_t *tab2 = actw + (size_t)P.nb * 4 * 8;
@@ -186,8 +186,6 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) gemv_mma_kernel(const uint8_t 
         const uint8_t *src = W + (size_t)16 * gi * row_bytes + (size_t)sb * W_BLOCK_BYTES;
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");       // the slot was read through ordinary loads
         if (lane == 0) {
-            const int missing = P.pairs_max - (sl >> 1);                    // pairs this tile does not have
-            if (missing > 0) mbar_arrive_n(&done[slot], (uint32_t)missing);
             if (P.contiguous) {
                 // a ragged last group of rows whose length is no multiple of 16 bytes (n_in / 128 not a multiple of
                 // 8): the last few bytes by plain loads, stored before the arrive that releases them to the waiters
@@ -207,7 +205,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) gemv_mma_kernel(const uint8_t 
     if (threadIdx.x == 0) {
         for (int s = 0; s < MMA_MAX_SLOTS; ++s) {
             mbar_init(&full[s], 1);
-            mbar_init(&done[s], (uint32_t)P.pairs_max);
+            mbar_init(&done[s], MMA_C);
             mbar_init(&freeb[s], 1);
         }
         mbar_fence_init();
@@ -245,36 +243,41 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) gemv_mma_kernel(const uint8_t 
             m[bl][0] = ((g >> 2) == bl && (g & 3) == (t >> 1)) ? 0xFFFFFFFFu : 0u;
             m[bl][1] = ((g >> 2) == bl && (g & 3) == 2 + (t >> 1)) ? 0xFFFFFFFFu : 0u;
         }
-        const int nitems = ntiles * P.pairs_max;
-        for (int item = wid; item < nitems; item += MMA_C) {
-            const int T = (int)fast_div((uint32_t)item, P.magic_pairs);
-            const int p = item - T * P.pairs_max;
+        // Every warp goes through EVERY tile in order: waits for it to land, works on the pairs that fall to it (pair p
+        // of tile T is item T * pairs_max + p, items go round-robin over the warps), then arrives on the tile's `done`
+        // barrier.  A slot's barriers are reused every nslot tiles and a phase is told from the one before only by its
+        // parity, so no warp may be two phases away when it asks; here none can: the slot is refilled only after all
+        // warps have arrived for its tile, and a warp arrives only after it has seen the tile land.
+        for (int T = 0; T < ntiles; ++T) {
             int gi, j;
             tile_of(T, gi, j);
             const int sb = mma_seg_start(P, j), sl = mma_seg_len(P, j);
-            if (p >= (sl >> 1)) continue;                       // the copy warp has arrived for the pairs a short segment lacks
             const int lap = (int)fast_div((uint32_t)T, P.magic_nslot);
             const int slot = T - lap * P.nslot;
             if (!mbar_wait_bounded(&full[slot], (uint32_t)(lap & 1))) break;
-            MmaPairB B;
-            mma_pair_setup(B, actw, tab2, (sb >> 1) + p, g, t, m);
-            float sum[2];
-            int J[4];
-            mma_pair_rows(ring + (size_t)slot * P.slot_bytes + (size_t)68 * p, P.stride, g, t, B, sum, J);
-            if (DUMP) {
-                const int chunk = 8 * ((sb >> 1) + p) + 2 * t;
-                const int r0 = 16 * gi + g, r1 = r0 + 8;
-                const size_t nch = (size_t)P.nb * 4;
-                if (r0 < P.n_out) { dump[r0 * nch + chunk] = J[0] >> 6; dump[r0 * nch + chunk + 1] = J[1] >> 6; }
-                if (r1 < P.n_out) { dump[r1 * nch + chunk] = J[2] >> 6; dump[r1 * nch + chunk + 1] = J[3] >> 6; }
-            }
+            int p = wid - (int)((unsigned)(T * P.pairs_max) % (unsigned)MMA_C);
+            if (p < 0) p += MMA_C;
+            for (; p < (sl >> 1); p += MMA_C) {
+                MmaPairB B;
+                mma_pair_setup(B, actw, tab2, (sb >> 1) + p, g, t, m);
+                float sum[2];
+                int J[4];
+                mma_pair_rows(ring + (size_t)slot * P.slot_bytes + (size_t)68 * p, P.stride, g, t, B, sum, J);
+                if (DUMP) {
+                    const int chunk = 8 * ((sb >> 1) + p) + 2 * t;
+                    const int r0 = 16 * gi + g, r1 = r0 + 8;
+                    const size_t nch = (size_t)P.nb * 4;
+                    if (r0 < P.n_out) { dump[r0 * nch + chunk] = J[0] >> 6; dump[r0 * nch + chunk + 1] = J[1] >> 6; }
+                    if (r1 < P.n_out) { dump[r1 * nch + chunk] = J[2] >> 6; dump[r1 * nch + chunk + 1] = J[3] >> 6; }
+                }
 #pragma unroll
-            for (int k = 0; k < 2; ++k) {
-                sum[k] = __fadd_rn(sum[k], __shfl_xor_sync(0xffffffffu, sum[k], 1));
-                sum[k] = __fadd_rn(sum[k], __shfl_xor_sync(0xffffffffu, sum[k], 2));
+                for (int k = 0; k < 2; ++k) {
+                    sum[k] = __fadd_rn(sum[k], __shfl_xor_sync(0xffffffffu, sum[k], 1));
+                    sum[k] = __fadd_rn(sum[k], __shfl_xor_sync(0xffffffffu, sum[k], 2));
+                }
+                float *ps = pairsum + ((size_t)slot * P.pairs_max + p) * 16;
+                if (t == 0) { ps[g] = sum[0]; ps[g + 8] = sum[1]; }
             }
-            float *ps = pairsum + ((size_t)slot * P.pairs_max + p) * 16;
-            if (t == 0) { ps[g] = sum[0]; ps[g + 8] = sum[1]; }
             __syncwarp();
             if (lane == 0) mbar_arrive(&done[slot]);            // release: the loads of the slot and the sums above are complete
         }
@@ -307,6 +310,219 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) gemv_mma_kernel(const uint8_t 
                     *ga = s;
                 }
                 if (j == P.nseg - 1 && row < P.n_out) y[row] = s;
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&freeb[slot]);
+        }
+    }
+}
+
+// ---- small token batches (2 .. 8 tokens): the same ring, the eight accumulator columns given to the tokens ----------
+// Replaces gemm_pq2_0_p40_kernel (src/kernels/gemm_p40.cu:44-139) for the token counts between the mat-vec and a
+// tensor-core tile -- the band the reference names as missing (docs/MTP.md:58): weights are streamed ONCE for all
+// tokens.  One instruction = 16 rows x one 32-weight chunk x 8 tokens: A = the chunk's codes extracted to bytes (field t
+// of the chunk's two code words for lane t of 4: the permuted order of src/pq2_0.h:158-166, so activation words t and
+// 4 + t are the matching B rows), C starts at -s (the activation sum), so D is the host's int32 sumi
+// (src/pq2_0.h:149-169) bit for bit.  Terms (dw * da) * (float)sumi as on the host, added in ascending chunk order
+// inside a quarter of a row segment, quarters and segments in ascending order.
+// Shared memory: int8 activation words [chunk][token 0..7][8] and the Q8_1 header words [chunk][token]; tokens past
+// n_tok are zero.  Xq is the chunk-major layout of bonsai_p40_gemm: block (chunk, tok) at chunk * n_tok + tok.
+constexpr int MMA_ITEMS = 4;          // items (quarters of a segment) per tile
+
+__host__ __device__ inline size_t mmab_fixed_bytes(const MmaGeom &P, int nslot) {
+    const size_t b = 512 + (size_t)P.nb * 4 * 288 + (size_t)nslot * MMA_ITEMS * 512 + MMA_GROUP_RING * 512;
+    return (b + 127) & ~(size_t)127;
+}
+
+template <bool DUMP>
+__global__ void __launch_bounds__(MMA_THREADS, 1) gemm_mma_kernel(const uint8_t *__restrict__ W, const uint32_t *__restrict__ Xq,
+                                                                 float *__restrict__ Y, const MmaGeom P, const int n_tok,
+                                                                 int32_t *__restrict__ dump) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem);
+    uint64_t *done = full + MMA_MAX_SLOTS;
+    uint64_t *freeb = done + MMA_MAX_SLOTS;
+    uint32_t *actb = reinterpret_cast<uint32_t *>(smem + 512);                 // [chunk][tok][8]
+    uint32_t *hdr = actb + (size_t)P.nb * 4 * 64;                              // [chunk][tok]
+    float *itemsum = reinterpret_cast<float *>(hdr + (size_t)P.nb * 4 * 8);   // [slot][item][row 16][tok 8]
+    float *gacc = itemsum + (size_t)P.nslot * MMA_ITEMS * 128;
+    uint8_t *ring = smem + mmab_fixed_bytes(P, P.nslot);
+
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int my_groups = ((int)blockIdx.x < P.ngroups) ? (P.ngroups - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+    const int ntiles = my_groups * P.nseg;
+    const size_t row_bytes = (size_t)P.nb * W_BLOCK_BYTES;
+    const uint64_t pol = policy_evict_first();
+    const int ppi = (P.pairs_max + MMA_ITEMS - 1) / MMA_ITEMS;                 // pairs per item
+
+    auto tile_of = [&](int T, int &gi, int &j) {
+        const int k = (int)fast_div((uint32_t)T, P.magic_nseg);
+        j = T - k * P.nseg;
+        gi = (int)blockIdx.x + k * (int)gridDim.x;
+    };
+    auto issue_tile = [&](int T) {          // whole copy warp
+        int gi, j;
+        tile_of(T, gi, j);
+        const int slot = T - (int)fast_div((uint32_t)T, P.magic_nslot) * P.nslot;
+        const int r_cnt = min(16, P.n_out - 16 * gi);
+        const int sb = mma_seg_start(P, j), sl = mma_seg_len(P, j);
+        uint8_t *dst = ring + (size_t)slot * P.slot_bytes;
+        const uint8_t *src = W + (size_t)16 * gi * row_bytes + (size_t)sb * W_BLOCK_BYTES;
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        if (lane == 0) {
+            if (P.contiguous) {
+                const uint32_t bytes = (uint32_t)(r_cnt * row_bytes), bulk = bytes & ~15u;
+                for (uint32_t o = bulk; o < bytes; o += 4) *reinterpret_cast<uint32_t *>(dst + o) = ldg_nc_u32(src + o);
+                mbar_expect_tx(&full[slot], bulk);
+                if (bulk) bulk_g2s(dst, src, bulk, &full[slot], pol);
+            } else {
+                mbar_expect_tx(&full[slot], (uint32_t)((size_t)r_cnt * sl * W_BLOCK_BYTES));
+            }
+        }
+        __syncwarp();
+        if (!P.contiguous && lane < r_cnt)
+            bulk_g2s(dst + (size_t)lane * P.stride, src + (size_t)lane * row_bytes, (uint32_t)(sl * W_BLOCK_BYTES), &full[slot], pol);
+    };
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < MMA_MAX_SLOTS; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&done[s], MMA_C);
+            mbar_init(&freeb[s], 1);
+        }
+        mbar_fence_init();
+    }
+    __syncthreads();
+    const int first_fill = min(P.nslot, ntiles);
+    if (wid == MMA_C)
+        for (int T = 0; T < min(2, first_fill); ++T) issue_tile(T);
+    pdl_launch_dependents();
+    pdl_wait_prior_grid();
+    {
+        const int total = P.nb * 4 * 8;                 // (chunk, token slot)
+        for (int i = threadIdx.x; i < total; i += MMA_THREADS) {
+            const int chunk = i >> 3, tok = i & 7;
+            uint32_t v[9];
+#pragma unroll
+            for (int w = 0; w < 9; ++w) v[w] = tok < n_tok ? __ldg(Xq + 9 * ((size_t)chunk * n_tok + tok) + w) : 0u;
+            *reinterpret_cast<uint4 *>(actb + (size_t)i * 8) = make_uint4(v[1], v[2], v[3], v[4]);
+            *reinterpret_cast<uint4 *>(actb + (size_t)i * 8 + 4) = make_uint4(v[5], v[6], v[7], v[8]);
+            hdr[i] = v[0];
+        }
+        if (wid == MMA_C)
+            for (int T = 2; T < first_fill; ++T) issue_tile(T);
+    }
+    __syncthreads();
+
+    if (wid < MMA_C) {
+        const int g = lane >> 2, t = lane & 3;
+        const size_t nch = (size_t)P.nb * 4;
+        // every warp goes through every tile in order (see gemv_mma_kernel); item k of tile T is item T * 4 + k
+        for (int T = 0; T < ntiles; ++T) {
+            int gi, j;
+            tile_of(T, gi, j);
+            const int sb = mma_seg_start(P, j), sl = mma_seg_len(P, j);
+            const int lap = (int)fast_div((uint32_t)T, P.magic_nslot);
+            const int slot = T - lap * P.nslot;
+            if (!mbar_wait_bounded(&full[slot], (uint32_t)(lap & 1))) break;
+            int k = wid - (int)((unsigned)(T * MMA_ITEMS) % (unsigned)MMA_C);
+            if (k < 0) k += MMA_C;
+            for (; k < MMA_ITEMS; k += MMA_C) {
+                const int p_lo = k * ppi, p_hi = min((k + 1) * ppi, sl >> 1);
+                if (p_lo >= p_hi) continue;                     // a short segment has fewer items; the adder skips them too
+                float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                for (int p = p_lo; p < p_hi; ++p) {
+                    const uint8_t *r0 = ring + (size_t)slot * P.slot_bytes + (size_t)68 * p + (size_t)g * P.stride;
+                    const uint8_t *r1 = r0 + 8 * (size_t)P.stride;
+                    const uint32_t *p0 = reinterpret_cast<const uint32_t *>(r0), *p1 = reinterpret_cast<const uint32_t *>(r1);
+                    uint32_t e0[17], e1[17];                        // the pair's 17 words of rows g and g + 8
+    #pragma unroll
+                    for (int i = 0; i < 17; ++i) { e0[i] = p0[i]; e1[i] = p1[i]; }
+    #pragma unroll
+                    for (int bl = 0; bl < 2; ++bl) {
+                        const float dw0 = f16_bits_to_f32(bl ? (e0[8] >> 16) : (e0[0] & 0xFFFFu));
+                        const float dw1 = f16_bits_to_f32(bl ? (e1[8] >> 16) : (e1[0] & 0xFFFFu));
+    #pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            uint32_t w[4];                          // row g word 0, row g + 8 word 0, row g word 1, row g + 8 word 1
+                            if (bl == 0) {                          // codes start two bytes into word 0
+                                w[0] = __funnelshift_r(e0[2 * c], e0[2 * c + 1], 16);
+                                w[1] = __funnelshift_r(e1[2 * c], e1[2 * c + 1], 16);
+                                w[2] = __funnelshift_r(e0[2 * c + 1], e0[2 * c + 2], 16);
+                                w[3] = __funnelshift_r(e1[2 * c + 1], e1[2 * c + 2], 16);
+                            } else {                                // word-aligned from word 9 on
+                                w[0] = e0[9 + 2 * c]; w[1] = e1[9 + 2 * c]; w[2] = e0[10 + 2 * c]; w[3] = e1[10 + 2 * c];
+                            }
+                            uint32_t a[4];
+    #pragma unroll
+                            for (int i = 0; i < 4; ++i) a[i] = (w[i] >> (2 * t)) & 0x03030303u;
+                            const int ci = 4 * (sb + 2 * p + bl) + c;
+                            const uint32_t *ab = actb + ((size_t)ci * 8 + g) * 8;
+                            const uint2 hh = *reinterpret_cast<const uint2 *>(hdr + (size_t)ci * 8 + 2 * t);
+                            const int cin[4] = {-(int)(short)(hh.x >> 16), -(int)(short)(hh.y >> 16), -(int)(short)(hh.x >> 16),
+                                                -(int)(short)(hh.y >> 16)};
+                            int d[4];
+                            mma_u8s8(d, a, ab[t], ab[4 + t], cin);
+                            const float da0 = f16_bits_to_f32(hh.x & 0xFFFFu), da1 = f16_bits_to_f32(hh.y & 0xFFFFu);
+                            acc[0] = __fadd_rn(acc[0], __fmul_rn(__fmul_rn(dw0, da0), (float)d[0]));
+                            acc[1] = __fadd_rn(acc[1], __fmul_rn(__fmul_rn(dw0, da1), (float)d[1]));
+                            acc[2] = __fadd_rn(acc[2], __fmul_rn(__fmul_rn(dw1, da0), (float)d[2]));
+                            acc[3] = __fadd_rn(acc[3], __fmul_rn(__fmul_rn(dw1, da1), (float)d[3]));
+                            if (DUMP) {
+                                const int ra = 16 * gi + g, rb = ra + 8, ta = 2 * t, tb = ta + 1;
+                                if (ra < P.n_out && ta < n_tok) dump[((size_t)ra * n_tok + ta) * nch + ci] = d[0];
+                                if (ra < P.n_out && tb < n_tok) dump[((size_t)ra * n_tok + tb) * nch + ci] = d[1];
+                                if (rb < P.n_out && ta < n_tok) dump[((size_t)rb * n_tok + ta) * nch + ci] = d[2];
+                                if (rb < P.n_out && tb < n_tok) dump[((size_t)rb * n_tok + tb) * nch + ci] = d[3];
+                            }
+                        }
+                    }
+                }
+                float *is = itemsum + ((size_t)slot * MMA_ITEMS + k) * 128;
+                *reinterpret_cast<float2 *>(is + g * 8 + 2 * t) = make_float2(acc[0], acc[1]);
+                *reinterpret_cast<float2 *>(is + (g + 8) * 8 + 2 * t) = make_float2(acc[2], acc[3]);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&done[slot]);
+        }
+    } else if (wid == MMA_C) {
+        for (int T = first_fill; T < ntiles; ++T) {
+            const int lap = (int)fast_div((uint32_t)T, P.magic_nslot);
+            const int slot = T - lap * P.nslot;
+            if (!mbar_wait_bounded(&freeb[slot], (uint32_t)((lap - 1) & 1))) return;
+            issue_tile(T);
+        }
+    } else {
+        // adder warp: lane l owns outputs (row l / 2, tokens 4 * (l % 2) .. + 3) of the tile
+        for (int T = 0; T < ntiles; ++T) {
+            int gi, j;
+            tile_of(T, gi, j);
+            const int lap = (int)fast_div((uint32_t)T, P.magic_nslot);
+            const int slot = T - lap * P.nslot;
+            if (!mbar_wait_bounded(&done[slot], (uint32_t)(lap & 1))) return;
+            const int items = ((mma_seg_len(P, j) >> 1) + ppi - 1) / ppi;
+            const float *is = itemsum + (size_t)slot * MMA_ITEMS * 128 + 4 * lane;
+            float4 s = *reinterpret_cast<const float4 *>(is);
+            for (int k = 1; k < items; ++k) {
+                const float4 v = *reinterpret_cast<const float4 *>(is + k * 128);
+                s.x = __fadd_rn(s.x, v.x); s.y = __fadd_rn(s.y, v.y); s.z = __fadd_rn(s.z, v.z); s.w = __fadd_rn(s.w, v.w);
+            }
+            if (P.nseg > 1) {
+                float4 *ga = reinterpret_cast<float4 *>(gacc + ((T / P.nseg) & (MMA_GROUP_RING - 1)) * 128) + lane;
+                if (j > 0) {
+                    const float4 o = *ga;
+                    s.x = __fadd_rn(o.x, s.x); s.y = __fadd_rn(o.y, s.y); s.z = __fadd_rn(o.z, s.z); s.w = __fadd_rn(o.w, s.w);
+                }
+                *ga = s;
+            }
+            if (j == P.nseg - 1) {
+                const int row = 16 * gi + (lane >> 1), tok0 = 4 * (lane & 1);
+                if (row < P.n_out) {
+                    const float out[4] = {s.x, s.y, s.z, s.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e)
+                        if (tok0 + e < n_tok) Y[(size_t)row * n_tok + tok0 + e] = out[e];
+                }
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&freeb[slot]);

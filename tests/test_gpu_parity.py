@@ -432,6 +432,8 @@ def test_row_partition_assembles_full_result(gpu, port, n_in, n_out, n_tok):
                 assert gpu.gemv(Wd[b0:b1], xqd, y[lo:hi], hi - lo, n_in) == 0
         assert_close_and_exact(host(y), want)
     else:
+        # batch 8 takes the streaming small-batch kernel: within the bound of the host loop, and the slices give the
+        # bits of the unsplit call (a row's sum does not depend on where the row sits)
         Xq = port.quantize_batch_chunk_major(X)
         want = port.gemm(W, Xq, n_out, n_in, n_tok, threads=8)
         Xqd = dev(Xq)
@@ -440,7 +442,10 @@ def test_row_partition_assembles_full_result(gpu, port, n_in, n_out, n_tok):
             lo, hi = partition.row_slice(n_out, r, 8)
             b0, b1 = partition.byte_slice(n_out, n_in, r, 8)
             assert gpu.gemm(Wd[b0:b1], Xqd, Y[lo:hi], hi - lo, n_in, n_tok) == 0
-        assert_close_and_exact(host(Y), want)
+        assert_close(host(Y), want)
+        Yu = torch.zeros(n_out, n_tok, device="cuda")
+        assert gpu.gemm(Wd, Xqd, Yu, n_out, n_in, n_tok) == 0
+        assert np.array_equal(bits(host(Y)), bits(host(Yu)))
 
 
 @pytest.mark.parametrize("n_out,n_in,n_tok", [(128, 128, 64), (64, 256, 5), (300, 5120, 100), (1024, 5120, 512), (200, 17408, 130),
@@ -477,9 +482,11 @@ def _chunk_ints(port, W, Xq, n_out, n_in, n_tok, rows, toks):
 
 
 @pytest.mark.parametrize("n_out,n_in,n_tok", [(128, 128, 64), (64, 256, 5), (300, 1024, 100), (256, 5120, 128), (129, 384, 65),
-                                              (6400, 256, 384), (19072, 256, 130)])
+                                              (6400, 256, 384), (19072, 256, 130), (203, 5120, 8), (100, 17408, 8),
+                                              (37, 1024, 2), (1500, 6144, 3), (130, 2304, 7), (33, 8192, 8)])
 def test_gemm_tensor_core_ints_and_bound(gpu, port, n_out, n_in, n_tok):
-    """tcgen05 kernel (gemm_path 1): the int32 the tensor core produced for every (row, token, chunk) -- written out
+    """The two tensor-core mat-muls -- tcgen05 for token batches (gemm_path 1), mma.sync with the weights streamed once
+    for 2 .. 8 tokens (gemm_path 2) -- : the int32 the tensor core produced for every (row, token, chunk) -- written out
     by bonsai_b200_gemm_dump -- equals the host loop's integer bit for bit on sampled rows and tokens, and Y is
     within 1e-5 of max |Y| of the host loop (fp32 side: fused multiply-adds per block, see csrc/gemm_tc.cuh); the
     plain entry point gives the same Y bits as the dumping one.  Full tiles, ragged rows and tokens, odd block
@@ -503,7 +510,7 @@ def test_gemm_tensor_core_ints_and_bound(gpu, port, n_out, n_in, n_tok):
     assert not (host(sums) == -12345).any()          # every (row, token, chunk) was produced
     Y2 = torch.full((n_out, n_tok), 555.0, dtype=torch.float32, device="cuda")
     try:
-        assert gpu.set_option("gemm_path", 1) == 0
+        assert gpu.set_option("gemm_path", 2 if n_tok <= 8 else 1) == 0
         assert gpu.gemm(Wd, Xqd, Y2, n_out, n_in, n_tok) == 0
         torch.cuda.synchronize()
     finally:
@@ -513,11 +520,12 @@ def test_gemm_tensor_core_ints_and_bound(gpu, port, n_out, n_in, n_tok):
 
 
 def test_gemm_default_dispatch(gpu, port):
-    """By token count: few tokens take the kernel that keeps the host's bits, a prefill batch the tensor cores."""
+    """By token count: one token, and 9 .. 47, take the kernel that keeps the host's bits; 2 .. 8 the streaming
+    small-batch kernel; a prefill batch the tcgen05 kernel."""
     import torch
     n_out, n_in = 256, 1024
     W = synth.pq2_0_weights(n_out, n_in, seed=9)
-    for n_tok, exact in ((8, True), (512, False)):
+    for n_tok, exact in ((1, True), (8, False), (20, True), (512, False)):
         X = synth.activations(n_in, seed=n_tok, batch=n_tok)
         Xq = port.quantize_batch_chunk_major(X)
         Y = torch.zeros((n_out, n_tok), dtype=torch.float32, device="cuda")
@@ -532,7 +540,11 @@ def test_gemm_default_dispatch(gpu, port):
 def test_gemm_golden(gpu, golden):
     import torch
     Y = torch.zeros((16, 5), dtype=torch.float32, device="cuda")
-    assert gpu.gemm(dev(golden["Wg"]), dev(golden["Xq"]), Y, 16, 256, 5) == 0
+    try:
+        assert gpu.set_option("gemm_path", 0) == 0          # the kernel that keeps the host loop's bits
+        assert gpu.gemm(dev(golden["Wg"]), dev(golden["Xq"]), Y, 16, 256, 5) == 0
+    finally:
+        gpu.set_option("gemm_path", -1)
     assert np.array_equal(bits(host(Y)).reshape(-1), golden["gemm_Y"].reshape(-1))
 
 
