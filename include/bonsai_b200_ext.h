@@ -203,6 +203,11 @@ int bonsai_b200_chain_create_tp(const bonsai_b200_op *ops, int64_t n_ops, int ra
  * slots, bytes per slot, CTAs): for benchmarks and tests. */
 int bonsai_b200_chain_info(const bonsai_b200_chain *chain, int64_t out[4]);
 
+/* Device pointers of the K and V arrays of a cache made by bonsai_kv_create (include/bonsai_kv.h) and the size of
+ * each: lets a test read the Q8_0 bytes back.  No counterpart in the reference, whose cache object is opaque. */
+struct bonsai_kv_cache;
+int bonsai_b200_kv_arrays(struct bonsai_kv_cache *kv, void **k, void **v, int64_t *bytes_each);
+
 /* Version of this build as major * 100 + minor. */
 int bonsai_b200_version(void);
 

@@ -421,3 +421,75 @@ void bo_attn(const float *q, const float *k, const float *v, float *out, int n_t
     free(acc);
 }
 
+/* ---- K/V cache numeric core ---------------------------------------------------------------------
+ * Q8_0 rows as src/kv_cache.h:100-117 (d = amax / 127, lroundf, clamp, fp16 scale by bo_f32_to_f16); block score as
+ * src/kv_cache.h:129-145; attention of one query position over positions 0..pos of one layer, every query head, as the
+ * recurrence of src/kernels/kv_p40.cu:178-199 (one position at a time, online softmax) on the cache layout of
+ * src/kv_cache.h:81-84: block[((layer * n_kv + kvh) * capacity + pos) * 8 + blk], 34-byte blocks. */
+void bo_kv_quantize_row_q8_0(const float *x, uint8_t *y, int n) {
+    for (int b = 0; b < n / 32; ++b) {
+        const float *src = x + b * 32;
+        uint8_t *blk = y + b * 34;
+        float amax = 0.0f;
+        for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(src[i]));
+        const float d = amax / 127.0f;
+        const float id = d > 0.0f ? 1.0f / d : 0.0f;
+        const uint16_t dh = bo_f32_to_f16(d);
+        memcpy(blk, &dh, 2);
+        for (int i = 0; i < 32; ++i) {
+            int v = (int)lroundf(src[i] * id);
+            if (v < -127) v = -127;
+            if (v > 127) v = 127;
+            blk[2 + i] = (uint8_t)(int8_t)v;
+        }
+    }
+}
+
+void bo_kv_dequantize_row_q8_0(const uint8_t *x, float *y, int n) {
+    for (int b = 0; b < n / 32; ++b) {
+        uint16_t dh;
+        memcpy(&dh, x + b * 34, 2);
+        const float d = bo_f16_to_f32(dh);
+        for (int i = 0; i < 32; ++i) y[b * 32 + i] = (float)(int8_t)x[b * 34 + 2 + i] * d;
+    }
+}
+
+float bo_kv_score(const uint8_t *q, const uint8_t *k, int nblocks) {
+    float acc = 0.0f;
+    for (int b = 0; b < nblocks; ++b) {
+        int sumi = 0;
+        for (int i = 0; i < 32; ++i) sumi += (int)(int8_t)q[b * 34 + 2 + i] * (int)(int8_t)k[b * 34 + 2 + i];
+        uint16_t dq, dk;
+        memcpy(&dq, q + b * 34, 2);
+        memcpy(&dk, k + b * 34, 2);
+        acc += bo_f16_to_f32(dq) * bo_f16_to_f32(dk) * (float)sumi;
+    }
+    return acc;
+}
+
+/* K, V: whole cache arrays; q, out: [n_head][256]. */
+void bo_kv_attn_decode(const uint8_t *K, const uint8_t *V, const float *q, float *out, int capacity, int layer, int pos,
+                       int n_head, int n_kv_head, float scale) {
+    const int D = 256, nblk = 8;
+    uint8_t q8[8 * 34];
+    float vrow[256], acc[256];
+    for (int head = 0; head < n_head; ++head) {
+        const int kvh = head / (n_head / n_kv_head);
+        bo_kv_quantize_row_q8_0(q + (size_t)head * D, q8, D);
+        const size_t base = ((size_t)layer * n_kv_head + kvh) * (size_t)capacity;
+        float m = -INFINITY, l = 0.0f;
+        for (int d = 0; d < D; ++d) acc[d] = 0.0f;
+        for (int p = 0; p <= pos; ++p) {
+            const uint8_t *kb = K + (base + p) * nblk * 34, *vb = V + (base + p) * nblk * 34;
+            const float s = bo_kv_score(q8, kb, nblk) * scale;
+            const float m_new = fmaxf(m, s);
+            const float alpha = expf(m - m_new), pw = expf(s - m_new);
+            l = l * alpha + pw;
+            bo_kv_dequantize_row_q8_0(vb, vrow, D);
+            for (int d = 0; d < D; ++d) acc[d] = acc[d] * alpha + pw * vrow[d];
+            m = m_new;
+        }
+        for (int d = 0; d < D; ++d) out[(size_t)head * D + d] = acc[d] / l;
+    }
+}
+

@@ -45,10 +45,11 @@ def build_reference(reference=DEFAULT_REFERENCE, force=False):
     if not os.path.isfile(os.path.join(inc, "pq2_0.h")):
         return REF_SO if os.path.exists(REF_SO) else None
     src = os.path.join(HERE, "ref_shim.cpp")
-    deps = [src] + [os.path.join(inc, h) for h in ("pq2_0.h", "fwht.h", "pq2_0_repack.h", "p40_common.h", "ops.h")]
+    deps = [src] + [os.path.join(inc, h) for h in ("pq2_0.h", "fwht.h", "pq2_0_repack.h", "p40_common.h", "ops.h", "kv_cache.h")]
     if force or _stale(REF_SO, deps):
         os.makedirs(REF_DIR, exist_ok=True)
-        subprocess.check_call(["g++", "-std=c++17", *FP_FLAGS, "-I", inc, "-o", REF_SO, src, "-lpthread"])
+        subprocess.check_call(["g++", "-std=c++17", *FP_FLAGS, "-I", inc, "-I", os.path.join(reference, "include"), "-o", REF_SO, src,
+                               "-lpthread"])
     return REF_SO
 
 

@@ -61,7 +61,15 @@ class Oracle:
         f("rmsnorm", None, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_float])
         f("swiglu", None, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64])
         f("gdn_step", None, [C.c_void_p] * 7 + [C.c_int] * 4)
+        f("kv_quantize_row_q8_0", None, [C.c_void_p, C.c_void_p, C.c_int])
+        f("kv_dequantize_row_q8_0", None, [C.c_void_p, C.c_void_p, C.c_int])
+        f("kv_score", C.c_float, [C.c_void_p, C.c_void_p, C.c_int])
+        if kind == "reference":
+            f("kv_block_index", C.c_int64, [C.c_int] * 5)
+            f("kv_total_bytes", C.c_int64, [C.c_int])
+            f("kv_gdn_bytes", C.c_int64, [])
         if kind == "port":
+            f("kv_attn_decode", None, [C.c_void_p] * 4 + [C.c_int] * 5 + [C.c_float])
             f("attn", None, [C.c_void_p] * 4 + [C.c_int] * 4 + [C.c_float])
             f("chunk_sumi", C.c_int32, [C.c_void_p, C.c_void_p, C.c_int])
             f("row_chunk_sums", None, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p])
@@ -212,3 +220,30 @@ class Oracle:
         out = np.zeros(n_tok * n_head * D, dtype=np.float32)
         self._attn(_p(a[0]), _p(a[1]), _p(a[2]), _p(out), n_tok, n_head, n_head_kv, D, float(scale))
         return out
+
+    # ---- K/V cache --------------------------------------------------------------------------------------
+    def kv_quantize_row(self, x):
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        out = np.zeros(x.size // 32 * 34, dtype=np.uint8)
+        self._kv_quantize_row_q8_0(_p(x), _p(out), x.size)
+        return out
+
+    def kv_dequantize_row(self, blocks):
+        blocks = np.ascontiguousarray(blocks, dtype=np.uint8)
+        y = np.zeros(blocks.size // 34 * 32, dtype=np.float32)
+        self._kv_dequantize_row_q8_0(_p(blocks), _p(y), y.size)
+        return y
+
+    def kv_score(self, q8, k8):
+        q8 = np.ascontiguousarray(q8, dtype=np.uint8)
+        k8 = np.ascontiguousarray(k8, dtype=np.uint8)
+        return np.float32(self._kv_score(_p(q8), _p(k8), q8.size // 34))
+
+    def kv_attn_decode(self, K, V, q, capacity, layer, pos, n_head=24, n_kv_head=4, scale=0.0625):
+        K = np.ascontiguousarray(K, dtype=np.uint8)
+        V = np.ascontiguousarray(V, dtype=np.uint8)
+        q = np.ascontiguousarray(q, dtype=np.float32)
+        out = np.zeros(n_head * 256, dtype=np.float32)
+        self._kv_attn_decode(_p(K), _p(V), _p(q), _p(out), capacity, layer, pos, n_head, n_kv_head, float(scale))
+        return out
+

@@ -9,6 +9,7 @@
 // Compiled with g++ (never nvcc), so the headers take their non-CUDA branches: software
 // f32_to_f16 / f16_to_f32 and the dp4a emulation.
 #include "fwht.h"
+#include "kv_cache.h"
 #include "ops.h"
 #include "pq2_0.h"
 #include "pq2_0_repack.h"
@@ -112,5 +113,16 @@ void ref_gdn_step(float *state, const float *q, const float *k, const float *v, 
                  out + (size_t)vh * V, K, V);
     }
 }
+
+// ---- K/V cache numeric core (src/kv_cache.h) -------------------------------------------------------------------
+static_assert(sizeof(block_q8_0) == 34, "Q8_0 block is 34 bytes");
+void ref_kv_quantize_row_q8_0(const float *x, void *y, int n) { kv_quantize_row_q8_0(x, (block_q8_0 *)y, n); }
+void ref_kv_dequantize_row_q8_0(const void *x, float *y, int n) { kv_dequantize_row_q8_0((const block_q8_0 *)x, y, n); }
+float ref_kv_score(const void *q, const void *k, int nblocks) { return kv_score((const block_q8_0 *)q, (const block_q8_0 *)k, nblocks); }
+int64_t ref_kv_block_index(int capacity, int layer, int kv_head, int pos, int blk) {
+    return kv_geometry::for_27b(capacity).block_index(layer, kv_head, pos, blk);
+}
+int64_t ref_kv_total_bytes(int capacity) { return kv_geometry::for_27b(capacity).total_bytes(); }
+int64_t ref_kv_gdn_bytes() { return gdn_state_bytes(); }
 
 }  // extern "C"

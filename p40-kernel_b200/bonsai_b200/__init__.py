@@ -48,6 +48,16 @@ SIGNATURES = {
     "bonsai_b200_chain_run": (_INT, [_VP, _VP]),
     "bonsai_b200_chain_destroy": (_INT, [_VP]),
     "bonsai_b200_chain_info": (_INT, [_VP, _VP]),
+    "bonsai_b200_kv_arrays": (_INT, [_VP, _VP, _VP, _VP]),
+    "bonsai_kv_bytes": (_I64, [_INT]),
+    "bonsai_kv_gdn_bytes": (_I64, []),
+    "bonsai_kv_create": (_VP, [_INT, _VP]),
+    "bonsai_kv_free": (None, [_VP]),
+    "bonsai_kv_reset": (None, [_VP, _VP]),
+    "bonsai_kv_append": (_INT, [_VP, _INT, _INT, _VP, _VP, _VP]),
+    "bonsai_kv_append_batch": (_INT, [_VP, _INT, _INT, _INT, _VP, _VP, _VP]),
+    "bonsai_kv_attn_decode": (_INT, [_VP, _INT, _INT, _VP, _VP, _VP]),
+    "bonsai_kv_gdn_state": (_VP, [_VP, _INT]),
     "bonsai_b200_set_option": (_INT, [C.c_char_p, _I64]),
     "bonsai_b200_device_status": (_INT, []),
     "bonsai_b200_clear_status": (_INT, []),
@@ -251,3 +261,49 @@ class Chain:
             self.close()
         except Exception:
             pass
+
+
+# ---- include/bonsai_kv.h ---------------------------------------------------------------------------------
+class KVCache:
+    """bonsai_kv_create / _free and the calls on the handle.  Geometry of the 27B model: 16 cached layers, 4 kv heads,
+    24 query heads, head dimension 256; 48 delta-net layers with [48][128][128] fp32 state."""
+    N_LAYERS, N_KV_HEADS, N_HEADS, HEAD_DIM = 16, 4, 24, 256
+
+    def __init__(self, capacity):
+        self._h = lib().bonsai_kv_create(int(capacity), _stream())
+        if not self._h:
+            raise RuntimeError("bonsai_kv_create failed")
+        self.capacity = capacity
+
+    def append(self, layer, pos, k, v):
+        return lib().bonsai_kv_append(self._h, layer, pos, _dev(k, "k"), _dev(v, "v"), _stream())
+
+    def append_batch(self, layer, pos0, n_tok, k, v):
+        return lib().bonsai_kv_append_batch(self._h, layer, pos0, n_tok, _dev(k, "k"), _dev(v, "v"), _stream())
+
+    def attn_decode(self, layer, pos, q, out):
+        return lib().bonsai_kv_attn_decode(self._h, layer, pos, _dev(q, "q"), _dev(out, "out"), _stream())
+
+    def gdn_state(self, layer):
+        return lib().bonsai_kv_gdn_state(self._h, layer)
+
+    def reset(self):
+        lib().bonsai_kv_reset(self._h, _stream())
+
+    def arrays(self):
+        """(K pointer, V pointer, bytes of each) on the device."""
+        k, v, n = C.c_void_p(), C.c_void_p(), C.c_int64()
+        assert lib().bonsai_b200_kv_arrays(self._h, C.byref(k), C.byref(v), C.byref(n)) == 0
+        return k.value, v.value, n.value
+
+    def close(self):
+        if self._h:
+            lib().bonsai_kv_free(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+

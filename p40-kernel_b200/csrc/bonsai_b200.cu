@@ -5,6 +5,7 @@
 // gemv_repack_p40.cu:196-220, elementwise_p40.cu:75-80): validate, compute a grid, launch on the
 // caller's stream, return cudaGetLastError().  No allocation, no synchronisation, no CPU fallback.
 #include "../../include/bonsai_b200_ext.h"
+#include "../../include/bonsai_kv.h"
 
 #include "activation.cuh"
 #include "gemm_simt.cuh"
@@ -13,6 +14,7 @@
 #include "gemv_stream.cuh"
 #include "gemv_chain.cuh"
 #include "gemv_mma.cuh"
+#include "kv.cuh"
 #include "ops.cuh"
 #include "probe.cuh"
 #include "repack.cuh"
@@ -1072,6 +1074,105 @@ int bonsai_p40_attn(const float *q, const float *k, const float *v, float *out, 
     if (blocks > INT32_MAX) return 1;
     attn_kernel<<<(unsigned)blocks, ATT_WARPS * 32, 0, as_stream(stream)>>>(q, k, v, out, n_tok, n_head, n_head_kv, scale);
     return (int)cudaGetLastError();
+}
+
+// ---- K/V cache (reference: include/bonsai_kv.h, src/kernels/kv_p40.cu:247-367) ----------------------------------
+// Geometry of the 27B model (include/bonsai_model.h:29-52): 16 full-attention layers, 24 query / 4 kv heads of 256;
+// 48 linear-attention layers with 48 value heads of 128 x 128 state.
+namespace {
+constexpr int KVM_FULL = 16, KVM_HEADS = 24, KVM_KV_HEADS = 4, KVM_CONTEXT = 262144;
+constexpr int KVM_LINEAR = 48, KVM_V_HEADS = 48, KVM_STATE = 128;
+constexpr int KV_MAX_SPLIT = 64;
+constexpr size_t KV_SPLIT_SMEM = 128 + 4 * KV_TILE * KV_ROW + KV_TILE * KV_D * 4 + KV_MAX_GROUP * 64 * 4 + KV_MAX_GROUP * 8 * 4;
+inline int64_t kv_array_bytes(int capacity) { return (int64_t)KVM_FULL * KVM_KV_HEADS * capacity * KV_ROW; }
+inline int64_t kv_gdn_bytes() { return (int64_t)KVM_LINEAR * KVM_V_HEADS * KVM_STATE * KVM_STATE * (int64_t)sizeof(float); }
+}  // namespace
+
+struct bonsai_kv_cache {
+    int capacity = 0;
+    uint8_t *d_k = nullptr, *d_v = nullptr;
+    float *d_gdn = nullptr, *d_ws = nullptr;
+};
+
+int64_t bonsai_kv_bytes(int capacity) {
+    if (capacity <= 0) return 0;
+    if (capacity > KVM_CONTEXT) capacity = KVM_CONTEXT;
+    return 2 * kv_array_bytes(capacity);
+}
+int64_t bonsai_kv_gdn_bytes(void) { return kv_gdn_bytes(); }
+
+bonsai_kv_cache *bonsai_kv_create(int capacity, bonsai_stream stream) {
+    if (capacity <= 0) return nullptr;
+    if (capacity > KVM_CONTEXT) capacity = KVM_CONTEXT;
+    bonsai_kv_cache *kv = new (std::nothrow) bonsai_kv_cache;
+    if (!kv) return nullptr;
+    kv->capacity = capacity;
+    const size_t ws = (size_t)KVM_HEADS * KV_MAX_SPLIT * KV_WS * sizeof(float);
+    if (cudaMalloc(&kv->d_k, (size_t)kv_array_bytes(capacity)) != cudaSuccess || cudaMalloc(&kv->d_v, (size_t)kv_array_bytes(capacity)) != cudaSuccess ||
+        cudaMalloc(&kv->d_gdn, (size_t)kv_gdn_bytes()) != cudaSuccess || cudaMalloc(&kv->d_ws, ws) != cudaSuccess ||
+        cudaFuncSetAttribute(kv_attn_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)KV_SPLIT_SMEM) != cudaSuccess) {
+        bonsai_kv_free(kv);
+        return nullptr;
+    }
+    (void)cudaMemsetAsync(kv->d_gdn, 0, (size_t)kv_gdn_bytes(), as_stream(stream));
+    return kv;
+}
+
+void bonsai_kv_free(bonsai_kv_cache *kv) {
+    if (!kv) return;
+    cudaFree(kv->d_k);
+    cudaFree(kv->d_v);
+    cudaFree(kv->d_gdn);
+    cudaFree(kv->d_ws);
+    delete kv;
+}
+
+void bonsai_kv_reset(bonsai_kv_cache *kv, bonsai_stream stream) {
+    if (kv) (void)cudaMemsetAsync(kv->d_gdn, 0, (size_t)kv_gdn_bytes(), as_stream(stream));
+}
+
+float *bonsai_kv_gdn_state(bonsai_kv_cache *kv, int layer) {
+    if (!kv || layer < 0 || layer >= KVM_LINEAR) return nullptr;
+    return kv->d_gdn + (size_t)layer * KVM_V_HEADS * KVM_STATE * KVM_STATE;
+}
+
+int bonsai_kv_append_batch(bonsai_kv_cache *kv, int layer, int pos0, int n_tok, const float *k, const float *v,
+                           bonsai_stream stream) {
+    if (!kv || !k || !v) return 1;
+    if (layer < 0 || layer >= KVM_FULL) return 1;
+    if (n_tok <= 0 || pos0 < 0 || (long long)pos0 + n_tok > kv->capacity) return 1;
+    const int nrow = n_tok * KVM_KV_HEADS;
+    kv_append_kernel<<<(nrow + 7) / 8, 256, 0, as_stream(stream)>>>(kv->d_k, kv->d_v, k, v, pos0, n_tok, KVM_KV_HEADS, kv->capacity, layer);
+    return (int)cudaGetLastError();
+}
+
+int bonsai_kv_append(bonsai_kv_cache *kv, int layer, int pos, const float *k, const float *v, bonsai_stream stream) {
+    return bonsai_kv_append_batch(kv, layer, pos, 1, k, v, stream);
+}
+
+int bonsai_kv_attn_decode(bonsai_kv_cache *kv, int layer, int pos, const float *q, float *out, bonsai_stream stream) {
+    if (!kv || !q || !out) return 1;
+    if (layer < 0 || layer >= KVM_FULL) return 1;
+    if (pos < 0 || pos >= kv->capacity) return 1;
+    // splits of at least 8 tiles each; at long context 64 splits x 4 kv heads = 256 CTAs of 6 warps
+    int n_split = (pos + 1 + 8 * KV_TILE - 1) / (8 * KV_TILE);
+    if (n_split > KV_MAX_SPLIT) n_split = KV_MAX_SPLIT;
+    const int grp = KVM_HEADS / KVM_KV_HEADS;
+    kv_attn_split_kernel<<<dim3((unsigned)n_split, KVM_KV_HEADS), grp * 32, KV_SPLIT_SMEM, as_stream(stream)>>>(
+        q, kv->d_k, kv->d_v, kv->d_ws, pos, n_split, KVM_KV_HEADS, kv->capacity, layer, 0.0625f, grp);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return (int)e;
+    kv_attn_combine_kernel<<<KVM_HEADS, 32, 0, as_stream(stream)>>>(kv->d_ws, out, n_split);
+    return (int)cudaGetLastError();
+}
+
+// Test access to the cache arrays (byte parity of the quantiser): device pointers of K and V.
+int bonsai_b200_kv_arrays(bonsai_kv_cache *kv, void **k, void **v, int64_t *bytes_each) {
+    if (!kv || !k || !v || !bytes_each) return 1;
+    *k = kv->d_k;
+    *v = kv->d_v;
+    *bytes_each = kv_array_bytes(kv->capacity);
+    return 0;
 }
 
 }  // extern "C"

@@ -11,10 +11,10 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 def declared_symbols():
     names = set()
-    for h in ("bonsai_p40.h", "bonsai_b200_ext.h"):
+    for h in ("bonsai_p40.h", "bonsai_b200_ext.h", "bonsai_kv.h"):
         text = open(os.path.join(ROOT, "include", h)).read()
         text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-        names |= set(re.findall(r"\bint\s+(bonsai_\w+)\s*\(", text))
+        names |= set(re.findall(r"\b(?:int|int64_t|void|float \*|bonsai_kv_cache \*)\s*(bonsai_\w+)\s*\(", text))
     return names
 
 

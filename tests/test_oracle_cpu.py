@@ -180,3 +180,55 @@ def test_port_f32_to_f16_equals_reference_dense(port, ref):
     vals = rng.integers(0, 2 ** 32, size=20000, dtype=np.uint64).astype(np.uint32).view(np.float32)
     for v in vals:
         assert port.f32_to_f16(v) == ref.f32_to_f16(v)
+
+
+def test_port_ops_equal_reference(port, ref):
+    """RMSNorm, SwiGLU and the delta-net step of the C restatement against the reference's src/ops.h, bit for bit."""
+    rng = np.random.default_rng(11)
+    x = rng.uniform(-2, 2, size=(3, 5120)).astype(np.float32)
+    w = rng.uniform(0, 2, size=5120).astype(np.float32)
+    assert np.array_equal(port.rmsnorm(x, w, 1e-6).view(np.uint32), ref.rmsnorm(x, w, 1e-6).view(np.uint32))
+    g = rng.uniform(-4, 4, size=17408).astype(np.float32)
+    u = rng.uniform(-2, 2, size=17408).astype(np.float32)
+    assert np.array_equal(port.swiglu(g, u).view(np.uint32), ref.swiglu(g, u).view(np.uint32))
+    S = (rng.uniform(-1, 1, size=(8, 128, 128)) * 0.1).astype(np.float32)
+    q, k = rng.uniform(-1, 1, size=(2, 4, 128)).astype(np.float32)
+    v = rng.uniform(-1, 1, size=(8, 128)).astype(np.float32)
+    gg = (-rng.uniform(0.1, 1, size=8)).astype(np.float32)
+    b = rng.uniform(0.1, 1, size=8).astype(np.float32)
+    a, c = port.gdn_step(S, q, k, v, gg, b, 4, 8, 128, 128), ref.gdn_step(S, q, k, v, gg, b, 4, 8, 128, 128)
+    assert np.array_equal(a[0].view(np.uint32), c[0].view(np.uint32)) and np.array_equal(a[1].view(np.uint32), c[1].view(np.uint32))
+
+
+def test_port_kv_core_equals_reference(port, ref):
+    """Q8_0 row quantiser, dequantiser and block score of src/kv_cache.h:100-145, bit for bit; exact ties and zeros."""
+    rng = np.random.default_rng(12)
+    x = (rng.standard_normal(4096) * 5).astype(np.float32)
+    x[:32] = 0.0
+    x[32:64] = np.arange(32, dtype=np.float32) + 0.5          # amax 31.5: many exact .5 ties after scaling
+    a, b = port.kv_quantize_row(x), ref.kv_quantize_row(x)
+    assert np.array_equal(a, b)
+    assert np.array_equal(port.kv_dequantize_row(a).view(np.uint32), ref.kv_dequantize_row(a).view(np.uint32))
+    for i in range(0, 16):
+        qa, ka = a[i * 272:(i + 1) * 272], a[(15 - i) * 272:(16 - i) * 272]
+        assert port.kv_score(qa, ka).view(np.uint32) == ref.kv_score(qa, ka).view(np.uint32)
+
+
+def test_attention_recurrence_matches_full_softmax(port):
+    """The online-softmax recurrence of the checker against a double-precision full softmax (the reference's own test of
+    the recurrence, tests/test_p40.cpp:264-309, uses 1e-4)."""
+    rng = np.random.default_rng(13)
+    n_tok, n_head, n_kv, D = 33, 6, 2, 256
+    q = rng.uniform(-1, 1, size=(n_tok, n_head, D)).astype(np.float32)
+    k = rng.uniform(-1, 1, size=(n_tok, n_kv, D)).astype(np.float32)
+    v = rng.uniform(-1, 1, size=(n_tok, n_kv, D)).astype(np.float32)
+    scale = 1.0 / 16.0
+    got = port.attn(q, k, v, n_tok, n_head, n_kv, D, scale).reshape(n_tok, n_head, D)
+    for qi in (0, 7, 32):
+        for h in (0, 5):
+            kvh = h // (n_head // n_kv)
+            s = (k[:qi + 1, kvh].astype(np.float64) @ q[qi, h].astype(np.float64)) * scale
+            p = np.exp(s - s.max())
+            want = (p[:, None] * v[:qi + 1, kvh].astype(np.float64)).sum(0) / p.sum()
+            assert float(np.abs(got[qi, h] - want).max()) < 1e-5
+
