@@ -83,6 +83,16 @@ int bonsai_b200_gemv_dump(const void *W, const void *xq, float *y, int32_t *sums
 int bonsai_b200_gemm_dump(const void *W, const void *Xq, float *Y, int32_t *sums, int64_t n_out, int64_t n_in,
                           int64_t n_tok, bonsai_stream stream);
 
+/* PTQ1_0: the denser packing of the same ternary weights, 28 bytes per 128 weights instead of 34 (described, not
+ * implemented, by the reference: docs/NEXT_STEPS.md:76-83).  Block = qs[24] (five base-3 digits per byte, weights
+ * 0..119), qh[2] (four digits per byte, weights 120..127), fp16 d; digit = PQ2_0 code 0, 1, 2; weight j < 120 is digit
+ * j % 5 of byte j / 5, least significant first.  pack converts n_blocks PQ2_0 blocks (src, 34 bytes each) to PTQ1_0
+ * (dst, 28 bytes each) and ADDS to *code3_count (device memory, 8-byte aligned, zeroed by the caller) the number of
+ * weights whose code is 3 (+2, not representable; stored as +1): the conversion is lossless exactly when the count
+ * stays 0.  unpack converts back to PQ2_0 blocks that the mat-vec / mat-mul entry points read.  Load-time steps. */
+int bonsai_b200_ptq1_pack(const void *src, void *dst, int64_t n_blocks, uint64_t *code3_count, bonsai_stream stream);
+int bonsai_b200_ptq1_unpack(const void *src, void *dst, int64_t n_blocks, bonsai_stream stream);
+
 /* Synthetic PQ2_0 weights written on the device: n_blocks blocks whose codes are drawn per
  * element from {0,1,2} with p = {0.33,0.34,0.33} plus code 3 at p = 0.001, and whose fp16
  * scale is |z| * 0.02 with z approximately standard normal.  Counter-based: block i of a

@@ -23,6 +23,35 @@ def _p(a):
     return a.ctypes.data_as(C.c_void_p)
 
 
+def ptq1_pack(pq2):
+    """PQ2_0 blocks (34 bytes) -> PTQ1_0 blocks (28 bytes: qs[24] five base-3 digits per byte, qh[2] four digits per
+    byte, fp16 d), the packing the reference describes in docs/NEXT_STEPS.md:76-83; digit order: weight j < 120 is digit
+    j % 5 of byte j / 5, least significant first.  Returns (bytes, number of weights with code 3, stored as code 2)."""
+    b = np.ascontiguousarray(pq2, dtype=np.uint8).reshape(-1, W_BYTES)
+    codes = np.stack([(b[:, 2:] >> f) & 3 for f in (0, 2, 4, 6)], axis=2).reshape(b.shape[0], 128).astype(np.int64)
+    bad = int((codes == 3).sum())
+    codes = np.minimum(codes, 2)
+    out = np.zeros((b.shape[0], 28), dtype=np.uint8)
+    out[:, :24] = (codes[:, :120].reshape(-1, 24, 5) * (3 ** np.arange(5))).sum(2)
+    out[:, 24:26] = (codes[:, 120:].reshape(-1, 2, 4) * (3 ** np.arange(4))).sum(2)
+    out[:, 26:28] = b[:, 0:2]
+    return out.reshape(-1), bad
+
+
+def ptq1_unpack(ptq):
+    p = np.ascontiguousarray(ptq, dtype=np.uint8).reshape(-1, 28).astype(np.int64)
+    codes = np.zeros((p.shape[0], 128), dtype=np.int64)
+    for k in range(5):
+        codes[:, k:120:5] = (p[:, :24] // 3 ** k) % 3
+    for k in range(4):
+        codes[:, 120 + k::4] = (p[:, 24:26] // 3 ** k) % 3
+    out = np.zeros((p.shape[0], W_BYTES), dtype=np.uint8)
+    out[:, 0:2] = p[:, 26:28]
+    c = codes.reshape(-1, 32, 4)
+    out[:, 2:] = c[:, :, 0] | (c[:, :, 1] << 2) | (c[:, :, 2] << 4) | (c[:, :, 3] << 6)
+    return out.reshape(-1)
+
+
 def reference_available():
     return os.path.exists(REF_SO)
 

@@ -17,6 +17,7 @@
 #include "kv.cuh"
 #include "ops.cuh"
 #include "probe.cuh"
+#include "ptq.cuh"
 #include "repack.cuh"
 #include "synth.cuh"
 
@@ -953,6 +954,28 @@ int bonsai_p40_gemv_repack(const void *W, const float *x, float *y, int64_t n_ou
         else e = go(gemv_repack_kernel<4, false>, opt[5]);
     }
     return (int)e;
+}
+
+int bonsai_b200_ptq1_pack(const void *src, void *dst, int64_t n_blocks, uint64_t *code3_count, bonsai_stream stream) {
+    if (n_blocks <= 0) return n_blocks == 0 ? 0 : 1;
+    if ((reinterpret_cast<uintptr_t>(src) & 1u) || (reinterpret_cast<uintptr_t>(dst) & 1u) || !code3_count ||
+        (reinterpret_cast<uintptr_t>(code3_count) & 7u))
+        return 1;
+    long long blocks = (n_blocks + 255) / 256;
+    if (blocks > 16 * SM_COUNT) blocks = 16 * SM_COUNT;
+    ptq1_pack_kernel<<<(unsigned)blocks, 256, 0, as_stream(stream)>>>(static_cast<const uint8_t *>(src), static_cast<uint8_t *>(dst),
+                                                                      n_blocks, reinterpret_cast<unsigned long long *>(code3_count));
+    return (int)cudaGetLastError();
+}
+
+int bonsai_b200_ptq1_unpack(const void *src, void *dst, int64_t n_blocks, bonsai_stream stream) {
+    if (n_blocks <= 0) return n_blocks == 0 ? 0 : 1;
+    if ((reinterpret_cast<uintptr_t>(src) & 1u) || (reinterpret_cast<uintptr_t>(dst) & 1u)) return 1;
+    long long blocks = (n_blocks + 255) / 256;
+    if (blocks > 16 * SM_COUNT) blocks = 16 * SM_COUNT;
+    ptq1_unpack_kernel<<<(unsigned)blocks, 256, 0, as_stream(stream)>>>(static_cast<const uint8_t *>(src), static_cast<uint8_t *>(dst),
+                                                                        n_blocks);
+    return (int)cudaGetLastError();
 }
 
 int bonsai_b200_synth_pq2_0(void *W, int64_t first_block, int64_t n_blocks, uint64_t seed, bonsai_stream stream) {
