@@ -111,7 +111,9 @@ int bonsai_b200_stream_probe(const void *buf, int64_t bytes, int mode, void *sin
  * key "gemv_order": 0 (default) = the streaming mat-vec, whose fp32 terms equal the host's bit for
  * bit and are added in a fixed tree order (outputs within 1e-5 of the host's, identical from launch
  * to launch); 1 = the mat-vec that also adds them in the host's sequential order (outputs
- * bit-identical to src/pq2_0.h:183-191, slower).
+ * bit-identical to src/pq2_0.h:183-191, slower); 2 = the mat-vec whose integer products run on mma.sync
+ * (csrc/gemv_mma.cuh: same terms, another fixed tree; measured slower than 0 at batch 1, kept as the measured
+ * alternative and as the body of the 2 .. 8 token kernel).
  * key "gemm_path": -1 (default) = the mat-mul picks its kernel by token count (2 .. 8 tokens: the streaming
  * small-batch kernel; 48 tokens and more: tcgen05; else the integer SIMT kernel), 0 = integer SIMT kernel (Y
  * bit-identical to the host loop), 1 = tcgen05 tensor-core kernel, 2 = the small-batch kernel where it takes the
@@ -120,7 +122,10 @@ int bonsai_b200_stream_probe(const void *buf, int64_t bytes, int mode, void *sin
  * key "fuse_linear": 0 (default) = bonsai_b200_linear is two launches, 1 = one kernel when it can (saves a
  * launch, but every CTA then waits for its own rotation before its first multiply: measured ~6 % slower
  * on the 401-projection decode chain).
- * key "gemv_variant": -1 = automatic, otherwise a tuning index used by the benchmark sweep.
+ * Options are process-wide: set them once at start-up, not from threads that call the library concurrently.
+ * A library compiled with -DBONSAI_B200_TUNING (the test build) also takes geometry keys ("gemv_variant",
+ * "chain_threads", "chain_seg", "chain_tile_kb", "chain_spread_nb") that force a tiling; they change no result bits
+ * beyond what the documented options say and are not part of the interface.
  * Returns 0, or 1 for an unknown key. */
 int bonsai_b200_set_option(const char *key, int64_t value);
 

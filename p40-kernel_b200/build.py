@@ -38,10 +38,12 @@ def stale():
     return any(os.path.getmtime(s) > t for s in sources())
 
 
-def build(force=False, verbose=False):
+def build(force=False, verbose=False, tuning=True):
+    """tuning: compile the geometry knobs of bonsai_b200_set_option in (the parity tests force every tiling through
+    them); a production build passes tuning=False (--no-tuning) and keeps only the documented options."""
     if not (force or stale()):
         return LIB
-    cmd = [NVCC, *FLAGS, "-o", LIB, os.path.join(CSRC, "bonsai_b200.cu")]
+    cmd = [NVCC, *FLAGS, *(["-DBONSAI_B200_TUNING"] if tuning else []), "-o", LIB, os.path.join(CSRC, "bonsai_b200.cu")]
     if verbose:
         cmd[1:1] = ["-Xptxas", "-v"]
     subprocess.check_call(cmd)
@@ -52,6 +54,7 @@ if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true", help="print ptxas register / shared-memory usage")
+    ap.add_argument("--no-tuning", action="store_true", help="leave the test-only geometry knobs out of the library")
     a = ap.parse_args()
-    print(build(a.force, a.verbose))
+    print(build(a.force or a.no_tuning, a.verbose, not a.no_tuning))
     sys.exit(0)

@@ -1010,7 +1010,6 @@ int bonsai_b200_stream_probe(const void *buf, int64_t bytes, int mode, void *sin
 int bonsai_b200_set_option(const char *key, int64_t value) {
     if (!key) return 1;
     if (!std::strcmp(key, "pdl")) { g_opt_pdl.store(value != 0); return 0; }
-    if (!std::strcmp(key, "gemv_variant")) { g_opt_gemv_variant.store((int)value); return 0; }
     if (!std::strcmp(key, "gemv_order")) {
         if (value < 0 || value > 2) return 1;
         g_opt_gemv_order.store((int)value);
@@ -1018,6 +1017,10 @@ int bonsai_b200_set_option(const char *key, int64_t value) {
     }
     if (!std::strcmp(key, "gemm_path")) { g_opt_gemm_path.store((int)value); return 0; }
     if (!std::strcmp(key, "fuse_linear")) { g_opt_fuse_linear.store(value != 0); return 0; }
+#ifdef BONSAI_B200_TUNING
+    // Geometry knobs of the test build (build.py --tuning, the default of this repository's build script): they let the
+    // parity tests force every tiling.  A build without the macro has no such keys and always uses the tuned defaults.
+    if (!std::strcmp(key, "gemv_variant")) { g_opt_gemv_variant.store((int)value); return 0; }
     if (!std::strcmp(key, "chain_threads")) {
         if (value != 512 && value != 640 && value != 768) return 1;
         g_opt_chain_threads.store((int)value);
@@ -1038,6 +1041,7 @@ int bonsai_b200_set_option(const char *key, int64_t value) {
         g_opt_chain_tile_kb.store((int)value);
         return 0;
     }
+#endif
     return 1;
 }
 

@@ -7,17 +7,19 @@
 // fold it into fp32 registers.  The integers are exact: weights are expanded to signed bytes code - 1, so one MMA
 // gives sum(code * a) - sum(a) of the chunk, the very int32 of the host loop (tests/test_p40.cpp:460-467,
 // src/pq2_0.h:149-169).  The fp32 side uses the tolerance the path states (1e-5 of max |Y|) to spend two
-// instructions per output and chunk instead of five: per pair of chunks  s = da0*v0 + da1*v1  by fused
+// instructions per output and chunk instead of five: per block  s = da0*v0 + da1*v1 + da2*v2 + da3*v3  by fused
 // multiply-adds, then  acc += dw * s  -- the host computes (dw*da_c)*v_c term by term; same sums, other roundings.
 // (The integer SIMT kernel, gemm_simt.cuh, keeps the host's bits; bonsai_b200_set_option("gemm_path", 0).)
 //
-// CTA tile: 128 weight rows x 128 tokens, one CTA per SM (it owns the SM's 512 TMEM columns: 4 stages x 128), K
-// stepped one weight block (4 chunks = 4 MMAs of M 128 x N 128 x K 32) at a time:
+// CTA tile: 128 weight rows x 64 tokens, one CTA per SM (it owns the SM's 512 TMEM columns: 8 stages x 64, i.e. the
+// chunk results of two whole weight blocks are in flight, so the tensor core runs ahead of the epilogue and its
+// round trip -- issue, MMA, commit, barrier -- never shows; with 128-token tiles, 4 stages, it cost 1.6 us per block),
+// K stepped one weight block (4 chunks = 4 MMAs of M 128 x N 64 x K 32) at a time:
 //   warps 0-15  : epilogue; warp w owns TMEM lanes 32 * (w % 4) .. (one weight row per thread) and tokens
-//                 32 * (w / 4) .. + 31: 32 accumulators per thread, block sums 16 tokens at a time
+//                 16 * (w / 4) .. + 15: 16 accumulators + 16 block sums per thread
 //   warps 16-19 : producers; thread p expands the 2-bit codes of row p of the block to int8 (code - 1) in the
 //                 K-major core-matrix layout the MMA reads (8 rows x 16 bytes per core matrix) and copies the int8
-//                 activations and the scale of token p for the block's four chunks
+//                 activations and the scale of token p (p < 64) for the block's four chunks
 //   warp 20     : one thread issues the MMAs and commits them to mbarriers; the warp owns the TMEM allocation
 //   warp 21     : (TMA form) bulk async copies of the raw bytes into shared memory, two buffers each: the weight
 //                 rows 8 blocks (272 bytes, a 16-byte multiple) at a time, the Q8_1 blocks of the tile's tokens one
@@ -42,17 +44,18 @@
 
 namespace b200 {
 
-constexpr int TC_M = 128, TC_N = 128;
-constexpr int TC_STAGES = 2;                               // shared-memory stages (one weight block each)
+constexpr int TC_M = 128, TC_N = 64;
+constexpr int TC_TMEM_STAGES = 8;                          // chunk results in flight in tensor memory: 8 x 64 columns = two whole blocks
+constexpr int TC_STAGES = 3;                               // shared-memory stages (one weight block each)
 constexpr int TC_XBUFS = 4;                                // raw Q8_1 buffers in flight (TMA form): bulk copies take ~1 us to land
 constexpr int TC_A_BYTES = 4 * TC_M * 32;                  // 4 chunks x 128 rows x 32 bytes
-constexpr int TC_B_BYTES = 4 * TC_N * 32;
+constexpr int TC_B_BYTES = 4 * TC_N * 32;                  // 4 chunks x 64 tokens x 32 bytes
 constexpr int TC_STAGE_BYTES = TC_A_BYTES + TC_B_BYTES + TC_M * 4 + 4 * TC_N * 4;
 constexpr int TC_EPI_WARPS = 16, TC_PROD_WARPS = 4;
 constexpr int TC_EPI_THREADS = TC_EPI_WARPS * 32, TC_PROD_THREADS = TC_PROD_WARPS * 32;
 constexpr int TC_THREADS = TC_EPI_THREADS + TC_PROD_THREADS + 64;       // + issuer warp + loader warp
 constexpr int TC_WRAW_BYTES = TC_M * 272;                  // raw PQ2_0 bytes of 8 consecutive blocks of 128 rows
-constexpr int TC_XRAW_BYTES = 4 * TC_N * A_BLOCK_BYTES;    // raw Q8_1 blocks of 4 chunks x 128 tokens
+constexpr int TC_XRAW_BYTES = 4 * TC_N * A_BLOCK_BYTES;    // raw Q8_1 blocks of 4 chunks x 64 tokens
 constexpr int TC_SMEM_BYTES = 1024 + TC_STAGES * TC_STAGE_BYTES;
 constexpr int TC_SMEM_BYTES_TMA = TC_SMEM_BYTES + 2 * TC_WRAW_BYTES + TC_XBUFS * TC_XRAW_BYTES;
 constexpr int TC_FLAG_SETS = 8, TC_MAX_CTAS = 256;
@@ -164,9 +167,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const uint8_t *_
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t *full = reinterpret_cast<uint64_t *>(smem);               // [4] producers -> issuer
     uint64_t *released = full + TC_STAGES;                              // [4] tensor core + epilogue -> producers
-    uint64_t *mma_done = released + TC_STAGES;                          // [4] tensor core -> epilogue (one per chunk of a block)
-    uint64_t *tmem_empty = mma_done + 4;                                // [4] epilogue -> issuer
-    uint64_t *wfull = tmem_empty + 4;                                   // [2] loader -> producers: 8 blocks of weight rows landed
+    uint64_t *mma_done = released + TC_STAGES;                          // [8] tensor core -> epilogue (one per chunk result in flight)
+    uint64_t *tmem_empty = mma_done + TC_TMEM_STAGES;                   // [8] epilogue -> issuer
+    uint64_t *wfull = tmem_empty + TC_TMEM_STAGES;                                   // [2] loader -> producers: 8 blocks of weight rows landed
     uint64_t *wfree = wfull + 2;                                        // [2] producers -> loader
     uint64_t *xfull = wfree + 2;                                        // [4] loader -> producers: a block's Q8_1 blocks landed
     uint64_t *xfree = xfull + TC_XBUFS;                                 // [4] producers -> loader
@@ -180,7 +183,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const uint8_t *_
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < TC_STAGES; ++s) { mbar_init(&full[s], TC_PROD_THREADS); mbar_init(&released[s], 1 + TC_EPI_WARPS); }
-        for (int s = 0; s < 4; ++s) { mbar_init(&mma_done[s], 1); mbar_init(&tmem_empty[s], TC_EPI_WARPS); }
+        for (int s = 0; s < TC_TMEM_STAGES; ++s) { mbar_init(&mma_done[s], 1); mbar_init(&tmem_empty[s], TC_EPI_WARPS); }
         for (int s = 0; s < 2; ++s) { mbar_init(&wfull[s], 1); mbar_init(&wfree[s], TC_PROD_THREADS); }
         for (int s = 0; s < TC_XBUFS; ++s) { mbar_init(&xfull[s], 1); mbar_init(&xfree[s], TC_PROD_THREADS); }
         mbar_fence_init();
@@ -199,7 +202,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const uint8_t *_
     int tile, kb0, kb1;
 
     if (wid < TC_EPI_WARPS) {
-        // ---------------- epilogue: one weight row per thread, 32 tokens ----------------
+        // ---------------- epilogue: one weight row per thread, 16 tokens ----------------
         const int q = wid & 3, cg = wid >> 2;
         const int row_l = 32 * q + lane;
         unsigned int *flags = g_gemm_flags[P.epoch & (TC_FLAG_SETS - 1)];
@@ -207,76 +210,58 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const uint8_t *_
         int n = 0;                              // weight blocks consumed by this CTA so far
         while (ok && walk.next(P, tile, kb0, kb1)) {
             const int rt = tile / P.tiles_tok, tt = tile - rt * P.tiles_tok;
-            const int row = rt * TC_M + row_l, tokb = tt * TC_N + 32 * cg;
-            float acc[32];
+            const int row = rt * TC_M + row_l, tokb = tt * TC_N + 16 * cg;
+            float acc[16];
 #pragma unroll
-            for (int j = 0; j < 32; ++j) acc[j] = 0.0f;
+            for (int j = 0; j < 16; ++j) acc[j] = 0.0f;
+            const uint32_t tlane = tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(16 * cg);
             for (int kb = kb0; kb < kb1 && ok; ++kb, ++n) {
                 const int s = n % TC_STAGES;
                 const TcStage st = tc_stage(stages, s);
-                // The block's four chunks are folded in as two pairs, each pair in two passes of 16 tokens (32 accumulators
-                // + 16 pair sums live): a pair's tensor-memory columns are released as soon as its second pass has them in
-                // registers, i.e. in the middle of the block, so the tensor core works on the next block's first pair
-                // while this block's second pair is folded in.  (Held to the end of the block, every block would wait
-                // for the round trip issue -> MMA -> commit: measured 1.8 us per block whatever the epilogue did.)
-                // A pass is four loads of 8 columns; the next load is in flight while the current one is folded in.
+                // Chunk c of block n lives in tensor-memory stage (4 n + c) % 8: the tensor core works up to two blocks
+                // ahead of this loop, so the round trip issue -> MMA -> commit never shows.  The load of the next chunk is
+                // in flight while the current one is folded in.
+                const int m0 = 4 * n;
+                float accb[16];
+                int v[2][16];
+                if (!mbar_wait_hot(&mma_done[m0 & 7], (uint32_t)((m0 >> 3) & 1))) { ok = false; break; }
+                tc_fence_after();
+                tc_ld16(tlane + (uint32_t)((m0 & 7) * TC_N), v[0]);
 #pragma unroll
-                for (int pr = 0; pr < 2; ++pr) {
-#pragma unroll
-                    for (int h = 0; h < 2; ++h) {
-                        float accb[16];
-                        int v[2][8];
-                        const uint32_t tbase = tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(32 * cg + 16 * h);
-                        if (h == 0) {
-                            if (!mbar_wait_hot(&mma_done[2 * pr], (uint32_t)(n & 1))) { ok = false; break; }
-                            tc_fence_after();
-                        }
-                        tc_ld8(tbase + (uint32_t)(2 * pr * TC_N), v[0]);
-#pragma unroll
-                        for (int k = 0; k < 4; ++k) {
-                            const int cc = k >> 1, q8 = k & 1, c = 2 * pr + cc;
-                            tc_ld_wait();
-                            if (h == 1 && q8 == 1) {    // all of this chunk is in registers: the tensor core may overwrite it
-                                tc_fence_before();
-                                __syncwarp();
-                                if (lane == 0) mbar_arrive(&tmem_empty[c]);
-                            }
-                            if (k < 3) {
-                                const int cn = 2 * pr + ((k + 1) >> 1);
-                                if (h == 0 && q8 == 1) {
-                                    if (!mbar_wait_hot(&mma_done[cn], (uint32_t)(n & 1))) { ok = false; break; }
-                                    tc_fence_after();
-                                }
-                                tc_ld8(tbase + (uint32_t)(cn * TC_N + 8 * ((k + 1) & 1)), v[(k + 1) & 1]);
-                            }
-                            const float4 *da4 = reinterpret_cast<const float4 *>(st.da + c * TC_N + 32 * cg + 16 * h + 8 * q8);
-#pragma unroll
-                            for (int g4 = 0; g4 < 2; ++g4) {
-                                const float4 d = da4[g4];
-                                const float dd[4] = {d.x, d.y, d.z, d.w};
-#pragma unroll
-                                for (int e = 0; e < 4; ++e) {
-                                    const int jj = 8 * q8 + 4 * g4 + e;
-                                    const float f = (float)v[k & 1][4 * g4 + e];
-                                    accb[jj] = (cc == 0) ? __fmul_rn(dd[e], f) : __fmaf_rn(dd[e], f, accb[jj]);
-                                }
-                            }
-                            if (DUMP && row < n_out) {
-#pragma unroll
-                                for (int e = 0; e < 8; ++e) {
-                                    const int tok = tokb + 16 * h + 8 * q8 + e;
-                                    if (tok < n_tok) dump[((size_t)row * n_tok + tok) * (4 * (size_t)nblocks) + 4 * kb + c] = v[k & 1][e];
-                                }
-                            }
-                        }
-                        if (!ok) break;
-                        const float dw = st.dw[row_l];          // written by the producers: read behind the waits above
-#pragma unroll
-                        for (int jj = 0; jj < 16; ++jj) acc[16 * h + jj] = __fmaf_rn(dw, accb[jj], acc[16 * h + jj]);
+                for (int c = 0; c < 4; ++c) {
+                    const int m = m0 + c;
+                    tc_ld_wait();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&tmem_empty[m & 7]);     // chunk c is in registers: its columns may be overwritten
+                    if (c < 3) {
+                        if (!mbar_wait_hot(&mma_done[(m + 1) & 7], (uint32_t)(((m + 1) >> 3) & 1))) { ok = false; break; }
+                        tc_fence_after();
+                        tc_ld16(tlane + (uint32_t)(((m + 1) & 7) * TC_N), v[(c + 1) & 1]);
                     }
-                    if (!ok) break;
+                    const float4 *da4 = reinterpret_cast<const float4 *>(st.da + c * TC_N + 16 * cg);
+#pragma unroll
+                    for (int g4 = 0; g4 < 4; ++g4) {
+                        const float4 d = da4[g4];
+                        const float dd[4] = {d.x, d.y, d.z, d.w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float f = (float)v[c & 1][4 * g4 + e];
+                            accb[4 * g4 + e] = (c == 0) ? __fmul_rn(dd[e], f) : __fmaf_rn(dd[e], f, accb[4 * g4 + e]);
+                        }
+                    }
+                    if (DUMP && row < n_out) {
+#pragma unroll
+                        for (int e = 0; e < 16; ++e) {
+                            const int tok = tokb + e;
+                            if (tok < n_tok) dump[((size_t)row * n_tok + tok) * (4 * (size_t)nblocks) + 4 * kb + c] = v[c & 1][e];
+                        }
+                    }
                 }
                 if (!ok) break;
+                const float dw = st.dw[row_l];          // written by the producers: read behind the waits above
+#pragma unroll
+                for (int j = 0; j < 16; ++j) acc[j] = __fmaf_rn(dw, accb[j], acc[j]);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&released[s]);          // the scale tables of this stage are free
             }
@@ -306,18 +291,18 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const uint8_t *_
                 tc_epi_barrier();
                 if (row < n_out) {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j)
+                    for (int j = 0; j < 16; ++j)
                         if (tokb + j < n_tok) acc[j] = __fadd_rn(acc[j], __ldcg(yrow + j));
                 }
             }
             if (row < n_out) {
                 if (vec) {
 #pragma unroll
-                    for (int j = 0; j < 32; j += 4)
+                    for (int j = 0; j < 16; j += 4)
                         if (tokb + j < n_tok) *reinterpret_cast<float4 *>(yrow + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
                 } else {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j)
+                    for (int j = 0; j < 16; ++j)
                         if (tokb + j < n_tok) yrow[j] = acc[j];
                 }
             }
@@ -336,8 +321,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const uint8_t *_
         while (ok && walk.next(P, tile, kb0, kb1)) {
             const int rt = tile / P.tiles_tok, tt = tile - rt * P.tiles_tok;
             const int row = min(rt * TC_M + p, n_out - 1);      // rows past the end repeat the last one (never stored)
-            const int tok = tt * TC_N + p;
-            const bool tok_ok = tok < n_tok;
+            const int tok = tt * TC_N + p;                      // threads 0..63 also lay out one token each
+            const bool tok_mine = p < TC_N, tok_ok = tok_mine && tok < n_tok;
             const uint8_t *wrow = W + (size_t)row * nblocks * W_BLOCK_BYTES;
             for (int kb = kb0; kb < kb1; ++kb, ++n) {
                 const int s = n % TC_STAGES;
@@ -391,10 +376,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const uint8_t *_
                     uint8_t *ac = st.a + c * (TC_M * 32) + a_off;
                     *reinterpret_cast<uint4 *>(ac) = lo;             // bytes 0..15 of the chunk: first K core matrix
                     *reinterpret_cast<uint4 *>(ac + 128) = hi;       // bytes 16..31: second K core matrix
-                    uint8_t *bc = st.b + c * (TC_N * 32) + a_off;
-                    *reinterpret_cast<uint4 *>(bc) = make_uint4(av[c][1], av[c][2], av[c][3], av[c][4]);
-                    *reinterpret_cast<uint4 *>(bc + 128) = make_uint4(av[c][5], av[c][6], av[c][7], av[c][8]);
-                    st.da[c * TC_N + p] = f16_bits_to_f32(av[c][0] & 0xFFFFu);
+                    if (tok_mine) {
+                        uint8_t *bc = st.b + c * (TC_N * 32) + a_off;
+                        *reinterpret_cast<uint4 *>(bc) = make_uint4(av[c][1], av[c][2], av[c][3], av[c][4]);
+                        *reinterpret_cast<uint4 *>(bc + 128) = make_uint4(av[c][5], av[c][6], av[c][7], av[c][8]);
+                        st.da[c * TC_N + p] = f16_bits_to_f32(av[c][0] & 0xFFFFu);
+                    }
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");    // the tensor core reads through the async proxy
                 mbar_arrive(&full[s]);
@@ -452,11 +439,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const uint8_t *_
                 const TcStage st = tc_stage(stages, s);
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
-                    if (!mbar_wait_hot(&tmem_empty[c], (uint32_t)((n & 1) ^ 1))) { ok = false; break; }
+                    const int m = 4 * n + c, ts = m & (TC_TMEM_STAGES - 1);       // the chunk's stage of tensor memory
+                    if (!mbar_wait_hot(&tmem_empty[ts], (uint32_t)(((m >> 3) & 1) ^ 1))) { ok = false; break; }
                     tc_fence_after();
-                    tc_mma_i8(tmem_base + (uint32_t)(c * TC_N), tc_smem_desc(smem_u32(st.a + c * (TC_M * 32))),
+                    tc_mma_i8(tmem_base + (uint32_t)(ts * TC_N), tc_smem_desc(smem_u32(st.a + c * (TC_M * 32))),
                               tc_smem_desc(smem_u32(st.b + c * (TC_N * 32))));
-                    tc_commit(&mma_done[c]);
+                    tc_commit(&mma_done[ts]);
                 }
                 if (!ok) break;
                 tc_commit(&released[s]);        // arrives when the four MMAs above have read the stage

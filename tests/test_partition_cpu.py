@@ -60,3 +60,42 @@ def test_slices_cover_and_align():
             assert all(lo % 16 == 0 for lo, _ in edges)
     with pytest.raises(ValueError):
         partition.row_slice(10, 0, 4)
+
+
+def _ledger_worker(rank, world, port, skip_step, out_dir):
+    sys.path.insert(0, os.path.join(ROOT, "p40-kernel_b200"))
+    import json
+    from datetime import timedelta
+    import torch.distributed as dist
+    from bonsai_b200 import partition
+
+    store = dist.TCPStore("127.0.0.1", port, world, is_master=(rank == 0), timeout=timedelta(seconds=20))
+    ledger = partition.StepLedger(store, rank, world)
+    launched, seen_late = [], {}
+    for step in (1, 2, 3):
+        if rank == 1 and step == skip_step:
+            break                                   # this rank leaves between steps: it never announces `step`
+        ledger.announce(step)
+        late = ledger.laggards(step, timeout_s=0.5)
+        if late:
+            seen_late[step] = late
+            break                                   # do not launch: a peer is missing
+        launched.append(step)                       # stands for bonsai_b200_chain_run of this step
+    with open(os.path.join(out_dir, f"ledger{rank}.json"), "w") as f:
+        json.dump({"launched": launched, "late": seen_late}, f)
+    store.set(f"done/{rank}", "1")
+    if rank == 0:                                   # the store's owner stays until everybody has written
+        store.wait([f"done/{r}" for r in range(world)])
+
+
+def test_a_rank_that_skips_a_step_is_named_before_the_launch(tmp_path):
+    """Rank 1 of 2 leaves before step 2.  Rank 0 learns it on the host (no device wait is started), names rank 1 and
+    launches nothing further; both launched step 1."""
+    import json
+    import torch.multiprocessing as mp
+    tcp = 31500 + os.getpid() % 2000
+    mp.spawn(_ledger_worker, args=(2, tcp, 2, str(tmp_path)), nprocs=2, join=True)
+    r0 = json.load(open(tmp_path / "ledger0.json"))
+    r1 = json.load(open(tmp_path / "ledger1.json"))
+    assert r0["launched"] == [1] and r0["late"] == {"2": [1]}
+    assert r1["launched"] == [1] and r1["late"] == {}
