@@ -807,6 +807,31 @@ int bonsai_b200_gemv_dump(const void *W, const void *xq, float *y, int32_t *sums
                        false, static_cast<const uint8_t *>(W), static_cast<const uint32_t *>(xq), y, mp, sums);
 }
 
+// Tensor map of a PQ2_0 matrix seen as [n_out][row_bytes / 4] 32-bit words, box = 68 words (8 blocks) x 128 rows.
+// The encoder is a driver entry point; it is looked up through the runtime so that the library links against
+// nothing but cudart.  false: not available (the caller takes the form that needs no map).
+static bool encode_w_map(CUtensorMap *map, const void *W, int64_t n_out, int64_t row_bytes) {
+    using Encode = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static Encode encode = [] {
+        void *fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            fn = nullptr;
+        return reinterpret_cast<Encode>(fn);
+    }();
+    if (!encode) return false;
+    const cuuint64_t dims[2] = {(cuuint64_t)(row_bytes / 4), (cuuint64_t)n_out};
+    const cuuint64_t strides[1] = {(cuuint64_t)row_bytes};
+    const cuuint32_t box[2] = {68u, (cuuint32_t)TC_M};
+    const cuuint32_t estr[2] = {1u, 1u};
+    return encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void *>(W), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 // The tensor-core mat-mul: one CTA per SM walks its share of the (tile, weight block) iterations.
 static int launch_gemm_tc(const void *W, const void *Xq, float *Y, int64_t n_out, int64_t n_in, int64_t n_tok,
                           int32_t *dump, cudaStream_t st) {
@@ -842,13 +867,16 @@ static int launch_gemm_tc(const void *W, const void *Xq, float *Y, int64_t n_out
     const uint8_t *w8 = static_cast<const uint8_t *>(W);
     const uint32_t *x32 = static_cast<const uint32_t *>(Xq);
     // bulk-copy staging of the raw bytes needs 16-byte multiples everywhere; other shapes load from global memory
-    const bool tma = P.nblocks % 8 == 0 && n_tok % 4 == 0 && aligned16(W) && aligned16(Xq);
+    alignas(64) CUtensorMap wmap;
+    std::memset(&wmap, 0, sizeof(wmap));
+    const bool tma = P.nblocks % 8 == 0 && n_tok % 4 == 0 && aligned16(W) && aligned16(Xq) &&
+                     encode_w_map(&wmap, W, n_out, (int64_t)P.nblocks * W_BLOCK_BYTES);
     static SmemOptIn opt[4];
     auto go = [&](auto kernel, SmemOptIn &o, int smem) -> int {
         cudaError_t err = o.ensure(kernel);
         if (err != cudaSuccess) return (int)err;
         cfg.dynamicSmemBytes = (size_t)smem;
-        return (int)cudaLaunchKernelEx(&cfg, kernel, w8, x32, Y, P, dump);
+        return (int)cudaLaunchKernelEx(&cfg, kernel, w8, x32, Y, P, dump, wmap);
     };
     if (dump) return tma ? go(gemm_tc_kernel<true, true>, opt[0], TC_SMEM_BYTES_TMA) : go(gemm_tc_kernel<true, false>, opt[1], TC_SMEM_BYTES);
     return tma ? go(gemm_tc_kernel<false, true>, opt[2], TC_SMEM_BYTES_TMA) : go(gemm_tc_kernel<false, false>, opt[3], TC_SMEM_BYTES);
