@@ -122,13 +122,14 @@ class ClockSampler(threading.Thread):
 
 # ---- timing on the device ---------------------------------------------------------------------------
 def graph_of(torch, fn):
-    """Runs fn once eagerly (validates it, warms caches), then captures it; returns the replay function."""
-    fn()
-    torch.cuda.synchronize()
+    """Runs fn once eagerly on the capture stream (validates it, warms caches, lets the library allocate the scratch
+    it keeps per stream: nothing may be allocated during capture), then captures it; returns the replay function."""
     graph = torch.cuda.CUDAGraph()
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
     with torch.cuda.stream(side):
+        fn()
+        torch.cuda.synchronize()
         with torch.cuda.graph(graph, stream=side):
             fn()
     torch.cuda.current_stream().wait_stream(side)

@@ -10,6 +10,7 @@
 #include "activation.cuh"
 #include "gemm_simt.cuh"
 #include "gemm_tc.cuh"
+#include "gemm_tc16.cuh"
 #include "gemv.cuh"
 #include "gemv_stream.cuh"
 #include "gemv_chain.cuh"
@@ -23,6 +24,7 @@
 
 #include <atomic>
 #include <cstring>
+#include <mutex>
 #include <new>
 #include <vector>
 
@@ -42,7 +44,7 @@ std::atomic<int> g_opt_chain_spread_nb{64};      // dependent ops with at least 
                                                  // once for the grid instead of once per CTA; 0 = never
 std::atomic<int> g_opt_chain_tile_kb{16};
 std::atomic<int> g_opt_chain_seg{40};            // longest row segment of one task, in blocks: 8, 16, 24, 32 or 40        // target bytes of one ring slot
-std::atomic<int> g_opt_gemm_path{-1};          // -1: by token count, 0: integer SIMT kernel, 1: tensor-core kernel          // 0: streaming kernel (fixed tree order), 1: the host's sequential order
+std::atomic<int> g_opt_gemm_path{-1};          // -1: by token count, 0: integer SIMT kernel, 1: tensor cores, 2: small-batch kernel, 3: integer tensor-core kernel          // 0: streaming kernel (fixed tree order), 1: the host's sequential order
 
 inline cudaStream_t as_stream(bonsai_stream s) { return reinterpret_cast<cudaStream_t>(s); }
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -807,10 +809,11 @@ int bonsai_b200_gemv_dump(const void *W, const void *xq, float *y, int32_t *sums
                        false, static_cast<const uint8_t *>(W), static_cast<const uint32_t *>(xq), y, mp, sums);
 }
 
-// Tensor map of a PQ2_0 matrix seen as [n_out][row_bytes / 4] 32-bit words, box = 68 words (8 blocks) x 128 rows.
-// The encoder is a driver entry point; it is looked up through the runtime so that the library links against
-// nothing but cudart.  false: not available (the caller takes the form that needs no map).
-static bool encode_w_map(CUtensorMap *map, const void *W, int64_t n_out, int64_t row_bytes) {
+// 2-D tensor map: dims {d0 (fastest), d1}, row stride in bytes, box {b0, b1}.  The encoder is a driver entry point; it is
+// looked up through the runtime so that the library links against nothing but cudart.  false: not available (the
+// caller takes a form that needs no map).
+static bool tensor_map_2d(CUtensorMap *map, CUtensorMapDataType type, const void *base, uint64_t d0, uint64_t d1,
+                          uint64_t stride_bytes, uint32_t b0, uint32_t b1, CUtensorMapSwizzle swizzle) {
     using Encode = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
                                 const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -823,28 +826,134 @@ static bool encode_w_map(CUtensorMap *map, const void *W, int64_t n_out, int64_t
         return reinterpret_cast<Encode>(fn);
     }();
     if (!encode) return false;
-    const cuuint64_t dims[2] = {(cuuint64_t)(row_bytes / 4), (cuuint64_t)n_out};
-    const cuuint64_t strides[1] = {(cuuint64_t)row_bytes};
-    const cuuint32_t box[2] = {68u, (cuuint32_t)TC_M};
+    const cuuint64_t dims[2] = {(cuuint64_t)d0, (cuuint64_t)d1};
+    const cuuint64_t strides[1] = {(cuuint64_t)stride_bytes};
+    const cuuint32_t box[2] = {b0, b1};
     const cuuint32_t estr[2] = {1u, 1u};
-    return encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void *>(W), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    return encode(map, type, 2, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+// The two fp16 planes of the split activations, [2][n_tok][n_in]: box = 64 values x 64 tokens x both planes, landing with
+// the 128-byte swizzle the MMA reads; tokens past the end arrive as zeros.
+static bool tensor_map_planes(CUtensorMap *map, const void *planes, uint64_t n_in, uint64_t n_tok) {
+    using Encode = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    void *fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess || !fn)
+        return false;
+    const cuuint64_t dims[3] = {n_in, n_tok, 2};
+    const cuuint64_t strides[2] = {n_in * 2, n_tok * n_in * 2};
+    const cuuint32_t box[3] = {64u, (cuuint32_t)T16_N, 2u};
+    const cuuint32_t estr[3] = {1u, 1u, 1u};
+    return reinterpret_cast<Encode>(fn)(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void *>(planes), dims, strides, box, estr,
+                                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+// A PQ2_0 matrix seen as [n_out][row_bytes / 4] 32-bit words, box = 68 words (8 blocks) x 128 rows.
+static bool encode_w_map(CUtensorMap *map, const void *W, int64_t n_out, int64_t row_bytes) {
+    return tensor_map_2d(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, W, (uint64_t)(row_bytes / 4), (uint64_t)n_out, (uint64_t)row_bytes,
+                         68u, (uint32_t)TC_M, CU_TENSOR_MAP_SWIZZLE_NONE);
+}
+
+// Scratch of the fp16 tensor-core mat-mul (the activations as two fp16 planes + the per-token scales): one buffer per
+// (device, stream), grown with cudaMalloc when a call needs more -- never while the stream is being captured (then,
+// and when 16 buffers exist already, the caller takes the integer kernel, which needs no scratch).
+struct GemmScratch { int dev; cudaStream_t st; void *ptr; size_t bytes; };
+static std::mutex g_scratch_mu;
+static std::vector<GemmScratch> g_scratch;
+static void *gemm_scratch(size_t bytes, cudaStream_t st) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+    std::lock_guard<std::mutex> lock(g_scratch_mu);
+    GemmScratch *e = nullptr;
+    for (auto &g : g_scratch)
+        if (g.dev == dev && g.st == st) e = &g;
+    if (e && e->bytes >= bytes) return e->ptr;
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(st, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) return nullptr;
+    if (!e) {
+        if (g_scratch.size() >= 16) return nullptr;
+        g_scratch.push_back(GemmScratch{dev, st, nullptr, 0});
+        e = &g_scratch.back();
+    }
+    if (e->ptr) cudaFree(e->ptr);               // synchronises the device: nothing in flight reads the old buffer
+    e->ptr = nullptr;
+    e->bytes = 0;
+    void *pnew = nullptr;
+    if (cudaMalloc(&pnew, bytes) != cudaSuccess) { (void)cudaGetLastError(); return nullptr; }
+    e->ptr = pnew;
+    e->bytes = bytes;
+    return pnew;
+}
+
+static std::atomic<unsigned int> g_gemm_epoch{0};       // launch number of the tensor-core mat-muls (tags partial-tile flags)
+
+static void fill_tc_params(TcParams &P, int64_t n_out, int64_t n_in, int64_t n_tok, int tile_m, int tile_n) {
+    P.n_out = (int)n_out;
+    P.nblocks = (int)(n_in / 128);
+    P.n_tok = (int)n_tok;
+    P.tiles_tok = (int)((n_tok + tile_n - 1) / tile_n);
+    P.n_tiles = (int)(((n_out + tile_m - 1) / tile_m) * P.tiles_tok);
+    P.total_it = (long long)P.n_tiles * P.nblocks;
+}
+
+// The fp16 tensor-core mat-mul (gemm_tc16.cuh).  -1: not taken (shape, alignment, no scratch, no tensor-map encoder).
+static int launch_gemm_tc16(const void *W, const void *Xq, float *Y, int64_t n_out, int64_t n_in, int64_t n_tok, cudaStream_t st) {
+    const int64_t nblocks = n_in / 128;
+    if (nblocks % 8 != 0 || !aligned16(W) || !aligned4(Xq) || n_tok > (1 << 28)) return -1;
+    const long long tiles = (long long)((n_out + T16_M - 1) / T16_M) * ((n_tok + T16_N - 1) / T16_N);
+    if (tiles > INT32_MAX) return -1;
+    const size_t plane_bytes = (size_t)n_tok * (size_t)n_in * sizeof(__half);
+    const size_t bytes = 2 * plane_bytes + 2 * (size_t)n_tok * sizeof(float);
+    uint8_t *ws = static_cast<uint8_t *>(gemm_scratch(bytes, st));
+    if (!ws) return -1;
+    __half *planes = reinterpret_cast<__half *>(ws);
+    float *scale = reinterpret_cast<float *>(ws + 2 * plane_bytes);
+    alignas(64) Tc16Maps maps;
+    std::memset(&maps, 0, sizeof(maps));
+    if (!encode_w_map(&maps.w, W, n_out, nblocks * W_BLOCK_BYTES)) return -1;
+    if (!tensor_map_planes(&maps.x, planes, (uint64_t)n_in, (uint64_t)n_tok)) return -1;
+    TcParams P{};
+    fill_tc_params(P, n_out, n_in, n_tok, T16_M, T16_N);
+    int dev = 0, sms = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return (int)e;
+    if (sms > TC_MAX_CTAS - 1) sms = TC_MAX_CTAS - 1;
+    const int grid = (int)(tiles < sms ? tiles : sms);
+    P.stream_k = (tiles % grid != 0 && P.total_it / grid >= P.nblocks) ? 1 : 0;
+    P.epoch = g_gemm_epoch.fetch_add(1) + 1u;
+    const int n_chunks = (int)(n_in / 32);
+    const uint32_t *x32 = static_cast<const uint32_t *>(Xq);
+    tc16_tokscale_kernel<<<(unsigned)((n_tok + 31) / 32), 256, 0, st>>>(x32, n_chunks, (int)n_tok, scale);
+    const long long items = (long long)n_chunks * n_tok;
+    tc16_split_kernel<<<(unsigned)((items + 255) / 256), 256, 0, st>>>(x32, n_chunks, (int)n_tok, scale, planes);
+    static SmemOptIn opt;
+    e = opt.ensure(gemm_tc16_kernel);
+    if (e != cudaSuccess) return (int)e;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(T16_THREADS);
+    cfg.dynamicSmemBytes = T16_SMEM_BYTES;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeCooperative;
+    attr[0].val.cooperative = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return (int)cudaLaunchKernelEx(&cfg, gemm_tc16_kernel, Y, P, (const float *)scale, maps);
 }
 
 // The tensor-core mat-mul: one CTA per SM walks its share of the (tile, weight block) iterations.
 static int launch_gemm_tc(const void *W, const void *Xq, float *Y, int64_t n_out, int64_t n_in, int64_t n_tok,
                           int32_t *dump, cudaStream_t st) {
-    static std::atomic<unsigned int> epoch{0};
     TcParams P{};
-    P.n_out = (int)n_out;
-    P.nblocks = (int)(n_in / 128);
-    P.n_tok = (int)n_tok;
-    P.tiles_tok = (int)((n_tok + TC_N - 1) / TC_N);
-    const long long tiles = (long long)((n_out + TC_M - 1) / TC_M) * P.tiles_tok;
+    const long long tiles = (long long)((n_out + TC_M - 1) / TC_M) * ((n_tok + TC_N - 1) / TC_N);
     if (tiles > INT32_MAX) return 1;
-    P.n_tiles = (int)tiles;
-    P.total_it = tiles * P.nblocks;
+    fill_tc_params(P, n_out, n_in, n_tok, TC_M, TC_N);
     int dev = 0, sms = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -853,7 +962,7 @@ static int launch_gemm_tc(const void *W, const void *Xq, float *Y, int64_t n_out
     const int grid = (int)(tiles < sms ? tiles : sms);
     // contiguous ranges when they are at least one tile long (then a tile is cut at most once); whole tiles otherwise
     P.stream_k = (tiles % grid != 0 && P.total_it / grid >= P.nblocks) ? 1 : 0;
-    P.epoch = epoch.fetch_add(1) + 1u;
+    P.epoch = g_gemm_epoch.fetch_add(1) + 1u;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
     cfg.blockDim = dim3(TC_THREADS);
@@ -910,8 +1019,14 @@ int bonsai_p40_gemm(const void *W, const void *Xq, float *Y, int64_t n_out, int6
     if (n_out <= 0 || n_tok <= 0) return 0;
     if (n_out > INT32_MAX || n_tok > INT32_MAX || !aligned4(Xq)) return 1;
     const int path = g_opt_gemm_path.load();
-    const bool tensor = path == 1 || (path < 0 && n_tok >= 48);       // a 128-token tile needs tokens to fill it
-    if (tensor) return launch_gemm_tc(W, Xq, Y, n_out, n_in, n_tok, nullptr, as_stream(stream));
+    const bool tensor = path == 1 || path == 3 || (path < 0 && n_tok >= 48);       // a 64-token tile needs tokens to fill it
+    if (tensor) {
+        if (path != 3) {                                              // the fp16 form first; -1: it does not take the call
+            const int rc = launch_gemm_tc16(W, Xq, Y, n_out, n_in, n_tok, as_stream(stream));
+            if (rc >= 0) return rc;
+        }
+        return launch_gemm_tc(W, Xq, Y, n_out, n_in, n_tok, nullptr, as_stream(stream));
+    }
     if (path == 2 || (path < 0 && n_tok >= 2 && n_tok <= 8)) {        // a handful of tokens: weights streamed once for all of them
         const int rc = launch_gemm_small(W, Xq, Y, n_out, n_in, n_tok, nullptr, as_stream(stream));
         if (rc >= 0) return rc;                                       // -1: the shape does not fit, the kernel below takes it

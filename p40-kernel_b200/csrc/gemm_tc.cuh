@@ -48,7 +48,7 @@ namespace b200 {
 
 constexpr int TC_M = 128, TC_N = 64;
 constexpr int TC_TMEM_STAGES = 8;                          // chunk results in flight in tensor memory: 8 x 64 columns = two whole blocks
-constexpr int TC_STAGES = 3;                               // shared-memory stages (one weight block each)
+constexpr int TC_STAGES = 4;                               // shared-memory stages (one weight block each)
 constexpr int TC_XBUFS = 4;                                // raw Q8_1 buffers in flight (TMA form): bulk copies take ~1 us to land
 constexpr int TC_A_BYTES = 4 * TC_M * 32;                  // 4 chunks x 128 rows x 32 bytes
 constexpr int TC_B_BYTES = 4 * TC_N * 32;                  // 4 chunks x 64 tokens x 32 bytes
@@ -57,7 +57,7 @@ constexpr int TC_SCALE_BYTES = TC_M * 4 + 4 * TC_N * 4;                 // dw[12
 constexpr int TC_EPI_WARPS = 16, TC_PRODA_WARPS = 4, TC_PRODB_WARPS = 2;
 constexpr int TC_EPI_THREADS = TC_EPI_WARPS * 32, TC_PRODA_THREADS = TC_PRODA_WARPS * 32, TC_PRODB_THREADS = TC_PRODB_WARPS * 32;
 constexpr int TC_THREADS = TC_EPI_THREADS + TC_PRODA_THREADS + TC_PRODB_THREADS + 64;       // + issuer warp + loader warp
-constexpr int TC_WBUFS = 3;                                // raw weight pieces in flight (TMA form)
+constexpr int TC_WBUFS = 2;                                // raw weight pieces in flight (TMA form)
 constexpr int TC_WRAW_BYTES = TC_M * 272;                  // raw PQ2_0 bytes of 8 consecutive blocks of 128 rows
 constexpr int TC_XRAW_BYTES = 4 * TC_N * A_BLOCK_BYTES;    // raw Q8_1 blocks of 4 chunks x 64 tokens
 constexpr int TC_SMEM_BYTES = 2048 + TC_STAGES * (TC_STAGE_BYTES + TC_SCALE_BYTES);   // barriers + slack to align to 1024

@@ -1,0 +1,432 @@
+// gemm_tc16.cuh -- prefill mat-mul with the WHOLE contraction on the tensor cores (tcgen05.mma.kind::f16).
+//
+// gemm_tc.cuh keeps the integers of the host loop (one int8 MMA per 32-weight chunk, the per-chunk scales folded in
+// by the CUDA cores) and is bound by exactly that fold: ~5400 warp instructions per 128 x 64 x 128 unit, 70 % of the
+// issue slots, the tensor pipe 6.5 % busy.  This kernel moves the per-chunk activation scale to the OTHER side of the
+// tensor core.  The dequantised activation  xh = da * a  (fp16 scale x int8, 18 significant bits) is split once per
+// call into two fp16 numbers H + L = xh * 2^S exactly (S per token, a power of two that puts the token's largest
+// value just under 2^15; L is the exact remainder, and where it underflows the loss is below 2^-38 of the token's
+// largest value), the codes go to the tensor core as fp16 -1, 0, 1, 2, and one accumulator in tensor memory
+// collects  sum_k (code_k - 1) * (H_k + L_k)  over a whole 128-weight block: products are exact, sums are the tensor
+// core's fp32.  The CUDA cores are left with one fused multiply-add per output and BLOCK (the fp16 weight scale) and
+// the expansion of the codes: ~4x fewer instructions per unit than the integer kernel.
+// Accuracy: the only roundings are the tensor core's fp32 additions inside a block (256 terms) and one fp32 FMA per
+// block, against the host's one rounding per chunk term: Y is held to 1e-5 of max |Y| like the integer kernel's
+// (measured ~1e-6); the INTEGERS of the host loop are not formed here: bonsai_b200_gemm_dump and
+// bonsai_b200_set_option("gemm_path", 3) keep the integer kernel.
+// Oracle: tests/test_p40.cpp:438-467 + src/pq2_0.h:149-169 (the host loop); kernel replaced: src/kernels/gemm_p40.cu:44-139.
+//
+// CTA tile 128 rows x 64 tokens, one CTA per SM, K stepped one weight block at a time = 16 MMAs (M 128, N 64, K 16):
+// two K halves of 64 values x {H, L} x four K = 16 steps, all into one 64-column accumulator (4 in flight).
+//   warps 0-7   : epilogue: per block two tcgen05.ld of 16 columns, acc += dw * D (one row x 32 tokens per thread)
+//   warps 8-23  : code producers: thread (row p, K quarter h) turns 32 two-bit codes into 32 fp16 (half of a 128-byte
+//                 swizzled row) with byte permutes: the fp16 patterns of -1, 0, 1, 2 differ only in their high byte
+//   warps 24-25 : issuers (alternate blocks)
+//   warps 26-27 : loaders (tiled TMA copies): weight pieces of 8 blocks x 128 rows; per block two boxes of 64 values x
+//                 64 tokens x {H, L}, landing swizzled as the MMA reads them
+// Work split, partial tiles and time-outs as in gemm_tc.cuh (same walk, same flag words).
+#pragma once
+
+#include "gemm_tc.cuh"
+
+namespace b200 {
+
+constexpr int T16_M = 128, T16_N = 64;
+// Operands move in units of one K half of a weight block (64 values).  The codes (A) never touch shared memory: the
+// producers write the fp16 values straight into TENSOR memory (tcgen05.st, lane = weight row, 32 columns per unit) and
+// the MMA takes A from there -- with both operands in shared memory the tensor core's operand reads alone (6 KB per
+// 128 x 64 x 16 MMA, 96 KB per block) ate 3/4 of the shared-memory bandwidth of the block's whole time budget.  The
+// activations (B: the H and L planes of 64 tokens, 8 + 8 KB per unit) land in a shared-memory ring by TMA, asked for
+// as far ahead as the ring allows: the boxes come from L2 and take ~1000-1500 cycles.
+constexpr int T16_NA = 8;                                  // A ring: half-block units in tensor memory
+constexpr int T16_NB = 4;                                  // B ring: whole blocks (32 KB: K half x {H, L}) in shared memory
+constexpr int T16_UNIT_BYTES = 128 * 128;                  // 16 KB
+constexpr int T16_A_COL0 = 256, T16_A_UNIT_COLS = 32;      // tensor memory: 4 accumulators x 64 columns, then 8 A units x 32
+constexpr int T16_ACC = 4;                                 // accumulators in flight in tensor memory (64 columns each)
+constexpr int T16_WBUFS = 2;
+constexpr int T16_DWRING = 8;                              // weight scales of the last 8 blocks (epilogue lags the producers)
+constexpr int T16_EPI_WARPS = 8, T16_PROD_WARPS = 16;
+constexpr int T16_EPI_THREADS = T16_EPI_WARPS * 32, T16_PROD_THREADS = T16_PROD_WARPS * 32;
+constexpr int T16_EPI_TOKS = T16_N / (T16_EPI_WARPS / 4);        // tokens per epilogue thread (32)
+constexpr int T16_ISSUERS = 2;                             // issuing warps: warp k takes the blocks n with n % 2 == k
+constexpr int T16_THREADS = T16_EPI_THREADS + T16_PROD_THREADS + 32 * (T16_ISSUERS + 2);    // + two loader warps
+constexpr int T16_SMEM_BYTES = 2048 + T16_NB * 2 * T16_UNIT_BYTES + T16_DWRING * T16_M * 4 + T16_WBUFS * TC_WRAW_BYTES;
+
+// D = fp32, A and B fp16, both K-major, N = 64, M = 128.
+constexpr uint32_t T16_IDESC = (1u << 4) | ((T16_N >> 3) << 17) | ((T16_M >> 4) << 24);
+
+// The descriptors' upper words are the same for every operand of this kernel (128-byte swizzle, 1024 bytes between
+// 8-row groups); only the 14-bit address field of the lower word moves.  The issuing thread runs alone, one dependent
+// instruction every few cycles, so an MMA is issued with two independent 32-bit adds and nothing else (building both
+// 64-bit descriptors from an address cost ~75 cycles per MMA, 16 times per block).
+constexpr uint32_t T16_DESC_HI = (uint32_t)(1024 >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t tc16_desc_lo(uint32_t smem_addr) { return ((smem_addr >> 4) & 0x3FFFu) | (1u << 16); }
+template <bool ACC>
+__device__ __forceinline__ void tc_mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        ".reg .b64 db;\n\t"
+        "mov.b64 db, {%2, %4};\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %3, {%6, %6, %6, %6}, p;\n\t"
+        "}\n"
+        ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(T16_IDESC), "r"(T16_DESC_HI), "n"(ACC ? 1 : 0), "r"(0u)
+        : "memory");
+}
+__device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t (&v)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};\n"
+        ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+          "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+        : "memory");
+}
+__device__ __forceinline__ void tc_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map, int x, int y, int z, uint64_t *bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                 ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "elect.sync _|p, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}"
+        : "=r"(pred));
+    return pred != 0;
+}
+__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+                 : "memory");
+}
+
+// ---- once per call: the activations as two fp16 planes ------------------------------------------------------------
+// scale[tok] = 2^-S, scale[n_tok + tok] = 2^S with S = 8 - exponent(max_c da_c): every |da * a * 2^S| < 2^15.
+__global__ void __launch_bounds__(256) tc16_tokscale_kernel(const uint32_t *__restrict__ Xq, int n_chunks, int n_tok,
+                                                            float *__restrict__ scale) {
+    __shared__ float part[8][32];
+    const int tl = threadIdx.x & 31, grp = threadIdx.x >> 5;
+    const int tok = blockIdx.x * 32 + tl;
+    float m = 0.0f;
+    if (tok < n_tok)
+        for (int c = grp; c < n_chunks; c += 8)
+            m = fmaxf(m, f16_bits_to_f32(__ldg(Xq + 9 * ((size_t)c * n_tok + tok)) & 0xFFFFu));
+    part[grp][tl] = m;
+    __syncthreads();
+    if (grp == 0 && tok < n_tok) {
+#pragma unroll
+        for (int g = 1; g < 8; ++g) m = fmaxf(m, part[g][tl]);
+        int ex = 0;
+        if (m > 0.0f) (void)frexpf(m, &ex);            // m = f * 2^ex, 0.5 <= f < 1  =>  m * 128 < 2^(ex + 7)
+        const int S = m > 0.0f ? 8 - ex : 0;
+        scale[tok] = ldexpf(1.0f, -S);
+        scale[n_tok + tok] = ldexpf(1.0f, S);
+    }
+}
+// Thread = (chunk, token): 32 values -> 32 + 32 fp16, in the order the quantiser stored them (the order in which the
+// code producers emit the codes).  planes: H at [tok][n_in], L at [n_tok + tok][n_in].
+__global__ void __launch_bounds__(256) tc16_split_kernel(const uint32_t *__restrict__ Xq, int n_chunks, int n_tok,
+                                                         const float *__restrict__ scale, __half *__restrict__ planes) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)n_chunks * n_tok) return;
+    const int c = (int)(i / n_tok), tok = (int)(i - (long long)c * n_tok);
+    const uint32_t *src = Xq + 9 * (size_t)i;
+    uint32_t w[9];
+#pragma unroll
+    for (int k = 0; k < 9; ++k) w[k] = __ldg(src + k);
+    const float ds = __fmul_rn(f16_bits_to_f32(w[0] & 0xFFFFu), scale[n_tok + tok]);        // da * 2^S: exact (a power of two)
+    const size_t n_in = (size_t)n_chunks * 32;
+    uint4 *hp = reinterpret_cast<uint4 *>(planes + (size_t)tok * n_in + (size_t)c * 32);
+    uint4 *lp = reinterpret_cast<uint4 *>(planes + ((size_t)n_tok + tok) * n_in + (size_t)c * 32);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {                       // 8 values per 16-byte store
+        uint32_t h[4], l[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const uint32_t word = w[1 + 2 * q + (e >> 1)];
+            const int a0 = (int)(int8_t)(word >> (16 * (e & 1))), a1 = (int)(int8_t)(word >> (16 * (e & 1) + 8));
+            const float v0 = __fmul_rn(ds, (float)a0), v1 = __fmul_rn(ds, (float)a1);      // exact: 11 x 7 bits
+            const __half h0 = __float2half_rn(v0), h1 = __float2half_rn(v1);
+            const __half l0 = __float2half_rn(__fsub_rn(v0, __half2float(h0))), l1 = __float2half_rn(__fsub_rn(v1, __half2float(h1)));
+            h[e] = (uint32_t)__half_as_ushort(h0) | ((uint32_t)__half_as_ushort(h1) << 16);
+            l[e] = (uint32_t)__half_as_ushort(l0) | ((uint32_t)__half_as_ushort(l1) << 16);
+        }
+        hp[q] = make_uint4(h[0], h[1], h[2], h[3]);
+        lp[q] = make_uint4(l[0], l[1], l[2], l[3]);
+    }
+}
+
+// 16 two-bit codes of one word -> 16 fp16 (-1, 0, 1, 2) in eight words, element 4 k + b = field k of byte b
+// (the order of the quantiser's words, src/pq2_0.h:120-125, 158-166).  The four fp16 patterns 0xBC00, 0x0000, 0x3C00,
+// 0x4000 have a zero low byte, so a byte permute with the code as selector builds two of them at once.
+__device__ __forceinline__ void tc16_expand(uint32_t w, uint32_t *o) {
+    constexpr uint32_t TB = 0x403C00BCu;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const uint32_t t = (w >> (2 * k)) & 0x03030303u;
+        o[2 * k] = __byte_perm(TB, 0u, (t << 4) + 0x0404u);
+        o[2 * k + 1] = __byte_perm(TB, 0u, (t >> 12) + 0x0404u);
+    }
+}
+
+struct Tc16Maps {
+    CUtensorMap w;        // PQ2_0 matrix as [n_out][row words], box 68 x 128
+    CUtensorMap x;        // fp16 planes as [2][n_tok][n_in], box 64 values x 64 tokens x 2 planes, 128-byte swizzle
+};
+
+__global__ void __launch_bounds__(T16_THREADS, 1) gemm_tc16_kernel(float *Y, const TcParams P, const float *__restrict__ tokscale,
+                                                                   const __grid_constant__ Tc16Maps maps) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    // unit u = 2 * block + K half lives in slot u % NA of the code ring and slot u % NB of the activation ring
+    uint64_t *afull = reinterpret_cast<uint64_t *>(smem);              // [NA] code producers -> issuer
+    uint64_t *afree = afull + T16_NA;                                   // [NA] tensor core -> code producers
+    uint64_t *bfull = afree + T16_NA;                                   // [NB] loader (bytes landed) -> issuer
+    uint64_t *bfree = bfull + T16_NB;                                   // [NB] tensor core -> loader
+    uint64_t *mma_done = bfree + T16_NB;                                // [4] tensor core -> epilogue
+    uint64_t *tmem_empty = mma_done + T16_ACC;                          // [4] epilogue -> issuer
+    uint64_t *wfull = tmem_empty + T16_ACC;                             // [2] loader -> producers
+    uint64_t *wfree = wfull + T16_WBUFS;                                // [2] producers -> loader
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(wfree + T16_WBUFS);
+    uint8_t *stages = smem + 1024 + ((1024u - (smem_u32(smem) & 1023u)) & 1023u);
+    uint8_t *bring = stages;
+    float *dwring = reinterpret_cast<float *>(bring + T16_NB * 2 * T16_UNIT_BYTES);
+    uint8_t *wraw = reinterpret_cast<uint8_t *>(dwring + T16_DWRING * T16_M);
+
+    const int wid = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nblocks = P.nblocks, n_tok = P.n_tok, n_out = P.n_out;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < T16_NA; ++s) { mbar_init(&afull[s], T16_PROD_THREADS / 2); mbar_init(&afree[s], 1); }
+        for (int s = 0; s < T16_NB; ++s) { mbar_init(&bfull[s], 1); mbar_init(&bfree[s], 1); }
+        for (int s = 0; s < T16_ACC; ++s) { mbar_init(&mma_done[s], 1); mbar_init(&tmem_empty[s], T16_EPI_WARPS); }
+        for (int s = 0; s < T16_WBUFS; ++s) { mbar_init(&wfull[s], 1); mbar_init(&wfree[s], T16_PROD_THREADS); }
+        mbar_fence_init();
+    }
+    constexpr int ISSUER = T16_EPI_WARPS + T16_PROD_WARPS, LOADER = ISSUER + T16_ISSUERS;
+    if (threadIdx.x == LOADER * 32) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&maps.w) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&maps.x) : "memory");
+    }
+    if (wid == ISSUER) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    TcWalk walk;
+    walk.start(P);
+    int tile, kb0, kb1;
+
+    if (wid < T16_EPI_WARPS) {
+        // ---------------- epilogue: one weight row per thread, 32 tokens ----------------
+        const int q = wid & 3, cg = wid >> 2;
+        const int row_l = 32 * q + lane;
+        unsigned int *flags = g_gemm_flags[P.epoch & (TC_FLAG_SETS - 1)];
+        bool ok = true;
+        int n = 0;
+        while (ok && walk.next(P, tile, kb0, kb1)) {
+            const int rt = tile / P.tiles_tok, tt = tile - rt * P.tiles_tok;
+            const int row = rt * T16_M + row_l, tokb = tt * T16_N + T16_EPI_TOKS * cg;
+            float acc[T16_EPI_TOKS];
+#pragma unroll
+            for (int j = 0; j < T16_EPI_TOKS; ++j) acc[j] = 0.0f;
+            const uint32_t tlane = tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(T16_EPI_TOKS * cg);
+            for (int kb = kb0; kb < kb1; ++kb, ++n) {
+                const int t = n & (T16_ACC - 1);
+                if (!mbar_wait_bounded(&mma_done[t], (uint32_t)((n / T16_ACC) & 1), 20, 80)) { ok = false; break; }
+                tc_fence_after();
+                int v[16];
+                tc_ld16(tlane + (uint32_t)(t * T16_N), v);
+                const float dw = dwring[(n & (T16_DWRING - 1)) * T16_M + row_l];
+                tc_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 16; ++j) acc[j] = __fmaf_rn(dw, __int_as_float(v[j]), acc[j]);
+                tc_ld16(tlane + (uint32_t)(t * T16_N + 16), v);
+                tc_ld_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&tmem_empty[t]);          // the block's sums are in registers
+#pragma unroll
+                for (int j = 0; j < 16; ++j) acc[16 + j] = __fmaf_rn(dw, __int_as_float(v[j]), acc[16 + j]);
+            }
+            if (!ok) break;
+            // ---- the tile (or this CTA's part of it) is done: undo the token's power-of-two scale
+#pragma unroll
+            for (int j = 0; j < T16_EPI_TOKS; ++j) acc[j] = __fmul_rn(acc[j], tokb + j < n_tok ? __ldg(tokscale + tokb + j) : 0.0f);
+            const bool late_part = kb0 > 0, early_part = kb1 < nblocks;
+            float *yrow = Y + (size_t)row * n_tok + tokb;
+            const bool vec = (n_tok & 3) == 0 && (reinterpret_cast<uintptr_t>(Y) & 15u) == 0;
+            if (early_part) {
+                // the CTA after this one computed the later blocks of this tile first and left them in Y
+                if (threadIdx.x == 0) {
+                    const unsigned int *f = flags + blockIdx.x + 1;
+                    uint32_t ns = 64;
+                    bool there = false;
+                    for (uint32_t k = 0; k < (1u << 22); ++k) {
+                        unsigned int fv;
+                        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(fv) : "l"(f) : "memory");
+                        if (fv != 0u) { there = true; break; }
+                        __nanosleep(ns);
+                        ns = min(ns * 2, 1024u);
+                    }
+                    if (!there) atomicExch(&g_device_status, STATUS_GRID_TIMEOUT);
+                    *const_cast<volatile unsigned int *>(f) = 0u;     // lowered by its only reader (graph replays reuse the number)
+                }
+                asm volatile("bar.sync 1, %0;" ::"n"(T16_EPI_THREADS) : "memory");
+                if (row < n_out) {
+#pragma unroll
+                    for (int j = 0; j < T16_EPI_TOKS; ++j)
+                        if (tokb + j < n_tok) acc[j] = __fadd_rn(acc[j], __ldcg(yrow + j));
+                }
+            }
+            if (row < n_out) {
+                if (vec) {
+#pragma unroll
+                    for (int j = 0; j < T16_EPI_TOKS; j += 4)
+                        if (tokb + j < n_tok) *reinterpret_cast<float4 *>(yrow + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < T16_EPI_TOKS; ++j)
+                        if (tokb + j < n_tok) yrow[j] = acc[j];
+                }
+            }
+            if (late_part) {
+                __threadfence();
+                asm volatile("bar.sync 1, %0;" ::"n"(T16_EPI_THREADS) : "memory");
+                if (threadIdx.x == 0) asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(flags + blockIdx.x), "r"(P.epoch) : "memory");
+            }
+        }
+    } else if (wid < ISSUER) {
+        // ---------------- code producers: thread (row p, K quarter h): 32 codes -> 64 bytes of the row ----------------
+        const int pi = threadIdx.x - T16_EPI_THREADS;
+        // A warp reaches only the 32 tensor-memory lanes of its own quarter (warp index mod 4): producer warp pw takes
+        // rows 32 (pw % 4) + lane and K quarter pw / 4.
+        const int pw = pi >> 5, h = pw >> 2, p = 32 * (pw & 3) + lane, g = h >> 1;          // g: the K half (its own barriers)
+        const uint32_t a_lane = tmem_base + ((uint32_t)(32 * (pw & 3)) << 16) + (uint32_t)(T16_A_COL0 + 16 * (h & 1));
+        bool ok = true;
+        int n = 0, oct = 0;
+        while (ok && walk.next(P, tile, kb0, kb1)) {
+            for (int kb = kb0; kb < kb1; ++kb, ++n) {
+                const int u = 2 * n + g, sa = u % T16_NA;
+                if (kb == kb0 || (kb & 7) == 0) {
+                    if (!mbar_wait_bounded(&wfull[oct % T16_WBUFS], (uint32_t)((oct / T16_WBUFS) & 1))) { ok = false; break; }
+                    ++oct;
+                }
+                const int wbuf = (oct - 1) % T16_WBUFS;
+                // The quarter's two code words sit at byte 34 j + 2 + 8 h of the row's 272-byte piece, 2-byte aligned:
+                // three aligned words and a funnel shift by 0 or 16 bits.  (Rows are 68 words apart: a warp's loads
+                // spread over eight banks, four passes each -- as many as 16-byte loads of the whole block would take.)
+                const uint32_t off = (uint32_t)(kb & 7) * 34u + 2u + 8u * (uint32_t)h;
+                const uint8_t *rowp = wraw + (size_t)wbuf * TC_WRAW_BYTES + (size_t)p * 272;
+                const uint32_t *wa = reinterpret_cast<const uint32_t *>(rowp + (off & ~3u));
+                const uint32_t x0 = wa[0], x1 = wa[1], x2 = wa[2], sh = (off & 2u) * 8u;
+                const uint32_t dbits = h == 0 ? (uint32_t)*reinterpret_cast<const unsigned short *>(rowp + (kb & 7) * 34) : 0u;
+                uint32_t pc[16];
+                tc16_expand(__funnelshift_r(x0, x1, sh), pc);
+                tc16_expand(__funnelshift_r(x1, x2, sh), pc + 8);
+                if (!mbar_wait_bounded(&afree[sa], (uint32_t)(((u / T16_NA) & 1) ^ 1), 20, 80)) { ok = false; break; }
+                tc_fence_after();
+                if (h == 0) dwring[(n & (T16_DWRING - 1)) * T16_M + p] = f16_bits_to_f32(dbits);
+                tc_st16(a_lane + (uint32_t)(sa * T16_A_UNIT_COLS), pc);     // 32 fp16 = 16 columns of this thread's lane
+                tc_st_wait();
+                tc_fence_before();
+                mbar_arrive(&afull[sa]);
+                if ((kb & 7) == 7 || kb == kb1 - 1) mbar_arrive(&wfree[wbuf]);
+            }
+        }
+    } else if (wid == LOADER) {
+        // ---------------- weight loader: a piece (8 blocks x 128 rows, one tiled copy) as soon as its buffer is free ----------------
+        int oct = 0;
+        bool ok = true;
+        while (ok && walk.next(P, tile, kb0, kb1)) {
+            for (int kb = kb0; kb < kb1 && ok; kb = min(kb1, (kb | 7) + 1), ++oct) {
+                const int wb = oct % T16_WBUFS;
+                if (!mbar_wait_bounded(&wfree[wb], (uint32_t)(((oct / T16_WBUFS) & 1) ^ 1))) { ok = false; break; }
+                if (elect_one()) {
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    mbar_expect_tx(&wfull[wb], (uint32_t)TC_WRAW_BYTES);
+                    tma_load_2d(wraw + (size_t)wb * TC_WRAW_BYTES, &maps.w, (kb >> 3) * 68, (tile / P.tiles_tok) * T16_M, &wfull[wb]);
+                }
+                __syncwarp();
+            }
+        }
+    } else if (wid == LOADER + 1) {
+        // ---------------- activation loader: a block's boxes (two copies of 64 values x 64 tokens x {H, L}) ----------------
+        int n = 0;
+        bool ok = true;
+        while (ok && walk.next(P, tile, kb0, kb1)) {
+            const int tt = tile % P.tiles_tok;
+            for (int kb = kb0; kb < kb1; ++kb, ++n) {
+                const int sb = n % T16_NB;
+                if (!mbar_wait_bounded(&bfree[sb], (uint32_t)(((n / T16_NB) & 1) ^ 1), 20, 80)) { ok = false; break; }
+                if (elect_one()) {
+                    uint8_t *b = bring + (size_t)sb * (2 * T16_UNIT_BYTES);
+                    mbar_expect_tx(&bfull[sb], (uint32_t)(2 * T16_UNIT_BYTES));
+                    tma_load_3d(b, &maps.x, kb * 128, tt * T16_N, 0, &bfull[sb]);
+                    tma_load_3d(b + T16_UNIT_BYTES, &maps.x, kb * 128 + 64, tt * T16_N, 0, &bfull[sb]);
+                }
+                __syncwarp();
+            }
+        }
+    } else {
+        // ---------------- issuer: sixteen K = 16 MMAs per weight block, one accumulator ----------------
+        // The whole warp walks the loop and waits; one elected lane issues.  Kept warp-uniform on purpose: the MMA takes
+        // its operands from uniform registers, and inside a one-lane branch every operand had to be moved there first
+        // (~70 cycles per MMA, measured).  Two such warps take alternate blocks: one warp's waits, fences and commits
+        // are a serial chain of ~2000 cycles per block, more than the block's MMAs take; blocks use different
+        // accumulators, so their MMAs may interleave, and a commit covers the issuing thread's own MMAs.
+        const int me = wid - ISSUER;
+        bool ok = true;
+        int n = 0;
+        while (ok && walk.next(P, tile, kb0, kb1)) {
+            for (int kb = kb0; kb < kb1; ++kb, ++n) {
+                if ((n & (T16_ISSUERS - 1)) != me) continue;
+                const int t = n & (T16_ACC - 1);
+                const uint32_t d = tmem_base + (uint32_t)(t * T16_N);
+                // K half 0, then K half 1: each half's 8 MMAs (H and L planes x four K steps) go out as soon as its two
+                // units are there, and the units are handed back as soon as the MMAs have read them.
+#pragma unroll
+                for (int g = 0; g < 2; ++g) {
+                    const int u = 2 * n + g, sa = u % T16_NA, sb = n % T16_NB;
+                    if (!mbar_wait_hot(&afull[sa], (uint32_t)((u / T16_NA) & 1))) { ok = false; break; }
+                    if (g == 0 && (!mbar_wait_hot(&bfull[sb], (uint32_t)((n / T16_NB) & 1)) ||
+                                   !mbar_wait_hot(&tmem_empty[t], (uint32_t)(((n / T16_ACC) & 1) ^ 1)))) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_t = tmem_base + (uint32_t)(T16_A_COL0 + sa * T16_A_UNIT_COLS);
+                    const uint32_t b_lo = tc16_desc_lo(smem_u32(bring + (size_t)(2 * sb + g) * T16_UNIT_BYTES));
+                    if (elect_one()) {
+#pragma unroll
+                        for (int m = 0; m < 8; ++m) {
+                            const int pl = m >> 2, i = m & 3;
+                            if (g == 0 && m == 0) tc_mma_f16_ts<false>(d, a_t, b_lo);        // K step i: 16 fp16 = 8 columns of A
+                            else tc_mma_f16_ts<true>(d, a_t + (uint32_t)(8 * i), b_lo + (uint32_t)(pl * ((T16_N * 128) >> 4) + 2 * i));
+                        }
+                        tc_commit(&afree[sa]);
+                        if (g == 1) {
+                            tc_commit(&bfree[sb]);
+                            tc_commit(&mma_done[t]);
+                        }
+                    }
+                    __syncwarp();
+                }
+                if (!ok) break;
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (wid == ISSUER) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    }
+}
+
+}  // namespace b200

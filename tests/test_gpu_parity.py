@@ -510,13 +510,52 @@ def test_gemm_tensor_core_ints_and_bound(gpu, port, n_out, n_in, n_tok):
     assert not (host(sums) == -12345).any()          # every (row, token, chunk) was produced
     Y2 = torch.full((n_out, n_tok), 555.0, dtype=torch.float32, device="cuda")
     try:
-        assert gpu.set_option("gemm_path", 2 if n_tok <= 8 else 1) == 0
+        assert gpu.set_option("gemm_path", 2 if n_tok <= 8 else 3) == 0
         assert gpu.gemm(Wd, Xqd, Y2, n_out, n_in, n_tok) == 0
         torch.cuda.synchronize()
     finally:
         gpu.set_option("gemm_path", -1)
     assert np.array_equal(bits(host(Y2)), bits(host(Y)))
     assert gpu.device_status() == 0
+
+
+@pytest.mark.parametrize("n_out,n_in,n_tok", [(128, 1024, 64), (300, 1024, 100), (256, 5120, 128), (129, 2048, 65),
+                                              (6400, 1024, 384), (19072, 1024, 130), (1000, 17408, 48), (5120, 5120, 512)])
+def test_gemm_tensor_core_fp16_bound(gpu, port, n_out, n_in, n_tok):
+    """The fp16 tensor-core mat-mul (gemm_path 1: activations split into two fp16 planes, whole blocks accumulated in
+    tensor memory, csrc/gemm_tc16.cuh): Y within 1e-5 of max |Y| of the host loop on sampled rows, every element
+    written, the same bits on a second call.  Full tiles, ragged rows and tokens, tiles cut in two between CTAs; a
+    second shape on the same stream (the scratch grows), and large activation ranges (per-token power-of-two scale)."""
+    import torch
+    W = synth.pq2_0_weights(n_out, n_in, seed=n_tok + 3)
+    X = synth.activations(n_in, seed=n_out + 1, batch=n_tok)
+    X[::3] *= 1000.0                                    # tokens of very different magnitude
+    X[1::7] *= 1e-4
+    Xq = port.quantize_batch_chunk_major(X)
+    Wd, Xqd = dev(W), dev(Xq)
+    Y = torch.full((n_out, n_tok), float("nan"), dtype=torch.float32, device="cuda")
+    Y2 = torch.full((n_out, n_tok), float("nan"), dtype=torch.float32, device="cuda")
+    try:
+        assert gpu.set_option("gemm_path", 1) == 0
+        assert gpu.gemm(Wd, Xqd, Y, n_out, n_in, n_tok) == 0
+        assert gpu.gemm(Wd, Xqd, Y2, n_out, n_in, n_tok) == 0
+        torch.cuda.synchronize()
+    finally:
+        gpu.set_option("gemm_path", -1)
+    assert gpu.device_status() == 0
+    y = host(Y)
+    assert np.isfinite(y).all()
+    assert np.array_equal(bits(y), bits(host(Y2)))
+    rows = np.unique(np.concatenate([np.arange(min(n_out, 130)), np.arange(max(0, n_out - 130), n_out),
+                                     np.linspace(0, n_out - 1, 64).astype(np.int64)]))
+    row_bytes = n_in // 128 * 34
+    Wsub = np.concatenate([W[r * row_bytes:(r + 1) * row_bytes] for r in rows])
+    want = port.gemm(Wsub, Xq, len(rows), n_in, n_tok, threads=8)
+    # the bound is per token: tokens differ by seven orders of magnitude here
+    for t in range(n_tok):
+        ref = want[:, t]
+        err = np.abs(y[rows, t] - ref).max()
+        assert err <= 1e-5 * max(np.abs(ref).max(), 1e-30), (t, err, np.abs(ref).max())
 
 
 def test_gemm_default_dispatch(gpu, port):
