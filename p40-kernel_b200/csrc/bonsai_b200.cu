@@ -928,9 +928,13 @@ static int launch_gemm_tc16(const void *W, const void *Xq, float *Y, int64_t n_o
     P.epoch = g_gemm_epoch.fetch_add(1) + 1u;
     const int n_chunks = (int)(n_in / 32);
     const uint32_t *x32 = static_cast<const uint32_t *>(Xq);
-    tc16_tokscale_kernel<<<(unsigned)((n_tok + 31) / 32), 256, 0, st>>>(x32, n_chunks, (int)n_tok, scale);
-    const long long items = (long long)n_chunks * n_tok;
-    tc16_split_kernel<<<(unsigned)((items + 255) / 256), 256, 0, st>>>(x32, n_chunks, (int)n_tok, scale, planes);
+    unsigned int *maxd = reinterpret_cast<unsigned int *>(scale + n_tok);
+    e = cudaMemsetAsync(maxd, 0, (size_t)n_tok * sizeof(unsigned int), st);
+    if (e != cudaSuccess) return (int)e;
+    const int slices = n_chunks >= 64 ? 16 : 1;
+    tc16_tokmax_kernel<<<dim3((unsigned)((n_tok + 31) / 32), (unsigned)slices), 256, 0, st>>>(x32, n_chunks, (int)n_tok, maxd);
+    const long long warps = ((n_tok + 3) / 4) * (long long)((n_chunks + 7) / 8);
+    tc16_split_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, st>>>(x32, n_chunks, (int)n_tok, maxd, scale, planes);
     static SmemOptIn opt;
     e = opt.ensure(gemm_tc16_kernel);
     if (e != cudaSuccess) return (int)e;

@@ -19,8 +19,8 @@
 // CTA tile 128 rows x 64 tokens, one CTA per SM, K stepped one weight block at a time = 16 MMAs (M 128, N 64, K 16):
 // two K halves of 64 values x {H, L} x four K = 16 steps, all into one 64-column accumulator (4 in flight).
 //   warps 0-7   : epilogue: per block two tcgen05.ld of 16 columns, acc += dw * D (one row x 32 tokens per thread)
-//   warps 8-23  : code producers: thread (row p, K quarter h) turns 32 two-bit codes into 32 fp16 (half of a 128-byte
-//                 swizzled row) with byte permutes: the fp16 patterns of -1, 0, 1, 2 differ only in their high byte
+//   warps 8-23  : code producers: thread (row p, K half g), every second block: 64 two-bit codes -> 64 fp16 with byte
+//                 permutes (the fp16 patterns of -1, 0, 1, 2 differ only in their high byte), written to tensor memory
 //   warps 24-25 : issuers (alternate blocks)
 //   warps 26-27 : loaders (tiled TMA copies): weight pieces of 8 blocks x 128 rows; per block two boxes of 64 values x
 //                 64 tokens x {H, L}, landing swizzled as the MMA reads them
@@ -82,6 +82,17 @@ __device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t (&v)[16])
           "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
         : "memory");
 }
+__device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};\n"
+        ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+          "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]),
+          "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]),
+          "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+        : "memory");
+}
 __device__ __forceinline__ void tc_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map, int x, int y, int z, uint64_t *bar) {
     asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
@@ -106,40 +117,46 @@ __device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, i
 }
 
 // ---- once per call: the activations as two fp16 planes ------------------------------------------------------------
-// scale[tok] = 2^-S, scale[n_tok + tok] = 2^S with S = 8 - exponent(max_c da_c): every |da * a * 2^S| < 2^15.
-__global__ void __launch_bounds__(256) tc16_tokscale_kernel(const uint32_t *__restrict__ Xq, int n_chunks, int n_tok,
-                                                            float *__restrict__ scale) {
-    __shared__ float part[8][32];
+// maxd[tok] = bits of the largest chunk scale of the token (non-negative floats order like their bit patterns);
+// zeroed by the caller.  Block = 32 tokens x 8 chunk lanes, grid.y slices the chunks.
+__global__ void __launch_bounds__(256) tc16_tokmax_kernel(const uint32_t *__restrict__ Xq, int n_chunks, int n_tok,
+                                                          unsigned int *__restrict__ maxd) {
     const int tl = threadIdx.x & 31, grp = threadIdx.x >> 5;
     const int tok = blockIdx.x * 32 + tl;
-    float m = 0.0f;
-    if (tok < n_tok)
-        for (int c = grp; c < n_chunks; c += 8)
-            m = fmaxf(m, f16_bits_to_f32(__ldg(Xq + 9 * ((size_t)c * n_tok + tok)) & 0xFFFFu));
-    part[grp][tl] = m;
-    __syncthreads();
-    if (grp == 0 && tok < n_tok) {
-#pragma unroll
-        for (int g = 1; g < 8; ++g) m = fmaxf(m, part[g][tl]);
-        int ex = 0;
-        if (m > 0.0f) (void)frexpf(m, &ex);            // m = f * 2^ex, 0.5 <= f < 1  =>  m * 128 < 2^(ex + 7)
-        const int S = m > 0.0f ? 8 - ex : 0;
-        scale[tok] = ldexpf(1.0f, -S);
-        scale[n_tok + tok] = ldexpf(1.0f, S);
-    }
+    if (tok >= n_tok) return;
+    const int per = (n_chunks + (int)gridDim.y - 1) / (int)gridDim.y;
+    const int c0 = (int)blockIdx.y * per, c1 = min(n_chunks, c0 + per);
+    unsigned int m = 0;
+    for (int c = c0 + grp; c < c1; c += 8) m = max(m, __ldg(Xq + 9 * ((size_t)c * n_tok + tok)) & 0x7FFFu);
+    if (m) atomicMax(maxd + tok, m);
+}
+// 2^S for the token: S = 8 - exponent(max_c da_c), so that every |da * a * 2^S| < 2^15 (da = f * 2^ex, 0.5 <= f < 1,
+// times 128 is below 2^(ex + 7)).
+__device__ __forceinline__ int tc16_shift(unsigned int maxd_bits) {
+    const float m = f16_bits_to_f32(maxd_bits);
+    int ex = 0;
+    if (m > 0.0f) (void)frexpf(m, &ex);
+    return m > 0.0f ? 8 - ex : 0;
 }
 // Thread = (chunk, token): 32 values -> 32 + 32 fp16, in the order the quantiser stored them (the order in which the
-// code producers emit the codes).  planes: H at [tok][n_in], L at [n_tok + tok][n_in].
+// code producers emit the codes).  planes: H at [tok][n_in], L at [n_tok + tok][n_in]; scale[tok] = 2^-S for the
+// epilogue.  A warp takes 4 tokens x 8 consecutive chunks: its stores are four runs of 512 bytes per plane.
 __global__ void __launch_bounds__(256) tc16_split_kernel(const uint32_t *__restrict__ Xq, int n_chunks, int n_tok,
-                                                         const float *__restrict__ scale, __half *__restrict__ planes) {
-    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= (long long)n_chunks * n_tok) return;
-    const int c = (int)(i / n_tok), tok = (int)(i - (long long)c * n_tok);
-    const uint32_t *src = Xq + 9 * (size_t)i;
+                                                         const unsigned int *__restrict__ maxd, float *__restrict__ scale,
+                                                         __half *__restrict__ planes) {
+    const int lane = threadIdx.x & 31;
+    const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int cgroups = (n_chunks + 7) >> 3;
+    const int tg = (int)(warp / cgroups), cgp = (int)(warp - (long long)tg * cgroups);
+    const int tok = 4 * tg + (lane >> 3), c = 8 * cgp + (lane & 7);
+    if (tok >= n_tok || c >= n_chunks) return;
+    const int S = tc16_shift(maxd[tok]);
+    if (c == 0) scale[tok] = ldexpf(1.0f, -S);
+    const uint32_t *src = Xq + 9 * ((size_t)c * n_tok + tok);
     uint32_t w[9];
 #pragma unroll
     for (int k = 0; k < 9; ++k) w[k] = __ldg(src + k);
-    const float ds = __fmul_rn(f16_bits_to_f32(w[0] & 0xFFFFu), scale[n_tok + tok]);        // da * 2^S: exact (a power of two)
+    const float ds = __fmul_rn(f16_bits_to_f32(w[0] & 0xFFFFu), ldexpf(1.0f, S));        // da * 2^S: exact (a power of two)
     const size_t n_in = (size_t)n_chunks * 32;
     uint4 *hp = reinterpret_cast<uint4 *>(planes + (size_t)tok * n_in + (size_t)c * 32);
     uint4 *lp = reinterpret_cast<uint4 *>(planes + ((size_t)n_tok + tok) * n_in + (size_t)c * 32);
@@ -201,7 +218,7 @@ __global__ void __launch_bounds__(T16_THREADS, 1) gemm_tc16_kernel(float *Y, con
     const int nblocks = P.nblocks, n_tok = P.n_tok, n_out = P.n_out;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < T16_NA; ++s) { mbar_init(&afull[s], T16_PROD_THREADS / 2); mbar_init(&afree[s], 1); }
+        for (int s = 0; s < T16_NA; ++s) { mbar_init(&afull[s], T16_PROD_THREADS / 4); mbar_init(&afree[s], 1); }
         for (int s = 0; s < T16_NB; ++s) { mbar_init(&bfull[s], 1); mbar_init(&bfree[s], 1); }
         for (int s = 0; s < T16_ACC; ++s) { mbar_init(&mma_done[s], 1); mbar_init(&tmem_empty[s], T16_EPI_WARPS); }
         for (int s = 0; s < T16_WBUFS; ++s) { mbar_init(&wfull[s], 1); mbar_init(&wfree[s], T16_PROD_THREADS); }
@@ -305,42 +322,58 @@ __global__ void __launch_bounds__(T16_THREADS, 1) gemm_tc16_kernel(float *Y, con
             }
         }
     } else if (wid < ISSUER) {
-        // ---------------- code producers: thread (row p, K quarter h): 32 codes -> 64 bytes of the row ----------------
+        // ---------------- code producers: thread (row p, K half g) of every second block: 64 codes -> 64 fp16 ----------------
         const int pi = threadIdx.x - T16_EPI_THREADS;
         // A warp reaches only the 32 tensor-memory lanes of its own quarter (warp index mod 4): producer warp pw takes
-        // rows 32 (pw % 4) + lane and K quarter pw / 4.
-        const int pw = pi >> 5, h = pw >> 2, p = 32 * (pw & 3) + lane, g = h >> 1;          // g: the K half (its own barriers)
-        const uint32_t a_lane = tmem_base + ((uint32_t)(32 * (pw & 3)) << 16) + (uint32_t)(T16_A_COL0 + 16 * (h & 1));
+        // rows 32 (pw % 4) + lane, K half (pw / 4) % 2, and the blocks n with n % 2 == pw / 8.  Two sets on alternate
+        // blocks because a warp's own chain per block -- raw loads, expansion, tcgen05.st, wait::st, fence, arrive -- is
+        // ~1300 cycles long and was the kernel's period when every warp took every block.  The store of one block is
+        // completed (wait::st, fence, arrive) only after the NEXT own block has been loaded and expanded.
+        const int pw = pi >> 5, p = 32 * (pw & 3) + lane, g = (pw >> 2) & 1, set = pw >> 3;
+        const uint32_t a_lane = tmem_base + ((uint32_t)(32 * (pw & 3)) << 16) + (uint32_t)T16_A_COL0;
         bool ok = true;
-        int n = 0, oct = 0;
+        int n = 0, oct = 0, pending = -1;           // pending: slot whose store is in flight
         while (ok && walk.next(P, tile, kb0, kb1)) {
             for (int kb = kb0; kb < kb1; ++kb, ++n) {
-                const int u = 2 * n + g, sa = u % T16_NA;
                 if (kb == kb0 || (kb & 7) == 0) {
                     if (!mbar_wait_bounded(&wfull[oct % T16_WBUFS], (uint32_t)((oct / T16_WBUFS) & 1))) { ok = false; break; }
                     ++oct;
                 }
                 const int wbuf = (oct - 1) % T16_WBUFS;
-                // The quarter's two code words sit at byte 34 j + 2 + 8 h of the row's 272-byte piece, 2-byte aligned:
-                // three aligned words and a funnel shift by 0 or 16 bits.  (Rows are 68 words apart: a warp's loads
-                // spread over eight banks, four passes each -- as many as 16-byte loads of the whole block would take.)
-                const uint32_t off = (uint32_t)(kb & 7) * 34u + 2u + 8u * (uint32_t)h;
-                const uint8_t *rowp = wraw + (size_t)wbuf * TC_WRAW_BYTES + (size_t)p * 272;
-                const uint32_t *wa = reinterpret_cast<const uint32_t *>(rowp + (off & ~3u));
-                const uint32_t x0 = wa[0], x1 = wa[1], x2 = wa[2], sh = (off & 2u) * 8u;
-                const uint32_t dbits = h == 0 ? (uint32_t)*reinterpret_cast<const unsigned short *>(rowp + (kb & 7) * 34) : 0u;
-                uint32_t pc[16];
-                tc16_expand(__funnelshift_r(x0, x1, sh), pc);
-                tc16_expand(__funnelshift_r(x1, x2, sh), pc + 8);
-                if (!mbar_wait_bounded(&afree[sa], (uint32_t)(((u / T16_NA) & 1) ^ 1), 20, 80)) { ok = false; break; }
-                tc_fence_after();
-                if (h == 0) dwring[(n & (T16_DWRING - 1)) * T16_M + p] = f16_bits_to_f32(dbits);
-                tc_st16(a_lane + (uint32_t)(sa * T16_A_UNIT_COLS), pc);     // 32 fp16 = 16 columns of this thread's lane
-                tc_st_wait();
-                tc_fence_before();
-                mbar_arrive(&afull[sa]);
+                if ((n & 1) == set) {
+                    const int u = 2 * n + g, sa = u % T16_NA;
+                    // The half's four code words sit at byte 34 j + 2 + 16 g of the row's 272-byte piece, 2-byte aligned:
+                    // five aligned words and funnel shifts by 0 or 16 bits.  (Rows are 68 words apart: a warp's loads
+                    // spread over eight banks, four passes each.)
+                    const uint32_t off = (uint32_t)(kb & 7) * 34u + 2u + 16u * (uint32_t)g;
+                    const uint8_t *rowp = wraw + (size_t)wbuf * TC_WRAW_BYTES + (size_t)p * 272;
+                    const uint32_t *wa = reinterpret_cast<const uint32_t *>(rowp + (off & ~3u));
+                    const uint32_t x0 = wa[0], x1 = wa[1], x2 = wa[2], x3 = wa[3], x4 = wa[4], sh = (off & 2u) * 8u;
+                    const uint32_t dbits = g == 0 ? (uint32_t)*reinterpret_cast<const unsigned short *>(rowp + (kb & 7) * 34) : 0u;
+                    uint32_t pc[32];
+                    tc16_expand(__funnelshift_r(x0, x1, sh), pc);
+                    tc16_expand(__funnelshift_r(x1, x2, sh), pc + 8);
+                    tc16_expand(__funnelshift_r(x2, x3, sh), pc + 16);
+                    tc16_expand(__funnelshift_r(x3, x4, sh), pc + 24);
+                    if (pending >= 0) {
+                        tc_st_wait();
+                        tc_fence_before();
+                        mbar_arrive(&afull[pending]);
+                    }
+                    if (!mbar_wait_bounded(&afree[sa], (uint32_t)(((u / T16_NA) & 1) ^ 1), 20, 80)) { ok = false; pending = -1; break; }
+                    tc_fence_after();
+                    if (g == 0) dwring[(n & (T16_DWRING - 1)) * T16_M + p] = f16_bits_to_f32(dbits);
+                    tc_st32(a_lane + (uint32_t)(sa * T16_A_UNIT_COLS), pc);     // 64 fp16 = 32 columns of this thread's lane
+                    pending = sa;
+                }
+                // every producer passes every block: at a piece's last block it has read all it needs of the piece
                 if ((kb & 7) == 7 || kb == kb1 - 1) mbar_arrive(&wfree[wbuf]);
             }
+        }
+        if (pending >= 0) {
+            tc_st_wait();
+            tc_fence_before();
+            mbar_arrive(&afull[pending]);
         }
     } else if (wid == LOADER) {
         // ---------------- weight loader: a piece (8 blocks x 128 rows, one tiled copy) as soon as its buffer is free ----------------
