@@ -160,13 +160,15 @@ __global__ void __launch_bounds__(256) tc16_split_kernel(const uint32_t *__restr
     const size_t n_in = (size_t)n_chunks * 32;
     uint4 *hp = reinterpret_cast<uint4 *>(planes + (size_t)tok * n_in + (size_t)c * 32);
     uint4 *lp = reinterpret_cast<uint4 *>(planes + ((size_t)n_tok + tok) * n_in + (size_t)c * 32);
+    const int8_t *ab = reinterpret_cast<const int8_t *>(w + 1);      // the chunk's 32 int8 in stored order
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {                       // 8 values per 16-byte store
+    for (int q = 0; q < 4; ++q) {                       // 8 values per 16-byte store, in the order of tc16_expand
         uint32_t h[4], l[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-            const uint32_t word = w[1 + 2 * q + (e >> 1)];
-            const int a0 = (int)(int8_t)(word >> (16 * (e & 1))), a1 = (int)(int8_t)(word >> (16 * (e & 1) + 8));
+            constexpr unsigned char PERM[16] = {0, 8, 1, 9, 4, 12, 5, 13, 2, 10, 3, 11, 6, 14, 7, 15};
+            const int j0 = 16 * (q >> 1) + PERM[8 * (q & 1) + 2 * e], j1 = 16 * (q >> 1) + PERM[8 * (q & 1) + 2 * e + 1];
+            const int a0 = (int)ab[j0], a1 = (int)ab[j1];
             const float v0 = __fmul_rn(ds, (float)a0), v1 = __fmul_rn(ds, (float)a1);      // exact: 11 x 7 bits
             const __half h0 = __float2half_rn(v0), h1 = __float2half_rn(v1);
             const __half l0 = __float2half_rn(__fsub_rn(v0, __half2float(h0))), l1 = __float2half_rn(__fsub_rn(v1, __half2float(h1)));
@@ -178,19 +180,27 @@ __global__ void __launch_bounds__(256) tc16_split_kernel(const uint32_t *__restr
     }
 }
 
-// 16 two-bit codes of one word -> 16 fp16 (-1, 0, 1, 2) in eight words, element 4 k + b = field k of byte b
-// (the order of the quantiser's words, src/pq2_0.h:120-125, 158-166).  The four fp16 patterns 0xBC00, 0x0000, 0x3C00,
-// 0x4000 have a zero low byte, so a byte permute with the code as selector builds two of them at once.
+// 16 two-bit codes of one word -> 16 fp16 (-1, 0, 1, 2) in eight words.  The four fp16 patterns 0xBC00, 0x0000, 0x3C00,
+// 0x4000 have a zero low byte, so the high bytes are looked up four at a time by a byte permute whose selector nibbles
+// ARE the codes (w & 0x3333 leaves a code in every nibble), and a second permute spreads them over two words.  19
+// integer instructions per word: the expansion runs on the half-rate integer pipe, which this kernel keeps busiest.
+// Order of the 16 values (the split kernel writes the activations in the same order): code (byte b, field k)
+// of the word pairs with activation byte 4 k + b of the word's 16 (src/pq2_0.h:120-125, 158-166);
+//   o[0..1] = (b0k0 b0k2 b1k0 b1k2)   o[2..3] = (b0k1 b0k3 b1k1 b1k3)   o[4..5], o[6..7]: the same for bytes 2, 3.
 __device__ __forceinline__ void tc16_expand(uint32_t w, uint32_t *o) {
     constexpr uint32_t TB = 0x403C00BCu;
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-        const uint32_t t = (w >> (2 * k)) & 0x03030303u;
-        o[2 * k] = __byte_perm(TB, 0u, (t << 4) + 0x0404u);
-        o[2 * k + 1] = __byte_perm(TB, 0u, (t >> 12) + 0x0404u);
-    }
+    const uint32_t wh = w >> 16;
+    const uint32_t s0 = w & 0x3333u, s1 = (w >> 2) & 0x3333u, s2 = wh & 0x3333u, s3 = (wh >> 2) & 0x3333u;
+    const uint32_t h0 = __byte_perm(TB, 0u, s0), h1 = __byte_perm(TB, 0u, s1), h2 = __byte_perm(TB, 0u, s2), h3 = __byte_perm(TB, 0u, s3);
+    o[0] = __byte_perm(h0, 0u, 0x1404u);
+    o[1] = __byte_perm(h0, 0u, 0x3424u);
+    o[2] = __byte_perm(h1, 0u, 0x1404u);
+    o[3] = __byte_perm(h1, 0u, 0x3424u);
+    o[4] = __byte_perm(h2, 0u, 0x1404u);
+    o[5] = __byte_perm(h2, 0u, 0x3424u);
+    o[6] = __byte_perm(h3, 0u, 0x1404u);
+    o[7] = __byte_perm(h3, 0u, 0x3424u);
 }
-
 struct Tc16Maps {
     CUtensorMap w;        // PQ2_0 matrix as [n_out][row words], box 68 x 128
     CUtensorMap x;        // fp16 planes as [2][n_tok][n_in], box 64 values x 64 tokens x 2 planes, 128-byte swizzle
