@@ -848,6 +848,9 @@ def prefill_leg(args, torch, bb, dist):
         Y = torch.empty(n_out, n_tok, device="cuda")
         mats.append((n_in, n_out, W, X, Xq, Y))
 
+    path = getattr(args, "gemm_path", -1)
+    bb.set_option("gemm_path", path)
+
     def step():
         for n_in, n_out, W, X, Xq, Y in mats:
             assert bb.quant_batch(X, None, Xq, n_in, n_tok, True) == 0
@@ -874,7 +877,7 @@ def prefill_leg(args, torch, bb, dist):
             Yref = torch.empty(rows, n_tok, device="cuda")
             bb.set_option("gemm_path", 0)
             assert bb.gemm(Wsub, Xq, Yref, rows, n_in, n_tok) == 0
-            bb.set_option("gemm_path", -1)
+            bb.set_option("gemm_path", path)
             torch.cuda.synchronize()
             got = Y[r0:r0 + rows]
             rel = float(((got - Yref).abs().max() / Yref.abs().max()).item())
@@ -886,7 +889,11 @@ def prefill_leg(args, torch, bb, dist):
     ops = sum(2.0 * n_tok * a * b for a, b, *_ in mats)
     tops = ops / (ms_step * 1e-3) / 1e12
     _, bf16, kind = measured_peaks()
-    peak = 2.0 * bf16
+    # The default kernel runs fp16 MMAs, two per useful product (the activations are split into two exact fp16 halves):
+    # the denominator is the measured dense bf16 peak, and the kernel's own ceiling is half of it.  The integer
+    # tensor-core kernel (--gemm-path 3) is held against twice that peak (int8).
+    fp16_form = path in (-1, 1)
+    peak = bf16 if fp16_form else 2.0 * bf16
     # a dense int8 figure measured here, beside the denominator above: the library's int8 mat-mul (cuBLASLt through
     # torch._int_mm) on 8192^3, best of 10 -- a measuring stick, not on the path
     int8_lib = None
@@ -909,7 +916,12 @@ def prefill_leg(args, torch, bb, dist):
         pass
     return {"metric": "pq2_0_prefill_gemm", "value": tops, "unit": "TOPS", "n_tok": n_tok, "ms_per_step": ms_step,
             "steps": steps, "passes_per_step": reps, "gpu_launches": 4 * steps * reps, "per_matrix": per,
-            "frac": tops / peak, "peak": peak, "peak_kind": f"2 x {kind} dense bf16",
+            "frac": tops / peak, "peak": peak,
+            "peak_kind": (f"{kind} dense bf16; the kernel issues two fp16 MMAs per useful product, its ceiling is half"
+                          if fp16_form else f"2 x {kind} dense bf16 (int8)"),
+            "kernel": "gemm_tc16_kernel (fp16 split)" if fp16_form else ("gemm_tc_kernel (int8)" if path == 3 else f"gemm_path {path}"),
+            "dtype": ("fp16 x fp16 -> fp32 (tcgen05), activations int8 x fp16 split exactly into two fp16" if fp16_form
+                      else "int8 x int8 -> int32 (tcgen05), fp32 scale"),
             "library_int8_dense_tops_measured": int8_lib,
             "parity": {"checked_rows_per_matrix": rows, "mismatches": bad, "max_rel_to_max_abs": worst_rel, "bound": 1e-5,
                        "against": "the integer SIMT mat-mul (host-loop bits) on the same rows"},
@@ -926,8 +938,8 @@ def run_prefill(args):
         "metric": leg["metric"], "value": leg["value"], "unit": "TOPS", "n_gpus": 1, "steps": leg["steps"],
         "warmup": max(3, min(args.warmup, 5)), "ms_per_step": leg["ms_per_step"] * leg["passes_per_step"],
         "higher_is_better": True, "scaling": "strong",
-        "vs_baseline": None, "dtype": "int8 x int8 -> int32 (tcgen05), fp32 scale", "data": "synthetic",
-        "config": {"workload": "prefill", "n_tok": leg["n_tok"], "shapes_nin_nout": [[5120, 17408], [17408, 5120]],
+        "vs_baseline": None, "dtype": leg["dtype"], "data": "synthetic",
+        "config": {"workload": "prefill", "kernel": leg["kernel"], "n_tok": leg["n_tok"], "shapes_nin_nout": [[5120, 17408], [17408, 5120]],
                    "launch": "cuda_graph_per_step", "passes_per_step": leg["passes_per_step"], "per_matrix": leg["per_matrix"]},
         "gpu_launches": leg["gpu_launches"], "clocks": leg["clocks"], "parity": leg["parity"],
         "roofline": {"bound": "tensor", "achieved": leg["value"], "peak": leg["peak"], "unit": "TOPS", "frac": leg["frac"],
@@ -1107,6 +1119,8 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from Python instead of replaying a graph")
     ap.add_argument("--single", type=int, nargs=2, metavar=("N_IN", "N_OUT"), help="profiling aid: launch one shape only")
     ap.add_argument("--copies", type=int, default=8)
+    ap.add_argument("--gemm-path", type=int, default=-1, help="prefill workload: -1 default kernel choice, 3 the integer "
+                    "tensor-core kernel, 0 the integer SIMT kernel (bonsai_b200_set_option gemm_path)")
     ap.add_argument("--order", type=int, default=-1, help="1: the mat-vec that keeps the host's summation order")
     args = ap.parse_args()
     if args.single:

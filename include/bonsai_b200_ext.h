@@ -115,10 +115,12 @@ int bonsai_b200_stream_probe(const void *buf, int64_t bytes, int mode, void *sin
  * (csrc/gemv_mma.cuh: same terms, another fixed tree; measured slower than 0 at batch 1, kept as the measured
  * alternative and as the body of the 2 .. 8 token kernel).
  * key "gemm_path": -1 (default) = the mat-mul picks its kernel by token count (2 .. 8 tokens: the streaming
- * small-batch kernel; 48 tokens and more: tcgen05; else the integer SIMT kernel), 0 = integer SIMT kernel (Y
- * bit-identical to the host loop), 1 = tcgen05 tensor-core kernel, 2 = the small-batch kernel where it takes the
- * shape.  All give the host's int32 chunk sums; 1 and 2 hold fp32 Y to 1e-5 of max |Y| (csrc/gemm_tc.cuh,
- * csrc/gemv_mma.cuh).
+ * small-batch kernel; 48 tokens and more: the tensor cores; else the integer SIMT kernel), 0 = integer SIMT kernel (Y
+ * bit-identical to the host loop), 1 = tensor cores (the fp16 form, csrc/gemm_tc16.cuh, where it takes the call,
+ * else the integer form), 2 = the small-batch kernel where it takes the shape, 3 = the integer tensor-core kernel
+ * (csrc/gemm_tc.cuh: forms the host's int32 chunk sums, needs no scratch).  1, 2 and 3 hold fp32 Y to 1e-5 of
+ * max |Y|.  The fp16 form keeps one scratch buffer per (device, stream), 4 bytes per token and input value, allocated
+ * with cudaMalloc on first use or growth -- never while the stream is being captured (then the integer form runs).
  * key "fuse_linear": 0 (default) = bonsai_b200_linear is two launches, 1 = one kernel when it can (saves a
  * launch, but every CTA then waits for its own rotation before its first multiply: measured ~6 % slower
  * on the 401-projection decode chain).
