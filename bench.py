@@ -265,6 +265,10 @@ def run_b200(args):
         bb.set_option("pdl", args.pdl)
     if args.order >= 0:
         bb.set_option("gemv_order", args.order)
+    for kv in args.opt:                                 # library options by name (bonsai_b200_set_option), for sweeps
+        key, _, val = kv.partition("=")
+        if bb.set_option(key, int(val)) != 0:
+            raise SystemExit(f"--opt {kv}: the library does not know this key (tuning keys need the tuning build)")
 
     sets = args.sets
     # ---- resident tensors: weights generated on the device, row slice of this rank only ----------
@@ -1121,6 +1125,8 @@ def main():
     ap.add_argument("--copies", type=int, default=8)
     ap.add_argument("--gemm-path", type=int, default=-1, help="prefill workload: -1 default kernel choice, 3 the integer "
                     "tensor-core kernel, 0 the integer SIMT kernel (bonsai_b200_set_option gemm_path)")
+    ap.add_argument("--opt", action="append", default=[], metavar="KEY=VALUE",
+                    help="bonsai_b200_set_option(KEY, VALUE) before anything is built; may be given several times")
     ap.add_argument("--order", type=int, default=-1, help="1: the mat-vec that keeps the host's summation order")
     args = ap.parse_args()
     if args.single:
