@@ -609,7 +609,8 @@ def run_b200(args):
         sec = {}
         legs = [("batch8", batch_leg)]              # at every N; the others on one GPU
         if world == 1:
-            legs += [("decode_step", decode_step_leg), ("prefill", prefill_leg), ("repack_gemv", repack_leg)]
+            legs += [("decode_step", decode_step_leg), ("prefill", prefill_leg), ("repack_gemv", repack_leg),
+                     ("beside_the_path", beside_leg)]
         for name, leg in legs:
             try:
                 sec[name] = leg(args, torch, bb, dist)
@@ -1002,6 +1003,94 @@ def repack_leg(args, torch, bb, dist):
             "parity": {"checked": 4, "mismatches": bad, "max_rel_to_max_abs": worst, "bound": 1e-5,
                        "against": "bonsai_p40_gemv on the un-repacked matrix"},
             "device_status": bb.device_status()}
+
+
+# ---- the operators, the cache and the load-time steps beside the mat-vec path ------------------------------------
+def beside_leg(args, torch, bb, dist):
+    """Device-timed throughput of the rows next to the hot path, each on a working set larger than L2 and against the
+    bound that applies (HBM bytes that must move, or fp32 FLOP/s for the causal attention): RMSNorm, the gated delta-net
+    step over the 48 layers' state, causal attention of a 2048-token prefill, K/V append and decode attention at 32 768
+    cached positions over the 16 cached layers, PQ2_0 -> repacked layout, PQ2_0 <-> PTQ1_0.  Results are checked against
+    the CPU checker by tests/test_gpu_ops.py, test_gpu_kv.py, test_gpu_load.py; here only the status word is read."""
+    peak, _, kind = measured_peaks()
+    out = {}
+
+    def rate(fn, nbytes, launches, steps=5):
+        ms, reps, _ = timed(torch, fn, steps, 2, None, None, True)
+        us = ms * 1e3 / (steps * reps)
+        return {"GB/s": nbytes / us / 1e3, "us": us, "frac": nbytes / us / 1e3 / peak, "gpu_launches": launches}
+
+    g = torch.Generator(device="cpu").manual_seed(args.seed + 21)
+    # RMSNorm: 8192 rows of 5120 (168 MB in, 168 MB out)
+    rows, n = 8192, 5120
+    x = torch.randn(rows, n, generator=g).cuda()
+    w = torch.randn(n, generator=g).cuda()
+    y = torch.empty_like(x)
+    out["rmsnorm_8192x5120"] = rate(lambda: bb.rmsnorm(x, w, y, rows, n, 1e-6), 2 * rows * n * 4, 1)
+    del x, y
+    # delta-net step: 48 layers x [48 heads][128][128] fp32 state, read and written once (151 MB each way)
+    layers, nk, nv, K, V = 48, 16, 48, 128, 128
+    st = [torch.randn(nv, K, V, generator=g).cuda() * 0.01 for _ in range(layers)]
+    q = torch.randn(nk, K, generator=g).cuda()
+    k = torch.randn(nk, K, generator=g).cuda() * 0.1
+    v = torch.randn(nv, V, generator=g).cuda()
+    gg = -torch.rand(nv, generator=g).cuda()
+    be = torch.rand(nv, generator=g).cuda()
+    o = torch.empty(nv, V, device="cuda")
+
+    def gdn():
+        for s_ in st:
+            assert bb.gdn_step(s_, q, k, v, gg, be, o, nk, nv, K, V) == 0
+    out["gdn_step_48_layers"] = rate(gdn, 2 * layers * nv * K * V * 4, layers)
+    del st
+    # causal attention, prefill of 2048 tokens: 24 heads over 4 kv heads, head dimension 256, fp32 on the CUDA cores
+    T, H, HKV, D = 2048, 24, 4, 256
+    qa = torch.randn(T, H, D, generator=g).cuda()
+    ka = torch.randn(T, HKV, D, generator=g).cuda()
+    va = torch.randn(T, HKV, D, generator=g).cuda()
+    oa = torch.empty_like(qa)
+    ms, reps, _ = timed(torch, lambda: bb.attn(qa, ka, va, oa, T, H, HKV, D, 1.0 / 16.0), 3, 1, None, None, True)
+    us = ms * 1e3 / (3 * reps)
+    flops = 4.0 * H * D * (T * (T + 1) / 2)
+    out["attn_prefill_2048"] = {"TFLOP/s": flops / us / 1e6, "us": us, "bound": "fp32 FMA on the CUDA cores (no tensor cores: "
+                                "the reference's kernel and its test are fp32)", "gpu_launches": 1}
+    del qa, ka, va, oa
+    # K/V cache: 32 768 positions in every one of the 16 cached layers (1.14 GB of Q8_0 blocks)
+    P = 32768
+    kv = bb.KVCache(P)
+    try:
+        chunk = 4096
+        kk = torch.randn(chunk, 4, 256, generator=g).cuda()
+        vv = torch.randn(chunk, 4, 256, generator=g).cuda()
+
+        def fill():
+            for layer in range(16):
+                for p0 in range(0, P, chunk):
+                    assert kv.append_batch(layer, p0, chunk, kk, vv) == 0
+        # bytes that must move: fp32 rows in (2 x 4 x 256 x 4 per position), Q8_0 blocks out (2 x 4 x 272)
+        out["kv_append_16x32768"] = rate(fill, 16 * P * (2 * 4 * 256 * 4 + 2 * 4 * 272), 16 * (P // chunk), steps=2)
+        qd = torch.randn(24, 256, generator=g).cuda()
+        od = torch.empty(24, 256, device="cuda")
+
+        def decode():
+            for layer in range(16):
+                assert kv.attn_decode(layer, P - 1, qd, od) == 0
+        out["kv_attn_decode_16_layers_at_32768"] = rate(decode, 16 * P * 2 * 4 * 272, 32)
+    finally:
+        kv.close()
+    # load-time steps on 5120 x 17408 x 8 copies (190 MB of PQ2_0): repack (read + write), PTQ1_0 pack and unpack
+    n_in, n_out, copies = 5120, 17408, 8
+    nblk = n_out * (n_in // 128) * copies
+    W = torch.empty(nblk * 34, dtype=torch.uint8, device="cuda")
+    assert bb.synth_pq2_0(W, 0, nblk, args.seed + 5) == 0
+    Wr = torch.empty_like(W)
+    out["repack_5120x17408x8"] = rate(lambda: bb.repack(W, Wr, n_out * copies, n_in), 2 * nblk * 34, 1)
+    Pk = torch.empty(nblk * 28, dtype=torch.uint8, device="cuda")
+    c3 = torch.zeros(1, dtype=torch.int64, device="cuda")
+    out["ptq1_pack"] = rate(lambda: bb.ptq1_pack(W, Pk, nblk, c3), nblk * (34 + 28), 1)
+    out["ptq1_unpack"] = rate(lambda: bb.ptq1_unpack(Pk, Wr, nblk), nblk * (34 + 28), 1)
+    return {"metric": "rows_beside_the_path", "peak_GB/s": peak, "peak_kind": kind, "rows": out,
+            "gpu_launches": sum(v["gpu_launches"] for v in out.values()), "device_status": bb.device_status()}
 
 
 # ---- row-partitioned small batch -----------------------------------------------------------------------

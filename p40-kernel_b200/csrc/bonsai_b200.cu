@@ -1256,8 +1256,8 @@ int bonsai_p40_attn(const float *q, const float *k, const float *v, float *out, 
 namespace {
 constexpr int KVM_FULL = 16, KVM_HEADS = 24, KVM_KV_HEADS = 4, KVM_CONTEXT = 262144;
 constexpr int KVM_LINEAR = 48, KVM_V_HEADS = 48, KVM_STATE = 128;
-constexpr int KV_MAX_SPLIT = 64;
-constexpr size_t KV_SPLIT_SMEM = 128 + 4 * KV_TILE * KV_ROW + KV_TILE * KV_D * 4 + KV_MAX_GROUP * 64 * 4 + KV_MAX_GROUP * 8 * 4;
+constexpr int KV_MAX_SPLIT = KV_COMBINE_MAX;
+constexpr size_t KV_SPLIT_SMEM = KV_SPLIT_SMEM_BYTES;
 inline int64_t kv_array_bytes(int capacity) { return (int64_t)KVM_FULL * KVM_KV_HEADS * capacity * KV_ROW; }
 inline int64_t kv_gdn_bytes() { return (int64_t)KVM_LINEAR * KVM_V_HEADS * KVM_STATE * KVM_STATE * (int64_t)sizeof(float); }
 }  // namespace
@@ -1284,7 +1284,7 @@ bonsai_kv_cache *bonsai_kv_create(int capacity, bonsai_stream stream) {
     const size_t ws = (size_t)KVM_HEADS * KV_MAX_SPLIT * KV_WS * sizeof(float);
     if (cudaMalloc(&kv->d_k, (size_t)kv_array_bytes(capacity)) != cudaSuccess || cudaMalloc(&kv->d_v, (size_t)kv_array_bytes(capacity)) != cudaSuccess ||
         cudaMalloc(&kv->d_gdn, (size_t)kv_gdn_bytes()) != cudaSuccess || cudaMalloc(&kv->d_ws, ws) != cudaSuccess ||
-        cudaFuncSetAttribute(kv_attn_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)KV_SPLIT_SMEM) != cudaSuccess) {
+        cudaFuncSetAttribute(kv_attn_split_kernel<KVM_HEADS / KVM_KV_HEADS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)KV_SPLIT_SMEM) != cudaSuccess) {
         bonsai_kv_free(kv);
         return nullptr;
     }
@@ -1328,15 +1328,25 @@ int bonsai_kv_attn_decode(bonsai_kv_cache *kv, int layer, int pos, const float *
     if (!kv || !q || !out) return 1;
     if (layer < 0 || layer >= KVM_FULL) return 1;
     if (pos < 0 || pos >= kv->capacity) return 1;
-    // splits of at least 8 tiles each; at long context 64 splits x 4 kv heads = 256 CTAs of 6 warps
-    int n_split = (pos + 1 + 8 * KV_TILE - 1) / (8 * KV_TILE);
-    if (n_split > KV_MAX_SPLIT) n_split = KV_MAX_SPLIT;
+    // splits of at least 4 tiles each, and no more CTAs than are resident at once (one wave): at long context
+    // 2 CTAs per SM x 148 SMs / 4 kv heads = 74 splits
     const int grp = KVM_HEADS / KVM_KV_HEADS;
-    kv_attn_split_kernel<<<dim3((unsigned)n_split, KVM_KV_HEADS), grp * 32, KV_SPLIT_SMEM, as_stream(stream)>>>(
-        q, kv->d_k, kv->d_v, kv->d_ws, pos, n_split, KVM_KV_HEADS, kv->capacity, layer, 0.0625f, grp);
+    static int slots = 0;
+    if (slots == 0) {
+        int per_sm = 0, dev = 0, sms = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kv_attn_split_kernel<KVM_HEADS / KVM_KV_HEADS>, grp * 32, KV_SPLIT_SMEM) != cudaSuccess ||
+            cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+            return (int)cudaGetLastError();
+        slots = per_sm * sms > 0 ? per_sm * sms : 1;
+    }
+    int n_split = (pos + 1 + 4 * KV_TILE - 1) / (4 * KV_TILE);
+    if (n_split > slots / KVM_KV_HEADS) n_split = slots / KVM_KV_HEADS > 0 ? slots / KVM_KV_HEADS : 1;
+    if (n_split > KV_MAX_SPLIT) n_split = KV_MAX_SPLIT;
+    kv_attn_split_kernel<KVM_HEADS / KVM_KV_HEADS><<<dim3((unsigned)n_split, KVM_KV_HEADS), grp * 32, KV_SPLIT_SMEM, as_stream(stream)>>>(
+        q, kv->d_k, kv->d_v, kv->d_ws, pos, n_split, KVM_KV_HEADS, kv->capacity, layer, 0.0625f);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
-    kv_attn_combine_kernel<<<KVM_HEADS, 32, 0, as_stream(stream)>>>(kv->d_ws, out, n_split);
+    kv_attn_combine_kernel<<<KVM_HEADS, KV_D, 0, as_stream(stream)>>>(kv->d_ws, out, n_split);
     return (int)cudaGetLastError();
 }
 
