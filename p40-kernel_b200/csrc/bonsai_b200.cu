@@ -1233,8 +1233,8 @@ int bonsai_p40_gdn_step(float *state, const float *q, const float *k, const floa
     // rejections of src/kernels/attn_p40.cu:121-124
     if (V <= 0 || V % 32 != 0 || K <= 0 || K > GDN_KMAX) return 1;
     if (n_v_heads <= 0 || n_k_heads <= 0 || n_v_heads % n_k_heads != 0) return 1;
-    const int blocks = n_v_heads * ((V + 63) / 64);
-    gdn_step_kernel<<<blocks, 64, 0, as_stream(stream)>>>(state, q, k, v, g, beta, out, n_k_heads, n_v_heads, K, V);
+    const int blocks = n_v_heads * (V / 32);
+    gdn_step_kernel<<<blocks, GDN_WARPS * 32, 0, as_stream(stream)>>>(state, q, k, v, g, beta, out, n_k_heads, n_v_heads, K, V);
     return (int)cudaGetLastError();
 }
 
