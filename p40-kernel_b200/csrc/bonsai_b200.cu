@@ -26,6 +26,7 @@
 #include <cstring>
 #include <mutex>
 #include <new>
+#include <type_traits>
 #include <vector>
 
 using namespace b200;
@@ -1083,23 +1084,39 @@ int bonsai_p40_gemv_repack(const void *W, const float *x, float *y, int64_t n_ou
     GemvPlan p = plan_rows(n_out, row_bytes, act_bytes, 1, g_opt_gemv_variant.load());
     if (p.threads > 256) p.threads = 256;
     const dim3 grid((unsigned)p.ctas);
-    static SmemOptIn opt[6];
+    static SmemOptIn opt[12];
     auto go = [&](auto kernel, SmemOptIn &o) -> cudaError_t {
         cudaError_t err = o.ensure(kernel);
         if (err != cudaSuccess) return err;
         return launch(kernel, grid, dim3(p.threads), (size_t)p.smem_bytes, as_stream(stream), pdl,
                       static_cast<const uint8_t *>(W), x, y, (int)n_out, nb, p.rows_per_cta, p.rows_per_stage);
     };
-    cudaError_t e;
-    if (aligned16(x)) {
-        if (p.rr == 1) e = go(gemv_repack_kernel<1, true>, opt[0]);
-        else if (p.rr == 2) e = go(gemv_repack_kernel<2, true>, opt[1]);
-        else e = go(gemv_repack_kernel<4, true>, opt[2]);
-    } else {
-        if (p.rr == 1) e = go(gemv_repack_kernel<1, false>, opt[3]);
-        else if (p.rr == 2) e = go(gemv_repack_kernel<2, false>, opt[4]);
-        else e = go(gemv_repack_kernel<4, false>, opt[5]);
+    // gemv_order 1: the terms of a row added in unit order by one lane (the bits of repack_row_dot); otherwise by a warp
+    const bool tree = g_opt_gemv_order.load() != 1;
+    const bool vec = aligned16(x);
+    // the streaming kernel (ring of tiles, quantiser in the prologue) when it takes the shape: the default
+    {
+        StreamParams sp;
+        int threads = 0, smem_bytes = 0;
+        if (tree && vec && n_in % FWHT_N == 0 && plan_stream(n_out, nb, g_opt_gemv_variant.load(), sp, threads, smem_bytes)) {
+            static SmemOptIn sopt;
+            cudaError_t err = sopt.ensure(gemv_stream_kernel<true, true>);
+            if (err != cudaSuccess) return (int)err;
+            return (int)launch(gemv_stream_kernel<true, true>, dim3((unsigned)((n_out + sp.rows_per_cta - 1) / sp.rows_per_cta)),
+                               dim3(threads), (size_t)smem_bytes, as_stream(stream), pdl, static_cast<const uint8_t *>(W),
+                               static_cast<const uint32_t *>(nullptr), y, sp, x, static_cast<const float *>(nullptr),
+                               static_cast<uint32_t *>(nullptr));
+        }
     }
+    auto pick = [&](auto t, auto v, int base) -> cudaError_t {
+        constexpr bool T = decltype(t)::value, V = decltype(v)::value;
+        if (p.rr == 1) return go(gemv_repack_kernel<1, V, T>, opt[base]);
+        if (p.rr == 2) return go(gemv_repack_kernel<2, V, T>, opt[base + 1]);
+        return go(gemv_repack_kernel<4, V, T>, opt[base + 2]);
+    };
+    cudaError_t e;
+    if (tree) e = vec ? pick(std::true_type{}, std::true_type{}, 0) : pick(std::true_type{}, std::false_type{}, 3);
+    else e = vec ? pick(std::false_type{}, std::true_type{}, 6) : pick(std::false_type{}, std::false_type{}, 9);
     return (int)e;
 }
 

@@ -145,6 +145,49 @@ __device__ __forceinline__ float stream_task(const uint8_t *rowp, int bl, int b0
     return stream_task_ragged<MAXSTEPS>(rowp, bl, b0, blocks, act_q, act_s, act_i, release);
 }
 
+// The same task over the REPACKED row layout (repack.cuh: nb fp16 scales, then four planes of nb 8-byte units; the
+// unit of plane p and block b holds the codes that meet activation chunk 4 b + p): `row` is the start of the row in
+// the slot, gb the block index in the row.  Eight-byte aligned loads, no funnel shifts; same terms (dw * da) * sumi,
+// added per lane in ascending block and chunk order like the tasks above.
+template <int MAXSTEPS, typename Release>
+__device__ __forceinline__ float stream_task_repack(const uint8_t *row, int nb, int bl, int b0, int blocks, const uint32_t *act_q,
+                                                    const float *act_s, const int *act_i, Release release) {
+    uint2 cw[MAXSTEPS][4];
+    float dw[MAXSTEPS];
+    const unsigned short *sc16 = reinterpret_cast<const unsigned short *>(row);
+    const uint2 *units = reinterpret_cast<const uint2 *>(row + 2 * nb);
+#pragma unroll
+    for (int k = 0; k < MAXSTEPS; ++k) {
+        const int gb = b0 + min(bl + 8 * k, blocks - 1);
+        dw[k] = f16_bits_to_f32(sc16[gb]);
+#pragma unroll
+        for (int p = 0; p < 4; ++p) cw[k][p] = units[p * nb + gb];
+    }
+    release();
+    float acc = 0.0f;
+#pragma unroll
+    for (int k = 0; k < MAXSTEPS; ++k) {
+        const int b = bl + 8 * k;
+        if (b < blocks) {
+            const int gb = b0 + b;
+            const float4 sc = *reinterpret_cast<const float4 *>(act_s + 4 * gb);
+            const int4 in = *reinterpret_cast<const int4 *>(act_i + 4 * gb);
+            const float scale[4] = {sc.x, sc.y, sc.z, sc.w};
+            const int inits[4] = {in.x, in.y, in.z, in.w};
+            const uint32_t *aq = act_q + gb * STREAM_ACT_WORDS;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int4 lo = *reinterpret_cast<const int4 *>(aq + c * 8);
+                const int4 hi = *reinterpret_cast<const int4 *>(aq + c * 8 + 4);
+                const int a[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+                const int sumi = chunk_sumi_scaled(cw[k][c].x, cw[k][c].y, a, inits[c]);
+                acc = __fadd_rn(acc, __fmul_rn(__fmul_rn(dw[k], scale[c]), (float)sumi));
+            }
+        }
+    }
+    return acc;
+}
+
 // Shared memory: [full[256] | done[256]] [act int8: nb * 36 words] [act scale: nb * 4 floats]
 // [act -64*sum: nb * 4 ints] [partials: rows_per_cta * nseg floats] [quad counters: rows_per_cta / 4]
 // [task counter] [ring: nslot * (tr * 34 * nb + 16)].
@@ -156,7 +199,9 @@ __device__ __forceinline__ float stream_task(const uint8_t *rowp, int bl, int b0
 // blocks, rotates it (FWHT-1024, one warp per 1024-block) and quantises it straight into its own
 // shared-memory tables while its first weight tiles are in flight; CTA 0 also writes the Q8_1 blocks
 // to `xq_out` so that the caller's scratch holds what the two-launch form would have left there.
-template <bool FUSED>
+// REPACK = true (with FUSED) is bonsai_p40_gemv_repack: W is in the repacked layout and x is quantised WITHOUT a
+// rotation (src/kernels/gemv_repack_p40.cu:91-162 fuses exactly that).
+template <bool FUSED, bool REPACK = false>
 __global__ void __launch_bounds__(512, 1) gemv_stream_kernel(const uint8_t *__restrict__ W, const uint32_t *__restrict__ xq,
                                                              float *__restrict__ y, const StreamParams P,
                                                              const float *__restrict__ x, const float *__restrict__ signs,
@@ -242,7 +287,7 @@ __global__ void __launch_bounds__(512, 1) gemv_stream_kernel(const uint8_t *__re
                 first = false;
             }
             if (live) {
-                if (signs) {
+                if (!REPACK && signs) {
 #pragma unroll
                     for (int r = 0; r < 8; ++r) {
                         const float4 sg = *reinterpret_cast<const float4 *>(signs + (size_t)fb * FWHT_N + r * 128 + 4 * lane);
@@ -250,7 +295,7 @@ __global__ void __launch_bounds__(512, 1) gemv_stream_kernel(const uint8_t *__re
                         v[r][2] = __fmul_rn(v[r][2], sg.z); v[r][3] = __fmul_rn(v[r][3], sg.w);
                     }
                 }
-                fwht1024_warp(v, lane);
+                if (!REPACK) fwht1024_warp(v, lane);
 #pragma unroll
                 for (int r = 0; r < 8; ++r) {
                     uint32_t word, header;
@@ -317,10 +362,13 @@ __global__ void __launch_bounds__(512, 1) gemv_stream_kernel(const uint8_t *__re
             // a funnel shift by 16 or 0 aligns them.  Phase B multiplies from registers against the
             // broadcast activation words.  (rowp is word-aligned: rows start on a word since nb is even,
             // and so do segments since seg_blocks is even.)
-            float acc = stream_task<STREAM_STEPS>(rowp, bl, b0, blocks, act_q, act_s, act_i, [&]() {
+            auto release = [&]() {
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&done[t]);   // release: every lane's loads above are complete
-            });
+            };
+            float acc = REPACK ? stream_task_repack<STREAM_STEPS>(ring + (size_t)slot * slot_bytes + (size_t)(quad * 4 + rr) * row_bytes,
+                                                                  P.nb, bl, b0, blocks, act_q, act_s, act_i, release)
+                               : stream_task<STREAM_STEPS>(rowp, bl, b0, blocks, act_q, act_s, act_i, release);
             acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 4));
             acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 8));
             acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 16));

@@ -7,7 +7,11 @@
 // Replaces, for sm_100a, repack_pq2_0_kernel and gemv_repack_p40_kernel
 // (src/kernels/gemv_repack_p40.cu:165-192, 91-162).  The output row value is the reference's host
 // function repack_row_dot (src/pq2_0_repack.h:122-138): terms (dw * da) * (float)sumi added in
-// UNIT order, i.e. plane-major -- a different fp32 order from the plain mat-vec, kept here.
+// UNIT order, i.e. plane-major -- a different fp32 order from the plain mat-vec.  The kernel of this file keeps that
+// order when asked to (bonsai_b200_set_option("gemv_order", 1): bit-identical, its whole share resident in shared
+// memory) and otherwise adds the terms of a row by a warp; the DEFAULT of bonsai_p40_gemv_repack is the streaming
+// kernel of gemv_stream.cuh (REPACK form: ring of tiles, 8-byte aligned unit loads, the lane order of the plain
+// mat-vec, to whose result it is bit-identical) whenever the vector is 16-byte aligned and n_in a multiple of 1024.
 #pragma once
 
 #include "activation.cuh"
@@ -37,7 +41,10 @@ __global__ void __launch_bounds__(256) repack_kernel(const uint8_t *__restrict__
     }
 }
 
-template <int RR, bool VEC>
+// TREE: the terms of a row are added by a warp (lane l adds units l, l + 32, ... in ascending order, then a 5-step
+// butterfly) -- a fixed order like that of the default mat-vec, within 1e-5 of repack_row_dot; !TREE: by one lane in
+// unit order, bit-identical to repack_row_dot (bonsai_b200_set_option("gemv_order", 1)), several times slower.
+template <int RR, bool VEC, bool TREE>
 __global__ void __launch_bounds__(256) gemv_repack_kernel(const uint8_t *__restrict__ W, const float *__restrict__ x,
                                                           float *__restrict__ y, int n_out, int nb, int rows_per_cta,
                                                           int rows_per_stage) {
@@ -128,6 +135,18 @@ __global__ void __launch_bounds__(256) gemv_repack_kernel(const uint8_t *__restr
     }
     __syncthreads();
 
+    if (TREE) {
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+        for (int r = warp; r < rows_here; r += nwarp) {
+            const float *base = reinterpret_cast<const float *>(wsm) + (size_t)r * row_words + codes_w;
+            float acc = 0.0f;
+            for (int u = lane; u < nunits; u += 32) acc = __fadd_rn(acc, base[2 * u]);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, o));
+            if (lane == 0) y[row0 + r] = acc;
+        }
+        return;
+    }
     // one lane per row: terms added in unit order, four loads in flight per step
     int skew, max_skew;
     row_skew(row_words, threadIdx.x & 31, skew, max_skew);

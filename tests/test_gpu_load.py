@@ -25,9 +25,15 @@ def test_gguf_upload_repack_matvec(gpu, port, tmp_path):
     rep = gguf.upload(h, p, "blk.0.ffn_up.weight", repack=True)
     assert np.array_equal(host(rep), port.repack(W, n_out, n_in))             # the bytes of repack_row_pq2_0
     y = torch.zeros(n_out, device="cuda")
-    assert gpu.gemv_repack(rep, torch.from_numpy(x).cuda(), y, n_out, n_in) == 0
     want = port.gemv_repack(port.repack(W, n_out, n_in), x, n_out, n_in)
-    assert np.array_equal(host(y).view(np.uint32), want.view(np.uint32))      # repacked mat-vec keeps the host's order
+    assert gpu.gemv_repack(rep, torch.from_numpy(x).cuda(), y, n_out, n_in) == 0
+    assert np.abs(host(y) - want).max() <= 1e-5 * np.abs(want).max()          # default: a fixed tree order
+    try:
+        assert gpu.set_option("gemv_order", 1) == 0
+        assert gpu.gemv_repack(rep, torch.from_numpy(x).cuda(), y, n_out, n_in) == 0
+    finally:
+        gpu.set_option("gemv_order", 0)
+    assert np.array_equal(host(y).view(np.uint32), want.view(np.uint32))      # gemv_order 1 keeps the host's order
 
 
 @pytest.mark.parametrize("n_blocks", [1, 7, 4096, 100003])

@@ -363,8 +363,15 @@ def test_repack_bytes_and_gemv(gpu, port, n_out, n_in):
     want_r = port.repack(W, n_out, n_in)
     assert np.array_equal(host(Wr), want_r)
     y = torch.zeros(n_out, dtype=torch.float32, device="cuda")
-    assert gpu.gemv_repack(Wr, dev(x), y, n_out, n_in) == 0
-    assert_close_and_exact(host(y), port.gemv_repack(want_r, x, n_out, n_in))
+    want = port.gemv_repack(want_r, x, n_out, n_in)
+    assert gpu.gemv_repack(Wr, dev(x), y, n_out, n_in) == 0          # default: terms of a row added by a warp, fixed tree
+    assert_close(host(y), want)
+    y2 = torch.zeros(n_out, dtype=torch.float32, device="cuda")
+    assert gpu.gemv_repack(Wr, dev(x), y2, n_out, n_in) == 0
+    assert np.array_equal(bits(host(y2)), bits(host(y)))               # ... the same bits on every launch
+    with host_order(gpu):                                              # unit order: the bits of repack_row_dot
+        assert gpu.gemv_repack(Wr, dev(x), y, n_out, n_in) == 0
+    assert_close_and_exact(host(y), want)
 
 
 def test_repack_golden(gpu, golden):
@@ -373,7 +380,8 @@ def test_repack_golden(gpu, golden):
     assert gpu.repack(dev(golden["W"]), Wr, 12, 1024) == 0
     assert np.array_equal(host(Wr), golden["W_repacked"])
     y = torch.zeros(12, dtype=torch.float32, device="cuda")
-    assert gpu.gemv_repack(Wr, dev(golden["x"][:1024]), y, 12, 1024) == 0
+    with host_order(gpu):
+        assert gpu.gemv_repack(Wr, dev(golden["x"][:1024]), y, 12, 1024) == 0
     assert np.array_equal(bits(host(y)), golden["gemv_repack_y"])
 
 
@@ -385,12 +393,16 @@ def test_gemv_repack_every_tiling(gpu, port, variant):
     x = synth.activations(n_in, seed=variant)
     want_r = port.repack(W, n_out, n_in)
     y = torch.zeros(n_out, dtype=torch.float32, device="cuda")
+    want = port.gemv_repack(want_r, x, n_out, n_in)
     try:
         gpu.set_option("gemv_variant", variant)
         assert gpu.gemv_repack(dev(want_r), dev(x), y, n_out, n_in) == 0
+        assert_close(host(y), want)
+        with host_order(gpu):
+            assert gpu.gemv_repack(dev(want_r), dev(x), y, n_out, n_in) == 0
     finally:
         gpu.set_option("gemv_variant", -1)
-    assert_close_and_exact(host(y), port.gemv_repack(want_r, x, n_out, n_in))
+    assert_close_and_exact(host(y), want)
 
 
 # ---- mat-mul ---------------------------------------------------------------------------------------------
@@ -655,10 +667,17 @@ def test_float_vectors_at_odd_offsets(gpu, port, offset):
     Wr = torch.zeros(W.size, dtype=torch.uint8, device="cuda")
     assert gpu.repack(dev(W), Wr, n_out, n) == 0
     y = torch.zeros(n_out, device="cuda")
-    assert gpu.gemv_repack(Wr, xv, y, n_out, n) == 0
     y_al = torch.zeros(n_out, device="cuda")
+    # default order: a 16-byte aligned vector takes the streaming kernel, another one the resident kernel -- two fixed
+    # trees over the same terms; in host order both run the same kernel and agree to the bit
+    assert gpu.gemv_repack(Wr, xv, y, n_out, n) == 0
     assert gpu.gemv_repack(Wr, dev(x), y_al, n_out, n) == 0
+    assert_close(host(y), host(y_al))
+    with host_order(gpu):
+        assert gpu.gemv_repack(Wr, xv, y, n_out, n) == 0
+        assert gpu.gemv_repack(Wr, dev(x), y_al, n_out, n) == 0
     assert np.array_equal(bits(host(y)), bits(host(y_al)))
+    assert_close_and_exact(host(y), port.gemv_repack(port.repack(W, n_out, n), x, n_out, n))
     # a pointer that is not even float-aligned is refused
     raw = torch.zeros(4 * n + 64, dtype=torch.uint8, device="cuda")
     assert gpu.lib().bonsai_p40_fwht(raw.data_ptr() + 2, None, 1024, None) == 1
