@@ -60,9 +60,10 @@ int bonsai_p40_gemm(const void *W, const void *Xq, float *Y, int64_t n_out, int6
 /* Aligned repacked layout, same size as the source (row stride 34 * n_in/128): per row the
  * n_in/128 fp16 scales, then four planes of 8-byte code units.  Both calls return 1 unless
  * n_in % 128 == 0, n_out > 0 and (n_in/128) % 8 == 0.  bonsai_p40_gemv_repack takes the fp32
- * activation vector and quantises it itself (it does NOT rotate it); its y equals bonsai_p40_gemv's on the
- * un-repacked matrix bit for bit (same terms, same fixed order; within 1e-5 of the reference's repack_row_dot, whose
- * plane-major order bonsai_b200_set_option("gemv_order", 1) restores to the bit).
+ * activation vector and quantises it itself (it does NOT rotate it); its y is within 1e-5 of the reference's
+ * repack_row_dot (same terms, a fixed launch-independent order: for a 16-byte aligned x and n_in % 1024 == 0 the
+ * order of bonsai_p40_gemv, to whose result on the un-repacked matrix it is then bit-identical);
+ * bonsai_b200_set_option("gemv_order", 1) restores repack_row_dot's plane-major order to the bit.
  * Replace include/bonsai_p40.h:35-36 / src/kernels/gemv_repack_p40.cu:196,209. */
 int bonsai_p40_repack(const void *src, void *dst, int64_t n_out, int64_t n_in, bonsai_stream stream);
 int bonsai_p40_gemv_repack(const void *W, const float *x, float *y, int64_t n_out, int64_t n_in,
