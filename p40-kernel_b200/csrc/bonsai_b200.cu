@@ -1261,9 +1261,12 @@ int bonsai_p40_attn(const float *q, const float *k, const float *v, float *out, 
     if (head_dim != ATT_D || n_head_kv == 0 || (n_head % n_head_kv) != 0) return 1;
     if (n_tok <= 0 || n_head <= 0 || n_head_kv <= 0) return (n_tok <= 0) ? 0 : 1;
     if (!aligned16(k) || !aligned16(v) || !aligned4(q) || !aligned4(out)) return 1;    // rows of 256 floats: 16-byte loads
-    const long long blocks = (long long)n_head * ((n_tok + ATT_WARPS - 1) / ATT_WARPS);
+    const long long blocks = (long long)n_head * ((n_tok + ATT_QPC - 1) / ATT_QPC);
     if (blocks > INT32_MAX) return 1;
-    attn_kernel<<<(unsigned)blocks, ATT_WARPS * 32, 0, as_stream(stream)>>>(q, k, v, out, n_tok, n_head, n_head_kv, scale);
+    static SmemOptIn opt;
+    cudaError_t err = opt.ensure(attn_kernel);
+    if (err != cudaSuccess) return (int)err;
+    attn_kernel<<<(unsigned)blocks, ATT_WARPS * 32, ATT_SMEM_BYTES, as_stream(stream)>>>(q, k, v, out, n_tok, n_head, n_head_kv, scale);
     return (int)cudaGetLastError();
 }
 

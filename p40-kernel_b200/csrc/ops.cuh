@@ -147,32 +147,60 @@ __global__ void __launch_bounds__(GDN_WARPS * 32) gdn_step_kernel(float *__restr
 }
 
 // ---- causal attention, head_dim 256 ------------------------------------------------------------------------------
-// One warp per (head, query); lane l owns dimensions 8l .. 8l+7.  The eight warps of a CTA take eight consecutive
-// queries of ONE head, so they walk the same keys and values: a tile of 16 keys (K and V rows, 32 KB) is staged in
-// shared memory once per CTA and read by all eight warps.  Online softmax in the order of the reference's kernel
-// (src/kernels/attn_p40.cu:101-113): one key at a time, running maximum, rescale, accumulate.
-constexpr int ATT_D = 256, ATT_TILE = 16, ATT_WARPS = 8;
+// A warp owns FOUR consecutive queries of a head; lane l owns dimensions 8l .. 8l+7 of q and of the outputs.  The eight
+// warps of a CTA take 32 consecutive queries of ONE head, so they walk the same keys and values: a tile of 32 keys (K
+// and V rows, 64 KB) is staged in shared memory once per CTA, and every row a warp reads from it serves four queries
+// (with one query per warp the kernel was bound by shared-memory bandwidth: 2 KB read per (query, key)).  Scores: for
+// eight keys at a time the lanes' partial dot products of the 4 x 8 (query, key) pairs go through one transposing
+// reduction (31 shuffles for 32 scores instead of 5 per score), which leaves lane (query, key) with its score.  The
+// softmax step is taken a tile at a time -- one running maximum, one rescale and four exps per lane per 32 keys: the
+// online softmax of the reference's kernel (src/kernels/attn_p40.cu:101-113) with 32 keys per step instead of one.
+// fp32 on the CUDA cores throughout; outputs are held to 1e-5 of the largest output.
+constexpr int ATT_D = 256, ATT_TILE = 32, ATT_WARPS = 8, ATT_QPW = 4, ATT_QPC = ATT_WARPS * ATT_QPW;
+constexpr int ATT_SMEM_BYTES = 2 * ATT_TILE * ATT_D * 4;
+
+// part[r] of every lane -> returned value of lane r = sum over the lanes of part[r] (r = 0 .. 31).
+__device__ __forceinline__ float transpose_sum32(float (&part)[32], int lane) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const bool up = (lane & o) != 0;
+#pragma unroll
+        for (int i = 0; i < o; ++i) {
+            // the lane keeps the half of the values whose index has bit `o` equal to its own, and takes the partner's
+            const float keep = up ? part[i + o] : part[i], give = up ? part[i] : part[i + o];
+            part[i] = __fadd_rn(keep, __shfl_xor_sync(0xffffffffu, give, o));
+        }
+    }
+    return part[0];
+}
+
 __global__ void __launch_bounds__(ATT_WARPS * 32) attn_kernel(const float *__restrict__ q, const float *__restrict__ k,
                                                               const float *__restrict__ v, float *__restrict__ out,
                                                               int n_tok, int n_head, int n_head_kv, float scale) {
-    __shared__ __align__(16) float kt[ATT_TILE][ATT_D];
-    __shared__ __align__(16) float vt[ATT_TILE][ATT_D];
+    extern __shared__ __align__(16) float att_smem[];
+    float (*kt)[ATT_D] = reinterpret_cast<float (*)[ATT_D]>(att_smem);
+    float (*vt)[ATT_D] = reinterpret_cast<float (*)[ATT_D]>(att_smem + ATT_TILE * ATT_D);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int qblocks = (n_tok + ATT_WARPS - 1) / ATT_WARPS;
+    const int qblocks = (n_tok + ATT_QPC - 1) / ATT_QPC;
     const int head = blockIdx.x / qblocks, qb = blockIdx.x - head * qblocks;
-    const int qi = qb * ATT_WARPS + warp;
+    const int q0 = qb * ATT_QPC + ATT_QPW * warp;           // the warp's first query
     const int kvh = head / (n_head / n_head_kv);
-    const bool live = qi < n_tok;
-    float qreg[8], oreg[8];
+    const int myq = lane >> 3, mykk = lane & 7;             // after the reduction: lane = (query of the warp, key of the group of 8)
+    float qreg[ATT_QPW][8], oreg[ATT_QPW][8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) { qreg[i] = 0.0f; oreg[i] = 0.0f; }
-    if (live) {
-        const float *qp = q + ((size_t)qi * n_head + head) * ATT_D + 8 * lane;
+    for (int a = 0; a < ATT_QPW; ++a) {
+        const int qi = q0 + a;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) qreg[i] = __fmul_rn(qp[i], scale);
+        for (int i = 0; i < 8; ++i) { qreg[a][i] = 0.0f; oreg[a][i] = 0.0f; }
+        if (qi < n_tok) {
+            const float *qp = q + ((size_t)qi * n_head + head) * ATT_D + 8 * lane;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) qreg[a][i] = __fmul_rn(qp[i], scale);
+        }
     }
-    float m = -INFINITY, l = 0.0f;
-    const int last = min(n_tok - 1, qb * ATT_WARPS + ATT_WARPS - 1);        // keys 0 .. last serve the CTA's queries
+    float m = -INFINITY, l = 0.0f;                          // of query q0 + myq (the same in the 8 lanes of its group)
+    const int last = min(n_tok - 1, qb * ATT_QPC + ATT_QPC - 1);            // keys 0 .. last serve the CTA's queries
+    const int wlast = min(n_tok - 1, q0 + ATT_QPW - 1);                     // ... 0 .. wlast this warp's
     for (int j0 = 0; j0 <= last; j0 += ATT_TILE) {
         __syncthreads();
         const int nk = min(ATT_TILE, last + 1 - j0);
@@ -183,27 +211,87 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_kernel(const float *__res
             *reinterpret_cast<float4 *>(&vt[r][4 * c4]) = *reinterpret_cast<const float4 *>(v + src);
         }
         __syncthreads();
-        if (!live) continue;
-        for (int r = 0; r < nk && j0 + r <= qi; ++r) {
-            float part = 0.0f;
+        if (q0 >= n_tok || j0 > wlast) continue;
+        const int wn = min(nk, wlast - j0 + 1);             // keys of this tile that any of the warp's queries may see
+        float sc[4];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) part = __fadd_rn(part, __fmul_rn(qreg[i], kt[r][8 * lane + i]));
+        for (int st = 0; st < 4; ++st) {
+            sc[st] = -INFINITY;
+            if (8 * st < wn) {                              // warp-uniform
+                float part[32];
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) part = __fadd_rn(part, __shfl_xor_sync(0xffffffffu, part, o));
-            const float m_new = fmaxf(m, part);
-            const float alpha = expf(__fsub_rn(m, m_new));
-            const float p = expf(__fsub_rn(part, m_new));
-            l = __fadd_rn(__fmul_rn(l, alpha), p);
+                for (int kk = 0; kk < 8; ++kk) {
+                    const int r = 8 * st + kk;              // rows past wn hold stale data: masked below
+                    const float4 ka = *reinterpret_cast<const float4 *>(&kt[r][8 * lane]);
+                    const float4 kb = *reinterpret_cast<const float4 *>(&kt[r][8 * lane + 4]);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) oreg[i] = __fadd_rn(__fmul_rn(oreg[i], alpha), __fmul_rn(p, vt[r][8 * lane + i]));
-            m = m_new;
+                    for (int a = 0; a < ATT_QPW; ++a) {
+                        float pr = __fmul_rn(qreg[a][0], ka.x);
+                        pr = __fmaf_rn(qreg[a][1], ka.y, pr); pr = __fmaf_rn(qreg[a][2], ka.z, pr); pr = __fmaf_rn(qreg[a][3], ka.w, pr);
+                        pr = __fmaf_rn(qreg[a][4], kb.x, pr); pr = __fmaf_rn(qreg[a][5], kb.y, pr); pr = __fmaf_rn(qreg[a][6], kb.z, pr);
+                        pr = __fmaf_rn(qreg[a][7], kb.w, pr);
+                        part[8 * a + kk] = pr;
+                    }
+                }
+                const float s = transpose_sum32(part, lane);            // lane (myq, mykk): score of key j0 + 8 st + mykk
+                const int key = j0 + 8 * st + mykk;
+                sc[st] = (key <= q0 + myq && key < n_tok && q0 + myq < n_tok) ? s : -INFINITY;
+            }
+        }
+        // softmax step of the tile, per query (groups of 8 lanes)
+        float tmax = fmaxf(fmaxf(sc[0], sc[1]), fmaxf(sc[2], sc[3]));
+#pragma unroll
+        for (int o = 1; o < 8; o <<= 1) tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, o));
+        const float m_new = fmaxf(m, tmax);
+        const float alpha = m_new == -INFINITY ? 1.0f : expf(__fsub_rn(m, m_new));      // a query with no key yet
+        float p[4], psum = 0.0f;
+#pragma unroll
+        for (int st = 0; st < 4; ++st) {
+            p[st] = sc[st] == -INFINITY ? 0.0f : expf(__fsub_rn(sc[st], m_new));
+            psum = __fadd_rn(psum, p[st]);
+        }
+#pragma unroll
+        for (int o = 1; o < 8; o <<= 1) psum = __fadd_rn(psum, __shfl_xor_sync(0xffffffffu, psum, o));
+        l = __fadd_rn(__fmul_rn(l, alpha), psum);
+        m = m_new;
+#pragma unroll
+        for (int a = 0; a < ATT_QPW; ++a) {
+            const float al = __shfl_sync(0xffffffffu, alpha, 8 * a);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) oreg[a][i] = __fmul_rn(oreg[a][i], al);
+        }
+#pragma unroll
+        for (int st = 0; st < 4; ++st) {
+            if (8 * st < wn) {
+#pragma unroll
+                for (int kk = 0; kk < 8; ++kk) {
+                    const int r = 8 * st + kk;
+                    if (r < wn) {                           // warp-uniform
+                        const float4 va = *reinterpret_cast<const float4 *>(&vt[r][8 * lane]);
+                        const float4 vb = *reinterpret_cast<const float4 *>(&vt[r][8 * lane + 4]);
+#pragma unroll
+                        for (int a = 0; a < ATT_QPW; ++a) {
+                            const float pr = __shfl_sync(0xffffffffu, p[st], 8 * a + kk);
+                            oreg[a][0] = __fmaf_rn(pr, va.x, oreg[a][0]); oreg[a][1] = __fmaf_rn(pr, va.y, oreg[a][1]);
+                            oreg[a][2] = __fmaf_rn(pr, va.z, oreg[a][2]); oreg[a][3] = __fmaf_rn(pr, va.w, oreg[a][3]);
+                            oreg[a][4] = __fmaf_rn(pr, vb.x, oreg[a][4]); oreg[a][5] = __fmaf_rn(pr, vb.y, oreg[a][5]);
+                            oreg[a][6] = __fmaf_rn(pr, vb.z, oreg[a][6]); oreg[a][7] = __fmaf_rn(pr, vb.w, oreg[a][7]);
+                        }
+                    }
+                }
+            }
         }
     }
-    if (live) {
-        const float inv = __fdiv_rn(1.0f, l);
-        float *op = out + ((size_t)qi * n_head + head) * ATT_D + 8 * lane;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) op[i] = __fmul_rn(oreg[i], inv);
+    for (int a = 0; a < ATT_QPW; ++a) {
+        const int qi = q0 + a;
+        const float la = __shfl_sync(0xffffffffu, l, 8 * a);
+        if (qi < n_tok) {
+            const float inv = __fdiv_rn(1.0f, la);
+            float *op = out + ((size_t)qi * n_head + head) * ATT_D + 8 * lane;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) op[i] = __fmul_rn(oreg[a][i], inv);
+        }
     }
 }
 
