@@ -13,7 +13,8 @@ import os
 
 _PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 _ROOT = os.path.dirname(_PKG_DIR)
-LIB_PATH = os.path.join(_ROOT, "libbonsai_p40.so")
+# the in-tree build; BONSAI_B200_LIB names another build of the same library (A/B timing of two builds in one process tree)
+LIB_PATH = os.environ.get("BONSAI_B200_LIB") or os.path.join(_ROOT, "libbonsai_p40.so")
 
 W_BLOCK_BYTES = 34
 A_BLOCK_BYTES = 36
