@@ -1,6 +1,7 @@
 """Worker of test_gpu_tp.py: one process per GPU (torch.distributed.run), a list with dependent, shared-input and
 Q8_1 ops over row slices, outputs stored into every rank's buffer by the kernel; every rank compares every full
-output vector with the per-matrix entry points on the unsplit matrices, bit for bit."""
+output vector with the per-matrix entry points on the unsplit matrices, bit for bit, and sampled rows of every op
+with the CPU checker (1e-5 of the largest output)."""
 import os, sys
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, ROOT); sys.path.insert(0, os.path.join(ROOT, "p40-kernel_b200"))
@@ -83,6 +84,23 @@ for _ in range(50): g.replay()
 e1.record(); torch.cuda.synchronize()
 for i in range(n_ops):
     ok &= torch.equal(region(i), ref[i + 1])
+# ... and directly against the CPU checker, not only through the one-GPU entry points: sampled rows of every op of the
+# dependent run, the checker fed this rank's own input of the op (the previous op's assembled output)
+from oracle.oracle import Oracle
+orc = Oracle("port")
+for i in range(n_ops):
+    n_in_i, n_out_i = widths[i], widths[i + 1]
+    x_i = x0 if i == 0 else region(i - 1).cpu().numpy()
+    xq_i = orc.quantize_q8_1(orc.fwht_blocks(np.ascontiguousarray(x_i, dtype=np.float32)), True)
+    rows = np.unique(np.linspace(0, n_out_i - 1, 48).astype(np.int64))
+    row_bytes = n_in_i // 128 * 34
+    Wsub = np.concatenate([Ws[i].reshape(-1)[r * row_bytes:(r + 1) * row_bytes] for r in rows])
+    want = orc.gemv(Wsub, xq_i, len(rows), n_in_i)
+    got = region(i).cpu().numpy()[rows]
+    err = float(np.abs(got - want).max()); bound = 1e-5 * float(np.abs(want).max())
+    if not err <= bound:
+        ok = False
+        print(f"rank {rank}: op {i} differs from the CPU checker: {err:.3e} > {bound:.3e}")
 status = bb.device_status()
 print(f"rank {rank}: ok={ok} status={status} {e0.elapsed_time(e1)/50*1e3:.1f} us per run of {len(ops)} ops", flush=True)
 dist.barrier()
