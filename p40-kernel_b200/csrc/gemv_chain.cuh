@@ -397,7 +397,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_chain_kernel(const ChainOp *_
                                 }
                             }
                             if (flags & CHAIN_RMSNORM) {
-                                // the whole vector is in the registers of this round (the host refuses longer ones): slice sums
+                                // the whole vector is in the registers of this pass (the host refuses longer ones): slice sums
                                 // of squares, meet, every warp adds them in slice order, scales and applies the weights
 #pragma unroll
                                 for (int k = 0; k < UPW; ++k) {
