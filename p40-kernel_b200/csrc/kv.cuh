@@ -231,12 +231,17 @@ __global__ void __launch_bounds__(GRP * 32) kv_attn_split_kernel(const float *__
             const unsigned short *src = reinterpret_cast<const unsigned short *>(vt + (size_t)p * KV_ROW + (lane >> 2) * 34);
             const float dv = f16_bits_to_f32(src[0]);
             const unsigned short *b8 = src + 1 + 4 * (lane & 3);
+            // int8 -> fp32 without the conversion unit: the byte, with its sign bit flipped (value + 128), is placed under
+            // the exponent of 2^23 by a byte permute, and 2^23 + 128 is subtracted: exact
             float v[8];
 #pragma unroll
-            for (int h2 = 0; h2 < 4; ++h2) {
-                const unsigned short two = b8[h2];
-                v[2 * h2] = __fmul_rn((float)(int)(signed char)(two & 0xFF), dv);
-                v[2 * h2 + 1] = __fmul_rn((float)(int)(signed char)(two >> 8), dv);
+            for (int h2 = 0; h2 < 2; ++h2) {
+                const uint32_t four = ((uint32_t)b8[2 * h2] | ((uint32_t)b8[2 * h2 + 1] << 16)) ^ 0x80808080u;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float f = __uint_as_float(__byte_perm(four, 0x4B000000u, 0x7440u + (uint32_t)e));
+                    v[4 * h2 + e] = __fmul_rn(__fsub_rn(f, 8388736.0f), dv);
+                }
             }
 #pragma unroll
             for (int h = 0; h < GRP; ++h) {
