@@ -83,6 +83,13 @@ int bonsai_b200_gemv_dump(const void *W, const void *xq, float *y, int32_t *sums
 int bonsai_b200_gemm_dump(const void *W, const void *Xq, float *Y, int32_t *sums, int64_t n_out, int64_t n_in,
                           int64_t n_tok, bonsai_stream stream);
 
+/* Makes sure that the scratch buffer which bonsai_p40_gemm keeps per (device, stream) for its tensor-core form is large
+ * enough for n_tok tokens of n_in values (4 bytes each), allocating it now (cudaMalloc) if it is not.  Call it once,
+ * outside stream capture, before capturing graphs that contain bonsai_p40_gemm on `stream`: a call that would have to
+ * allocate during capture runs the integer tensor-core kernel instead, which needs no scratch and is slower.  Returns
+ * 0, 1 for bad arguments, cudaErrorMemoryAllocation (2) when the buffer cannot be had.  No reference counterpart. */
+int bonsai_b200_gemm_reserve(int64_t n_in, int64_t n_tok, bonsai_stream stream);
+
 /* PTQ1_0: the denser packing of the same ternary weights, 28 bytes per 128 weights instead of 34 (described, not
  * implemented, by the reference: docs/NEXT_STEPS.md:76-83).  Block = qs[24] (five base-3 digits per byte, weights
  * 0..119), qh[2] (four digits per byte, weights 120..127), fp16 d; digit = PQ2_0 code 0, 1, 2; weight j < 120 is digit

@@ -1044,6 +1044,12 @@ int bonsai_p40_gemm(const void *W, const void *Xq, float *Y, int64_t n_out, int6
     return (int)cudaGetLastError();
 }
 
+int bonsai_b200_gemm_reserve(int64_t n_in, int64_t n_tok, bonsai_stream stream) {
+    if (n_in <= 0 || n_in % 128 != 0 || n_tok <= 0 || n_tok > (1 << 28)) return 1;
+    const size_t bytes = 2 * (size_t)n_tok * (size_t)n_in * sizeof(__half) + 2 * (size_t)n_tok * sizeof(float);
+    return gemm_scratch(bytes, as_stream(stream)) ? 0 : (int)cudaErrorMemoryAllocation;
+}
+
 int bonsai_b200_gemm_dump(const void *W, const void *Xq, float *Y, int32_t *sums, int64_t n_out, int64_t n_in,
                           int64_t n_tok, bonsai_stream stream) {
     if (n_in <= 0 || n_in % 128 != 0 || n_out <= 0 || n_tok <= 0 || !sums) return 1;

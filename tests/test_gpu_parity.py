@@ -699,3 +699,41 @@ def test_rejections_and_stubs_on_device(gpu):
 
 def test_no_bounded_wait_gave_up(gpu):
     assert gpu.device_status() == 0
+
+
+def test_gemm_in_a_captured_graph_after_reserve(gpu, port):
+    """A caller that captures graphs reserves the mat-mul's scratch for the capturing stream first
+    (bonsai_b200_gemm_reserve); the captured launch then runs, replay after replay, with the same bits as the plain
+    call, and within the bound of the host loop.  Without the reservation a captured call still gives a result within
+    the bound (the integer tensor-core kernel, which needs no scratch)."""
+    import torch
+    n_out, n_in, n_tok = 384, 2048, 96
+    W = synth.pq2_0_weights(n_out, n_in, seed=21)
+    X = synth.activations(n_in, seed=22, batch=n_tok)
+    Xq = port.quantize_batch_chunk_major(X)
+    Wd, Xqd = dev(W), dev(Xq)
+    want = port.gemm(W, Xq, n_out, n_in, n_tok, threads=8)
+    Y_plain = torch.zeros((n_out, n_tok), dtype=torch.float32, device="cuda")
+    assert gpu.gemm(Wd, Xqd, Y_plain, n_out, n_in, n_tok) == 0
+    torch.cuda.synchronize()
+    assert_close(host(Y_plain), want)
+    for reserve in (False, True):
+        side = torch.cuda.Stream()
+        Y = torch.zeros((n_out, n_tok), dtype=torch.float32, device="cuda")
+        graph = torch.cuda.CUDAGraph()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            if reserve:
+                assert gpu.gemm_reserve(n_in, n_tok) == 0
+            with torch.cuda.graph(graph, stream=side):
+                assert gpu.gemm(Wd, Xqd, Y, n_out, n_in, n_tok) == 0
+        torch.cuda.current_stream().wait_stream(side)
+        for _ in range(3):
+            Y.fill_(777.0)
+            graph.replay()
+            torch.cuda.synchronize()
+            assert_close(host(Y), want)
+            if reserve:
+                assert np.array_equal(bits(host(Y)), bits(host(Y_plain)))
+    assert gpu.gemm_reserve(100, 8) == 1 and gpu.gemm_reserve(1024, 0) == 1
+    assert gpu.device_status() == 0
