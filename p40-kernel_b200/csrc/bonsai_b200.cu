@@ -44,6 +44,7 @@ std::atomic<int> g_opt_chain_threads{512};       // threads per CTA of the chain
 std::atomic<int> g_opt_chain_spread_nb{64};      // dependent ops with at least this many blocks per row rotate their input
                                                  // once for the grid instead of once per CTA; 0 = never
 std::atomic<int> g_opt_chain_tile_kb{16};
+std::atomic<int> g_opt_gemm_tile{0};              // fp16 tensor-core mat-mul: 0 by token count, 64 or 128 tokens per tile
 std::atomic<int> g_opt_chain_seg{40};            // longest row segment of one task, in blocks: 8, 16, 24, 32 or 40        // target bytes of one ring slot
 std::atomic<int> g_opt_gemm_path{-1};          // -1: by token count, 0: integer SIMT kernel, 1: tensor cores, 2: small-batch kernel, 3: integer tensor-core kernel          // 0: streaming kernel (fixed tree order), 1: the host's sequential order
 
@@ -834,9 +835,9 @@ static bool tensor_map_2d(CUtensorMap *map, CUtensorMapDataType type, const void
     return encode(map, type, 2, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
-// The two fp16 planes of the split activations, [2][n_tok][n_in]: box = 64 values x 64 tokens x both planes, landing with
+// The two fp16 planes of the split activations, [2][n_tok][n_in]: box = 64 values x one tile of tokens x both planes, landing with
 // the 128-byte swizzle the MMA reads; tokens past the end arrive as zeros.
-static bool tensor_map_planes(CUtensorMap *map, const void *planes, uint64_t n_in, uint64_t n_tok) {
+static bool tensor_map_planes(CUtensorMap *map, const void *planes, uint64_t n_in, uint64_t n_tok, uint32_t tile_tokens) {
     using Encode = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
                                 const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -847,7 +848,7 @@ static bool tensor_map_planes(CUtensorMap *map, const void *planes, uint64_t n_i
         return false;
     const cuuint64_t dims[3] = {n_in, n_tok, 2};
     const cuuint64_t strides[2] = {n_in * 2, n_tok * n_in * 2};
-    const cuuint32_t box[3] = {64u, (cuuint32_t)T16_N, 2u};
+    const cuuint32_t box[3] = {64u, (cuuint32_t)tile_tokens, 2u};
     const cuuint32_t estr[3] = {1u, 1u, 1u};
     return reinterpret_cast<Encode>(fn)(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void *>(planes), dims, strides, box, estr,
                                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
@@ -902,7 +903,10 @@ static void fill_tc_params(TcParams &P, int64_t n_out, int64_t n_in, int64_t n_t
 }
 
 // The fp16 tensor-core mat-mul (gemm_tc16.cuh).  -1: not taken (shape, alignment, no scratch, no tensor-map encoder).
-static int launch_gemm_tc16(const void *W, const void *Xq, float *Y, int64_t n_out, int64_t n_in, int64_t n_tok, cudaStream_t st) {
+extern "C++" {
+template <int TN>
+static int launch_gemm_tc16_n(const void *W, const void *Xq, float *Y, int64_t n_out, int64_t n_in, int64_t n_tok, cudaStream_t st) {
+    constexpr int T16_N = TN;
     const int64_t nblocks = n_in / 128;
     if (nblocks % 8 != 0 || !aligned16(W) || !aligned4(Xq) || n_tok > (1 << 28)) return -1;
     const long long tiles = (long long)((n_out + T16_M - 1) / T16_M) * ((n_tok + T16_N - 1) / T16_N);
@@ -916,7 +920,7 @@ static int launch_gemm_tc16(const void *W, const void *Xq, float *Y, int64_t n_o
     alignas(64) Tc16Maps maps;
     std::memset(&maps, 0, sizeof(maps));
     if (!encode_w_map(&maps.w, W, n_out, nblocks * W_BLOCK_BYTES)) return -1;
-    if (!tensor_map_planes(&maps.x, planes, (uint64_t)n_in, (uint64_t)n_tok)) return -1;
+    if (!tensor_map_planes(&maps.x, planes, (uint64_t)n_in, (uint64_t)n_tok, (uint32_t)TN)) return -1;
     TcParams P{};
     fill_tc_params(P, n_out, n_in, n_tok, T16_M, T16_N);
     int dev = 0, sms = 0;
@@ -937,19 +941,26 @@ static int launch_gemm_tc16(const void *W, const void *Xq, float *Y, int64_t n_o
     const long long warps = ((n_tok + 3) / 4) * (long long)((n_chunks + 7) / 8);
     tc16_split_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, st>>>(x32, n_chunks, (int)n_tok, maxd, scale, planes);
     static SmemOptIn opt;
-    e = opt.ensure(gemm_tc16_kernel);
+    e = opt.ensure(gemm_tc16_kernel<TN>);
     if (e != cudaSuccess) return (int)e;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
-    cfg.blockDim = dim3(T16_THREADS);
-    cfg.dynamicSmemBytes = T16_SMEM_BYTES;
+    cfg.blockDim = dim3(T16C<TN>::THREADS);
+    cfg.dynamicSmemBytes = T16C<TN>::SMEM_BYTES;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeCooperative;
     attr[0].val.cooperative = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return (int)cudaLaunchKernelEx(&cfg, gemm_tc16_kernel, Y, P, (const float *)scale, maps);
+    return (int)cudaLaunchKernelEx(&cfg, gemm_tc16_kernel<TN>, Y, P, (const float *)scale, maps);
+}
+}  // extern "C++"
+// Tiles of 128 tokens from 96 tokens on (the code expansion, the kernel's busiest part, is paid once per tile), of 64 below.
+static int launch_gemm_tc16(const void *W, const void *Xq, float *Y, int64_t n_out, int64_t n_in, int64_t n_tok, cudaStream_t st) {
+    const int tile = g_opt_gemm_tile.load();
+    if (tile == 64 || (tile != 128 && n_tok < 96)) return launch_gemm_tc16_n<64>(W, Xq, Y, n_out, n_in, n_tok, st);
+    return launch_gemm_tc16_n<128>(W, Xq, Y, n_out, n_in, n_tok, st);
 }
 
 // The tensor-core mat-mul: one CTA per SM walks its share of the (tile, weight block) iterations.
@@ -1204,6 +1215,11 @@ int bonsai_b200_set_option(const char *key, int64_t value) {
     if (!std::strcmp(key, "chain_spread_nb")) {
         if (value < 0) return 1;
         g_opt_chain_spread_nb.store((int)value);
+        return 0;
+    }
+    if (!std::strcmp(key, "gemm_tile")) {
+        if (value != 0 && value != 64 && value != 128) return 1;
+        g_opt_gemm_tile.store((int)value);
         return 0;
     }
     if (!std::strcmp(key, "chain_tile_kb")) {

@@ -36,29 +36,36 @@
 
 namespace b200 {
 
-constexpr int T16_M = 128, T16_N = 64;
+constexpr int T16_M = 128;
 // Operands move in units of one K half of a weight block (64 values).  The codes (A) never touch shared memory: the
 // producers write the fp16 values straight into TENSOR memory (tcgen05.st, lane = weight row, 32 columns per unit) and
 // the MMA takes A from there -- with both operands in shared memory the tensor core's operand reads alone (6 KB per
 // 128 x 64 x 16 MMA, 96 KB per block) ate 3/4 of the shared-memory bandwidth of the block's whole time budget.  The
-// activations (B: the H and L planes of 64 tokens, 8 + 8 KB per unit) land in a shared-memory ring by TMA, asked for
-// as far ahead as the ring allows: the boxes come from L2 and take ~1000-1500 cycles.
+// activations (B: the H and L planes of the tile's tokens) land in a shared-memory ring by TMA, asked for as far ahead
+// as the ring allows: the boxes come from L2 and take ~1000-1500 cycles.
 constexpr int T16_NA = 8;                                  // A ring: half-block units in tensor memory
-constexpr int T16_NB = 4;                                  // B ring: whole blocks (32 KB: K half x {H, L}) in shared memory
-constexpr int T16_UNIT_BYTES = 128 * 128;                  // 16 KB
-constexpr int T16_A_COL0 = 256, T16_A_UNIT_COLS = 32;      // tensor memory: 4 accumulators x 64 columns, then 8 A units x 32
-constexpr int T16_ACC = 4;                                 // accumulators in flight in tensor memory (64 columns each)
+constexpr int T16_A_COL0 = 256, T16_A_UNIT_COLS = 32;      // tensor memory: accumulators in columns 0..255, then 8 A units x 32
 constexpr int T16_WBUFS = 2;
 constexpr int T16_DWRING = 8;                              // weight scales of the last 8 blocks (epilogue lags the producers)
-constexpr int T16_EPI_WARPS = 8, T16_PROD_WARPS = 16;
-constexpr int T16_EPI_THREADS = T16_EPI_WARPS * 32, T16_PROD_THREADS = T16_PROD_WARPS * 32;
-constexpr int T16_EPI_TOKS = T16_N / (T16_EPI_WARPS / 4);        // tokens per epilogue thread (32)
 constexpr int T16_ISSUERS = 2;                             // issuing warps: warp k takes the blocks n with n % 2 == k
-constexpr int T16_THREADS = T16_EPI_THREADS + T16_PROD_THREADS + 32 * (T16_ISSUERS + 2);    // + two loader warps
-constexpr int T16_SMEM_BYTES = 2048 + T16_NB * 2 * T16_UNIT_BYTES + T16_DWRING * T16_M * 4 + T16_WBUFS * TC_WRAW_BYTES;
+// The token width of a tile is a template parameter: 128 tokens per tile halve the code expansion per output (the
+// kernel's busiest part) and are used for large batches; 64 keep small batches from padding.
+template <int TN>
+struct T16C {
+    static constexpr int N = TN;
+    static constexpr int ACC = 256 / TN;                                    // accumulators in flight (TN columns each)
+    static constexpr int EPI_WARPS = TN / 8;                                // 4 lane quarters x (TN / 32) column groups of 32 tokens
+    static constexpr int PROD_SETS = TN == 64 ? 2 : 1;                      // sets of producer warps on alternate blocks
+    static constexpr int PROD_WARPS = 8 * PROD_SETS;                        // 4 row quarters x 2 K halves per set
+    static constexpr int EPI_THREADS = EPI_WARPS * 32, PROD_THREADS = PROD_WARPS * 32;
+    static constexpr int THREADS = EPI_THREADS + PROD_THREADS + 32 * (T16_ISSUERS + 2);      // + two loader warps
+    static constexpr int BUNIT = TN * 256;                                  // B bytes of one K half: {H, L} x TN tokens x 128 bytes
+    static constexpr int NB = (128 * 1024) / (2 * BUNIT);                   // B ring: whole blocks, 128 KB in all
+    static constexpr int SMEM_BYTES = 2048 + NB * 2 * BUNIT + T16_DWRING * T16_M * 4 + T16_WBUFS * TC_WRAW_BYTES;
+    // instruction descriptor: D = fp32, A and B fp16, both K-major, N = TN, M = 128
+    static constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(T16_M >> 4) << 24);
+};
 
-// D = fp32, A and B fp16, both K-major, N = 64, M = 128.
-constexpr uint32_t T16_IDESC = (1u << 4) | ((T16_N >> 3) << 17) | ((T16_M >> 4) << 24);
 
 // The descriptors' upper words are the same for every operand of this kernel (128-byte swizzle, 1024 bytes between
 // 8-row groups); only the 14-bit address field of the lower word moves.  The issuing thread runs alone, one dependent
@@ -67,7 +74,7 @@ constexpr uint32_t T16_IDESC = (1u << 4) | ((T16_N >> 3) << 17) | ((T16_M >> 4) 
 constexpr uint32_t T16_DESC_HI = (uint32_t)(1024 >> 4) | (1u << 14) | (2u << 29);
 __device__ __forceinline__ uint32_t tc16_desc_lo(uint32_t smem_addr) { return ((smem_addr >> 4) & 0x3FFFu) | (1u << 16); }
 template <bool ACC>
-__device__ __forceinline__ void tc_mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo) {
+__device__ __forceinline__ void tc_mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t idesc) {
     asm volatile(
         "{\n\t"
         ".reg .pred p;\n\t"
@@ -76,7 +83,7 @@ __device__ __forceinline__ void tc_mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, 
         "setp.ne.b32 p, %5, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %3, {%6, %6, %6, %6}, p;\n\t"
         "}\n"
-        ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(T16_IDESC), "r"(T16_DESC_HI), "n"(ACC ? 1 : 0), "r"(0u)
+        ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(idesc), "r"(T16_DESC_HI), "n"(ACC ? 1 : 0), "r"(0u)
         : "memory");
 }
 __device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t (&v)[16]) {
@@ -208,11 +215,16 @@ __device__ __forceinline__ void tc16_expand(uint32_t w, uint32_t *o) {
 }
 struct Tc16Maps {
     CUtensorMap w;        // PQ2_0 matrix as [n_out][row words], box 68 x 128
-    CUtensorMap x;        // fp16 planes as [2][n_tok][n_in], box 64 values x 64 tokens x 2 planes, 128-byte swizzle
+    CUtensorMap x;        // fp16 planes as [2][n_tok][n_in], box 64 values x TN tokens x 2 planes, 128-byte swizzle
 };
 
-__global__ void __launch_bounds__(T16_THREADS, 1) gemm_tc16_kernel(float *Y, const TcParams P, const float *__restrict__ tokscale,
-                                                                   const __grid_constant__ Tc16Maps maps) {
+template <int TN>
+__global__ void __launch_bounds__(T16C<TN>::THREADS, 1) gemm_tc16_kernel(float *Y, const TcParams P, const float *__restrict__ tokscale,
+                                                                         const __grid_constant__ Tc16Maps maps) {
+    using C = T16C<TN>;
+    constexpr int T16_N = TN, T16_ACC = C::ACC, T16_NB = C::NB, T16_BUNIT = C::BUNIT, T16_EPI_WARPS = C::EPI_WARPS,
+                  T16_PROD_WARPS = C::PROD_WARPS, T16_PROD_SETS = C::PROD_SETS, T16_EPI_THREADS = C::EPI_THREADS,
+                  T16_PROD_THREADS = C::PROD_THREADS, T16_EPI_TOKS = 32;
     extern __shared__ __align__(128) uint8_t smem[];
     // unit u = 2 * block + K half lives in slot u % NA of the code ring and slot u % NB of the activation ring
     uint64_t *afull = reinterpret_cast<uint64_t *>(smem);              // [NA] code producers -> issuer
@@ -226,14 +238,14 @@ __global__ void __launch_bounds__(T16_THREADS, 1) gemm_tc16_kernel(float *Y, con
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(wfree + T16_WBUFS);
     uint8_t *stages = smem + 1024 + ((1024u - (smem_u32(smem) & 1023u)) & 1023u);
     uint8_t *bring = stages;
-    float *dwring = reinterpret_cast<float *>(bring + T16_NB * 2 * T16_UNIT_BYTES);
+    float *dwring = reinterpret_cast<float *>(bring + T16_NB * 2 * T16_BUNIT);
     uint8_t *wraw = reinterpret_cast<uint8_t *>(dwring + T16_DWRING * T16_M);
 
     const int wid = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nblocks = P.nblocks, n_tok = P.n_tok, n_out = P.n_out;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < T16_NA; ++s) { mbar_init(&afull[s], T16_PROD_THREADS / 4); mbar_init(&afree[s], 1); }
+        for (int s = 0; s < T16_NA; ++s) { mbar_init(&afull[s], T16_PROD_THREADS / (2 * T16_PROD_SETS)); mbar_init(&afree[s], 1); }
         for (int s = 0; s < T16_NB; ++s) { mbar_init(&bfull[s], 1); mbar_init(&bfree[s], 1); }
         for (int s = 0; s < T16_ACC; ++s) { mbar_init(&mma_done[s], 1); mbar_init(&tmem_empty[s], T16_EPI_WARPS); }
         for (int s = 0; s < T16_WBUFS; ++s) { mbar_init(&wfull[s], 1); mbar_init(&wfree[s], T16_PROD_THREADS); }
@@ -344,7 +356,7 @@ __global__ void __launch_bounds__(T16_THREADS, 1) gemm_tc16_kernel(float *Y, con
         // blocks because a warp's own chain per block -- raw loads, expansion, tcgen05.st, wait::st, fence, arrive -- is
         // ~1300 cycles long and was the kernel's period when every warp took every block.  The store of one block is
         // completed (wait::st, fence, arrive) only after the NEXT own block has been loaded and expanded.
-        const int pw = pi >> 5, p = 32 * (pw & 3) + lane, g = (pw >> 2) & 1, set = pw >> 3;
+        const int pw = pi >> 5, p = 32 * (pw & 3) + lane, g = (pw >> 2) & 1, set = pw >> 3;    // set: 0 when there is one set
         const uint32_t a_lane = tmem_base + ((uint32_t)(32 * (pw & 3)) << 16) + (uint32_t)T16_A_COL0;
         bool ok = true;
         int n = 0, oct = 0, pending = -1;           // pending: slot whose store is in flight
@@ -355,7 +367,7 @@ __global__ void __launch_bounds__(T16_THREADS, 1) gemm_tc16_kernel(float *Y, con
                     ++oct;
                 }
                 const int wbuf = (oct - 1) % T16_WBUFS;
-                if ((n & 1) == set) {
+                if ((n & (T16_PROD_SETS - 1)) == set) {
                     const int u = 2 * n + g, sa = u % T16_NA;
                     // The half's four code words sit at byte 34 j + 2 + 16 g of the row's 272-byte piece, 2-byte aligned:
                     // five aligned words and funnel shifts by 0 or 16 bits.  (Rows are 68 words apart: a warp's loads
@@ -416,10 +428,10 @@ __global__ void __launch_bounds__(T16_THREADS, 1) gemm_tc16_kernel(float *Y, con
                 const int sb = n % T16_NB;
                 if (!mbar_wait_bounded(&bfree[sb], (uint32_t)(((n / T16_NB) & 1) ^ 1), 20, 80)) { ok = false; break; }
                 if (elect_one()) {
-                    uint8_t *b = bring + (size_t)sb * (2 * T16_UNIT_BYTES);
-                    mbar_expect_tx(&bfull[sb], (uint32_t)(2 * T16_UNIT_BYTES));
+                    uint8_t *b = bring + (size_t)sb * (2 * T16_BUNIT);
+                    mbar_expect_tx(&bfull[sb], (uint32_t)(2 * T16_BUNIT));
                     tma_load_3d(b, &maps.x, kb * 128, tt * T16_N, 0, &bfull[sb]);
-                    tma_load_3d(b + T16_UNIT_BYTES, &maps.x, kb * 128 + 64, tt * T16_N, 0, &bfull[sb]);
+                    tma_load_3d(b + T16_BUNIT, &maps.x, kb * 128 + 64, tt * T16_N, 0, &bfull[sb]);
                 }
                 __syncwarp();
             }
@@ -449,13 +461,13 @@ __global__ void __launch_bounds__(T16_THREADS, 1) gemm_tc16_kernel(float *Y, con
                                    !mbar_wait_hot(&tmem_empty[t], (uint32_t)(((n / T16_ACC) & 1) ^ 1)))) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t a_t = tmem_base + (uint32_t)(T16_A_COL0 + sa * T16_A_UNIT_COLS);
-                    const uint32_t b_lo = tc16_desc_lo(smem_u32(bring + (size_t)(2 * sb + g) * T16_UNIT_BYTES));
+                    const uint32_t b_lo = tc16_desc_lo(smem_u32(bring + (size_t)(2 * sb + g) * T16_BUNIT));
                     if (elect_one()) {
 #pragma unroll
                         for (int m = 0; m < 8; ++m) {
                             const int pl = m >> 2, i = m & 3;
-                            if (g == 0 && m == 0) tc_mma_f16_ts<false>(d, a_t, b_lo);        // K step i: 16 fp16 = 8 columns of A
-                            else tc_mma_f16_ts<true>(d, a_t + (uint32_t)(8 * i), b_lo + (uint32_t)(pl * ((T16_N * 128) >> 4) + 2 * i));
+                            if (g == 0 && m == 0) tc_mma_f16_ts<false>(d, a_t, b_lo, C::IDESC);        // K step i: 16 fp16 = 8 columns of A
+                            else tc_mma_f16_ts<true>(d, a_t + (uint32_t)(8 * i), b_lo + (uint32_t)(pl * ((T16_N * 128) >> 4) + 2 * i), C::IDESC);
                         }
                         tc_commit(&afree[sa]);
                         if (g == 1) {
