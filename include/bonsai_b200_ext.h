@@ -133,7 +133,7 @@ int bonsai_b200_stream_probe(const void *buf, int64_t bytes, int mode, void *sin
  * on the 401-projection decode chain).
  * Options are process-wide: set them once at start-up, not from threads that call the library concurrently.
  * A library compiled with -DBONSAI_B200_TUNING (the test build) also takes geometry keys ("gemv_variant",
- * "chain_threads", "chain_seg", "chain_tile_kb", "chain_spread_nb") that force a tiling; they change no result bits
+ * "chain_threads", "chain_seg", "chain_tile_kb", "chain_spread_nb", "gemm_tile") that force a tiling; they change no result bits
  * beyond what the documented options say and are not part of the interface.
  * Returns 0, or 1 for an unknown key. */
 int bonsai_b200_set_option(const char *key, int64_t value);

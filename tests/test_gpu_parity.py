@@ -737,3 +737,25 @@ def test_gemm_in_a_captured_graph_after_reserve(gpu, port):
                 assert np.array_equal(bits(host(Y)), bits(host(Y_plain)))
     assert gpu.gemm_reserve(100, 8) == 1 and gpu.gemm_reserve(1024, 0) == 1
     assert gpu.device_status() == 0
+
+
+@pytest.mark.parametrize("tile", [64, 128])
+def test_gemm_fp16_both_tile_widths(gpu, port, tile):
+    """The fp16 tensor-core mat-mul is built for token tiles of 64 and of 128 (picked by token count); each forced on a
+    batch the other would normally take: ragged rows and tokens, bound against the host loop."""
+    import torch
+    for n_out, n_in, n_tok in ((300, 2048, 100), (129, 1024, 513)):
+        W = synth.pq2_0_weights(n_out, n_in, seed=tile + n_tok)
+        X = synth.activations(n_in, seed=n_out, batch=n_tok)
+        Xq = port.quantize_batch_chunk_major(X)
+        Y = torch.full((n_out, n_tok), float("nan"), dtype=torch.float32, device="cuda")
+        try:
+            assert gpu.set_option("gemm_tile", tile) == 0
+            assert gpu.set_option("gemm_path", 1) == 0
+            assert gpu.gemm(dev(W), dev(Xq), Y, n_out, n_in, n_tok) == 0
+            torch.cuda.synchronize()
+        finally:
+            gpu.set_option("gemm_tile", 0)
+            gpu.set_option("gemm_path", -1)
+        assert_close(host(Y), port.gemm(W, Xq, n_out, n_in, n_tok, threads=8))
+    assert gpu.device_status() == 0
