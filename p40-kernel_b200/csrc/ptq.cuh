@@ -14,69 +14,147 @@
 namespace b200 {
 
 constexpr int PTQ_BLOCK_BYTES = 28;
+constexpr int PTQ_CTA_BLOCKS = 256;            // blocks per CTA pass = threads per CTA
 
-// One thread per block.  `code3` counts the weights whose PQ2_0 code is 3 (not representable: stored as code 2).
-__global__ void __launch_bounds__(256) ptq1_pack_kernel(const uint8_t *__restrict__ src, uint8_t *__restrict__ dst, long long n_blocks,
-                                                        unsigned long long *__restrict__ code3) {
-    unsigned int bad = 0;
-    for (long long b = (long long)blockIdx.x * blockDim.x + threadIdx.x; b < n_blocks; b += (long long)gridDim.x * blockDim.x) {
-        const uint8_t *s = src + b * W_BLOCK_BYTES;
-        uint8_t *d = dst + b * PTQ_BLOCK_BYTES;
-        uint8_t code[128];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            const uint32_t h = ldg_nc_u16(s + 2 + 2 * i);
-#pragma unroll
-            for (int k = 0; k < 8; ++k) {
-                uint32_t c = (h >> (2 * k)) & 3u;
-                if (c == 3u) { ++bad; c = 2u; }
-                code[8 * i + k] = (uint8_t)c;
-            }
-        }
-        unsigned short out[14];
-        uint8_t *ob = reinterpret_cast<uint8_t *>(out);
-#pragma unroll
-        for (int i = 0; i < 24; ++i)
-            ob[i] = (uint8_t)(code[5 * i] + 3 * code[5 * i + 1] + 9 * code[5 * i + 2] + 27 * code[5 * i + 3] + 81 * code[5 * i + 4]);
-#pragma unroll
-        for (int i = 0; i < 2; ++i)
-            ob[24 + i] = (uint8_t)(code[120 + 4 * i] + 3 * code[121 + 4 * i] + 9 * code[122 + 4 * i] + 27 * code[123 + 4 * i]);
-        out[13] = (unsigned short)ldg_nc_u16(s);
-#pragma unroll
-        for (int i = 0; i < 14; ++i) reinterpret_cast<unsigned short *>(d)[i] = out[i];     // 28-byte blocks start on even addresses
-    }
-    if (bad) atomicAdd(code3, (unsigned long long)bad);
+// Both directions: a CTA stages 256 blocks in shared memory with coalesced 4-byte accesses (source runs are 2-byte
+// aligned: the first and last halfword of a run are moved singly), every thread converts one block with table look-ups
+// (ten bits = five 2-bit codes <-> one byte), and the CTA writes the result back the same way.  A thread per block with
+// halfword accesses to global memory and a division chain per byte ran at a tenth of the memory bandwidth.
+
+// global (2-byte aligned) -> shared (4-byte aligned buffer), `bytes` even
+__device__ __forceinline__ void ptq_stage_in(uint8_t *sm, const uint8_t *g, int bytes) {
+    const int head = (int)((4 - (reinterpret_cast<uintptr_t>(g) & 3u)) & 3u);          // 0 or 2
+    if (threadIdx.x == 0 && head && bytes >= 2) *reinterpret_cast<unsigned short *>(sm + 2) = *reinterpret_cast<const unsigned short *>(g);
+    // the shared image is shifted so that global word k lands on a word: image offset = 4 - head for head != 0, else 0
+    const int shift = head ? 4 - head : 0;
+    const int words = (bytes - head) >> 2;
+    const uint32_t *gw = reinterpret_cast<const uint32_t *>(g + head);
+    uint32_t *sw = reinterpret_cast<uint32_t *>(sm + shift + head);
+    for (int i = threadIdx.x; i < words; i += blockDim.x) sw[i] = __ldg(gw + i);
+    const int tail = bytes - head - 4 * words;                                            // 0 or 2
+    if (threadIdx.x == 32 && tail) *reinterpret_cast<unsigned short *>(sm + shift + head + 4 * words) =
+                                       *reinterpret_cast<const unsigned short *>(g + head + 4 * words);
+}
+__device__ __forceinline__ int ptq_image_shift(const uint8_t *g) { return (reinterpret_cast<uintptr_t>(g) & 3u) ? 2 : 0; }
+// shared -> global, mirror of the above
+__device__ __forceinline__ void ptq_stage_out(uint8_t *g, const uint8_t *sm, int bytes) {
+    const int head = (int)((4 - (reinterpret_cast<uintptr_t>(g) & 3u)) & 3u);
+    const int shift = head ? 4 - head : 0;
+    if (threadIdx.x == 0 && head && bytes >= 2) *reinterpret_cast<unsigned short *>(g) = *reinterpret_cast<const unsigned short *>(sm + 2);
+    const int words = (bytes - head) >> 2;
+    uint32_t *gw = reinterpret_cast<uint32_t *>(g + head);
+    const uint32_t *sw = reinterpret_cast<const uint32_t *>(sm + shift + head);
+    for (int i = threadIdx.x; i < words; i += blockDim.x) gw[i] = sw[i];
+    const int tail = bytes - head - 4 * words;
+    if (threadIdx.x == 32 && tail) *reinterpret_cast<unsigned short *>(g + head + 4 * words) =
+                                       *reinterpret_cast<const unsigned short *>(sm + shift + head + 4 * words);
 }
 
-__global__ void __launch_bounds__(256) ptq1_unpack_kernel(const uint8_t *__restrict__ src, uint8_t *__restrict__ dst, long long n_blocks) {
-    for (long long b = (long long)blockIdx.x * blockDim.x + threadIdx.x; b < n_blocks; b += (long long)gridDim.x * blockDim.x) {
-        const uint8_t *s = src + b * PTQ_BLOCK_BYTES;
-        uint8_t code[128];
+// `code3` counts the weights whose PQ2_0 code is 3 (not representable: stored as code 2).
+__global__ void __launch_bounds__(PTQ_CTA_BLOCKS) ptq1_pack_kernel(const uint8_t *__restrict__ src, uint8_t *__restrict__ dst, long long n_blocks,
+                                                                   unsigned long long *__restrict__ code3) {
+    __shared__ __align__(16) uint8_t in[PTQ_CTA_BLOCKS * W_BLOCK_BYTES + 8];
+    __shared__ __align__(16) uint8_t out[PTQ_CTA_BLOCKS * PTQ_BLOCK_BYTES + 8];
+    __shared__ unsigned short lut[1024];        // ten bits (five codes, least significant first) -> byte | (count of code 3) << 8
+    for (int i = threadIdx.x; i < 1024; i += blockDim.x) {
+        unsigned v = 0, w = 1, bad = 0;
+        for (int k = 0; k < 5; ++k, w *= 3) {
+            unsigned c = (i >> (2 * k)) & 3u;
+            if (c == 3u) { ++bad; c = 2u; }
+            v += c * w;
+        }
+        lut[i] = (unsigned short)(v | (bad << 8));
+    }
+    unsigned int bad = 0;
+    for (long long b0 = (long long)blockIdx.x * PTQ_CTA_BLOCKS; b0 < n_blocks; b0 += (long long)gridDim.x * PTQ_CTA_BLOCKS) {
+        const int nb = (int)min((long long)PTQ_CTA_BLOCKS, n_blocks - b0);
+        const uint8_t *g = src + b0 * W_BLOCK_BYTES;
+        uint8_t *gd = dst + b0 * PTQ_BLOCK_BYTES;
+        __syncthreads();                                        // the table; the buffers of the previous pass
+        ptq_stage_in(in, g, nb * W_BLOCK_BYTES);
+        __syncthreads();
+        if ((int)threadIdx.x < nb) {
+            const unsigned short *s16 = reinterpret_cast<const unsigned short *>(in + ptq_image_shift(g) + threadIdx.x * W_BLOCK_BYTES);
+            unsigned short *d16 = reinterpret_cast<unsigned short *>(out + ptq_image_shift(gd) + threadIdx.x * PTQ_BLOCK_BYTES);
+            uint32_t w[8];                                      // the 256 code bits
 #pragma unroll
-        for (int i = 0; i < 13; ++i) {
-            const uint32_t h = ldg_nc_u16(s + 2 * i);
+            for (int i = 0; i < 8; ++i) w[i] = (uint32_t)s16[1 + 2 * i] | ((uint32_t)s16[2 + 2 * i] << 16);
+            uint32_t ob[13];
 #pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                uint32_t v = (h >> (8 * half)) & 0xFFu;
-                const int byte = 2 * i + half;
-                if (byte < 24) {
-#pragma unroll
-                    for (int k = 0; k < 5; ++k) { code[5 * byte + k] = (uint8_t)(v % 3u); v /= 3u; }
-                } else {
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) { code[120 + 4 * (byte - 24) + k] = (uint8_t)(v % 3u); v /= 3u; }
-                }
+            for (int i = 0; i < 12; ++i) {                      // bytes 2 i, 2 i + 1: bits 20 i .. 20 i + 19
+                const int bit = 20 * i, wi = bit >> 5, sh = bit & 31;
+                const uint32_t twenty = (sh <= 12 ? (w[wi] >> sh) : __funnelshift_r(w[wi], w[wi + 1 < 8 ? wi + 1 : 7], sh)) & 0xFFFFFu;
+                const unsigned a = lut[twenty & 1023u], c = lut[twenty >> 10];
+                bad += (a >> 8) + (c >> 8);
+                ob[i] = (a & 0xFFu) | ((c & 0xFFu) << 8);
             }
-        }
-        unsigned short *d = reinterpret_cast<unsigned short *>(dst + b * W_BLOCK_BYTES);
-        d[0] = (unsigned short)ldg_nc_u16(s + 26);
+            {                                                   // qh: weights 120..127 = the last 16 bits, four codes per byte
+                const uint32_t sixteen = w[7] >> 16;
+                const unsigned a = lut[sixteen & 255u], c = lut[sixteen >> 8];
+                bad += (a >> 8) + (c >> 8);
+                ob[12] = (a & 0xFFu) | ((c & 0xFFu) << 8);
+            }
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            uint32_t h = 0;
-#pragma unroll
-            for (int k = 0; k < 8; ++k) h |= (uint32_t)code[8 * i + k] << (2 * k);
-            d[1 + i] = (unsigned short)h;
+            for (int i = 0; i < 13; ++i) d16[i] = (unsigned short)ob[i];
+            d16[13] = s16[0];
         }
+        __syncthreads();
+        ptq_stage_out(gd, out, nb * PTQ_BLOCK_BYTES);
+    }
+    // one addition per CTA (one per thread onto the same word serialised into most of the kernel's time)
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) bad += __shfl_xor_sync(0xffffffffu, bad, o);
+    __shared__ unsigned int wsum[PTQ_CTA_BLOCKS / 32];
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) wsum[threadIdx.x >> 5] = bad;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned long long total = 0;
+        for (int i = 0; i < PTQ_CTA_BLOCKS / 32; ++i) total += wsum[i];
+        if (total) atomicAdd(code3, total);
+    }
+}
+
+__global__ void __launch_bounds__(PTQ_CTA_BLOCKS) ptq1_unpack_kernel(const uint8_t *__restrict__ src, uint8_t *__restrict__ dst, long long n_blocks) {
+    __shared__ __align__(16) uint8_t in[PTQ_CTA_BLOCKS * PTQ_BLOCK_BYTES + 8];
+    __shared__ __align__(16) uint8_t out[PTQ_CTA_BLOCKS * W_BLOCK_BYTES + 8];
+    __shared__ unsigned short lut[256];         // byte -> ten bits (five base-3 digits as 2-bit codes, least significant first)
+    for (int i = threadIdx.x; i < 256; i += blockDim.x) {
+        unsigned v = (unsigned)i, bits = 0;
+        for (int k = 0; k < 5; ++k) { bits |= (v % 3u) << (2 * k); v /= 3u; }
+        lut[i] = (unsigned short)bits;
+    }
+    for (long long b0 = (long long)blockIdx.x * PTQ_CTA_BLOCKS; b0 < n_blocks; b0 += (long long)gridDim.x * PTQ_CTA_BLOCKS) {
+        const int nb = (int)min((long long)PTQ_CTA_BLOCKS, n_blocks - b0);
+        const uint8_t *g = src + b0 * PTQ_BLOCK_BYTES;
+        uint8_t *gd = dst + b0 * W_BLOCK_BYTES;
+        __syncthreads();
+        ptq_stage_in(in, g, nb * PTQ_BLOCK_BYTES);
+        __syncthreads();
+        if ((int)threadIdx.x < nb) {
+            const unsigned short *s16 = reinterpret_cast<const unsigned short *>(in + ptq_image_shift(g) + threadIdx.x * PTQ_BLOCK_BYTES);
+            unsigned short *d16 = reinterpret_cast<unsigned short *>(out + ptq_image_shift(gd) + threadIdx.x * W_BLOCK_BYTES);
+            uint32_t w[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) w[i] = 0;
+#pragma unroll
+            for (int i = 0; i < 12; ++i) {                      // bytes 2 i, 2 i + 1 -> bits 20 i .. 20 i + 19
+                const unsigned h = s16[i];
+                const uint32_t twenty = (uint32_t)lut[h & 0xFFu] | ((uint32_t)lut[h >> 8] << 10);
+                const int bit = 20 * i, wi = bit >> 5, sh = bit & 31;
+                w[wi] |= twenty << sh;
+                if (sh > 12) w[wi + 1 < 8 ? wi + 1 : 7] |= twenty >> (32 - sh);
+            }
+            {
+                const unsigned h = s16[12];
+                w[7] |= ((uint32_t)(lut[h & 0xFFu] & 0xFFu) | ((uint32_t)(lut[h >> 8] & 0xFFu) << 8)) << 16;
+            }
+            d16[0] = s16[13];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { d16[1 + 2 * i] = (unsigned short)w[i]; d16[2 + 2 * i] = (unsigned short)(w[i] >> 16); }
+        }
+        __syncthreads();
+        ptq_stage_out(gd, out, nb * W_BLOCK_BYTES);
     }
 }
 
