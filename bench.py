@@ -247,6 +247,14 @@ def stream_probe_gbs(torch, bb, nbytes=1 << 30):
     return out
 
 
+def apply_opts(args, bb):
+    """--opt KEY=VALUE: library options by name (bonsai_b200_set_option), for sweeps."""
+    for kv in getattr(args, "opt", []):
+        key, _, val = kv.partition("=")
+        if bb.set_option(key, int(val)) != 0:
+            raise SystemExit(f"--opt {kv}: the library does not know this key (tuning keys need the tuning build)")
+
+
 def run_b200(args):
     import torch
     import bonsai_b200 as bb
@@ -265,10 +273,7 @@ def run_b200(args):
         bb.set_option("pdl", args.pdl)
     if args.order >= 0:
         bb.set_option("gemv_order", args.order)
-    for kv in args.opt:                                 # library options by name (bonsai_b200_set_option), for sweeps
-        key, _, val = kv.partition("=")
-        if bb.set_option(key, int(val)) != 0:
-            raise SystemExit(f"--opt {kv}: the library does not know this key (tuning keys need the tuning build)")
+    apply_opts(args, bb)
 
     sets = args.sets
     # ---- resident tensors: weights generated on the device, row slice of this rank only ----------
@@ -815,6 +820,7 @@ def run_decode_step(args):
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     bb.lib()
+    apply_opts(args, bb)
     leg = decode_step_leg(args, torch, bb, dist)
     if rank == 0:
         peak, _, peak_kind = measured_peaks()
@@ -938,6 +944,7 @@ def run_prefill(args):
     import bonsai_b200 as bb
     torch.cuda.set_device(0)
     bb.lib()
+    apply_opts(args, bb)
     leg = prefill_leg(args, torch, bb, None)
     print(json.dumps({
         "metric": leg["metric"], "value": leg["value"], "unit": "TOPS", "n_gpus": 1, "steps": leg["steps"],

@@ -41,7 +41,7 @@ std::atomic<int> g_opt_gemv_variant{-1};
 std::atomic<int> g_opt_gemv_order{0};
 std::atomic<int> g_opt_fuse_linear{0};         // 1: bonsai_b200_linear runs as one kernel when it can (measured slower)
 std::atomic<int> g_opt_chain_threads{512};       // threads per CTA of the chain kernel: 512 (5 blocks per lane and task), 640 (4), 768 (3)
-std::atomic<int> g_opt_chain_spread_nb{64};      // dependent ops with at least this many blocks per row rotate their input
+std::atomic<int> g_opt_chain_spread_nb{40};      // dependent ops with at least this many blocks per row rotate their input
                                                  // once for the grid instead of once per CTA; 0 = never
 std::atomic<int> g_opt_chain_tile_kb{16};
 std::atomic<int> g_opt_gemm_tile{0};              // fp16 tensor-core mat-mul: 0 by token count, 64 or 128 tokens per tile
@@ -645,7 +645,8 @@ static int chain_create_impl(const bonsai_b200_op *ops, int64_t n_ops, int tp_ra
         last_user[buf] = (int)i;
         if (!same && !rotate) r.ready_parity = ready_uses[buf]++ & 1;
         if (rotate) any_rotate = true; else any_q8 = true;
-        if (rotate && depends && !same && spread_nb > 0 && r.nb >= spread_nb && r.nb / 8 <= sms) {
+        // (an RMSNorm producer needs the whole vector in every CTA for its sum of squares: such an op rotates for itself)
+        if (rotate && depends && !same && !(r.flags & CHAIN_RMSNORM) && spread_nb > 0 && r.nb >= spread_nb && r.nb / 8 <= sms) {
             r.flags |= CHAIN_SPREAD;
             spread_total += (unsigned)(r.nb / 8);
             r.spread_blocks = spread_total;
