@@ -90,6 +90,10 @@ int bonsai_b200_gemm_dump(const void *W, const void *Xq, float *Y, int32_t *sums
  * 0, 1 for bad arguments, cudaErrorMemoryAllocation (2) when the buffer cannot be had.  No reference counterpart. */
 int bonsai_b200_gemm_reserve(int64_t n_in, int64_t n_tok, bonsai_stream stream);
 
+/* Frees every scratch buffer of bonsai_p40_gemm (all devices, all streams); they are otherwise kept for the life of the
+ * process.  No mat-mul of this library may be in flight or captured in a graph that will still be replayed.  Returns 0. */
+int bonsai_b200_gemm_release(void);
+
 /* PTQ1_0: the denser packing of the same ternary weights, 28 bytes per 128 weights instead of 34 (described, not
  * implemented, by the reference: docs/NEXT_STEPS.md:76-83).  Block = qs[24] (five base-3 digits per byte, weights
  * 0..119), qh[2] (four digits per byte, weights 120..127), fp16 d; digit = PQ2_0 code 0, 1, 2; weight j < 120 is digit

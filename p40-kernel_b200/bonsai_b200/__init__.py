@@ -43,6 +43,7 @@ SIGNATURES = {
     "bonsai_b200_gemv_dump": (_INT, [_VP, _VP, _VP, _VP, _I64, _I64, _VP]),
     "bonsai_b200_gemm_dump": (_INT, [_VP, _VP, _VP, _VP, _I64, _I64, _I64, _VP]),
     "bonsai_b200_gemm_reserve": (_INT, [_I64, _I64, _VP]),
+    "bonsai_b200_gemm_release": (_INT, []),
     "bonsai_b200_ptq1_pack": (_INT, [_VP, _VP, _I64, _VP, _VP]),
     "bonsai_b200_ptq1_unpack": (_INT, [_VP, _VP, _I64, _VP]),
     "bonsai_b200_synth_pq2_0": (_INT, [_VP, _I64, _I64, _U64, _VP]),
@@ -186,6 +187,10 @@ def gemm_dump(W, Xq, Y, sums, n_out, n_in, n_tok):
 
 def gemm_reserve(n_in, n_tok):
     return lib().bonsai_b200_gemm_reserve(n_in, n_tok, _stream())
+
+
+def gemm_release():
+    return lib().bonsai_b200_gemm_release()
 
 
 def ptq1_pack(src, dst, n_blocks, code3_count):

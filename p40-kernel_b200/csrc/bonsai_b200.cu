@@ -1056,6 +1056,20 @@ int bonsai_p40_gemm(const void *W, const void *Xq, float *Y, int64_t n_out, int6
     return (int)cudaGetLastError();
 }
 
+int bonsai_b200_gemm_release(void) {
+    std::lock_guard<std::mutex> lock(g_scratch_mu);
+    int dev = 0;
+    const bool have = cudaGetDevice(&dev) == cudaSuccess;
+    for (auto &g : g_scratch) {
+        if (!g.ptr) continue;
+        if (have) (void)cudaSetDevice(g.dev);
+        (void)cudaFree(g.ptr);
+    }
+    g_scratch.clear();
+    if (have) (void)cudaSetDevice(dev);
+    return 0;
+}
+
 int bonsai_b200_gemm_reserve(int64_t n_in, int64_t n_tok, bonsai_stream stream) {
     if (n_in <= 0 || n_in % 128 != 0 || n_tok <= 0 || n_tok > (1 << 28)) return 1;
     const size_t bytes = 2 * (size_t)n_tok * (size_t)n_in * sizeof(__half) + 2 * (size_t)n_tok * sizeof(float);

@@ -736,6 +736,15 @@ def test_gemm_in_a_captured_graph_after_reserve(gpu, port):
             if reserve:
                 assert np.array_equal(bits(host(Y)), bits(host(Y_plain)))
     assert gpu.gemm_reserve(100, 8) == 1 and gpu.gemm_reserve(1024, 0) == 1
+    del graph
+    torch.cuda.synchronize()
+    free0 = torch.cuda.mem_get_info()[0]
+    assert gpu.gemm_release() == 0                      # the buffers go back to the device ...
+    assert torch.cuda.mem_get_info()[0] > free0
+    Y3 = torch.zeros((n_out, n_tok), dtype=torch.float32, device="cuda")
+    assert gpu.gemm(Wd, Xqd, Y3, n_out, n_in, n_tok) == 0       # ... and the next call gets a new one
+    torch.cuda.synchronize()
+    assert np.array_equal(bits(host(Y3)), bits(host(Y_plain)))
     assert gpu.device_status() == 0
 
 
