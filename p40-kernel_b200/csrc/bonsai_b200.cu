@@ -155,7 +155,7 @@ bool plan_stream(long long n_out, int nb, int variant, StreamParams &p, int &thr
 // Geometry of the tensor-core mat-vec (gemv_mma.cuh): tiles of 16 rows x one row segment, a ring of slots as deep
 // as `cap_kb` of shared memory allows.  Rows must start on a word (nb even); rows longer than one segment are cut at
 // multiples of 8 blocks (16-byte aligned pieces), which needs nb % 8 == 0.
-bool plan_mma(long long n_out, int nb, int cap_kb, MmaGeom &P, int &smem_bytes, int &grid, bool batched = false) {
+bool plan_mma(long long n_out, int nb, int cap_kb, MmaGeom &P, int &smem_bytes, int &grid) {
     if (nb <= 0 || nb % 2 != 0) return false;
     P = MmaGeom{};
     P.n_out = (int)n_out;
@@ -186,7 +186,7 @@ bool plan_mma(long long n_out, int nb, int cap_kb, MmaGeom &P, int &smem_bytes, 
         P.stride = row_bytes;
     }
     P.slot_bytes = (16 * P.stride + 127) & ~127;
-    auto fixed = [&](int n) { return batched ? mmab_fixed_bytes(P, n) : mma_fixed_bytes(P, n); };
+    auto fixed = [&](int n) { return mma_fixed_bytes(P, n); };
     int nslot = MMA_MAX_SLOTS;
     while (nslot >= 2 && fixed(nslot) + (size_t)nslot * P.slot_bytes > (size_t)cap_kb * 1024) --nslot;
     if (nslot < 2) return false;
@@ -195,6 +195,52 @@ bool plan_mma(long long n_out, int nb, int cap_kb, MmaGeom &P, int &smem_bytes, 
     P.magic_nseg = magic_u32((uint32_t)P.nseg);
     P.magic_nslot = magic_u32((uint32_t)P.nslot);
     smem_bytes = (int)(fixed(nslot) + (size_t)nslot * P.slot_bytes);
+    grid = P.ngroups < SM_COUNT ? P.ngroups : SM_COUNT;
+    return true;
+}
+
+// Geometry of the small-batch mat-mul (gemv_mma.cuh, gemm_mma_kernel): tiles of 16 rows x one segment of at most
+// MMAB_SEG_UNITS * 8 blocks, brought by one tiled copy when rows are a multiple of 8 blocks (16-byte aligned segment
+// starts, row pitch a multiple of 16), else whole rows by one bulk copy (rows of at most 48 blocks).
+bool plan_mmab(long long n_out, int nb, int n_tok, int cap_kb, MmabGeom &P, int &smem_bytes, int &grid) {
+    if (nb <= 0 || nb % 2 != 0 || n_tok < 1 || n_tok > 8) return false;
+    P = MmabGeom{};
+    P.n_out = (int)n_out;
+    P.nb = nb;
+    P.ngroups = (int)((n_out + 15) / 16);
+    int seg_max;
+    if (nb % 8 == 0) {
+        const int units = nb / 8;
+        P.nseg = (units + MMAB_SEG_UNITS - 1) / MMAB_SEG_UNITS;
+        P.seg_q = units / P.nseg;
+        P.seg_r = units % P.nseg;
+        seg_max = 8 * (P.seg_q + (P.seg_r ? 1 : 0));
+        int s16 = seg_max * W_BLOCK_BYTES / 16;         // rows of a tile 16 * (odd) bytes apart
+        if (s16 % 2 == 0) ++s16;
+        P.stride = 16 * s16;
+        P.tiled = 1;
+    } else {
+        if (nb > 48) return false;
+        P.nseg = 1;
+        seg_max = nb;
+        P.stride = nb * W_BLOCK_BYTES;
+        P.tiled = 0;
+    }
+    P.pairs_max = seg_max / 2;
+    P.slot_bytes = (16 * P.stride + 127) & ~127;
+    P.act_bufs = P.nseg > 1 ? 3 : 1;
+    P.act_tab_off = (seg_max * 4 * n_tok * 36 + 8 * 36 + 127) & ~127;       // + what lanes past n_tok read beyond the last block
+    P.act_buf_bytes = P.act_tab_off + seg_max * 4 * 64;
+    int nslot = MMA_MAX_SLOTS;
+    while (nslot >= 2 && mmab_fixed_bytes(P, nslot) + (size_t)nslot * P.slot_bytes > (size_t)cap_kb * 1024) --nslot;
+    if (nslot < 2) return false;
+    P.nslot = nslot;
+    P.magic_nslot = magic_u32((uint32_t)nslot);
+    P.magic_bt = magic_u32((uint32_t)(MMAB_GB * P.nseg));
+    // tile and step numbers stay small enough for the multiplicative divisions of the kernel
+    const long long groups_per_cta = (P.ngroups + SM_COUNT - 1) / SM_COUNT;
+    if (groups_per_cta * P.nseg >= (1 << 20) || (groups_per_cta / MMAB_GB + 1) * P.nseg >= 65536) return false;
+    smem_bytes = (int)(mmab_fixed_bytes(P, nslot) + (size_t)nslot * P.slot_bytes);
     grid = P.ngroups < SM_COUNT ? P.ngroups : SM_COUNT;
     return true;
 }
@@ -1012,22 +1058,28 @@ static int launch_gemm_tc(const void *W, const void *Xq, float *Y, int64_t n_out
 // too long for the activations of 8 tokens to stay resident beside two ring slots, unaligned W).
 static int launch_gemm_small(const void *W, const void *Xq, float *Y, int64_t n_out, int64_t n_in, int64_t n_tok,
                              int32_t *dump, cudaStream_t st) {
-    if (n_tok < 1 || n_tok > 8 || !aligned16(W)) return -1;
-    MmaGeom mp;
+    if (n_tok < 1 || n_tok > 8 || !aligned16(W) || n_out > INT32_MAX - 16) return -1;
+    MmabGeom mp;
     int smem_bytes = 0, grid = 0;
-    if (!plan_mma(n_out, (int)(n_in / 128), 224, mp, smem_bytes, grid, true)) return -1;
+    const int nb = (int)(n_in / 128);
+    if (!plan_mmab(n_out, nb, (int)n_tok, 224, mp, smem_bytes, grid)) return -1;
+    CUtensorMap wmap;
+    std::memset(&wmap, 0, sizeof(wmap));
+    if (mp.tiled && !tensor_map_2d(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, W, (uint64_t)nb * W_BLOCK_BYTES / 4, (uint64_t)n_out,
+                                   (uint64_t)nb * W_BLOCK_BYTES, (uint32_t)(mp.stride / 4), 16u, CU_TENSOR_MAP_SWIZZLE_NONE))
+        return -1;
     static SmemOptIn opt, opt_dump;
     const bool pdl = g_opt_pdl.load() != 0;
     if (dump) {
         cudaError_t err = opt_dump.ensure(gemm_mma_kernel<true>);
         if (err != cudaSuccess) return (int)err;
-        return (int)launch(gemm_mma_kernel<true>, dim3((unsigned)grid), dim3(MMA_THREADS), (size_t)smem_bytes, st, false,
-                           static_cast<const uint8_t *>(W), static_cast<const uint32_t *>(Xq), Y, mp, (int)n_tok, dump);
+        return (int)launch(gemm_mma_kernel<true>, dim3((unsigned)grid), dim3(MMAB_THREADS), (size_t)smem_bytes, st, false,
+                           static_cast<const uint8_t *>(W), static_cast<const uint32_t *>(Xq), Y, mp, (int)n_tok, dump, wmap);
     }
     cudaError_t err = opt.ensure(gemm_mma_kernel<false>);
     if (err != cudaSuccess) return (int)err;
-    return (int)launch(gemm_mma_kernel<false>, dim3((unsigned)grid), dim3(MMA_THREADS), (size_t)smem_bytes, st, pdl,
-                       static_cast<const uint8_t *>(W), static_cast<const uint32_t *>(Xq), Y, mp, (int)n_tok, dump);
+    return (int)launch(gemm_mma_kernel<false>, dim3((unsigned)grid), dim3(MMAB_THREADS), (size_t)smem_bytes, st, pdl,
+                       static_cast<const uint8_t *>(W), static_cast<const uint32_t *>(Xq), Y, mp, (int)n_tok, dump, wmap);
 }
 
 int bonsai_p40_gemm(const void *W, const void *Xq, float *Y, int64_t n_out, int64_t n_in, int64_t n_tok,
@@ -1092,6 +1144,15 @@ int bonsai_p40_repack(const void *src, void *dst, int64_t n_out, int64_t n_in, b
     const int64_t nb = n_in / 128;
     if (nb <= 0 || nb % 8 != 0 || nb > INT32_MAX / 64) return 1;
     if (!aligned16(dst) || (reinterpret_cast<uintptr_t>(src) & 1u)) return 1;
+    const int64_t row_bytes = nb * W_BLOCK_BYTES;
+    if (aligned16(src) && row_bytes <= RPK_SMEM_BYTES) {
+        const int rows_per_pass = (int)(RPK_SMEM_BYTES / row_bytes);
+        long long passes = (n_out + rows_per_pass - 1) / rows_per_pass;
+        if (passes > 6 * SM_COUNT) passes = 6 * SM_COUNT;
+        repack_staged_kernel<<<(unsigned)passes, 256, RPK_SMEM_BYTES, as_stream(stream)>>>(
+            static_cast<const uint8_t *>(src), static_cast<uint8_t *>(dst), n_out, (int)nb, rows_per_pass);
+        return (int)cudaGetLastError();
+    }
     const long long total = n_out * 4 * nb;
     long long blocks = (total + 255) / 256;
     if (blocks > 32 * SM_COUNT) blocks = 32 * SM_COUNT;

@@ -30,6 +30,8 @@
 #include "common.cuh"
 #include "gemv.cuh"
 
+#include <cuda.h>          // CUtensorMap (type only: the encoder is looked up at run time)
+
 namespace b200 {
 
 constexpr int MMA_C = 15;                          // compute warps
@@ -317,124 +319,209 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) gemv_mma_kernel(const uint8_t 
     }
 }
 
-// ---- small token batches (2 .. 8 tokens): the same ring, the eight accumulator columns given to the tokens ----------
+// ---- small token batches (1 .. 8 tokens): the eight accumulator columns given to the tokens ---------------------------
 // Replaces gemm_pq2_0_p40_kernel (src/kernels/gemm_p40.cu:44-139) for the token counts between the mat-vec and a
 // tensor-core tile -- the band the reference names as missing (docs/MTP.md:58): weights are streamed ONCE for all
 // tokens.  One instruction = 16 rows x one 32-weight chunk x 8 tokens: A = the chunk's codes extracted to bytes (field t
 // of the chunk's two code words for lane t of 4: the permuted order of src/pq2_0.h:158-166, so activation words t and
-// 4 + t are the matching B rows), C starts at -s (the activation sum), so D is the host's int32 sumi
-// (src/pq2_0.h:149-169) bit for bit.  Terms (dw * da) * (float)sumi as on the host, added in ascending chunk order
-// inside a quarter of a row segment, quarters and segments in ascending order.
-// Shared memory: int8 activation words [chunk][token 0..7][8] and the Q8_1 header words [chunk][token]; tokens past
-// n_tok are zero.  Xq is the chunk-major layout of bonsai_p40_gemm: block (chunk, tok) at chunk * n_tok + tok.
-constexpr int MMA_ITEMS = 4;          // items (quarters of a segment) per tile
+// 4 + t are the matching B rows); with C = -s (the activation sum) D would be the host's int32 sumi
+// (src/pq2_0.h:149-169) bit for bit, and it is that plus a constant: C starts at 0x4B400000 - s, so
+// D = 0x4B400000 + sumi, which read as a float is 12582912 + sumi exactly (|sumi| <= 8192), and one subtraction gives
+// (float)sumi without a conversion instruction.  Terms (dw * da) * (float)sumi as on the host, added in ascending
+// chunk order inside a quarter of a row segment, quarters and segments in ascending order.
+//
+// Work of a CTA: its row groups (16 rows each) in batches of MMAB_GB; inside a batch the SEGMENT loop is the outer
+// one -- tile T = (batch, segment j, group l) -- so only the Q8_1 blocks of one segment have to be in shared memory
+// (three buffers, filled by bulk copies straight from Xq, whose chunk-major layout -- block (chunk, tok) at
+// chunk * n_tok + tok, 9 words -- is read as it is; a lane whose token is past n_tok reads a neighbour's block and
+// its accumulator column is never stored), and the ring of weight tiles gets the rest.  A tile is ONE copy: a
+// 2-D tiled copy of 16 rows x one segment (<= 24 blocks; box = `stride` bytes, 16 * odd so that the 8 rows one load
+// touches lie in different banks; what the box takes past the segment or the matrix is never read), or, for rows
+// that are not a multiple of 8 blocks, one bulk copy of 16 whole rows.  The sums of a batch's groups wait in
+// shared memory from segment to segment.
+constexpr int MMAB_ITEMS = 6;         // items (sixths of the longest segment) per tile
+constexpr int MMAB_C = 22;            // compute warps: item I = 6 * tile + sixth belongs to warp I % MMAB_C
+constexpr int MMAB_THREADS = (MMAB_C + 2) * 32;      // + weight warp + activation warp
+constexpr int MMAB_SEG_UNITS = 3;     // segment <= 3 units of 8 blocks
+constexpr int MMAB_GB = 16;           // row groups per batch
+constexpr int MMAB_MAGIC = 0x4B400000;
 
-__host__ __device__ inline size_t mmab_fixed_bytes(const MmaGeom &P, int nslot) {
-    const size_t b = 512 + (size_t)P.nb * 4 * 288 + (size_t)nslot * MMA_ITEMS * 512 + MMA_GROUP_RING * 512;
+struct MmabGeom {
+    int n_out, nb;
+    int ngroups;             // row groups of 16
+    int nseg, seg_q, seg_r;  // segments in units of 8 blocks: segment j has seg_q + (j < seg_r) units (nseg == 1: nb blocks)
+    int stride;              // bytes between the rows of a tile in its slot
+    int tiled;               // 1: a tile is one 2-D tiled copy; 0: one bulk copy of whole rows (nseg == 1)
+    int nslot, slot_bytes;
+    int pairs_max;           // block pairs in the longest segment
+    int act_bufs, act_buf_bytes;   // a buffer = the segment's Q8_1 blocks, then {da, 0x4B400000 - s} of every (chunk, token 0..7)
+    int act_tab_off;               // bytes from a buffer's start to that table
+    uint32_t magic_nslot, magic_bt;   // division by nslot, by the tiles of a full batch
+};
+__host__ __device__ inline int mmab_seg_start(const MmabGeom &P, int j) {
+    return P.nseg == 1 ? 0 : 8 * (j * P.seg_q + (j < P.seg_r ? j : P.seg_r));
+}
+__host__ __device__ inline int mmab_seg_len(const MmabGeom &P, int j) {
+    return P.nseg == 1 ? P.nb : 8 * (P.seg_q + (j < P.seg_r ? 1 : 0));
+}
+// Shared memory in front of the ring: barriers, activation buffers, item sums of every slot, sums of a batch's groups.
+__host__ __device__ inline size_t mmab_fixed_bytes(const MmabGeom &P, int nslot) {
+    const size_t b = 512 + (size_t)P.act_bufs * P.act_buf_bytes + (size_t)nslot * MMAB_ITEMS * 512 + MMAB_GB * 512;
     return (b + 127) & ~(size_t)127;
+}
+__device__ __forceinline__ void mmab_tile_copy(void *dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+                 : "memory");
 }
 
 template <bool DUMP>
-__global__ void __launch_bounds__(MMA_THREADS, 1) gemm_mma_kernel(const uint8_t *__restrict__ W, const uint32_t *__restrict__ Xq,
-                                                                 float *__restrict__ Y, const MmaGeom P, const int n_tok,
-                                                                 int32_t *__restrict__ dump) {
+__global__ void __launch_bounds__(MMAB_THREADS, 1) gemm_mma_kernel(const uint8_t *__restrict__ W, const uint32_t *__restrict__ Xq,
+                                                                  float *__restrict__ Y, const MmabGeom P, const int n_tok,
+                                                                  int32_t *__restrict__ dump,
+                                                                  const __grid_constant__ CUtensorMap wmap) {
     extern __shared__ __align__(128) uint8_t smem[];
-    uint64_t *full = reinterpret_cast<uint64_t *>(smem);
-    uint64_t *done = full + MMA_MAX_SLOTS;
-    uint64_t *freeb = done + MMA_MAX_SLOTS;
-    uint32_t *actb = reinterpret_cast<uint32_t *>(smem + 512);                 // [chunk][tok][8]
-    uint32_t *hdr = actb + (size_t)P.nb * 4 * 64;                              // [chunk][tok]
-    float *itemsum = reinterpret_cast<float *>(hdr + (size_t)P.nb * 4 * 8);   // [slot][item][row 16][tok 8]
-    float *gacc = itemsum + (size_t)P.nslot * MMA_ITEMS * 128;
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem);                       // [12] a tile has landed
+    uint64_t *freeb = full + MMA_MAX_SLOTS;                                    // [12] its sums are taken: the slot may be refilled
+    uint64_t *actfull = freeb + MMA_MAX_SLOTS;                                 // [3] a segment's Q8_1 blocks have landed
+    // [0] weight tiles given out so far, [1] steps whose Q8_1 blocks have landed and whose headers are decoded.  A
+    // compute warp visits only its own tiles, so before it tests a tile's barrier by parity it makes sure the copy it
+    // waits for has been ISSUED: that implies the barrier's previous phase is complete, and the phase after cannot
+    // complete before the warp arrives.  The activation side needs no parity at all: the count only grows.
+    volatile int *issued = reinterpret_cast<volatile int *>(smem + 256);
+    int *arrived = reinterpret_cast<int *>(smem + 272);                        // [12] item owners through with the slot's tile
+    volatile int *gstage = reinterpret_cast<volatile int *>(smem + 320);       // [16] next segment of the batch's group l
+    int *stepdone = reinterpret_cast<int *>(smem + 384);                       // [4] tiles of step q taken, at q % 4
+    uint8_t *actbuf = smem + 512;
+    float *itemsum = reinterpret_cast<float *>(actbuf + (size_t)P.act_bufs * P.act_buf_bytes);   // [slot][item][row 16][tok 8]
+    float *gacc = itemsum + (size_t)P.nslot * MMAB_ITEMS * 128;                 // [group of the batch][row 16][tok 8]
     uint8_t *ring = smem + mmab_fixed_bytes(P, P.nslot);
 
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-    const int my_groups = ((int)blockIdx.x < P.ngroups) ? (P.ngroups - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
-    const int ntiles = my_groups * P.nseg;
+    const int mg = ((int)blockIdx.x < P.ngroups) ? (P.ngroups - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+    const int ntiles = mg * P.nseg;
+    const int batch_tiles = MMAB_GB * P.nseg;
     const size_t row_bytes = (size_t)P.nb * W_BLOCK_BYTES;
-    const uint64_t pol = policy_evict_first();
-    const int ppi = (P.pairs_max + MMA_ITEMS - 1) / MMA_ITEMS;                 // pairs per item
+    const int ppi = (P.pairs_max + MMAB_ITEMS - 1) / MMAB_ITEMS;                 // pairs per item
 
-    auto tile_of = [&](int T, int &gi, int &j) {
-        const int k = (int)fast_div((uint32_t)T, P.magic_nseg);
-        j = T - k * P.nseg;
-        gi = (int)blockIdx.x + k * (int)gridDim.x;
-    };
-    auto issue_tile = [&](int T) {          // whole copy warp
-        int gi, j;
-        tile_of(T, gi, j);
-        const int slot = T - (int)fast_div((uint32_t)T, P.magic_nslot) * P.nslot;
-        const int r_cnt = min(16, P.n_out - 16 * gi);
-        const int sb = mma_seg_start(P, j), sl = mma_seg_len(P, j);
-        uint8_t *dst = ring + (size_t)slot * P.slot_bytes;
-        const uint8_t *src = W + (size_t)16 * gi * row_bytes + (size_t)sb * W_BLOCK_BYTES;
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        if (lane == 0) {
-            if (P.contiguous) {
-                const uint32_t bytes = (uint32_t)(r_cnt * row_bytes), bulk = bytes & ~15u;
-                for (uint32_t o = bulk; o < bytes; o += 4) *reinterpret_cast<uint32_t *>(dst + o) = ldg_nc_u32(src + o);
-                mbar_expect_tx(&full[slot], bulk);
-                if (bulk) bulk_g2s(dst, src, bulk, &full[slot], pol);
-            } else {
-                mbar_expect_tx(&full[slot], (uint32_t)((size_t)r_cnt * sl * W_BLOCK_BYTES));
-            }
+    // tile T -> row group gi, segment j, group l of its batch, step q (segments counted through the batches); the
+    // divisions are multiplications: a full batch has MMAB_GB groups, the last one gb_last
+    const int gb_last = mg - ((mg - 1) / MMAB_GB) * MMAB_GB;
+    const uint32_t magic_last = gb_last > 1 ? (uint32_t)(((1ull << 32) + (uint32_t)gb_last - 1) / (uint32_t)gb_last) : 0u;
+    auto tile_of = [&](int T, int &j, int &l, int &q) {
+        const int b = (int)fast_div((uint32_t)T, P.magic_bt);
+        const int r = T - b * batch_tiles;
+        if ((b + 1) * MMAB_GB <= mg) {
+            j = r / MMAB_GB;
+            l = r - j * MMAB_GB;
+        } else {
+            j = (int)fast_div((uint32_t)r, magic_last);
+            l = r - j * gb_last;
         }
-        __syncwarp();
-        if (!P.contiguous && lane < r_cnt)
-            bulk_g2s(dst + (size_t)lane * P.stride, src + (size_t)lane * row_bytes, (uint32_t)(sl * W_BLOCK_BYTES), &full[slot], pol);
+        q = b * P.nseg + j;
+        return (int)blockIdx.x + (b * MMAB_GB + l) * (int)gridDim.x;
+    };
+    auto slot_of = [&](int T, int &lap) {
+        lap = (int)fast_div((uint32_t)T, P.magic_nslot);
+        return T - lap * P.nslot;
+    };
+    auto third = [](int q) { return (int)(((uint32_t)q * 0xAAABu) >> 17); };   // q / 3 for q < 65536
+    // One lane gives out a tile.  No proxy fence: the slot was only READ by the compute warps, and their last reads
+    // are ordered before this copy by the barrier the copy warp waited on.
+    auto issue_tile = [&](int T) {
+        int j, l, q, lap;
+        const int gi = tile_of(T, j, l, q);
+        const int slot = slot_of(T, lap);
+        uint8_t *dst = ring + (size_t)slot * P.slot_bytes;
+        if (P.tiled) {
+            mbar_expect_tx(&full[slot], (uint32_t)(16 * P.stride));
+            mmab_tile_copy(dst, &wmap, (mmab_seg_start(P, j) >> 3) * 68, 16 * gi, &full[slot]);
+        } else {
+            const uint64_t pol = policy_evict_first();
+            const int r_cnt = min(16, P.n_out - 16 * gi);
+            const uint8_t *src = W + (size_t)16 * gi * row_bytes;
+            const uint32_t bytes = (uint32_t)(r_cnt * row_bytes), bulk = bytes & ~15u;
+            for (uint32_t o = bulk; o < bytes; o += 4) *reinterpret_cast<uint32_t *>(dst + o) = ldg_nc_u32(src + o);
+            mbar_expect_tx(&full[slot], bulk);
+            if (bulk) bulk_g2s(dst, src, bulk, &full[slot], pol);
+        }
     };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < MMA_MAX_SLOTS; ++s) {
             mbar_init(&full[s], 1);
-            mbar_init(&done[s], MMA_C);
             mbar_init(&freeb[s], 1);
+            arrived[s] = 0;
         }
+        for (int s = 0; s < 3; ++s) mbar_init(&actfull[s], 1);
+        for (int s = 0; s < MMAB_GB; ++s) gstage[s] = 0;
+        for (int s = 0; s < 4; ++s) stepdone[s] = 0;
+        issued[0] = 0;
+        issued[1] = 0;
         mbar_fence_init();
+        if (P.tiled) asm volatile("prefetch.tensormap [%0];" ::"l"(&wmap) : "memory");
     }
     __syncthreads();
     const int first_fill = min(P.nslot, ntiles);
-    if (wid == MMA_C)
-        for (int T = 0; T < min(2, first_fill); ++T) issue_tile(T);
+    if (wid == MMAB_C) {                                // the weights do not depend on the launch before this one
+        if (lane < first_fill) issue_tile(lane);
+        __syncwarp();
+        if (lane == 0) issued[0] = first_fill;
+    }
     pdl_launch_dependents();
     pdl_wait_prior_grid();
-    {
-        const int total = P.nb * 4 * 8;                 // (chunk, token slot)
-        for (int i = threadIdx.x; i < total; i += MMA_THREADS) {
-            const int chunk = i >> 3, tok = i & 7;
-            uint32_t v[9];
-#pragma unroll
-            for (int w = 0; w < 9; ++w) v[w] = tok < n_tok ? __ldg(Xq + 9 * ((size_t)chunk * n_tok + tok) + w) : 0u;
-            *reinterpret_cast<uint4 *>(actb + (size_t)i * 8) = make_uint4(v[1], v[2], v[3], v[4]);
-            *reinterpret_cast<uint4 *>(actb + (size_t)i * 8 + 4) = make_uint4(v[5], v[6], v[7], v[8]);
-            hdr[i] = v[0];
+    auto wait_count = [&](volatile int *c, int need) -> bool {
+        for (uint32_t n = 0; n < (1u << 22); ++n) {
+            if (*c >= need) return true;
+            __nanosleep(64);
         }
-        if (wid == MMA_C)
-            for (int T = 2; T < first_fill; ++T) issue_tile(T);
-    }
-    __syncthreads();
+        atomicExch(&g_device_status, STATUS_MBARRIER_TIMEOUT);
+        return false;
+    };
+    auto wait_equal = [&](volatile int *c, int want) -> bool {
+        for (uint32_t n = 0; n < (1u << 22); ++n) {
+            if (*c == want) return true;
+            __nanosleep(64);
+        }
+        atomicExch(&g_device_status, STATUS_MBARRIER_TIMEOUT);
+        return false;
+    };
 
-    if (wid < MMA_C) {
+    if (wid < MMAB_C) {
         const int g = lane >> 2, t = lane & 3;
         const size_t nch = (size_t)P.nb * 4;
-        // every warp goes through every tile in order (see gemv_mma_kernel); item k of tile T is item T * 4 + k
-        for (int T = 0; T < ntiles; ++T) {
-            int gi, j;
-            tile_of(T, gi, j);
-            const int sb = mma_seg_start(P, j), sl = mma_seg_len(P, j);
-            const int lap = (int)fast_div((uint32_t)T, P.magic_nslot);
-            const int slot = T - lap * P.nslot;
+        const int cstride = 9 * n_tok;                                  // words from a chunk's blocks to the next chunk's
+        const int off_b = 9 * g + 1 + t;                                // the lane's token: int8 words t and 4 + t
+        const int off_h = 4 * t;                                        // {da, c} of tokens 2t and 2t + 1 in a chunk's table row
+        const int sh0 = 16 + 2 * t, sh1 = 2 * t;
+        int q_seen = -1;
+        // a warp visits only the tiles it owns an item of; a tile's slot and a step's activation buffer cannot be given
+        // out again before every owner has arrived, so the barrier phases a warp skips are never more than one ahead
+        for (int I = wid; I < MMAB_ITEMS * ntiles; I += MMAB_C) {
+            const int T = I / MMAB_ITEMS, k = I - T * MMAB_ITEMS;
+            int j, l, q, lap;
+            const int gi = tile_of(T, j, l, q);
+            const int sb = mmab_seg_start(P, j), sl = mmab_seg_len(P, j);
+            const int q3 = third(q);
+            const int ab = P.nseg > 1 ? q - 3 * q3 : 0;
+            if (P.nseg > 1 ? q != q_seen : q_seen < 0) {        // the step's blocks have landed and their headers are decoded
+                if (!wait_count(&issued[1], P.nseg > 1 ? q + 1 : 1)) break;
+                __threadfence_block();
+                q_seen = q;
+            }
+            const uint32_t *act = reinterpret_cast<const uint32_t *>(actbuf + (size_t)ab * P.act_buf_bytes);
+            const int slot = slot_of(T, lap);
+            if (!wait_count(&issued[0], T + 1)) break;
             if (!mbar_wait_bounded(&full[slot], (uint32_t)(lap & 1))) break;
-            int k = wid - (int)((unsigned)(T * MMA_ITEMS) % (unsigned)MMA_C);
-            if (k < 0) k += MMA_C;
-            for (; k < MMA_ITEMS; k += MMA_C) {
-                const int p_lo = k * ppi, p_hi = min((k + 1) * ppi, sl >> 1);
-                if (p_lo >= p_hi) continue;                     // a short segment has fewer items; the adder skips them too
+            const int p_lo = k * ppi, p_hi = min((k + 1) * ppi, sl >> 1);   // empty in a short segment
+            if (p_lo < p_hi) {
                 float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                for (int p = p_lo; p < p_hi; ++p) {
-                    const uint8_t *r0 = ring + (size_t)slot * P.slot_bytes + (size_t)68 * p + (size_t)g * P.stride;
-                    const uint8_t *r1 = r0 + 8 * (size_t)P.stride;
-                    const uint32_t *p0 = reinterpret_cast<const uint32_t *>(r0), *p1 = reinterpret_cast<const uint32_t *>(r1);
+                const uint8_t *r0 = ring + (size_t)slot * P.slot_bytes + (size_t)68 * p_lo + (size_t)g * P.stride;
+                const uint32_t *pb = act + (size_t)8 * p_lo * cstride + off_b;
+                const uint32_t *ph = act + P.act_tab_off / 4 + (size_t)8 * p_lo * 16 + off_h;
+                for (int p = p_lo; p < p_hi; ++p, r0 += 68) {
+                    const uint32_t *p0 = reinterpret_cast<const uint32_t *>(r0);
+                    const uint32_t *p1 = reinterpret_cast<const uint32_t *>(r0 + 8 * (size_t)P.stride);
                     uint32_t e0[17], e1[17];                        // the pair's 17 words of rows g and g + 8
     #pragma unroll
                     for (int i = 0; i < 17; ++i) { e0[i] = p0[i]; e1[i] = p1[i]; }
@@ -443,77 +530,72 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) gemm_mma_kernel(const uint8_t 
                         const float dw0 = f16_bits_to_f32(bl ? (e0[8] >> 16) : (e0[0] & 0xFFFFu));
                         const float dw1 = f16_bits_to_f32(bl ? (e1[8] >> 16) : (e1[0] & 0xFFFFu));
     #pragma unroll
-                        for (int c = 0; c < 4; ++c) {
-                            uint32_t w[4];                          // row g word 0, row g + 8 word 0, row g word 1, row g + 8 word 1
-                            if (bl == 0) {                          // codes start two bytes into word 0
-                                w[0] = __funnelshift_r(e0[2 * c], e0[2 * c + 1], 16);
-                                w[1] = __funnelshift_r(e1[2 * c], e1[2 * c + 1], 16);
-                                w[2] = __funnelshift_r(e0[2 * c + 1], e0[2 * c + 2], 16);
-                                w[3] = __funnelshift_r(e1[2 * c + 1], e1[2 * c + 2], 16);
-                            } else {                                // word-aligned from word 9 on
-                                w[0] = e0[9 + 2 * c]; w[1] = e1[9 + 2 * c]; w[2] = e0[10 + 2 * c]; w[3] = e1[10 + 2 * c];
+                        for (int c = 0; c < 4; ++c, pb += cstride, ph += 16) {
+                            uint32_t a[4];          // row g word 0, row g + 8 word 0, row g word 1, row g + 8 word 1: field t
+                            if (bl == 0) {          // codes start two bytes into word 0: one funnel shift aligns and takes the field
+                                a[0] = __funnelshift_r(e0[2 * c], e0[2 * c + 1], sh0);
+                                a[1] = __funnelshift_r(e1[2 * c], e1[2 * c + 1], sh0);
+                                a[2] = __funnelshift_r(e0[2 * c + 1], e0[2 * c + 2], sh0);
+                                a[3] = __funnelshift_r(e1[2 * c + 1], e1[2 * c + 2], sh0);
+                            } else {                // word-aligned from word 9 on
+                                a[0] = e0[9 + 2 * c] >> sh1; a[1] = e1[9 + 2 * c] >> sh1;
+                                a[2] = e0[10 + 2 * c] >> sh1; a[3] = e1[10 + 2 * c] >> sh1;
                             }
-                            uint32_t a[4];
     #pragma unroll
-                            for (int i = 0; i < 4; ++i) a[i] = (w[i] >> (2 * t)) & 0x03030303u;
-                            const int ci = 4 * (sb + 2 * p + bl) + c;
-                            const uint32_t *ab = actb + ((size_t)ci * 8 + g) * 8;
-                            const uint2 hh = *reinterpret_cast<const uint2 *>(hdr + (size_t)ci * 8 + 2 * t);
-                            const int cin[4] = {-(int)(short)(hh.x >> 16), -(int)(short)(hh.y >> 16), -(int)(short)(hh.x >> 16),
-                                                -(int)(short)(hh.y >> 16)};
+                            for (int i = 0; i < 4; ++i) a[i] &= 0x03030303u;
+                            const uint4 hv = *reinterpret_cast<const uint4 *>(ph);
+                            const int cin[4] = {(int)hv.y, (int)hv.w, (int)hv.y, (int)hv.w};
                             int d[4];
-                            mma_u8s8(d, a, ab[t], ab[4 + t], cin);
-                            const float da0 = f16_bits_to_f32(hh.x & 0xFFFFu), da1 = f16_bits_to_f32(hh.y & 0xFFFFu);
-                            acc[0] = __fadd_rn(acc[0], __fmul_rn(__fmul_rn(dw0, da0), (float)d[0]));
-                            acc[1] = __fadd_rn(acc[1], __fmul_rn(__fmul_rn(dw0, da1), (float)d[1]));
-                            acc[2] = __fadd_rn(acc[2], __fmul_rn(__fmul_rn(dw1, da0), (float)d[2]));
-                            acc[3] = __fadd_rn(acc[3], __fmul_rn(__fmul_rn(dw1, da1), (float)d[3]));
+                            mma_u8s8(d, a, pb[0], pb[4], cin);
+                            const float da0 = __uint_as_float(hv.x), da1 = __uint_as_float(hv.z);
+                            const float f0 = __fsub_rn(__int_as_float(d[0]), 12582912.0f), f1 = __fsub_rn(__int_as_float(d[1]), 12582912.0f);
+                            const float f2 = __fsub_rn(__int_as_float(d[2]), 12582912.0f), f3 = __fsub_rn(__int_as_float(d[3]), 12582912.0f);
+                            acc[0] = __fadd_rn(acc[0], __fmul_rn(__fmul_rn(dw0, da0), f0));
+                            acc[1] = __fadd_rn(acc[1], __fmul_rn(__fmul_rn(dw0, da1), f1));
+                            acc[2] = __fadd_rn(acc[2], __fmul_rn(__fmul_rn(dw1, da0), f2));
+                            acc[3] = __fadd_rn(acc[3], __fmul_rn(__fmul_rn(dw1, da1), f3));
                             if (DUMP) {
+                                const int ci = 4 * (sb + 2 * p + bl) + c;
                                 const int ra = 16 * gi + g, rb = ra + 8, ta = 2 * t, tb = ta + 1;
-                                if (ra < P.n_out && ta < n_tok) dump[((size_t)ra * n_tok + ta) * nch + ci] = d[0];
-                                if (ra < P.n_out && tb < n_tok) dump[((size_t)ra * n_tok + tb) * nch + ci] = d[1];
-                                if (rb < P.n_out && ta < n_tok) dump[((size_t)rb * n_tok + ta) * nch + ci] = d[2];
-                                if (rb < P.n_out && tb < n_tok) dump[((size_t)rb * n_tok + tb) * nch + ci] = d[3];
+                                if (ra < P.n_out && ta < n_tok) dump[((size_t)ra * n_tok + ta) * nch + ci] = d[0] - MMAB_MAGIC;
+                                if (ra < P.n_out && tb < n_tok) dump[((size_t)ra * n_tok + tb) * nch + ci] = d[1] - MMAB_MAGIC;
+                                if (rb < P.n_out && ta < n_tok) dump[((size_t)rb * n_tok + ta) * nch + ci] = d[2] - MMAB_MAGIC;
+                                if (rb < P.n_out && tb < n_tok) dump[((size_t)rb * n_tok + tb) * nch + ci] = d[3] - MMAB_MAGIC;
                             }
                         }
                     }
                 }
-                float *is = itemsum + ((size_t)slot * MMA_ITEMS + k) * 128;
+                float *is = itemsum + ((size_t)slot * MMAB_ITEMS + k) * 128;
                 *reinterpret_cast<float2 *>(is + g * 8 + 2 * t) = make_float2(acc[0], acc[1]);
                 *reinterpret_cast<float2 *>(is + (g + 8) * 8 + 2 * t) = make_float2(acc[2], acc[3]);
             }
+            // the owner that arrives last adds the tile's items (ascending), joins them to the group's earlier
+            // segments (ascending: it waits for the segment before) and hands the slot back
             __syncwarp();
-            if (lane == 0) mbar_arrive(&done[slot]);
-        }
-    } else if (wid == MMA_C) {
-        for (int T = first_fill; T < ntiles; ++T) {
-            const int lap = (int)fast_div((uint32_t)T, P.magic_nslot);
-            const int slot = T - lap * P.nslot;
-            if (!mbar_wait_bounded(&freeb[slot], (uint32_t)((lap - 1) & 1))) return;
-            issue_tile(T);
-        }
-    } else {
-        // adder warp: lane l owns outputs (row l / 2, tokens 4 * (l % 2) .. + 3) of the tile
-        for (int T = 0; T < ntiles; ++T) {
-            int gi, j;
-            tile_of(T, gi, j);
-            const int lap = (int)fast_div((uint32_t)T, P.magic_nslot);
-            const int slot = T - lap * P.nslot;
-            if (!mbar_wait_bounded(&done[slot], (uint32_t)(lap & 1))) return;
-            const int items = ((mma_seg_len(P, j) >> 1) + ppi - 1) / ppi;
-            const float *is = itemsum + (size_t)slot * MMA_ITEMS * 128 + 4 * lane;
+            int before = 0;
+            if (lane == 0) {
+                __threadfence_block();
+                before = atomicAdd(&arrived[slot], 1);
+            }
+            before = __shfl_sync(0xFFFFFFFFu, before, 0);
+            if (before != MMAB_ITEMS - 1) continue;
+            __threadfence_block();
+            // lane owns outputs (row lane / 2, tokens 4 * (lane % 2) .. + 3)
+            const float *is = itemsum + (size_t)slot * MMAB_ITEMS * 128 + 4 * lane;
             float4 s = *reinterpret_cast<const float4 *>(is);
-            for (int k = 1; k < items; ++k) {
-                const float4 v = *reinterpret_cast<const float4 *>(is + k * 128);
+            for (int kk = 1; kk < MMAB_ITEMS && kk * ppi < (sl >> 1); ++kk) {
+                const float4 v = *reinterpret_cast<const float4 *>(is + kk * 128);
                 s.x = __fadd_rn(s.x, v.x); s.y = __fadd_rn(s.y, v.y); s.z = __fadd_rn(s.z, v.z); s.w = __fadd_rn(s.w, v.w);
             }
             if (P.nseg > 1) {
-                float4 *ga = reinterpret_cast<float4 *>(gacc + ((T / P.nseg) & (MMA_GROUP_RING - 1)) * 128) + lane;
+                if (!wait_equal(&gstage[l], j)) break;
+                __threadfence_block();
+                float4 *ga = reinterpret_cast<float4 *>(gacc + (size_t)l * 128) + lane;
                 if (j > 0) {
                     const float4 o = *ga;
                     s.x = __fadd_rn(o.x, s.x); s.y = __fadd_rn(o.y, s.y); s.z = __fadd_rn(o.z, s.z); s.w = __fadd_rn(o.w, s.w);
                 }
-                *ga = s;
+                if (j < P.nseg - 1) *ga = s;
             }
             if (j == P.nseg - 1) {
                 const int row = 16 * gi + (lane >> 1), tok0 = 4 * (lane & 1);
@@ -525,7 +607,97 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) gemm_mma_kernel(const uint8_t 
                 }
             }
             __syncwarp();
-            if (lane == 0) mbar_arrive(&freeb[slot]);
+            if (lane == 0) {
+                arrived[slot] = 0;
+                __threadfence_block();
+                if (P.nseg > 1) {
+                    gstage[l] = (j == P.nseg - 1) ? 0 : j + 1;
+                    atomicAdd(&stepdone[q & 3], 1);
+                }
+                mbar_arrive(&freeb[slot]);
+            }
+        }
+    } else if (wid == MMAB_C) {
+        // weight warp (one lane): the tiles past the first fill, each when its slot's previous tile is taken
+        if (lane == 0)
+            for (int T = first_fill; T < ntiles; ++T) {
+                int lap;
+                const int slot = slot_of(T, lap);
+                if (!mbar_wait_bounded(&freeb[slot], (uint32_t)((lap - 1) & 1))) break;
+                issue_tile(T);
+                issued[0] = T + 1;
+            }
+    } else {
+        // activation warp: a step's Q8_1 blocks are asked for up to two steps ahead (three buffers; a buffer is free when
+        // every tile of the step three before is taken), and when they have landed their headers are decoded once for
+        // all compute warps: {da as fp32, 0x4B400000 - s} per (chunk, token)
+        const bool bulk_ok = (reinterpret_cast<uintptr_t>(Xq) & 15u) == 0;
+        const uint64_t keep = policy_evict_normal();            // every CTA reads the same blocks: they stay in L2
+        const int nsteps = P.nseg > 1 ? ((mg + MMAB_GB - 1) / MMAB_GB) * P.nseg : (mg > 0 ? 1 : 0);
+        auto tiles_of_step = [&](int s) { return ((s / P.nseg) + 1) * MMAB_GB <= mg ? MMAB_GB : gb_last; };
+        int qa = 0;
+        bool ok = true;
+        auto ask = [&](bool block) -> bool {                    // the blocks of step qa; false: its buffer is still in use
+            if (qa >= 3) {
+                volatile int *cnt = stepdone + ((qa - 3) & 3);
+                const int need = tiles_of_step(qa - 3);
+                if (block) {
+                    if (!wait_equal(cnt, need)) { ok = false; return false; }
+                } else if (*cnt != need) {
+                    return false;
+                }
+                __syncwarp();
+                if (lane == 0) *cnt = 0;
+            }
+            const int j = P.nseg > 1 ? qa % P.nseg : 0;
+            const int ab = P.nseg > 1 ? qa - 3 * third(qa) : 0;
+            const uint32_t bytes = (uint32_t)mmab_seg_len(P, j) * 4u * (uint32_t)n_tok * 36u;
+            const uint8_t *src = reinterpret_cast<const uint8_t *>(Xq) + (size_t)mmab_seg_start(P, j) * 4 * n_tok * 36;
+            uint8_t *dst = actbuf + (size_t)ab * P.act_buf_bytes;
+            if (bulk_ok) {
+                constexpr uint32_t PIECE = 2048;                // several copies in flight land sooner than one long one
+                if (lane == 0) mbar_expect_tx(&actfull[ab], bytes);
+                __syncwarp();
+                for (uint32_t o = lane * PIECE; o < bytes; o += 32 * PIECE)
+                    bulk_g2s(dst + o, src + o, min(PIECE, bytes - o), &actfull[ab], keep);
+            } else {                                            // a vector that is only word-aligned: plain loads
+                for (uint32_t i = lane; i < bytes / 4; i += 32)
+                    reinterpret_cast<uint32_t *>(dst)[i] = __ldg(reinterpret_cast<const uint32_t *>(src) + i);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&actfull[ab]);
+            }
+            ++qa;
+            return true;
+        };
+        for (int qc = 0; qc < nsteps && ok; ++qc) {
+            while (qa < nsteps && qa <= qc + 2 && ask(qa == qc)) {}
+            if (!ok) break;
+            const int q3 = third(qc);
+            const int ab = P.nseg > 1 ? qc - 3 * q3 : 0;
+            if (!mbar_wait_bounded(&actfull[ab], P.nseg > 1 ? (uint32_t)(q3 & 1) : 0u)) break;
+            const int j = P.nseg > 1 ? qc % P.nseg : 0;
+            const uint32_t *blk = reinterpret_cast<const uint32_t *>(actbuf + (size_t)ab * P.act_buf_bytes);
+            uint2 *tab = reinterpret_cast<uint2 *>(actbuf + (size_t)ab * P.act_buf_bytes + P.act_tab_off);
+            const int n = mmab_seg_len(P, j) * 4 * 8;
+            for (int i0 = lane; i0 < n; i0 += 128) {
+                uint32_t h[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int i = i0 + 32 * u, chunk = i >> 3, tok = i & 7;
+                    h[u] = (i < n && tok < n_tok) ? blk[(size_t)(chunk * n_tok + tok) * 9] : 0u;
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int i = i0 + 32 * u;
+                    if (i < n)
+                        tab[i] = make_uint2(__float_as_uint(f16_bits_to_f32(h[u] & 0xFFFFu)), (uint32_t)(MMAB_MAGIC - ((int)h[u] >> 16)));
+                }
+            }
+            __syncwarp();
+            if (lane == 0) {
+                __threadfence_block();
+                issued[1] = qc + 1;
+            }
         }
     }
 }

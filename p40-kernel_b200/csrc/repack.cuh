@@ -41,6 +41,51 @@ __global__ void __launch_bounds__(256) repack_kernel(const uint8_t *__restrict__
     }
 }
 
+// The same with both sides moved as 16-byte words: a row of either layout is 34 * nb bytes, a multiple of 16 when
+// nb % 8 == 0, so a run of rows is one aligned range.  A CTA stages rows_per_pass source rows in shared memory, then
+// every thread builds one 16-byte destination word (8 scales, or two units of one plane) from 2-byte shared reads;
+// consecutive threads read blocks 68 bytes = 17 words apart, which no two lanes share a bank on.
+constexpr int RPK_SMEM_BYTES = 32 * 1024;
+
+__global__ void __launch_bounds__(256) repack_staged_kernel(const uint8_t *__restrict__ src, uint8_t *__restrict__ dst,
+                                                            long long n_out, int nb, int rows_per_pass) {
+    extern __shared__ __align__(16) uint8_t rpk_sm[];
+    const int row_bytes = nb * W_BLOCK_BYTES;
+    const int wpr = row_bytes / 16, scale_words = nb / 8;
+    const long long passes = (n_out + rows_per_pass - 1) / rows_per_pass;
+    for (long long ps = blockIdx.x; ps < passes; ps += gridDim.x) {
+        const long long r0 = ps * rows_per_pass;
+        const int rows = (int)((n_out - r0 < rows_per_pass) ? (n_out - r0) : rows_per_pass);
+        const int words = rows * wpr;
+        const uint4 *s4 = reinterpret_cast<const uint4 *>(src + (size_t)r0 * row_bytes);
+        uint4 *d4 = reinterpret_cast<uint4 *>(dst + (size_t)r0 * row_bytes);
+        for (int i = threadIdx.x; i < words; i += 256) reinterpret_cast<uint4 *>(rpk_sm)[i] = __ldg(s4 + i);
+        __syncthreads();
+        for (int i = threadIdx.x; i < words; i += 256) {
+            const int r = i / wpr, w = i - r * wpr;
+            const unsigned short *rs = reinterpret_cast<const unsigned short *>(rpk_sm + (size_t)r * row_bytes);
+            uint4 v;
+            if (w < scale_words) {
+                const unsigned short *q = rs + 17 * 8 * w;   // a block is 17 half-words
+                v.x = q[0] | ((uint32_t)q[17] << 16);
+                v.y = q[34] | ((uint32_t)q[51] << 16);
+                v.z = q[68] | ((uint32_t)q[85] << 16);
+                v.w = q[102] | ((uint32_t)q[119] << 16);
+            } else {
+                const int u = 2 * (w - scale_words);
+                const int p = u / nb, b = u - p * nb;
+                const unsigned short *q = rs + 17 * b + 1 + 4 * p;
+                v.x = q[0] | ((uint32_t)q[1] << 16);
+                v.y = q[2] | ((uint32_t)q[3] << 16);
+                v.z = q[17] | ((uint32_t)q[18] << 16);
+                v.w = q[19] | ((uint32_t)q[20] << 16);
+            }
+            d4[i] = v;
+        }
+        __syncthreads();
+    }
+}
+
 // TREE: the terms of a row are added by a warp (lane l adds units l, l + 32, ... in ascending order, then a 5-step
 // butterfly) -- a fixed order like that of the default mat-vec, within 1e-5 of repack_row_dot; !TREE: by one lane in
 // unit order, bit-identical to repack_row_dot (bonsai_b200_set_option("gemv_order", 1)), several times slower.

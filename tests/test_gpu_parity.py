@@ -374,6 +374,19 @@ def test_repack_bytes_and_gemv(gpu, port, n_out, n_in):
     assert_close_and_exact(host(y), want)
 
 
+def test_repack_source_two_byte_aligned(gpu, port):
+    # a source that is only 2-byte aligned takes the kernel with 2-byte loads: the same bytes
+    import torch
+    n_out, n_in = 67, 2048
+    W = synth.pq2_0_weights(n_out, n_in, seed=9)
+    buf = torch.zeros(W.size + 16, dtype=torch.uint8, device="cuda")
+    buf[2:2 + W.size] = dev(W)
+    Wr = torch.zeros(W.size, dtype=torch.uint8, device="cuda")
+    assert gpu.repack(buf[2:], Wr, n_out, n_in) == 0
+    assert np.array_equal(host(Wr), port.repack(W, n_out, n_in))
+    assert gpu.repack(buf[1:], Wr, n_out, n_in) == 1
+
+
 def test_repack_golden(gpu, golden):
     import torch
     Wr = torch.zeros(golden["W"].size, dtype=torch.uint8, device="cuda")
