@@ -655,7 +655,7 @@ __global__ void __launch_bounds__(MMAB_THREADS, 1) gemm_mma_kernel(const uint8_t
             const uint8_t *src = reinterpret_cast<const uint8_t *>(Xq) + (size_t)mmab_seg_start(P, j) * 4 * n_tok * 36;
             uint8_t *dst = actbuf + (size_t)ab * P.act_buf_bytes;
             if (bulk_ok) {
-                constexpr uint32_t PIECE = 2048;                // several copies in flight land sooner than one long one
+                constexpr uint32_t PIECE = 4096;                // several copies in flight land sooner than one long one
                 if (lane == 0) mbar_expect_tx(&actfull[ab], bytes);
                 __syncwarp();
                 for (uint32_t o = lane * PIECE; o < bytes; o += 32 * PIECE)
@@ -679,19 +679,19 @@ __global__ void __launch_bounds__(MMAB_THREADS, 1) gemm_mma_kernel(const uint8_t
             const uint32_t *blk = reinterpret_cast<const uint32_t *>(actbuf + (size_t)ab * P.act_buf_bytes);
             uint2 *tab = reinterpret_cast<uint2 *>(actbuf + (size_t)ab * P.act_buf_bytes + P.act_tab_off);
             const int n = mmab_seg_len(P, j) * 4 * 8;
-            for (int i0 = lane; i0 < n; i0 += 128) {
-                uint32_t h[4];
+            // record i = chunk * 8 + tok: lane's token is lane % 8, its chunks lane / 8, + 4, + 8, ...; all loads first
+            const int tok = lane & 7;
+            const uint32_t *src_h = blk + (size_t)((lane >> 3) * n_tok + tok) * 9;
+            constexpr int CONV_UNROLL = 24;                     // 24 * 32 records = a segment of 24 blocks
+            for (int i0 = lane; i0 < n; i0 += 32 * CONV_UNROLL, src_h += (size_t)4 * CONV_UNROLL * n_tok * 9) {
+                uint32_t h[CONV_UNROLL];
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const int i = i0 + 32 * u, chunk = i >> 3, tok = i & 7;
-                    h[u] = (i < n && tok < n_tok) ? blk[(size_t)(chunk * n_tok + tok) * 9] : 0u;
-                }
+                for (int u = 0; u < CONV_UNROLL; ++u)
+                    h[u] = (i0 + 32 * u < n && tok < n_tok) ? src_h[(size_t)4 * u * n_tok * 9] : 0u;
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const int i = i0 + 32 * u;
-                    if (i < n)
-                        tab[i] = make_uint2(__float_as_uint(f16_bits_to_f32(h[u] & 0xFFFFu)), (uint32_t)(MMAB_MAGIC - ((int)h[u] >> 16)));
-                }
+                for (int u = 0; u < CONV_UNROLL; ++u)
+                    if (i0 + 32 * u < n)
+                        tab[i0 + 32 * u] = make_uint2(__float_as_uint(f16_bits_to_f32(h[u] & 0xFFFFu)), (uint32_t)(MMAB_MAGIC - ((int)h[u] >> 16)));
             }
             __syncwarp();
             if (lane == 0) {
