@@ -508,14 +508,16 @@ def _chunk_ints(port, W, Xq, n_out, n_in, n_tok, rows, toks):
 
 @pytest.mark.parametrize("n_out,n_in,n_tok", [(128, 128, 64), (64, 256, 5), (300, 1024, 100), (256, 5120, 128), (129, 384, 65),
                                               (6400, 256, 384), (19072, 256, 130), (203, 5120, 8), (100, 17408, 8),
-                                              (37, 1024, 2), (1500, 6144, 3), (130, 2304, 7), (33, 8192, 8)])
+                                              (37, 1024, 2), (1500, 6144, 3), (130, 2304, 7), (33, 8192, 8),
+                                              (40000, 4096, 8), (38500, 256, 3)])
 def test_gemm_tensor_core_ints_and_bound(gpu, port, n_out, n_in, n_tok):
     """The two tensor-core mat-muls -- tcgen05 for token batches (gemm_path 1), mma.sync with the weights streamed once
     for 2 .. 8 tokens (gemm_path 2) -- : the int32 the tensor core produced for every (row, token, chunk) -- written out
     by bonsai_b200_gemm_dump -- equals the host loop's integer bit for bit on sampled rows and tokens, and Y is
     within 1e-5 of max |Y| of the host loop (fp32 side: fused multiply-adds per block, see csrc/gemm_tc.cuh); the
     plain entry point gives the same Y bits as the dumping one.  Full tiles, ragged rows and tokens, odd block
-    counts, and tile counts that do not divide over the SMs (tiles cut in two between neighbouring CTAs)."""
+    counts, tile counts that do not divide over the SMs (tiles cut in two between neighbouring CTAs), and for the
+    small-batch kernel more than 16 row groups per CTA (several batches of groups, with and without row segments)."""
     import torch
     W = synth.pq2_0_weights(n_out, n_in, seed=n_tok + 1)
     X = synth.activations(n_in, seed=n_out, batch=n_tok)
@@ -540,6 +542,25 @@ def test_gemm_tensor_core_ints_and_bound(gpu, port, n_out, n_in, n_tok):
         torch.cuda.synchronize()
     finally:
         gpu.set_option("gemm_path", -1)
+    assert np.array_equal(bits(host(Y2)), bits(host(Y)))
+    assert gpu.device_status() == 0
+
+
+def test_gemm_small_batch_word_aligned_activations(gpu, port):
+    """Xq that is only 4-byte aligned: the small-batch kernel stages the blocks with plain loads; same Y bits."""
+    import torch
+    n_out, n_in, n_tok = 200, 5120, 6
+    W = synth.pq2_0_weights(n_out, n_in, seed=21)
+    X = synth.activations(n_in, seed=22, batch=n_tok)
+    Xq = port.quantize_batch_chunk_major(X)
+    Wd = dev(W)
+    buf = torch.zeros(Xq.size + 16, dtype=torch.uint8, device="cuda")
+    buf[4:4 + Xq.size] = dev(Xq)
+    Y = torch.zeros(n_out, n_tok, device="cuda")
+    Y2 = torch.zeros(n_out, n_tok, device="cuda")
+    assert gpu.gemm(Wd, dev(Xq), Y, n_out, n_in, n_tok) == 0
+    assert gpu.gemm(Wd, buf[4:], Y2, n_out, n_in, n_tok) == 0
+    assert_close(host(Y), port.gemm(W, Xq, n_out, n_in, n_tok, threads=8))
     assert np.array_equal(bits(host(Y2)), bits(host(Y)))
     assert gpu.device_status() == 0
 
