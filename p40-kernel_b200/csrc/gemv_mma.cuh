@@ -458,15 +458,19 @@ __global__ void __launch_bounds__(MMAB_THREADS, 1) gemm_mma_kernel(const uint8_t
         for (int s = 0; s < 4; ++s) stepdone[s] = 0;
         issued[0] = 0;
         issued[1] = 0;
+        issued[2] = 0;                                  // steps whose Q8_1 blocks have been asked for
         mbar_fence_init();
         if (P.tiled) asm volatile("prefetch.tensormap [%0];" ::"l"(&wmap) : "memory");
     }
     __syncthreads();
-    const int first_fill = min(P.nslot, ntiles);
-    if (wid == MMAB_C) {                                // the weights do not depend on the launch before this one
-        if (lane < first_fill) issue_tile(lane);
+    // The weights do not depend on the launch before this one: two tiles go out at once.  The rest of the first fill
+    // goes out after the first step's Q8_1 blocks have been asked for -- copies complete in the order they were issued,
+    // and nothing can be multiplied before those blocks are there.
+    const int first_fill = min(P.nslot, ntiles), early = min(2, first_fill);
+    if (wid == MMAB_C) {
+        if (lane < early) issue_tile(lane);
         __syncwarp();
-        if (lane == 0) issued[0] = first_fill;
+        if (lane == 0) issued[0] = early;
     }
     pdl_launch_dependents();
     pdl_wait_prior_grid();
@@ -618,7 +622,11 @@ __global__ void __launch_bounds__(MMAB_THREADS, 1) gemm_mma_kernel(const uint8_t
             }
         }
     } else if (wid == MMAB_C) {
-        // weight warp (one lane): the tiles past the first fill, each when its slot's previous tile is taken
+        // weight warp: the rest of the first fill, then (one lane) every tile when its slot's previous tile is taken
+        if (ntiles > 0 && !wait_count(&issued[2], 1)) return;
+        if (lane >= early && lane < first_fill) issue_tile(lane);
+        __syncwarp();
+        if (lane == 0) issued[0] = first_fill;
         if (lane == 0)
             for (int T = first_fill; T < ntiles; ++T) {
                 int lap;
@@ -667,6 +675,7 @@ __global__ void __launch_bounds__(MMAB_THREADS, 1) gemm_mma_kernel(const uint8_t
                 if (lane == 0) mbar_arrive(&actfull[ab]);
             }
             ++qa;
+            if (lane == 0) issued[2] = qa;
             return true;
         };
         for (int qc = 0; qc < nsteps && ok; ++qc) {
