@@ -1054,8 +1054,8 @@ static int launch_gemm_tc(const void *W, const void *Xq, float *Y, int64_t n_out
     return tma ? go(gemm_tc_kernel<false, true>, opt[2], TC_SMEM_BYTES_TMA) : go(gemm_tc_kernel<false, false>, opt[3], TC_SMEM_BYTES);
 }
 
-// The streaming small-batch mat-mul (gemv_mma.cuh).  -1: shape not taken (more than 8 tokens, odd block count, rows
-// too long for the activations of 8 tokens to stay resident beside two ring slots, unaligned W).
+// The streaming small-batch mat-mul (gemv_mma.cuh).  -1: shape not taken (more than 8 tokens, odd block count, rows of
+// more than 48 blocks that are not a multiple of 8 blocks, unaligned W, no tensor-map encoder in the driver).
 static int launch_gemm_small(const void *W, const void *Xq, float *Y, int64_t n_out, int64_t n_in, int64_t n_tok,
                              int32_t *dump, cudaStream_t st) {
     if (n_tok < 1 || n_tok > 8 || !aligned16(W) || n_out > INT32_MAX - 16) return -1;
