@@ -1088,7 +1088,9 @@ int bonsai_p40_gemm(const void *W, const void *Xq, float *Y, int64_t n_out, int6
     if (n_out <= 0 || n_tok <= 0) return 0;
     if (n_out > INT32_MAX || n_tok > INT32_MAX || !aligned4(Xq)) return 1;
     const int path = g_opt_gemm_path.load();
-    const bool tensor = path == 1 || path == 3 || (path < 0 && n_tok >= 48);       // a 64-token tile needs tokens to fill it
+    // From 9 tokens on the tensor cores win even with a 64-token tile mostly empty (17408 x 5120 at 16 tokens:
+    // 41 us against 140 us of the integer SIMT kernel); 2 .. 8 tokens stream the weights once through mma.sync.
+    const bool tensor = path == 1 || path == 3 || (path < 0 && n_tok >= 9);
     if (tensor) {
         if (path != 3) {                                              // the fp16 form first; -1: it does not take the call
             const int rc = launch_gemm_tc16(W, Xq, Y, n_out, n_in, n_tok, as_stream(stream));

@@ -509,7 +509,7 @@ def _chunk_ints(port, W, Xq, n_out, n_in, n_tok, rows, toks):
 @pytest.mark.parametrize("n_out,n_in,n_tok", [(128, 128, 64), (64, 256, 5), (300, 1024, 100), (256, 5120, 128), (129, 384, 65),
                                               (6400, 256, 384), (19072, 256, 130), (203, 5120, 8), (100, 17408, 8),
                                               (37, 1024, 2), (1500, 6144, 3), (130, 2304, 7), (33, 8192, 8),
-                                              (40000, 4096, 8), (38500, 256, 3)])
+                                              (40000, 4096, 8), (38500, 256, 3), (300, 1024, 9), (200, 5120, 33)])
 def test_gemm_tensor_core_ints_and_bound(gpu, port, n_out, n_in, n_tok):
     """The two tensor-core mat-muls -- tcgen05 for token batches (gemm_path 1), mma.sync with the weights streamed once
     for 2 .. 8 tokens (gemm_path 2) -- : the int32 the tensor core produced for every (row, token, chunk) -- written out
@@ -566,7 +566,8 @@ def test_gemm_small_batch_word_aligned_activations(gpu, port):
 
 
 @pytest.mark.parametrize("n_out,n_in,n_tok", [(128, 1024, 64), (300, 1024, 100), (256, 5120, 128), (129, 2048, 65),
-                                              (6400, 1024, 384), (19072, 1024, 130), (1000, 17408, 48), (5120, 5120, 512)])
+                                              (6400, 1024, 384), (19072, 1024, 130), (1000, 17408, 48), (5120, 5120, 512),
+                                              (700, 5120, 9), (260, 17408, 20), (5120, 2048, 47)])
 def test_gemm_tensor_core_fp16_bound(gpu, port, n_out, n_in, n_tok):
     """The fp16 tensor-core mat-mul (gemm_path 1: activations split into two fp16 planes, whole blocks accumulated in
     tensor memory, csrc/gemm_tc16.cuh): Y within 1e-5 of max |Y| of the host loop on sampled rows, every element
@@ -605,12 +606,12 @@ def test_gemm_tensor_core_fp16_bound(gpu, port, n_out, n_in, n_tok):
 
 
 def test_gemm_default_dispatch(gpu, port):
-    """By token count: one token, and 9 .. 47, take the kernel that keeps the host's bits; 2 .. 8 the streaming
-    small-batch kernel; a prefill batch the tcgen05 kernel."""
+    """By token count: one token takes the kernel that keeps the host's bits; 2 .. 8 the streaming small-batch
+    kernel; 9 and more the tcgen05 kernel."""
     import torch
     n_out, n_in = 256, 1024
     W = synth.pq2_0_weights(n_out, n_in, seed=9)
-    for n_tok, exact in ((1, True), (8, False), (20, True), (512, False)):
+    for n_tok, exact in ((1, True), (8, False), (9, False), (20, False), (47, False), (512, False)):
         X = synth.activations(n_in, seed=n_tok, batch=n_tok)
         Xq = port.quantize_batch_chunk_major(X)
         Y = torch.zeros((n_out, n_tok), dtype=torch.float32, device="cuda")
