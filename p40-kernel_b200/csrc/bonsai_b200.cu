@@ -975,8 +975,17 @@ static int launch_gemm_tc16_n(const void *W, const void *Xq, float *Y, int64_t n
     if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (e != cudaSuccess) return (int)e;
     if (sms > TC_MAX_CTAS - 1) sms = TC_MAX_CTAS - 1;
-    const int grid = (int)(tiles < sms ? tiles : sms);
-    P.stream_k = (tiles % grid != 0 && P.total_it / grid >= P.nblocks) ? 1 : 0;
+    // Tiles for at most half of the SMs (a short token batch over few rows): up to four CTAs share a tile's blocks, at least 16
+    // blocks each.  A CTA whose whole range lies inside one tile is both a "late" and an "early" part: it waits for
+    // the part behind it, adds, stores, and raises its own flag -- the sums reach the tile's first CTA along the chain.
+    int grid = (int)(tiles < sms ? tiles : sms);
+    if (2 * tiles <= sms) {
+        long long g = P.total_it / 16;
+        if (g > 4 * tiles) g = 4 * tiles;
+        if (g > sms) g = sms;
+        if (g > grid) grid = (int)g;
+    }
+    P.stream_k = (tiles % grid != 0 && (grid > tiles || P.total_it / grid >= P.nblocks)) ? 1 : 0;
     P.epoch = g_gemm_epoch.fetch_add(1) + 1u;
     const int n_chunks = (int)(n_in / 32);
     const uint32_t *x32 = static_cast<const uint32_t *>(Xq);
@@ -1088,8 +1097,8 @@ int bonsai_p40_gemm(const void *W, const void *Xq, float *Y, int64_t n_out, int6
     if (n_out <= 0 || n_tok <= 0) return 0;
     if (n_out > INT32_MAX || n_tok > INT32_MAX || !aligned4(Xq)) return 1;
     const int path = g_opt_gemm_path.load();
-    // From 9 tokens on the tensor cores win even with a 64-token tile mostly empty (17408 x 5120 at 16 tokens:
-    // 41 us against 140 us of the integer SIMT kernel); 2 .. 8 tokens stream the weights once through mma.sync.
+    // From 9 tokens on the tensor cores win even with a 64-token tile mostly empty (5120 -> 17408 at 16 tokens:
+    // 40 us against 140 us of the integer SIMT kernel); 2 .. 8 tokens stream the weights once through mma.sync.
     const bool tensor = path == 1 || path == 3 || (path < 0 && n_tok >= 9);
     if (tensor) {
         if (path != 3) {                                              // the fp16 form first; -1: it does not take the call
