@@ -203,15 +203,18 @@ bool plan_mma(long long n_out, int nb, int cap_kb, MmaGeom &P, int &smem_bytes, 
 // MMAB_SEG_UNITS * 8 blocks, brought by one tiled copy when rows are a multiple of 8 blocks (16-byte aligned segment
 // starts, row pitch a multiple of 16), else whole rows by one bulk copy (rows of at most 48 blocks).
 bool plan_mmab(long long n_out, int nb, int n_tok, int cap_kb, MmabGeom &P, int &smem_bytes, int &grid) {
-    if (nb <= 0 || nb % 2 != 0 || n_tok < 1 || n_tok > 8) return false;
+    if (nb <= 0 || nb % 2 != 0 || n_tok < 1 || n_tok > 16) return false;
     P = MmabGeom{};
+    P.ntg = n_tok > 8 ? 2 : 1;
+    // 9 .. 16 tokens double a segment's activation blocks and every sum: segments of one unit keep the ring deep
+    const int seg_units = P.ntg == 2 ? 1 : MMAB_SEG_UNITS;
     P.n_out = (int)n_out;
     P.nb = nb;
     P.ngroups = (int)((n_out + 15) / 16);
     int seg_max;
     if (nb % 8 == 0) {
         const int units = nb / 8;
-        P.nseg = (units + MMAB_SEG_UNITS - 1) / MMAB_SEG_UNITS;
+        P.nseg = (units + seg_units - 1) / seg_units;
         P.seg_q = units / P.nseg;
         P.seg_r = units % P.nseg;
         seg_max = 8 * (P.seg_q + (P.seg_r ? 1 : 0));
@@ -220,7 +223,7 @@ bool plan_mmab(long long n_out, int nb, int n_tok, int cap_kb, MmabGeom &P, int 
         P.stride = 16 * s16;
         P.tiled = 1;
     } else {
-        if (nb > 48) return false;
+        if (nb > 48 || P.ntg > 1) return false;
         P.nseg = 1;
         seg_max = nb;
         P.stride = nb * W_BLOCK_BYTES;
@@ -229,8 +232,8 @@ bool plan_mmab(long long n_out, int nb, int n_tok, int cap_kb, MmabGeom &P, int 
     P.pairs_max = seg_max / 2;
     P.slot_bytes = (16 * P.stride + 127) & ~127;
     P.act_bufs = P.nseg > 1 ? 3 : 1;
-    P.act_tab_off = (seg_max * 4 * n_tok * 36 + 8 * 36 + 127) & ~127;       // + what lanes past n_tok read beyond the last block
-    P.act_buf_bytes = P.act_tab_off + seg_max * 4 * 64;
+    P.act_tab_off = (seg_max * 4 * n_tok * 36 + 8 * P.ntg * 36 + 127) & ~127;       // + what lanes past n_tok read beyond the last block
+    P.act_buf_bytes = P.act_tab_off + seg_max * 4 * 64 * P.ntg;
     int nslot = MMA_MAX_SLOTS;
     while (nslot >= 2 && mmab_fixed_bytes(P, nslot) + (size_t)nslot * P.slot_bytes > (size_t)cap_kb * 1024) --nslot;
     if (nslot < 2) return false;
@@ -1067,7 +1070,7 @@ static int launch_gemm_tc(const void *W, const void *Xq, float *Y, int64_t n_out
 // more than 48 blocks that are not a multiple of 8 blocks, unaligned W, no tensor-map encoder in the driver).
 static int launch_gemm_small(const void *W, const void *Xq, float *Y, int64_t n_out, int64_t n_in, int64_t n_tok,
                              int32_t *dump, cudaStream_t st) {
-    if (n_tok < 1 || n_tok > 8 || !aligned16(W) || n_out > INT32_MAX - 16) return -1;
+    if (n_tok < 1 || n_tok > 16 || (dump && n_tok > 8) || !aligned16(W) || n_out > INT32_MAX - 16) return -1;
     MmabGeom mp;
     int smem_bytes = 0, grid = 0;
     const int nb = (int)(n_in / 128);
@@ -1077,17 +1080,23 @@ static int launch_gemm_small(const void *W, const void *Xq, float *Y, int64_t n_
     if (mp.tiled && !tensor_map_2d(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, W, (uint64_t)nb * W_BLOCK_BYTES / 4, (uint64_t)n_out,
                                    (uint64_t)nb * W_BLOCK_BYTES, (uint32_t)(mp.stride / 4), 16u, CU_TENSOR_MAP_SWIZZLE_NONE))
         return -1;
-    static SmemOptIn opt, opt_dump;
+    static SmemOptIn opt, opt2, opt_dump;
     const bool pdl = g_opt_pdl.load() != 0;
-    if (dump) {
-        cudaError_t err = opt_dump.ensure(gemm_mma_kernel<true>);
+    if (mp.ntg == 2) {
+        cudaError_t err = opt2.ensure(gemm_mma_kernel<false, 2>);
         if (err != cudaSuccess) return (int)err;
-        return (int)launch(gemm_mma_kernel<true>, dim3((unsigned)grid), dim3(MMAB_THREADS), (size_t)smem_bytes, st, false,
+        return (int)launch(gemm_mma_kernel<false, 2>, dim3((unsigned)grid), dim3(MMAB_THREADS), (size_t)smem_bytes, st, pdl,
                            static_cast<const uint8_t *>(W), static_cast<const uint32_t *>(Xq), Y, mp, (int)n_tok, dump, wmap);
     }
-    cudaError_t err = opt.ensure(gemm_mma_kernel<false>);
+    if (dump) {
+        cudaError_t err = opt_dump.ensure(gemm_mma_kernel<true, 1>);
+        if (err != cudaSuccess) return (int)err;
+        return (int)launch(gemm_mma_kernel<true, 1>, dim3((unsigned)grid), dim3(MMAB_THREADS), (size_t)smem_bytes, st, false,
+                           static_cast<const uint8_t *>(W), static_cast<const uint32_t *>(Xq), Y, mp, (int)n_tok, dump, wmap);
+    }
+    cudaError_t err = opt.ensure(gemm_mma_kernel<false, 1>);
     if (err != cudaSuccess) return (int)err;
-    return (int)launch(gemm_mma_kernel<false>, dim3((unsigned)grid), dim3(MMAB_THREADS), (size_t)smem_bytes, st, pdl,
+    return (int)launch(gemm_mma_kernel<false, 1>, dim3((unsigned)grid), dim3(MMAB_THREADS), (size_t)smem_bytes, st, pdl,
                        static_cast<const uint8_t *>(W), static_cast<const uint32_t *>(Xq), Y, mp, (int)n_tok, dump, wmap);
 }
 
@@ -1099,17 +1108,19 @@ int bonsai_p40_gemm(const void *W, const void *Xq, float *Y, int64_t n_out, int6
     const int path = g_opt_gemm_path.load();
     // From 9 tokens on the tensor cores win even with a 64-token tile mostly empty (5120 -> 17408 at 16 tokens:
     // 40 us against 140 us of the integer SIMT kernel); 2 .. 8 tokens stream the weights once through mma.sync.
-    const bool tensor = path == 1 || path == 3 || (path < 0 && n_tok >= 9);
-    if (tensor) {
+    // 9 .. 16 tokens over a matrix of up to ~100 MB: the streaming kernel with two token groups is ahead of the tensor
+    // cores by its shorter start-up (31 against 40 us at 24 MB); on larger matrices its two mma.sync per chunk lose.
+    const bool small16 = n_tok >= 9 && n_tok <= 16 && (n_in / 128) % 8 == 0 && n_out * (n_in / 128) * W_BLOCK_BYTES <= (100ll << 20);
+    if (path == 2 || (path < 0 && n_tok >= 2 && (n_tok <= 8 || small16))) {     // a handful of tokens: weights streamed once for all of them
+        const int rc = launch_gemm_small(W, Xq, Y, n_out, n_in, n_tok, nullptr, as_stream(stream));
+        if (rc >= 0) return rc;                                       // -1: the shape does not fit, a kernel below takes it
+    }
+    if (path == 1 || path == 3 || (path < 0 && n_tok >= 9)) {
         if (path != 3) {                                              // the fp16 form first; -1: it does not take the call
             const int rc = launch_gemm_tc16(W, Xq, Y, n_out, n_in, n_tok, as_stream(stream));
             if (rc >= 0) return rc;
         }
         return launch_gemm_tc(W, Xq, Y, n_out, n_in, n_tok, nullptr, as_stream(stream));
-    }
-    if (path == 2 || (path < 0 && n_tok >= 2 && n_tok <= 8)) {        // a handful of tokens: weights streamed once for all of them
-        const int rc = launch_gemm_small(W, Xq, Y, n_out, n_in, n_tok, nullptr, as_stream(stream));
-        if (rc >= 0) return rc;                                       // -1: the shape does not fit, the kernel below takes it
     }
     const dim3 grid((unsigned)((n_out + GS_ROWS - 1) / GS_ROWS), (unsigned)((n_tok + GS_TOKS - 1) / GS_TOKS));
     if (grid.y > 65535) return 1;

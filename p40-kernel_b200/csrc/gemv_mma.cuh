@@ -356,6 +356,7 @@ struct MmabGeom {
     int pairs_max;           // block pairs in the longest segment
     int act_bufs, act_buf_bytes;   // a buffer = the segment's Q8_1 blocks, then {da, 0x4B400000 - s} of every (chunk, token 0..7)
     int act_tab_off;               // bytes from a buffer's start to that table
+    int ntg;                       // token groups of 8 (1: up to 8 tokens, 2: 9 .. 16)
     uint32_t magic_nslot, magic_bt;   // division by nslot, by the tiles of a full batch
 };
 __host__ __device__ inline int mmab_seg_start(const MmabGeom &P, int j) {
@@ -366,7 +367,7 @@ __host__ __device__ inline int mmab_seg_len(const MmabGeom &P, int j) {
 }
 // Shared memory in front of the ring: barriers, activation buffers, item sums of every slot, sums of a batch's groups.
 __host__ __device__ inline size_t mmab_fixed_bytes(const MmabGeom &P, int nslot) {
-    const size_t b = 512 + (size_t)P.act_bufs * P.act_buf_bytes + (size_t)nslot * MMAB_ITEMS * 512 + MMAB_GB * 512;
+    const size_t b = 512 + (size_t)P.act_bufs * P.act_buf_bytes + ((size_t)nslot * MMAB_ITEMS + MMAB_GB) * 512 * P.ntg;
     return (b + 127) & ~(size_t)127;
 }
 __device__ __forceinline__ void mmab_tile_copy(void *dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
@@ -375,7 +376,8 @@ __device__ __forceinline__ void mmab_tile_copy(void *dst, const CUtensorMap *map
                  : "memory");
 }
 
-template <bool DUMP>
+// NTG token groups of 8: the second group's MMA reuses the extracted code bytes of the first.
+template <bool DUMP, int NTG>
 __global__ void __launch_bounds__(MMAB_THREADS, 1) gemm_mma_kernel(const uint8_t *__restrict__ W, const uint32_t *__restrict__ Xq,
                                                                   float *__restrict__ Y, const MmabGeom P, const int n_tok,
                                                                   int32_t *__restrict__ dump,
@@ -393,8 +395,8 @@ __global__ void __launch_bounds__(MMAB_THREADS, 1) gemm_mma_kernel(const uint8_t
     volatile int *gstage = reinterpret_cast<volatile int *>(smem + 320);       // [16] next segment of the batch's group l
     int *stepdone = reinterpret_cast<int *>(smem + 384);                       // [4] tiles of step q taken, at q % 4
     uint8_t *actbuf = smem + 512;
-    float *itemsum = reinterpret_cast<float *>(actbuf + (size_t)P.act_bufs * P.act_buf_bytes);   // [slot][item][row 16][tok 8]
-    float *gacc = itemsum + (size_t)P.nslot * MMAB_ITEMS * 128;                 // [group of the batch][row 16][tok 8]
+    float *itemsum = reinterpret_cast<float *>(actbuf + (size_t)P.act_bufs * P.act_buf_bytes);   // [slot][item][token group][row 16][tok 8]
+    float *gacc = itemsum + (size_t)P.nslot * MMAB_ITEMS * NTG * 128;           // [group of the batch][token group][row 16][tok 8]
     uint8_t *ring = smem + mmab_fixed_bytes(P, P.nslot);
 
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
@@ -496,7 +498,7 @@ __global__ void __launch_bounds__(MMAB_THREADS, 1) gemm_mma_kernel(const uint8_t
         const size_t nch = (size_t)P.nb * 4;
         const int cstride = 9 * n_tok;                                  // words from a chunk's blocks to the next chunk's
         const int off_b = 9 * g + 1 + t;                                // the lane's token: int8 words t and 4 + t
-        const int off_h = 4 * t;                                        // {da, c} of tokens 2t and 2t + 1 in a chunk's table row
+        const int off_h = 4 * t;                                        // {da, c} of tokens 2t and 2t + 1 in a chunk's table row (8 NTG tokens)
         const int sh0 = 16 + 2 * t, sh1 = 2 * t;
         int q_seen = -1;
         // a warp visits only the tiles it owns an item of; a tile's slot and a step's activation buffer cannot be given
@@ -519,10 +521,12 @@ __global__ void __launch_bounds__(MMAB_THREADS, 1) gemm_mma_kernel(const uint8_t
             if (!mbar_wait_bounded(&full[slot], (uint32_t)(lap & 1))) break;
             const int p_lo = k * ppi, p_hi = min((k + 1) * ppi, sl >> 1);   // empty in a short segment
             if (p_lo < p_hi) {
-                float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                float acc[NTG][4];
+#pragma unroll
+                for (int u = 0; u < NTG; ++u) acc[u][0] = acc[u][1] = acc[u][2] = acc[u][3] = 0.0f;
                 const uint8_t *r0 = ring + (size_t)slot * P.slot_bytes + (size_t)68 * p_lo + (size_t)g * P.stride;
                 const uint32_t *pb = act + (size_t)8 * p_lo * cstride + off_b;
-                const uint32_t *ph = act + P.act_tab_off / 4 + (size_t)8 * p_lo * 16 + off_h;
+                const uint32_t *ph = act + P.act_tab_off / 4 + (size_t)8 * p_lo * 16 * NTG + off_h;
                 for (int p = p_lo; p < p_hi; ++p, r0 += 68) {
                     const uint32_t *p0 = reinterpret_cast<const uint32_t *>(r0);
                     const uint32_t *p1 = reinterpret_cast<const uint32_t *>(r0 + 8 * (size_t)P.stride);
@@ -534,7 +538,7 @@ __global__ void __launch_bounds__(MMAB_THREADS, 1) gemm_mma_kernel(const uint8_t
                         const float dw0 = f16_bits_to_f32(bl ? (e0[8] >> 16) : (e0[0] & 0xFFFFu));
                         const float dw1 = f16_bits_to_f32(bl ? (e1[8] >> 16) : (e1[0] & 0xFFFFu));
     #pragma unroll
-                        for (int c = 0; c < 4; ++c, pb += cstride, ph += 16) {
+                        for (int c = 0; c < 4; ++c, pb += cstride, ph += 16 * NTG) {
                             uint32_t a[4];          // row g word 0, row g + 8 word 0, row g word 1, row g + 8 word 1: field t
                             if (bl == 0) {          // codes start two bytes into word 0: one funnel shift aligns and takes the field
                                 a[0] = __funnelshift_r(e0[2 * c], e0[2 * c + 1], sh0);
@@ -547,31 +551,37 @@ __global__ void __launch_bounds__(MMAB_THREADS, 1) gemm_mma_kernel(const uint8_t
                             }
     #pragma unroll
                             for (int i = 0; i < 4; ++i) a[i] &= 0x03030303u;
-                            const uint4 hv = *reinterpret_cast<const uint4 *>(ph);
-                            const int cin[4] = {(int)hv.y, (int)hv.w, (int)hv.y, (int)hv.w};
-                            int d[4];
-                            mma_u8s8(d, a, pb[0], pb[4], cin);
-                            const float da0 = __uint_as_float(hv.x), da1 = __uint_as_float(hv.z);
-                            const float f0 = __fsub_rn(__int_as_float(d[0]), 12582912.0f), f1 = __fsub_rn(__int_as_float(d[1]), 12582912.0f);
-                            const float f2 = __fsub_rn(__int_as_float(d[2]), 12582912.0f), f3 = __fsub_rn(__int_as_float(d[3]), 12582912.0f);
-                            acc[0] = __fadd_rn(acc[0], __fmul_rn(__fmul_rn(dw0, da0), f0));
-                            acc[1] = __fadd_rn(acc[1], __fmul_rn(__fmul_rn(dw0, da1), f1));
-                            acc[2] = __fadd_rn(acc[2], __fmul_rn(__fmul_rn(dw1, da0), f2));
-                            acc[3] = __fadd_rn(acc[3], __fmul_rn(__fmul_rn(dw1, da1), f3));
+                            int d[NTG][4];
+#pragma unroll
+                            for (int u = 0; u < NTG; ++u) {
+                                const uint4 hv = *reinterpret_cast<const uint4 *>(ph + 16 * u);
+                                const int cin[4] = {(int)hv.y, (int)hv.w, (int)hv.y, (int)hv.w};
+                                mma_u8s8(d[u], a, pb[72 * u], pb[72 * u + 4], cin);
+                                const float da0 = __uint_as_float(hv.x), da1 = __uint_as_float(hv.z);
+                                const float f0 = __fsub_rn(__int_as_float(d[u][0]), 12582912.0f), f1 = __fsub_rn(__int_as_float(d[u][1]), 12582912.0f);
+                                const float f2 = __fsub_rn(__int_as_float(d[u][2]), 12582912.0f), f3 = __fsub_rn(__int_as_float(d[u][3]), 12582912.0f);
+                                acc[u][0] = __fadd_rn(acc[u][0], __fmul_rn(__fmul_rn(dw0, da0), f0));
+                                acc[u][1] = __fadd_rn(acc[u][1], __fmul_rn(__fmul_rn(dw0, da1), f1));
+                                acc[u][2] = __fadd_rn(acc[u][2], __fmul_rn(__fmul_rn(dw1, da0), f2));
+                                acc[u][3] = __fadd_rn(acc[u][3], __fmul_rn(__fmul_rn(dw1, da1), f3));
+                            }
                             if (DUMP) {
                                 const int ci = 4 * (sb + 2 * p + bl) + c;
                                 const int ra = 16 * gi + g, rb = ra + 8, ta = 2 * t, tb = ta + 1;
-                                if (ra < P.n_out && ta < n_tok) dump[((size_t)ra * n_tok + ta) * nch + ci] = d[0] - MMAB_MAGIC;
-                                if (ra < P.n_out && tb < n_tok) dump[((size_t)ra * n_tok + tb) * nch + ci] = d[1] - MMAB_MAGIC;
-                                if (rb < P.n_out && ta < n_tok) dump[((size_t)rb * n_tok + ta) * nch + ci] = d[2] - MMAB_MAGIC;
-                                if (rb < P.n_out && tb < n_tok) dump[((size_t)rb * n_tok + tb) * nch + ci] = d[3] - MMAB_MAGIC;
+                                if (ra < P.n_out && ta < n_tok) dump[((size_t)ra * n_tok + ta) * nch + ci] = d[0][0] - MMAB_MAGIC;
+                                if (ra < P.n_out && tb < n_tok) dump[((size_t)ra * n_tok + tb) * nch + ci] = d[0][1] - MMAB_MAGIC;
+                                if (rb < P.n_out && ta < n_tok) dump[((size_t)rb * n_tok + ta) * nch + ci] = d[0][2] - MMAB_MAGIC;
+                                if (rb < P.n_out && tb < n_tok) dump[((size_t)rb * n_tok + tb) * nch + ci] = d[0][3] - MMAB_MAGIC;
                             }
                         }
                     }
                 }
-                float *is = itemsum + ((size_t)slot * MMAB_ITEMS + k) * 128;
-                *reinterpret_cast<float2 *>(is + g * 8 + 2 * t) = make_float2(acc[0], acc[1]);
-                *reinterpret_cast<float2 *>(is + (g + 8) * 8 + 2 * t) = make_float2(acc[2], acc[3]);
+#pragma unroll
+                for (int u = 0; u < NTG; ++u) {
+                    float *is = itemsum + (((size_t)slot * MMAB_ITEMS + k) * NTG + u) * 128;
+                    *reinterpret_cast<float2 *>(is + g * 8 + 2 * t) = make_float2(acc[u][0], acc[u][1]);
+                    *reinterpret_cast<float2 *>(is + (g + 8) * 8 + 2 * t) = make_float2(acc[u][2], acc[u][3]);
+                }
             }
             // the owner that arrives last adds the tile's items (ascending), joins them to the group's earlier
             // segments (ascending: it waits for the segment before) and hands the slot back
@@ -584,30 +594,35 @@ __global__ void __launch_bounds__(MMAB_THREADS, 1) gemm_mma_kernel(const uint8_t
             before = __shfl_sync(0xFFFFFFFFu, before, 0);
             if (before != MMAB_ITEMS - 1) continue;
             __threadfence_block();
-            // lane owns outputs (row lane / 2, tokens 4 * (lane % 2) .. + 3)
-            const float *is = itemsum + (size_t)slot * MMAB_ITEMS * 128 + 4 * lane;
-            float4 s = *reinterpret_cast<const float4 *>(is);
-            for (int kk = 1; kk < MMAB_ITEMS && kk * ppi < (sl >> 1); ++kk) {
-                const float4 v = *reinterpret_cast<const float4 *>(is + kk * 128);
-                s.x = __fadd_rn(s.x, v.x); s.y = __fadd_rn(s.y, v.y); s.z = __fadd_rn(s.z, v.z); s.w = __fadd_rn(s.w, v.w);
-            }
+            // lane owns outputs (row lane / 2, tokens 4 * (lane % 2) .. + 3) of every token group
             if (P.nseg > 1) {
                 if (!wait_equal(&gstage[l], j)) break;
                 __threadfence_block();
-                float4 *ga = reinterpret_cast<float4 *>(gacc + (size_t)l * 128) + lane;
-                if (j > 0) {
-                    const float4 o = *ga;
-                    s.x = __fadd_rn(o.x, s.x); s.y = __fadd_rn(o.y, s.y); s.z = __fadd_rn(o.z, s.z); s.w = __fadd_rn(o.w, s.w);
-                }
-                if (j < P.nseg - 1) *ga = s;
             }
-            if (j == P.nseg - 1) {
-                const int row = 16 * gi + (lane >> 1), tok0 = 4 * (lane & 1);
-                if (row < P.n_out) {
-                    const float out[4] = {s.x, s.y, s.z, s.w};
 #pragma unroll
-                    for (int e = 0; e < 4; ++e)
-                        if (tok0 + e < n_tok) Y[(size_t)row * n_tok + tok0 + e] = out[e];
+            for (int u = 0; u < NTG; ++u) {
+                const float *is = itemsum + ((size_t)slot * MMAB_ITEMS * NTG + u) * 128 + 4 * lane;
+                float4 s = *reinterpret_cast<const float4 *>(is);
+                for (int kk = 1; kk < MMAB_ITEMS && kk * ppi < (sl >> 1); ++kk) {
+                    const float4 v = *reinterpret_cast<const float4 *>(is + kk * NTG * 128);
+                    s.x = __fadd_rn(s.x, v.x); s.y = __fadd_rn(s.y, v.y); s.z = __fadd_rn(s.z, v.z); s.w = __fadd_rn(s.w, v.w);
+                }
+                if (P.nseg > 1) {
+                    float4 *ga = reinterpret_cast<float4 *>(gacc + ((size_t)l * NTG + u) * 128) + lane;
+                    if (j > 0) {
+                        const float4 o = *ga;
+                        s.x = __fadd_rn(o.x, s.x); s.y = __fadd_rn(o.y, s.y); s.z = __fadd_rn(o.z, s.z); s.w = __fadd_rn(o.w, s.w);
+                    }
+                    if (j < P.nseg - 1) *ga = s;
+                }
+                if (j == P.nseg - 1) {
+                    const int row = 16 * gi + (lane >> 1), tok0 = 8 * u + 4 * (lane & 1);
+                    if (row < P.n_out) {
+                        const float out[4] = {s.x, s.y, s.z, s.w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e)
+                            if (tok0 + e < n_tok) Y[(size_t)row * n_tok + tok0 + e] = out[e];
+                    }
                 }
             }
             __syncwarp();
@@ -687,16 +702,18 @@ __global__ void __launch_bounds__(MMAB_THREADS, 1) gemm_mma_kernel(const uint8_t
             const int j = P.nseg > 1 ? qc % P.nseg : 0;
             const uint32_t *blk = reinterpret_cast<const uint32_t *>(actbuf + (size_t)ab * P.act_buf_bytes);
             uint2 *tab = reinterpret_cast<uint2 *>(actbuf + (size_t)ab * P.act_buf_bytes + P.act_tab_off);
-            const int n = mmab_seg_len(P, j) * 4 * 8;
-            // record i = chunk * 8 + tok: lane's token is lane % 8, its chunks lane / 8, + 4, + 8, ...; all loads first
-            const int tok = lane & 7;
-            const uint32_t *src_h = blk + (size_t)((lane >> 3) * n_tok + tok) * 9;
-            constexpr int CONV_UNROLL = 24;                     // 24 * 32 records = a segment of 24 blocks
-            for (int i0 = lane; i0 < n; i0 += 32 * CONV_UNROLL, src_h += (size_t)4 * CONV_UNROLL * n_tok * 9) {
+            // record i = chunk * TPC + tok (TPC = 8 NTG table entries per chunk): the lane's token is lane % TPC, its
+            // chunks lane / TPC, + 32 / TPC, ...; all loads of a round first
+            constexpr int TPC = 8 * NTG, CPW = 32 / TPC;
+            const int n = mmab_seg_len(P, j) * 4 * TPC;
+            const int tok = lane & (TPC - 1);
+            const uint32_t *src_h = blk + (size_t)((lane / TPC) * n_tok + tok) * 9;
+            constexpr int CONV_UNROLL = 24;
+            for (int i0 = lane; i0 < n; i0 += 32 * CONV_UNROLL, src_h += (size_t)CPW * CONV_UNROLL * n_tok * 9) {
                 uint32_t h[CONV_UNROLL];
 #pragma unroll
                 for (int u = 0; u < CONV_UNROLL; ++u)
-                    h[u] = (i0 + 32 * u < n && tok < n_tok) ? src_h[(size_t)4 * u * n_tok * 9] : 0u;
+                    h[u] = (i0 + 32 * u < n && tok < n_tok) ? src_h[(size_t)CPW * u * n_tok * 9] : 0u;
 #pragma unroll
                 for (int u = 0; u < CONV_UNROLL; ++u)
                     if (i0 + 32 * u < n)

@@ -546,6 +546,32 @@ def test_gemm_tensor_core_ints_and_bound(gpu, port, n_out, n_in, n_tok):
     assert gpu.device_status() == 0
 
 
+@pytest.mark.parametrize("n_out,n_in,n_tok", [(203, 5120, 9), (100, 17408, 16), (1500, 6144, 12), (40000, 4096, 13),
+                                              (33, 1024, 10)])
+def test_gemm_small_batch_up_to_16_tokens(gpu, port, n_out, n_in, n_tok):
+    """9 .. 16 tokens through the streaming kernel (two token groups per code extraction; the default for matrices of up
+    to ~100 MB, gemm_path 2 asks for it): Y within 1e-5 of max |Y| of the host loop, every element written, the same
+    bits on a second call and from the default dispatch."""
+    import torch
+    W = synth.pq2_0_weights(n_out, n_in, seed=n_tok + 5)
+    X = synth.activations(n_in, seed=n_out + 2, batch=n_tok)
+    Xq = port.quantize_batch_chunk_major(X)
+    Wd, Xqd = dev(W), dev(Xq)
+    Y = torch.full((n_out, n_tok), float("nan"), dtype=torch.float32, device="cuda")
+    Y2 = torch.full((n_out, n_tok), float("nan"), dtype=torch.float32, device="cuda")
+    try:
+        assert gpu.set_option("gemm_path", 2) == 0
+        assert gpu.gemm(Wd, Xqd, Y, n_out, n_in, n_tok) == 0
+    finally:
+        gpu.set_option("gemm_path", -1)
+    assert gpu.gemm(Wd, Xqd, Y2, n_out, n_in, n_tok) == 0
+    torch.cuda.synchronize()
+    assert gpu.device_status() == 0
+    assert np.isfinite(host(Y)).all()
+    assert_close(host(Y), port.gemm(W, Xq, n_out, n_in, n_tok, threads=8))
+    assert np.array_equal(bits(host(Y2)), bits(host(Y)))
+
+
 def test_gemm_small_batch_word_aligned_activations(gpu, port):
     """Xq that is only 4-byte aligned: the small-batch kernel stages the blocks with plain loads; same Y bits."""
     import torch
