@@ -126,7 +126,7 @@ int bonsai_b200_stream_probe(const void *buf, int64_t bytes, int mode, void *sin
  * (csrc/gemv_mma.cuh: same terms, another fixed tree; measured slower than 0 at batch 1, kept as the measured
  * alternative and as the body of the 2 .. 8 token kernel).
  * key "gemm_path": -1 (default) = the mat-mul picks its kernel by token count (2 .. 8 tokens: the streaming
- * small-batch kernel, which also takes 9 .. 16 tokens over matrices of up to ~100 MB; otherwise 9 tokens and more: the
+ * small-batch kernel, which also takes 9 .. 16 tokens when rows are a multiple of 8 blocks; otherwise 9 tokens and more: the
  * tensor cores; one token: the integer SIMT kernel), 0 = integer SIMT kernel (Y
  * bit-identical to the host loop), 1 = tensor cores (the fp16 form, csrc/gemm_tc16.cuh, where it takes the call,
  * else the integer form), 2 = the small-batch kernel where it takes the shape, 3 = the integer tensor-core kernel

@@ -206,8 +206,12 @@ bool plan_mmab(long long n_out, int nb, int n_tok, int cap_kb, MmabGeom &P, int 
     if (nb <= 0 || nb % 2 != 0 || n_tok < 1 || n_tok > 16) return false;
     P = MmabGeom{};
     P.ntg = n_tok > 8 ? 2 : 1;
+    // two row groups per tile (a chunk's activation and header loads serve two MMAs) pay when a CTA has enough groups
+    // to keep its warps busy with tiles of twice the size: measured 172 -> 160 us on 5120 x 248320, 23 -> 29 us on
+    // 17408 x 5120 (2 .. 3 groups per CTA)
+    P.nrg = (P.ntg == 1 && (n_out + 15) / 16 >= 6ll * SM_COUNT) ? 2 : 1;
     // 9 .. 16 tokens double a segment's activation blocks and every sum: segments of one unit keep the ring deep
-    const int seg_units = P.ntg == 2 ? 1 : MMAB_SEG_UNITS;
+    const int seg_units = P.ntg == 2 ? 1 : (P.nrg == 2 ? 2 : MMAB_SEG_UNITS);
     P.n_out = (int)n_out;
     P.nb = nb;
     P.ngroups = (int)((n_out + 15) / 16);
@@ -230,7 +234,9 @@ bool plan_mmab(long long n_out, int nb, int n_tok, int cap_kb, MmabGeom &P, int 
         P.tiled = 0;
     }
     P.pairs_max = seg_max / 2;
-    P.slot_bytes = (16 * P.stride + 127) & ~127;
+    P.ppi = P.ntg == 2 ? 1 : 2;                         // an item is 16 MMAs
+    P.items = (P.pairs_max + P.ppi - 1) / P.ppi;
+    P.slot_bytes = (P.nrg * 16 * P.stride + 127) & ~127;
     P.act_bufs = P.nseg > 1 ? 3 : 1;
     P.act_tab_off = (seg_max * 4 * n_tok * 36 + 8 * P.ntg * 36 + 127) & ~127;       // + what lanes past n_tok read beyond the last block
     P.act_buf_bytes = P.act_tab_off + seg_max * 4 * 64 * P.ntg;
@@ -239,10 +245,11 @@ bool plan_mmab(long long n_out, int nb, int n_tok, int cap_kb, MmabGeom &P, int 
     if (nslot < 2) return false;
     P.nslot = nslot;
     P.magic_nslot = magic_u32((uint32_t)nslot);
-    P.magic_bt = magic_u32((uint32_t)(MMAB_GB * P.nseg));
+    P.magic_bt = magic_u32((uint32_t)(MMAB_GB / P.nrg * P.nseg));
+    P.magic_items = magic_u32((uint32_t)P.items);
     // tile and step numbers stay small enough for the multiplicative divisions of the kernel
     const long long groups_per_cta = (P.ngroups + SM_COUNT - 1) / SM_COUNT;
-    if (groups_per_cta * P.nseg >= (1 << 20) || (groups_per_cta / MMAB_GB + 1) * P.nseg >= 65536) return false;
+    if (groups_per_cta * P.nseg * P.items >= (1 << 24) || (groups_per_cta / MMAB_GB + 1) * P.nseg >= 65536) return false;
     smem_bytes = (int)(mmab_fixed_bytes(P, nslot) + (size_t)nslot * P.slot_bytes);
     grid = P.ngroups < SM_COUNT ? P.ngroups : SM_COUNT;
     return true;
@@ -1083,21 +1090,20 @@ static int launch_gemm_small(const void *W, const void *Xq, float *Y, int64_t n_
     static SmemOptIn opt, opt2, opt_dump;
     const bool pdl = g_opt_pdl.load() != 0;
     if (mp.ntg == 2) {
-        cudaError_t err = opt2.ensure(gemm_mma_kernel<false, 2>);
+        cudaError_t err = opt2.ensure(gemm_mma_kernel<false, 2, 1>);
         if (err != cudaSuccess) return (int)err;
-        return (int)launch(gemm_mma_kernel<false, 2>, dim3((unsigned)grid), dim3(MMAB_THREADS), (size_t)smem_bytes, st, pdl,
+        return (int)launch(gemm_mma_kernel<false, 2, 1>, dim3((unsigned)grid), dim3(MMAB_THREADS), (size_t)smem_bytes, st, pdl,
                            static_cast<const uint8_t *>(W), static_cast<const uint32_t *>(Xq), Y, mp, (int)n_tok, dump, wmap);
     }
-    if (dump) {
-        cudaError_t err = opt_dump.ensure(gemm_mma_kernel<true, 1>);
+    auto go = [&](auto kernel, SmemOptIn &o, bool with_pdl) -> int {
+        cudaError_t err = o.ensure(kernel);
         if (err != cudaSuccess) return (int)err;
-        return (int)launch(gemm_mma_kernel<true, 1>, dim3((unsigned)grid), dim3(MMAB_THREADS), (size_t)smem_bytes, st, false,
+        return (int)launch(kernel, dim3((unsigned)grid), dim3(MMAB_THREADS), (size_t)smem_bytes, st, with_pdl,
                            static_cast<const uint8_t *>(W), static_cast<const uint32_t *>(Xq), Y, mp, (int)n_tok, dump, wmap);
-    }
-    cudaError_t err = opt.ensure(gemm_mma_kernel<false, 1>);
-    if (err != cudaSuccess) return (int)err;
-    return (int)launch(gemm_mma_kernel<false, 1>, dim3((unsigned)grid), dim3(MMAB_THREADS), (size_t)smem_bytes, st, pdl,
-                       static_cast<const uint8_t *>(W), static_cast<const uint32_t *>(Xq), Y, mp, (int)n_tok, dump, wmap);
+    };
+    static SmemOptIn opt_r2, opt_dump_r2;
+    if (dump) return mp.nrg == 2 ? go(gemm_mma_kernel<true, 1, 2>, opt_dump_r2, false) : go(gemm_mma_kernel<true, 1, 1>, opt_dump, false);
+    return mp.nrg == 2 ? go(gemm_mma_kernel<false, 1, 2>, opt_r2, pdl) : go(gemm_mma_kernel<false, 1, 1>, opt, pdl);
 }
 
 int bonsai_p40_gemm(const void *W, const void *Xq, float *Y, int64_t n_out, int64_t n_in, int64_t n_tok,
@@ -1108,9 +1114,9 @@ int bonsai_p40_gemm(const void *W, const void *Xq, float *Y, int64_t n_out, int6
     const int path = g_opt_gemm_path.load();
     // From 9 tokens on the tensor cores win even with a 64-token tile mostly empty (5120 -> 17408 at 16 tokens:
     // 40 us against 140 us of the integer SIMT kernel); 2 .. 8 tokens stream the weights once through mma.sync.
-    // 9 .. 16 tokens over a matrix of up to ~100 MB: the streaming kernel with two token groups is ahead of the tensor
-    // cores by its shorter start-up (31 against 40 us at 24 MB); on larger matrices its two mma.sync per chunk lose.
-    const bool small16 = n_tok >= 9 && n_tok <= 16 && (n_in / 128) % 8 == 0 && n_out * (n_in / 128) * W_BLOCK_BYTES <= (100ll << 20);
+    // 9 .. 16 tokens: the streaming kernel with two token groups per code extraction is ahead of the tensor cores
+    // (31 against 40 us at 24 MB, 297 against 312 us at 338 MB); it needs rows of a multiple of 8 blocks.
+    const bool small16 = n_tok >= 9 && n_tok <= 16 && (n_in / 128) % 8 == 0;
     if (path == 2 || (path < 0 && n_tok >= 2 && (n_tok <= 8 || small16))) {     // a handful of tokens: weights streamed once for all of them
         const int rc = launch_gemm_small(W, Xq, Y, n_out, n_in, n_tok, nullptr, as_stream(stream));
         if (rc >= 0) return rc;                                       // -1: the shape does not fit, a kernel below takes it

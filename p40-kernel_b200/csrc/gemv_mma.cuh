@@ -319,7 +319,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) gemv_mma_kernel(const uint8_t 
     }
 }
 
-// ---- small token batches (1 .. 8 tokens): the eight accumulator columns given to the tokens ---------------------------
+// ---- small token batches (1 .. 16 tokens): the eight accumulator columns given to the tokens --------------------------
 // Replaces gemm_pq2_0_p40_kernel (src/kernels/gemm_p40.cu:44-139) for the token counts between the mat-vec and a
 // tensor-core tile -- the band the reference names as missing (docs/MTP.md:58): weights are streamed ONCE for all
 // tokens.  One instruction = 16 rows x one 32-weight chunk x 8 tokens: A = the chunk's codes extracted to bytes (field t
@@ -328,19 +328,23 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) gemv_mma_kernel(const uint8_t 
 // (src/pq2_0.h:149-169) bit for bit, and it is that plus a constant: C starts at 0x4B400000 - s, so
 // D = 0x4B400000 + sumi, which read as a float is 12582912 + sumi exactly (|sumi| <= 8192), and one subtraction gives
 // (float)sumi without a conversion instruction.  Terms (dw * da) * (float)sumi as on the host, added in ascending
-// chunk order inside a quarter of a row segment, quarters and segments in ascending order.
+// chunk order inside an item, items and segments in ascending order.
 //
-// Work of a CTA: its row groups (16 rows each) in batches of MMAB_GB; inside a batch the SEGMENT loop is the outer
-// one -- tile T = (batch, segment j, group l) -- so only the Q8_1 blocks of one segment have to be in shared memory
-// (three buffers, filled by bulk copies straight from Xq, whose chunk-major layout -- block (chunk, tok) at
-// chunk * n_tok + tok, 9 words -- is read as it is; a lane whose token is past n_tok reads a neighbour's block and
-// its accumulator column is never stored), and the ring of weight tiles gets the rest.  A tile is ONE copy: a
-// 2-D tiled copy of 16 rows x one segment (<= 24 blocks; box = `stride` bytes, 16 * odd so that the 8 rows one load
-// touches lie in different banks; what the box takes past the segment or the matrix is never read), or, for rows
-// that are not a multiple of 8 blocks, one bulk copy of 16 whole rows.  The sums of a batch's groups wait in
-// shared memory from segment to segment.
-constexpr int MMAB_ITEMS = 6;         // items (sixths of the longest segment) per tile
-constexpr int MMAB_C = 22;            // compute warps: item I = 6 * tile + sixth belongs to warp I % MMAB_C
+// The kernel is bound by the shared-memory data pipe (loads of code words, of activation words and of the decoded
+// headers: ~12 wavefronts per MMA with one MMA per chunk), so a chunk's operand loads serve as many MMAs as fit:
+// NRG = 2 row groups of 16 rows (up to 8 tokens) or NTG = 2 token groups (9 .. 16 tokens).
+//
+// Work of a CTA: its row groups in batches of MMAB_GB; inside a batch the SEGMENT loop is the outer one -- tile T =
+// (batch, segment j, NRG neighbouring groups of the batch) -- so only the Q8_1 blocks of one segment have to be in
+// shared memory (three buffers, filled by bulk copies straight from Xq, whose chunk-major layout -- block (chunk, tok)
+// at chunk * n_tok + tok, 9 words -- is read as it is; a lane whose token is past n_tok reads a neighbour's block and
+// its accumulator column is never stored), and the ring of weight tiles gets the rest.  A group's part of a tile is ONE
+// copy: a 2-D tiled copy of 16 rows x one segment (<= 24 blocks; box = `stride` bytes, 16 * odd so that the 8 rows one
+// load touches lie in different banks; what the box takes past the segment or the matrix is never read), or, for rows
+// that are not a multiple of 8 blocks, one bulk copy of 16 whole rows.  An item is `ppi` block pairs of a tile; the
+// items of a tile add their sums into the slot's sums one after the other in item order (a counter passes the turn),
+// the last one joins them to the groups' earlier segments and hands the slot back.
+constexpr int MMAB_C = 22;            // compute warps: item I = items * tile + k belongs to warp I % MMAB_C
 constexpr int MMAB_THREADS = (MMAB_C + 2) * 32;      // + weight warp + activation warp
 constexpr int MMAB_SEG_UNITS = 3;     // segment <= 3 units of 8 blocks
 constexpr int MMAB_GB = 16;           // row groups per batch
@@ -351,13 +355,14 @@ struct MmabGeom {
     int ngroups;             // row groups of 16
     int nseg, seg_q, seg_r;  // segments in units of 8 blocks: segment j has seg_q + (j < seg_r) units (nseg == 1: nb blocks)
     int stride;              // bytes between the rows of a tile in its slot
-    int tiled;               // 1: a tile is one 2-D tiled copy; 0: one bulk copy of whole rows (nseg == 1)
-    int nslot, slot_bytes;
+    int tiled;               // 1: a group's rows come by one 2-D tiled copy; 0: by one bulk copy of whole rows (nseg == 1)
+    int nslot, slot_bytes;   // a slot holds nrg groups of 16 rows
     int pairs_max;           // block pairs in the longest segment
-    int act_bufs, act_buf_bytes;   // a buffer = the segment's Q8_1 blocks, then {da, 0x4B400000 - s} of every (chunk, token 0..7)
+    int items, ppi;          // items per tile, block pairs per item
+    int act_bufs, act_buf_bytes;   // a buffer = the segment's Q8_1 blocks, then {da, 0x4B400000 - s} of every (chunk, token)
     int act_tab_off;               // bytes from a buffer's start to that table
-    int ntg;                       // token groups of 8 (1: up to 8 tokens, 2: 9 .. 16)
-    uint32_t magic_nslot, magic_bt;   // division by nslot, by the tiles of a full batch
+    int ntg, nrg;                  // token groups of 8, row groups of 16 that share a chunk's operand loads
+    uint32_t magic_nslot, magic_bt, magic_items;   // division by nslot, by the tiles of a full batch, by items
 };
 __host__ __device__ inline int mmab_seg_start(const MmabGeom &P, int j) {
     return P.nseg == 1 ? 0 : 8 * (j * P.seg_q + (j < P.seg_r ? j : P.seg_r));
@@ -365,9 +370,10 @@ __host__ __device__ inline int mmab_seg_start(const MmabGeom &P, int j) {
 __host__ __device__ inline int mmab_seg_len(const MmabGeom &P, int j) {
     return P.nseg == 1 ? P.nb : 8 * (P.seg_q + (j < P.seg_r ? 1 : 0));
 }
-// Shared memory in front of the ring: barriers, activation buffers, item sums of every slot, sums of a batch's groups.
+// Shared memory in front of the ring: barriers and counters, activation buffers, the sums of every slot's tile, the sums
+// of a batch's groups.
 __host__ __device__ inline size_t mmab_fixed_bytes(const MmabGeom &P, int nslot) {
-    const size_t b = 512 + (size_t)P.act_bufs * P.act_buf_bytes + ((size_t)nslot * MMAB_ITEMS + MMAB_GB) * 512 * P.ntg;
+    const size_t b = 512 + (size_t)P.act_bufs * P.act_buf_bytes + ((size_t)nslot * P.nrg + MMAB_GB) * 512 * P.ntg;
     return (b + 127) & ~(size_t)127;
 }
 __device__ __forceinline__ void mmab_tile_copy(void *dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
@@ -376,8 +382,7 @@ __device__ __forceinline__ void mmab_tile_copy(void *dst, const CUtensorMap *map
                  : "memory");
 }
 
-// NTG token groups of 8: the second group's MMA reuses the extracted code bytes of the first.
-template <bool DUMP, int NTG>
+template <bool DUMP, int NTG, int NRG>
 __global__ void __launch_bounds__(MMAB_THREADS, 1) gemm_mma_kernel(const uint8_t *__restrict__ W, const uint32_t *__restrict__ Xq,
                                                                   float *__restrict__ Y, const MmabGeom P, const int n_tok,
                                                                   int32_t *__restrict__ dump,
@@ -386,66 +391,86 @@ __global__ void __launch_bounds__(MMAB_THREADS, 1) gemm_mma_kernel(const uint8_t
     uint64_t *full = reinterpret_cast<uint64_t *>(smem);                       // [12] a tile has landed
     uint64_t *freeb = full + MMA_MAX_SLOTS;                                    // [12] its sums are taken: the slot may be refilled
     uint64_t *actfull = freeb + MMA_MAX_SLOTS;                                 // [3] a segment's Q8_1 blocks have landed
-    // [0] weight tiles given out so far, [1] steps whose Q8_1 blocks have landed and whose headers are decoded.  A
-    // compute warp visits only its own tiles, so before it tests a tile's barrier by parity it makes sure the copy it
-    // waits for has been ISSUED: that implies the barrier's previous phase is complete, and the phase after cannot
-    // complete before the warp arrives.  The activation side needs no parity at all: the count only grows.
+    // [0] weight tiles given out so far, [1] steps whose Q8_1 blocks have landed and whose headers are decoded, [2] steps
+    // whose blocks have been asked for.  A compute warp visits only its own tiles, so before it tests a tile's barrier
+    // by parity it makes sure the copy it waits for has been ISSUED: that implies the barrier's previous phase is
+    // complete, and the phase after cannot complete before the warp is through.  Everything else a warp can fall
+    // behind on is a counter that only grows (or a turn number).
     volatile int *issued = reinterpret_cast<volatile int *>(smem + 256);
-    int *arrived = reinterpret_cast<int *>(smem + 272);                        // [12] item owners through with the slot's tile
+    volatile int *turn = reinterpret_cast<volatile int *>(smem + 272);         // [12] the item whose turn it is to add into the slot's sums
     volatile int *gstage = reinterpret_cast<volatile int *>(smem + 320);       // [16] next segment of the batch's group l
     int *stepdone = reinterpret_cast<int *>(smem + 384);                       // [4] tiles of step q taken, at q % 4
     uint8_t *actbuf = smem + 512;
-    float *itemsum = reinterpret_cast<float *>(actbuf + (size_t)P.act_bufs * P.act_buf_bytes);   // [slot][item][token group][row 16][tok 8]
-    float *gacc = itemsum + (size_t)P.nslot * MMAB_ITEMS * NTG * 128;           // [group of the batch][token group][row 16][tok 8]
+    float *tsum = reinterpret_cast<float *>(actbuf + (size_t)P.act_bufs * P.act_buf_bytes);   // [slot][row group][token group][row 16][tok 8]
+    float *gacc = tsum + (size_t)P.nslot * NRG * NTG * 128;                    // [group of the batch][token group][row 16][tok 8]
     uint8_t *ring = smem + mmab_fixed_bytes(P, P.nslot);
 
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const int mg = ((int)blockIdx.x < P.ngroups) ? (P.ngroups - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
-    const int ntiles = mg * P.nseg;
-    const int batch_tiles = MMAB_GB * P.nseg;
+    constexpr int GBP = MMAB_GB / NRG;                                          // tiles per segment of a full batch
+    const int batch_tiles = GBP * P.nseg;
+    const int nbatch = (mg + MMAB_GB - 1) / MMAB_GB;
+    const int gb_last = mg - (nbatch - 1) * MMAB_GB;                           // groups of the last batch (mg > 0)
+    const int gbp_last = (gb_last + NRG - 1) / NRG;
+    const int ntiles = mg > 0 ? (nbatch - 1) * batch_tiles + P.nseg * gbp_last : 0;
+    const uint32_t magic_lastp = gbp_last > 1 ? (uint32_t)(((1ull << 32) + (uint32_t)gbp_last - 1) / (uint32_t)gbp_last) : 0u;
     const size_t row_bytes = (size_t)P.nb * W_BLOCK_BYTES;
-    const int ppi = (P.pairs_max + MMAB_ITEMS - 1) / MMAB_ITEMS;                 // pairs per item
+    const int group_bytes = 16 * P.stride;
 
-    // tile T -> row group gi, segment j, group l of its batch, step q (segments counted through the batches); the
-    // divisions are multiplications: a full batch has MMAB_GB groups, the last one gb_last
-    const int gb_last = mg - ((mg - 1) / MMAB_GB) * MMAB_GB;
-    const uint32_t magic_last = gb_last > 1 ? (uint32_t)(((1ull << 32) + (uint32_t)gb_last - 1) / (uint32_t)gb_last) : 0u;
-    auto tile_of = [&](int T, int &j, int &l, int &q) {
-        const int b = (int)fast_div((uint32_t)T, P.magic_bt);
+    // tile T -> batch b, segment j, tile pl of the segment, step q (segments counted through the batches), groups of the
+    // batch gb; the divisions are multiplications
+    auto tile_of = [&](int T, int &b, int &j, int &pl, int &q, int &gb) {
+        b = (int)fast_div((uint32_t)T, P.magic_bt);
         const int r = T - b * batch_tiles;
-        if ((b + 1) * MMAB_GB <= mg) {
-            j = r / MMAB_GB;
-            l = r - j * MMAB_GB;
+        if (b < nbatch - 1) {
+            gb = MMAB_GB;
+            j = r / GBP;
+            pl = r - j * GBP;
         } else {
-            j = (int)fast_div((uint32_t)r, magic_last);
-            l = r - j * gb_last;
+            gb = gb_last;
+            j = (int)fast_div((uint32_t)r, magic_lastp);
+            pl = r - j * gbp_last;
         }
         q = b * P.nseg + j;
-        return (int)blockIdx.x + (b * MMAB_GB + l) * (int)gridDim.x;
     };
+    auto group_index = [&](int b, int l) { return (int)blockIdx.x + (b * MMAB_GB + l) * (int)gridDim.x; };
     auto slot_of = [&](int T, int &lap) {
         lap = (int)fast_div((uint32_t)T, P.magic_nslot);
         return T - lap * P.nslot;
     };
     auto third = [](int q) { return (int)(((uint32_t)q * 0xAAABu) >> 17); };   // q / 3 for q < 65536
     // One lane gives out a tile.  No proxy fence: the slot was only READ by the compute warps, and their last reads
-    // are ordered before this copy by the barrier the copy warp waited on.
+    // are ordered before this copy by the barrier the weight warp waited on.
     auto issue_tile = [&](int T) {
-        int j, l, q, lap;
-        const int gi = tile_of(T, j, l, q);
+        int b, j, pl, q, gb, lap;
+        tile_of(T, b, j, pl, q, gb);
         const int slot = slot_of(T, lap);
         uint8_t *dst = ring + (size_t)slot * P.slot_bytes;
+        const int present = min(NRG, gb - NRG * pl);
         if (P.tiled) {
-            mbar_expect_tx(&full[slot], (uint32_t)(16 * P.stride));
-            mmab_tile_copy(dst, &wmap, (mmab_seg_start(P, j) >> 3) * 68, 16 * gi, &full[slot]);
+            mbar_expect_tx(&full[slot], (uint32_t)(present * group_bytes));
+            for (int h = 0; h < present; ++h)
+                mmab_tile_copy(dst + (size_t)h * group_bytes, &wmap, (mmab_seg_start(P, j) >> 3) * 68,
+                               16 * group_index(b, NRG * pl + h), &full[slot]);
         } else {
             const uint64_t pol = policy_evict_first();
-            const int r_cnt = min(16, P.n_out - 16 * gi);
-            const uint8_t *src = W + (size_t)16 * gi * row_bytes;
-            const uint32_t bytes = (uint32_t)(r_cnt * row_bytes), bulk = bytes & ~15u;
-            for (uint32_t o = bulk; o < bytes; o += 4) *reinterpret_cast<uint32_t *>(dst + o) = ldg_nc_u32(src + o);
-            mbar_expect_tx(&full[slot], bulk);
-            if (bulk) bulk_g2s(dst, src, bulk, &full[slot], pol);
+            uint32_t total = 0;
+            for (int h = 0; h < present; ++h) {
+                const int gi = group_index(b, NRG * pl + h);
+                const int r_cnt = min(16, P.n_out - 16 * gi);
+                const uint8_t *src = W + (size_t)16 * gi * row_bytes;
+                uint8_t *d = dst + (size_t)h * group_bytes;
+                const uint32_t bytes = (uint32_t)(r_cnt * row_bytes), bulk = bytes & ~15u;
+                for (uint32_t o = bulk; o < bytes; o += 4) *reinterpret_cast<uint32_t *>(d + o) = ldg_nc_u32(src + o);
+                total += bulk;
+            }
+            mbar_expect_tx(&full[slot], total);
+            for (int h = 0; h < present; ++h) {
+                const int gi = group_index(b, NRG * pl + h);
+                const int r_cnt = min(16, P.n_out - 16 * gi);
+                const uint32_t bulk = (uint32_t)(r_cnt * row_bytes) & ~15u;
+                if (bulk) bulk_g2s(dst + (size_t)h * group_bytes, W + (size_t)16 * gi * row_bytes, bulk, &full[slot], pol);
+            }
         }
     };
 
@@ -453,14 +478,14 @@ __global__ void __launch_bounds__(MMAB_THREADS, 1) gemm_mma_kernel(const uint8_t
         for (int s = 0; s < MMA_MAX_SLOTS; ++s) {
             mbar_init(&full[s], 1);
             mbar_init(&freeb[s], 1);
-            arrived[s] = 0;
+            turn[s] = 0;
         }
         for (int s = 0; s < 3; ++s) mbar_init(&actfull[s], 1);
         for (int s = 0; s < MMAB_GB; ++s) gstage[s] = 0;
         for (int s = 0; s < 4; ++s) stepdone[s] = 0;
         issued[0] = 0;
         issued[1] = 0;
-        issued[2] = 0;                                  // steps whose Q8_1 blocks have been asked for
+        issued[2] = 0;
         mbar_fence_init();
         if (P.tiled) asm volatile("prefetch.tensormap [%0];" ::"l"(&wmap) : "memory");
     }
@@ -487,7 +512,7 @@ __global__ void __launch_bounds__(MMAB_THREADS, 1) gemm_mma_kernel(const uint8_t
     auto wait_equal = [&](volatile int *c, int want) -> bool {
         for (uint32_t n = 0; n < (1u << 22); ++n) {
             if (*c == want) return true;
-            __nanosleep(64);
+            __nanosleep(32);
         }
         atomicExch(&g_device_status, STATUS_MBARRIER_TIMEOUT);
         return false;
@@ -501,15 +526,13 @@ __global__ void __launch_bounds__(MMAB_THREADS, 1) gemm_mma_kernel(const uint8_t
         const int off_h = 4 * t;                                        // {da, c} of tokens 2t and 2t + 1 in a chunk's table row (8 NTG tokens)
         const int sh0 = 16 + 2 * t, sh1 = 2 * t;
         int q_seen = -1;
-        // a warp visits only the tiles it owns an item of; a tile's slot and a step's activation buffer cannot be given
-        // out again before every owner has arrived, so the barrier phases a warp skips are never more than one ahead
-        for (int I = wid; I < MMAB_ITEMS * ntiles; I += MMAB_C) {
-            const int T = I / MMAB_ITEMS, k = I - T * MMAB_ITEMS;
-            int j, l, q, lap;
-            const int gi = tile_of(T, j, l, q);
+        const int nitems = P.items * ntiles;
+        for (int I = wid; I < nitems; I += MMAB_C) {
+            const int T = (int)fast_div((uint32_t)I, P.magic_items), k = I - T * P.items;
+            int b, j, pl, q, gb, lap;
+            tile_of(T, b, j, pl, q, gb);
             const int sb = mmab_seg_start(P, j), sl = mmab_seg_len(P, j);
-            const int q3 = third(q);
-            const int ab = P.nseg > 1 ? q - 3 * q3 : 0;
+            const int ab = P.nseg > 1 ? q - 3 * third(q) : 0;
             if (P.nseg > 1 ? q != q_seen : q_seen < 0) {        // the step's blocks have landed and their headers are decoded
                 if (!wait_count(&issued[1], P.nseg > 1 ? q + 1 : 1)) break;
                 __threadfence_block();
@@ -519,118 +542,153 @@ __global__ void __launch_bounds__(MMAB_THREADS, 1) gemm_mma_kernel(const uint8_t
             const int slot = slot_of(T, lap);
             if (!wait_count(&issued[0], T + 1)) break;
             if (!mbar_wait_bounded(&full[slot], (uint32_t)(lap & 1))) break;
-            const int p_lo = k * ppi, p_hi = min((k + 1) * ppi, sl >> 1);   // empty in a short segment
-            if (p_lo < p_hi) {
-                float acc[NTG][4];
+            const int p_lo = k * P.ppi, p_hi = min(p_lo + P.ppi, sl >> 1);      // empty in a short segment
+            float acc[NRG][NTG][4];
 #pragma unroll
-                for (int u = 0; u < NTG; ++u) acc[u][0] = acc[u][1] = acc[u][2] = acc[u][3] = 0.0f;
+            for (int h = 0; h < NRG; ++h)
+#pragma unroll
+                for (int u = 0; u < NTG; ++u) acc[h][u][0] = acc[h][u][1] = acc[h][u][2] = acc[h][u][3] = 0.0f;
+            if (p_lo < p_hi) {
                 const uint8_t *r0 = ring + (size_t)slot * P.slot_bytes + (size_t)68 * p_lo + (size_t)g * P.stride;
                 const uint32_t *pb = act + (size_t)8 * p_lo * cstride + off_b;
                 const uint32_t *ph = act + P.act_tab_off / 4 + (size_t)8 * p_lo * 16 * NTG + off_h;
                 for (int p = p_lo; p < p_hi; ++p, r0 += 68) {
-                    const uint32_t *p0 = reinterpret_cast<const uint32_t *>(r0);
-                    const uint32_t *p1 = reinterpret_cast<const uint32_t *>(r0 + 8 * (size_t)P.stride);
-                    uint32_t e0[17], e1[17];                        // the pair's 17 words of rows g and g + 8
-    #pragma unroll
-                    for (int i = 0; i < 17; ++i) { e0[i] = p0[i]; e1[i] = p1[i]; }
-    #pragma unroll
+#pragma unroll
                     for (int bl = 0; bl < 2; ++bl) {
-                        const float dw0 = f16_bits_to_f32(bl ? (e0[8] >> 16) : (e0[0] & 0xFFFFu));
-                        const float dw1 = f16_bits_to_f32(bl ? (e1[8] >> 16) : (e1[0] & 0xFFFFu));
-    #pragma unroll
+                        // the block's 9 words of rows g and g + 8 of every row group: block 0 = words 0 .. 8 of the pair
+                        // (codes from byte 2 on), block 1 = words 8 .. 16 (scale in the high half of word 8, codes word-aligned)
+                        uint32_t e[NRG][2][9];
+#pragma unroll
+                        for (int h = 0; h < NRG; ++h) {
+                            const uint32_t *w0 = reinterpret_cast<const uint32_t *>(r0 + (size_t)h * group_bytes) + 8 * bl;
+                            const uint32_t *w1 = reinterpret_cast<const uint32_t *>(r0 + (size_t)h * group_bytes + 8 * (size_t)P.stride) + 8 * bl;
+#pragma unroll
+                            for (int i = 0; i < 9; ++i) { e[h][0][i] = w0[i]; e[h][1][i] = w1[i]; }
+                        }
+                        float dw[NRG][2];
+#pragma unroll
+                        for (int h = 0; h < NRG; ++h) {
+                            dw[h][0] = f16_bits_to_f32(bl ? (e[h][0][0] >> 16) : (e[h][0][0] & 0xFFFFu));
+                            dw[h][1] = f16_bits_to_f32(bl ? (e[h][1][0] >> 16) : (e[h][1][0] & 0xFFFFu));
+                        }
+#pragma unroll
                         for (int c = 0; c < 4; ++c, pb += cstride, ph += 16 * NTG) {
-                            uint32_t a[4];          // row g word 0, row g + 8 word 0, row g word 1, row g + 8 word 1: field t
-                            if (bl == 0) {          // codes start two bytes into word 0: one funnel shift aligns and takes the field
-                                a[0] = __funnelshift_r(e0[2 * c], e0[2 * c + 1], sh0);
-                                a[1] = __funnelshift_r(e1[2 * c], e1[2 * c + 1], sh0);
-                                a[2] = __funnelshift_r(e0[2 * c + 1], e0[2 * c + 2], sh0);
-                                a[3] = __funnelshift_r(e1[2 * c + 1], e1[2 * c + 2], sh0);
-                            } else {                // word-aligned from word 9 on
-                                a[0] = e0[9 + 2 * c] >> sh1; a[1] = e1[9 + 2 * c] >> sh1;
-                                a[2] = e0[10 + 2 * c] >> sh1; a[3] = e1[10 + 2 * c] >> sh1;
-                            }
-    #pragma unroll
-                            for (int i = 0; i < 4; ++i) a[i] &= 0x03030303u;
-                            int d[NTG][4];
+                            uint32_t bw[NTG][2];
+                            uint4 hv[NTG];
 #pragma unroll
                             for (int u = 0; u < NTG; ++u) {
-                                const uint4 hv = *reinterpret_cast<const uint4 *>(ph + 16 * u);
-                                const int cin[4] = {(int)hv.y, (int)hv.w, (int)hv.y, (int)hv.w};
-                                mma_u8s8(d[u], a, pb[72 * u], pb[72 * u + 4], cin);
-                                const float da0 = __uint_as_float(hv.x), da1 = __uint_as_float(hv.z);
-                                const float f0 = __fsub_rn(__int_as_float(d[u][0]), 12582912.0f), f1 = __fsub_rn(__int_as_float(d[u][1]), 12582912.0f);
-                                const float f2 = __fsub_rn(__int_as_float(d[u][2]), 12582912.0f), f3 = __fsub_rn(__int_as_float(d[u][3]), 12582912.0f);
-                                acc[u][0] = __fadd_rn(acc[u][0], __fmul_rn(__fmul_rn(dw0, da0), f0));
-                                acc[u][1] = __fadd_rn(acc[u][1], __fmul_rn(__fmul_rn(dw0, da1), f1));
-                                acc[u][2] = __fadd_rn(acc[u][2], __fmul_rn(__fmul_rn(dw1, da0), f2));
-                                acc[u][3] = __fadd_rn(acc[u][3], __fmul_rn(__fmul_rn(dw1, da1), f3));
+                                bw[u][0] = pb[72 * u];
+                                bw[u][1] = pb[72 * u + 4];
+                                hv[u] = *reinterpret_cast<const uint4 *>(ph + 16 * u);
                             }
-                            if (DUMP) {
-                                const int ci = 4 * (sb + 2 * p + bl) + c;
-                                const int ra = 16 * gi + g, rb = ra + 8, ta = 2 * t, tb = ta + 1;
-                                if (ra < P.n_out && ta < n_tok) dump[((size_t)ra * n_tok + ta) * nch + ci] = d[0][0] - MMAB_MAGIC;
-                                if (ra < P.n_out && tb < n_tok) dump[((size_t)ra * n_tok + tb) * nch + ci] = d[0][1] - MMAB_MAGIC;
-                                if (rb < P.n_out && ta < n_tok) dump[((size_t)rb * n_tok + ta) * nch + ci] = d[0][2] - MMAB_MAGIC;
-                                if (rb < P.n_out && tb < n_tok) dump[((size_t)rb * n_tok + tb) * nch + ci] = d[0][3] - MMAB_MAGIC;
+#pragma unroll
+                            for (int h = 0; h < NRG; ++h) {
+                                uint32_t a[4];      // row g word 0, row g + 8 word 0, row g word 1, row g + 8 word 1: field t
+                                if (bl == 0) {      // one funnel shift aligns and takes the field
+                                    a[0] = __funnelshift_r(e[h][0][2 * c], e[h][0][2 * c + 1], sh0);
+                                    a[1] = __funnelshift_r(e[h][1][2 * c], e[h][1][2 * c + 1], sh0);
+                                    a[2] = __funnelshift_r(e[h][0][2 * c + 1], e[h][0][2 * c + 2], sh0);
+                                    a[3] = __funnelshift_r(e[h][1][2 * c + 1], e[h][1][2 * c + 2], sh0);
+                                } else {
+                                    a[0] = e[h][0][1 + 2 * c] >> sh1; a[1] = e[h][1][1 + 2 * c] >> sh1;
+                                    a[2] = e[h][0][2 + 2 * c] >> sh1; a[3] = e[h][1][2 + 2 * c] >> sh1;
+                                }
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) a[i] &= 0x03030303u;
+#pragma unroll
+                                for (int u = 0; u < NTG; ++u) {
+                                    const int cin[4] = {(int)hv[u].y, (int)hv[u].w, (int)hv[u].y, (int)hv[u].w};
+                                    int d[4];
+                                    mma_u8s8(d, a, bw[u][0], bw[u][1], cin);
+                                    const float da0 = __uint_as_float(hv[u].x), da1 = __uint_as_float(hv[u].z);
+                                    const float f0 = __fsub_rn(__int_as_float(d[0]), 12582912.0f), f1 = __fsub_rn(__int_as_float(d[1]), 12582912.0f);
+                                    const float f2 = __fsub_rn(__int_as_float(d[2]), 12582912.0f), f3 = __fsub_rn(__int_as_float(d[3]), 12582912.0f);
+                                    acc[h][u][0] = __fadd_rn(acc[h][u][0], __fmul_rn(__fmul_rn(dw[h][0], da0), f0));
+                                    acc[h][u][1] = __fadd_rn(acc[h][u][1], __fmul_rn(__fmul_rn(dw[h][0], da1), f1));
+                                    acc[h][u][2] = __fadd_rn(acc[h][u][2], __fmul_rn(__fmul_rn(dw[h][1], da0), f2));
+                                    acc[h][u][3] = __fadd_rn(acc[h][u][3], __fmul_rn(__fmul_rn(dw[h][1], da1), f3));
+                                    if (DUMP && u == 0 && NRG * pl + h < gb) {
+                                        const int ci = 4 * (sb + 2 * p + bl) + c;
+                                        const int ra = 16 * group_index(b, NRG * pl + h) + g, rb = ra + 8, ta = 2 * t, tb = ta + 1;
+                                        if (ra < P.n_out && ta < n_tok) dump[((size_t)ra * n_tok + ta) * nch + ci] = d[0] - MMAB_MAGIC;
+                                        if (ra < P.n_out && tb < n_tok) dump[((size_t)ra * n_tok + tb) * nch + ci] = d[1] - MMAB_MAGIC;
+                                        if (rb < P.n_out && ta < n_tok) dump[((size_t)rb * n_tok + ta) * nch + ci] = d[2] - MMAB_MAGIC;
+                                        if (rb < P.n_out && tb < n_tok) dump[((size_t)rb * n_tok + tb) * nch + ci] = d[3] - MMAB_MAGIC;
+                                    }
+                                }
                             }
                         }
                     }
                 }
+            }
+            // the items of a tile add into the slot's sums in item order: wait for the turn, add, pass it on
+            if (!wait_equal(&turn[slot], k)) break;
+            __threadfence_block();
+            if (p_lo < p_hi) {
+#pragma unroll
+                for (int h = 0; h < NRG; ++h)
+#pragma unroll
+                    for (int u = 0; u < NTG; ++u) {
+                        float *ts = tsum + (((size_t)slot * NRG + h) * NTG + u) * 128;
+                        float2 *lo = reinterpret_cast<float2 *>(ts + g * 8 + 2 * t), *hi = reinterpret_cast<float2 *>(ts + (g + 8) * 8 + 2 * t);
+                        float2 vlo = make_float2(acc[h][u][0], acc[h][u][1]), vhi = make_float2(acc[h][u][2], acc[h][u][3]);
+                        if (k > 0) {
+                            const float2 olo = *lo, ohi = *hi;
+                            vlo.x = __fadd_rn(olo.x, vlo.x); vlo.y = __fadd_rn(olo.y, vlo.y);
+                            vhi.x = __fadd_rn(ohi.x, vhi.x); vhi.y = __fadd_rn(ohi.y, vhi.y);
+                        }
+                        *lo = vlo;
+                        *hi = vhi;
+                    }
+            }
+            __syncwarp();
+            if (k < P.items - 1) {
+                if (lane == 0) {
+                    __threadfence_block();
+                    turn[slot] = k + 1;
+                }
+                continue;
+            }
+            // the last item: the tile's sums join the groups' earlier segments (ascending: wait for the segment before)
+            __threadfence_block();
+#pragma unroll
+            for (int h = 0; h < NRG; ++h) {
+                const int l = NRG * pl + h;
+                if (l >= gb) break;
+                if (P.nseg > 1) {
+                    if (!wait_equal(&gstage[l], j)) break;
+                    __threadfence_block();
+                }
+                const int gi = group_index(b, l);
 #pragma unroll
                 for (int u = 0; u < NTG; ++u) {
-                    float *is = itemsum + (((size_t)slot * MMAB_ITEMS + k) * NTG + u) * 128;
-                    *reinterpret_cast<float2 *>(is + g * 8 + 2 * t) = make_float2(acc[u][0], acc[u][1]);
-                    *reinterpret_cast<float2 *>(is + (g + 8) * 8 + 2 * t) = make_float2(acc[u][2], acc[u][3]);
-                }
-            }
-            // the owner that arrives last adds the tile's items (ascending), joins them to the group's earlier
-            // segments (ascending: it waits for the segment before) and hands the slot back
-            __syncwarp();
-            int before = 0;
-            if (lane == 0) {
-                __threadfence_block();
-                before = atomicAdd(&arrived[slot], 1);
-            }
-            before = __shfl_sync(0xFFFFFFFFu, before, 0);
-            if (before != MMAB_ITEMS - 1) continue;
-            __threadfence_block();
-            // lane owns outputs (row lane / 2, tokens 4 * (lane % 2) .. + 3) of every token group
-            if (P.nseg > 1) {
-                if (!wait_equal(&gstage[l], j)) break;
-                __threadfence_block();
-            }
-#pragma unroll
-            for (int u = 0; u < NTG; ++u) {
-                const float *is = itemsum + ((size_t)slot * MMAB_ITEMS * NTG + u) * 128 + 4 * lane;
-                float4 s = *reinterpret_cast<const float4 *>(is);
-                for (int kk = 1; kk < MMAB_ITEMS && kk * ppi < (sl >> 1); ++kk) {
-                    const float4 v = *reinterpret_cast<const float4 *>(is + kk * NTG * 128);
-                    s.x = __fadd_rn(s.x, v.x); s.y = __fadd_rn(s.y, v.y); s.z = __fadd_rn(s.z, v.z); s.w = __fadd_rn(s.w, v.w);
-                }
-                if (P.nseg > 1) {
-                    float4 *ga = reinterpret_cast<float4 *>(gacc + ((size_t)l * NTG + u) * 128) + lane;
-                    if (j > 0) {
-                        const float4 o = *ga;
-                        s.x = __fadd_rn(o.x, s.x); s.y = __fadd_rn(o.y, s.y); s.z = __fadd_rn(o.z, s.z); s.w = __fadd_rn(o.w, s.w);
+                    // lane owns outputs (row lane / 2, tokens 4 * (lane % 2) .. + 3) of the token group
+                    float4 s = *(reinterpret_cast<const float4 *>(tsum + (((size_t)slot * NRG + h) * NTG + u) * 128) + lane);
+                    if (P.nseg > 1) {
+                        float4 *ga = reinterpret_cast<float4 *>(gacc + ((size_t)l * NTG + u) * 128) + lane;
+                        if (j > 0) {
+                            const float4 o = *ga;
+                            s.x = __fadd_rn(o.x, s.x); s.y = __fadd_rn(o.y, s.y); s.z = __fadd_rn(o.z, s.z); s.w = __fadd_rn(o.w, s.w);
+                        }
+                        if (j < P.nseg - 1) *ga = s;
                     }
-                    if (j < P.nseg - 1) *ga = s;
-                }
-                if (j == P.nseg - 1) {
-                    const int row = 16 * gi + (lane >> 1), tok0 = 8 * u + 4 * (lane & 1);
-                    if (row < P.n_out) {
-                        const float out[4] = {s.x, s.y, s.z, s.w};
+                    if (j == P.nseg - 1) {
+                        const int row = 16 * gi + (lane >> 1), tok0 = 8 * u + 4 * (lane & 1);
+                        if (row < P.n_out) {
+                            const float out[4] = {s.x, s.y, s.z, s.w};
 #pragma unroll
-                        for (int e = 0; e < 4; ++e)
-                            if (tok0 + e < n_tok) Y[(size_t)row * n_tok + tok0 + e] = out[e];
+                            for (int e2 = 0; e2 < 4; ++e2)
+                                if (tok0 + e2 < n_tok) Y[(size_t)row * n_tok + tok0 + e2] = out[e2];
+                        }
                     }
                 }
             }
             __syncwarp();
             if (lane == 0) {
-                arrived[slot] = 0;
+                turn[slot] = 0;
                 __threadfence_block();
                 if (P.nseg > 1) {
-                    gstage[l] = (j == P.nseg - 1) ? 0 : j + 1;
+                    for (int h = 0; h < NRG && NRG * pl + h < gb; ++h) gstage[NRG * pl + h] = (j == P.nseg - 1) ? 0 : j + 1;
                     atomicAdd(&stepdone[q & 3], 1);
                 }
                 mbar_arrive(&freeb[slot]);
@@ -656,8 +714,8 @@ __global__ void __launch_bounds__(MMAB_THREADS, 1) gemm_mma_kernel(const uint8_t
         // all compute warps: {da as fp32, 0x4B400000 - s} per (chunk, token)
         const bool bulk_ok = (reinterpret_cast<uintptr_t>(Xq) & 15u) == 0;
         const uint64_t keep = policy_evict_normal();            // every CTA reads the same blocks: they stay in L2
-        const int nsteps = P.nseg > 1 ? ((mg + MMAB_GB - 1) / MMAB_GB) * P.nseg : (mg > 0 ? 1 : 0);
-        auto tiles_of_step = [&](int s) { return ((s / P.nseg) + 1) * MMAB_GB <= mg ? MMAB_GB : gb_last; };
+        const int nsteps = P.nseg > 1 ? nbatch * P.nseg : (mg > 0 ? 1 : 0);
+        auto tiles_of_step = [&](int s) { return s / P.nseg < nbatch - 1 ? GBP : gbp_last; };
         int qa = 0;
         bool ok = true;
         auto ask = [&](bool block) -> bool {                    // the blocks of step qa; false: its buffer is still in use
