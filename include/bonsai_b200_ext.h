@@ -127,7 +127,7 @@ int bonsai_b200_stream_probe(const void *buf, int64_t bytes, int mode, void *sin
  * alternative and as the body of the 2 .. 8 token kernel).
  * key "gemm_path": -1 (default) = the mat-mul picks its kernel by token count (2 .. 8 tokens: the streaming
  * small-batch kernel, which also takes 9 .. 16 tokens when rows are a multiple of 8 blocks; otherwise 9 tokens and more: the
- * tensor cores; one token: the integer SIMT kernel), 0 = integer SIMT kernel (Y
+ * tensor cores; one token: the mat-vec of bonsai_p40_gemv), 0 = integer SIMT kernel (Y
  * bit-identical to the host loop), 1 = tensor cores (the fp16 form, csrc/gemm_tc16.cuh, where it takes the call,
  * else the integer form), 2 = the small-batch kernel where it takes the shape, 3 = the integer tensor-core kernel
  * (csrc/gemm_tc.cuh: forms the host's int32 chunk sums, needs no scratch).  1, 2 and 3 hold fp32 Y to 1e-5 of

@@ -1112,6 +1112,9 @@ int bonsai_p40_gemm(const void *W, const void *Xq, float *Y, int64_t n_out, int6
     if (n_out <= 0 || n_tok <= 0) return 0;
     if (n_out > INT32_MAX || n_tok > INT32_MAX || !aligned4(Xq)) return 1;
     const int path = g_opt_gemm_path.load();
+    // One token is the mat-vec (chunk-major Xq of one token is the plain Q8_1 vector, Y[n_out][1] the output vector):
+    // 8 us against 140 us of the integer SIMT kernel on 5120 -> 17408; same bits and options as bonsai_p40_gemv.
+    if (n_tok == 1 && path < 0) return bonsai_p40_gemv(W, Xq, Y, n_out, n_in, stream);
     // From 9 tokens on the tensor cores win even with a 64-token tile mostly empty (5120 -> 17408 at 16 tokens:
     // 40 us against 140 us of the integer SIMT kernel); 2 .. 8 tokens stream the weights once through mma.sync.
     // 9 .. 16 tokens: the streaming kernel with two token groups per code extraction is ahead of the tensor cores

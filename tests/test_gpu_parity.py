@@ -632,12 +632,11 @@ def test_gemm_tensor_core_fp16_bound(gpu, port, n_out, n_in, n_tok):
 
 
 def test_gemm_default_dispatch(gpu, port):
-    """By token count: one token takes the kernel that keeps the host's bits; 2 .. 8 the streaming small-batch
-    kernel; 9 and more the tcgen05 kernel."""
+    """By token count: one token is the mat-vec; 2 .. 16 the streaming small-batch kernel; more the tcgen05 kernel."""
     import torch
     n_out, n_in = 256, 1024
     W = synth.pq2_0_weights(n_out, n_in, seed=9)
-    for n_tok, exact in ((1, True), (8, False), (9, False), (20, False), (47, False), (512, False)):
+    for n_tok, exact in ((1, False), (8, False), (9, False), (20, False), (47, False), (512, False)):
         X = synth.activations(n_in, seed=n_tok, batch=n_tok)
         Xq = port.quantize_batch_chunk_major(X)
         Y = torch.zeros((n_out, n_tok), dtype=torch.float32, device="cuda")
@@ -665,10 +664,20 @@ def test_gemm_one_token_equals_gemv(gpu, port):
     n_out, n_in = 200, 5120
     W = synth.pq2_0_weights(n_out, n_in, seed=4)
     xq = port.quantize_q8_1(synth.activations(n_in, seed=4), True)
+    # one token is the mat-vec: the same bits as bonsai_p40_gemv, in its default order and in the host's
     Y = torch.zeros((n_out, 1), dtype=torch.float32, device="cuda")
     assert gpu.gemm(dev(W), dev(xq), Y, n_out, n_in, 1) == 0
+    assert np.array_equal(bits(host(Y)).reshape(-1), bits(run_gemv(gpu, W, xq, n_out, n_in)))
     with host_order(gpu):
+        assert gpu.gemm(dev(W), dev(xq), Y, n_out, n_in, 1) == 0
         assert np.array_equal(bits(host(Y)).reshape(-1), bits(run_gemv(gpu, W, xq, n_out, n_in)))
+        assert_close_and_exact(host(Y).reshape(-1), port.gemv(W, xq, n_out, n_in, threads=4))
+    try:                                                # the integer SIMT kernel keeps the host's bits at any token count
+        assert gpu.set_option("gemm_path", 0) == 0
+        assert gpu.gemm(dev(W), dev(xq), Y, n_out, n_in, 1) == 0
+    finally:
+        gpu.set_option("gemm_path", -1)
+    assert_close_and_exact(host(Y).reshape(-1), port.gemv(W, xq, n_out, n_in, threads=4))
 
 
 # ---- synthetic weights, status ----------------------------------------------------------------------------
