@@ -206,12 +206,13 @@ bool plan_mmab(long long n_out, int nb, int n_tok, int cap_kb, MmabGeom &P, int 
     if (nb <= 0 || nb % 2 != 0 || n_tok < 1 || n_tok > 16) return false;
     P = MmabGeom{};
     P.ntg = n_tok > 8 ? 2 : 1;
-    // two row groups per tile (a chunk's activation and header loads serve two MMAs) pay when a CTA has enough groups
-    // to keep its warps busy with tiles of twice the size: measured 172 -> 160 us on 5120 x 248320, 23 -> 29 us on
-    // 17408 x 5120 (2 .. 3 groups per CTA)
-    P.nrg = (P.ntg == 1 && (n_out + 15) / 16 >= 6ll * SM_COUNT) ? 2 : 1;
-    // 9 .. 16 tokens double a segment's activation blocks and every sum: segments of one unit keep the ring deep
-    const int seg_units = P.ntg == 2 ? 1 : (P.nrg == 2 ? 2 : MMAB_SEG_UNITS);
+    // The segments and the items fix the order in which a row's terms are added: they depend on the row's length and
+    // the token count only, never on n_out, so that a row slice gives the bits of the whole matrix.
+    const int seg_units = P.ntg == 2 ? 1 : (nb >= 64 ? MMAB_SEG_UNITS : 2);
+    // Two row groups per tile (a chunk's activation and header loads serve two MMAs) pay when a CTA has enough groups
+    // to keep its warps busy with tiles of twice the size, and when the ring stays deep (16-block segments): measured
+    // 172 -> 160 us on 5120 x 248320; with 2 .. 3 groups per CTA (17408 x 5120) 23 -> 29 us.
+    P.nrg = (P.ntg == 1 && seg_units == 2 && (n_out + 15) / 16 >= 6ll * SM_COUNT) ? 2 : 1;
     P.n_out = (int)n_out;
     P.nb = nb;
     P.ngroups = (int)((n_out + 15) / 16);

@@ -435,7 +435,7 @@ def test_gemm_bits(gpu, port, n_out, n_in, n_tok):
     assert_close_and_exact(host(Y), port.gemm(W, Xq, n_out, n_in, n_tok, threads=8))
 
 
-@pytest.mark.parametrize("n_in,n_out,n_tok", [(17408, 5120, 8), (5120, 17408, 1)])
+@pytest.mark.parametrize("n_in,n_out,n_tok", [(17408, 5120, 8), (5120, 17408, 1), (5120, 17408, 8), (2048, 20000, 5)])
 def test_row_partition_assembles_full_result(gpu, port, n_in, n_out, n_tok):
     """The multi-GPU split on one device: 8 ranks' row slices (contiguous byte ranges of W), each
     multiplied on its own, written where an all-gather would put them, equal the unsplit result bit
