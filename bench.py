@@ -614,7 +614,9 @@ def run_b200(args):
         sec = {}
         legs = [("batch8", batch_leg)]              # at every N; the others on one GPU
         if world == 1:
-            legs += [("decode_step", decode_step_leg), ("prefill", prefill_leg), ("repack_gemv", repack_leg),
+            legs += [("batch16", lambda a, t, b, d: batch_leg(a, t, b, d, n_tok=16)),
+                     ("batch32", lambda a, t, b, d: batch_leg(a, t, b, d, n_tok=32)),
+                     ("decode_step", decode_step_leg), ("prefill", prefill_leg), ("repack_gemv", repack_leg),
                      ("beside_the_path", beside_leg)]
         for name, leg in legs:
             try:
@@ -1102,10 +1104,10 @@ def beside_leg(args, torch, bb, dist):
 
 # ---- row-partitioned small batch -----------------------------------------------------------------------
 def batch_leg(args, torch, bb, dist, n_tok=8):
-    """The two large projections (5120 -> 17408, 17408 -> 5120) with a batch of 8 activation vectors: every rank
-    multiplies its row slice through bonsai_p40_gemm (2 .. 8 tokens: the kernel that streams the weights once for all
-    tokens), an NCCL all-gather assembles Y[n_out][8].  `--sets` copies of each matrix are resident.  Reports weight
-    GB/s (weight bytes of all launches / time) and token-weight GB/s (x 8).  Parity: the assembled Y of the last sweep
+    """The two large projections (5120 -> 17408, 17408 -> 5120) with a batch of n_tok activation vectors: every rank
+    multiplies its row slice through bonsai_p40_gemm (2 .. 16 tokens: the kernel that streams the weights once for all
+    tokens; more: the tensor cores), an NCCL all-gather assembles Y[n_out][n_tok].  `--sets` copies of each matrix are
+    resident.  Reports weight GB/s (weight bytes of all launches / time) and token-weight GB/s (x n_tok).  Parity: the assembled Y of the last sweep
     against the same entry point on the unsplit matrix, bit for bit (a row's sum does not depend on the split)."""
     from bonsai_b200 import partition
     rank, world, local = env_ranks()
@@ -1156,10 +1158,11 @@ def batch_leg(args, torch, bb, dist, n_tok=8):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         bad, worst = int(t[0].item()), float(t[1].item())
     peak, _, kind = measured_peaks()
-    return {"metric": "pq2_0_gemm_batch8_weight_stream", "value": gbs, "unit": UNIT, "n_tok": n_tok, "us_per_sweep": us,
-            "token_weight_gbs": gbs * n_tok, "gpu_launches": len(mats) * steps * reps,
+    kernels_per_call = 1 if n_tok <= 16 else 3      # streaming kernel; tensor cores: two launches prepare the fp16 planes
+    return {"metric": f"pq2_0_gemm_batch{n_tok}_weight_stream", "value": gbs, "unit": UNIT, "n_tok": n_tok, "us_per_sweep": us,
+            "token_weight_gbs": gbs * n_tok, "gpu_launches": len(mats) * steps * reps * kernels_per_call,
             "frac": gbs / world / peak, "peak_kind": kind, "resident_weight_bytes": total_w,
-            "call": "bonsai_p40_gemm (8 tokens) per matrix slice" + (" + NCCL all-gather" if world > 1 else ""),
+            "call": f"bonsai_p40_gemm ({n_tok} tokens) per matrix slice" + (" + NCCL all-gather" if world > 1 else ""),
             "parity": {"checked": 2, "mismatches": bad, "max_abs": worst,
                        "against": "bonsai_p40_gemm on the unsplit matrix, bit for bit, every rank"},
             "device_status": bb.device_status()}
