@@ -124,7 +124,7 @@ int bonsai_b200_stream_probe(const void *buf, int64_t bytes, int mode, void *sin
  * to launch); 1 = the mat-vec that also adds them in the host's sequential order (outputs
  * bit-identical to src/pq2_0.h:183-191, slower); 2 = the mat-vec whose integer products run on mma.sync
  * (csrc/gemv_mma.cuh: same terms, another fixed tree; measured slower than 0 at batch 1, kept as the measured
- * alternative and as the body of the 2 .. 8 token kernel).
+ * alternative and as the body of the 2 .. 16 token kernel).
  * key "gemm_path": -1 (default) = the mat-mul picks its kernel by token count (2 .. 8 tokens: the streaming
  * small-batch kernel, which also takes 9 .. 16 tokens when rows are a multiple of 8 blocks; otherwise 9 tokens and more: the
  * tensor cores; one token: the mat-vec of bonsai_p40_gemv), 0 = integer SIMT kernel (Y
