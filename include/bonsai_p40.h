@@ -52,8 +52,8 @@ int bonsai_p40_quant_activations(const float *x, void *out, int64_t n, bonsai_st
 /* Prefill mat-mul: Y[n_out][n_tok] (row-major fp32) = W . X, with Xq chunk-major
  * [n_in/32][n_tok] Q8_1 blocks.  Returns 1 on a bad n_in; 0 without a launch if n_out <= 0
  * or n_tok <= 0.  Replaces include/bonsai_p40.h:29 / src/kernels/gemm_p40.cu:143.
- * From 9 tokens on the call may allocate a scratch buffer once per (device, stream) and size, outside graph capture
- * (see "gemm_path" in bonsai_b200_ext.h). */
+ * From 17 tokens on (from 9 when rows are not a multiple of 1024 weights) the call may allocate a scratch buffer
+ * once per (device, stream) and size, outside graph capture (see "gemm_path" in bonsai_b200_ext.h). */
 int bonsai_p40_gemm(const void *W, const void *Xq, float *Y, int64_t n_out, int64_t n_in, int64_t n_tok,
                     bonsai_stream stream);
 
