@@ -460,9 +460,9 @@ def run_b200(args):
                     ev_out[b].record(s_out)
         run(4, 0)
         torch.cuda.synchronize()
-        # eight sweeps per graph (the three streams fork from and join the capturing stream); replays serialise,
-        # so one sweep in eight starts without a neighbour to overlap with
-        per_graph = 8
+        # 32 sweeps per graph (the three streams fork from and join the capturing stream); replays serialise,
+        # so one sweep in 32 starts without a neighbour to overlap with
+        per_graph = 32
         graph, cap = torch.cuda.CUDAGraph(), torch.cuda.Stream()
         with torch.cuda.graph(graph, stream=cap):
             for st in (s_in, s_k, s_out):
